@@ -1,0 +1,387 @@
+"""Public API: ``Buffer`` — load-balanced, dropless expert-parallel communication.
+
+Typical training step::
+
+    buf = Buffer(S=4096, H=7168, K=8, E=256, num_ep_ranks=8, num_sms=32, token_padding=128)
+    x_nvs, w_nvs, cu_seqlens, plan = buf.dispatch(x, gates, topk, tokens_per_expert)
+    buf.prefetch_weight(plan, full_gate_weight=wg, full_up_weight=wu, full_down_weight=wd)
+    y_nvs = experts(x_nvs, cu_seqlens, ...)            # grouped GEMMs over [E+B] groups
+    y, gates_back, _ = buf.combine(plan, y_nvs, w_nvs)
+    # backward: dispatch(grad_y, plan=plan) -> expert backward -> combine -> reduce_grad
+
+Parity: reference ``moonep_td/api.py:187-498`` (constructor signature, return
+tuples, ``async_finish`` events, ``zero_copy`` aliasing rules, ``destroy``).
+Differences by design: a fresh dispatch needs no separate inter-rank barrier
+(the planner's first exchange doubles as one), no host synchronisation happens
+inside any operation, and the non-zero-copy paths copy only rows that hold data.
+"""
+
+from __future__ import annotations
+
+import logging
+import warnings
+
+import torch
+
+from . import config
+from .constants import FLAG_PLAN, FLAG_READY
+from .layout import check_encoding_bounds, compute_layout
+from .parallel.world import World, make_world
+from .plan import MoonEPCommPlan, allocate_planning_outputs, check_plan_for_ctx, check_planning_outputs
+
+logger = logging.getLogger(__name__)
+
+
+def _create_context(S, H, K, E, num_ep_ranks, num_sms=None, token_padding=128, B=None, group=None, world=None) -> dict:
+    """Allocate the symmetric buffers and local scratch of one Buffer."""
+    w: World = make_world(num_ep_ranks, group=group, world=world)
+    ctx = compute_layout(S, H, K, E, w.size, B=B, num_sms=num_sms, token_padding=token_padding, gran_bytes=w.granularity())
+    check_encoding_bounds(ctx)
+    R, rank, dev = w.size, w.rank, w.device
+    ctx.update({"rank": rank, "group": group, "world": w, "device": dev})
+
+    hid = w.alloc_symmetric(ctx["NvS_padded"] * H, torch.bfloat16, ctx["gran_bytes"])
+    meta = w.alloc_symmetric(ctx["meta_chunk_padded"], torch.int32, ctx["gran_bytes"])
+    ctx["_symm"] = [hid, meta]
+    hidden_buf = hid.full.view(R * ctx["NvS_padded"], H)
+    meta_buf = meta.full
+    nvsp, ms = ctx["NvS_padded"], ctx["meta_chunk_padded"]
+    # Fresh or recycled memory: clear this rank's shards so pad rows, weights
+    # and flags start from zero.
+    hidden_buf[rank * nvsp : (rank + 1) * nvsp].zero_()
+    meta_buf[rank * ms : (rank + 1) * ms].zero_()
+    ctx["hidden_buf"] = hidden_buf
+    ctx["meta_buf"] = meta_buf
+    ctx["hidden_buf_local"] = hidden_buf[rank * nvsp : rank * nvsp + ctx["NvS"]]
+    ctx["weights_buf_local"] = meta_buf[rank * ms + ctx["WEIGHTS_OFF"] : rank * ms + ctx["WEIGHTS_OFF"] + ctx["NvS"]]
+
+    def i32(n, zero=False):
+        return (torch.zeros if zero else torch.empty)(max(int(n), 1), dtype=torch.int32, device=dev)
+
+    N = ctx["N"]
+    ctx["alloc"] = i32(E * R)
+    ctx["group_tokens"] = i32(R)
+    ctx["z"] = i32(R * R)
+    ctx["local_hist"] = i32(E * ctx["num_vblocks"])
+    ctx["grid_sync_bar"] = i32(1, zero=True)
+    ctx["primary_packed"] = i32(R * S)
+    ctx["kmask"] = i32(R * S)
+    ctx["kidx_to_loff"] = i32(R * S * K)
+    ctx["builder_bar"] = i32(1, zero=True)
+    del N
+
+    if w.is_cuda:
+        from .ops.cuda_backend import CudaBackend
+
+        ctx["_backend"] = CudaBackend(ctx, w)
+    else:
+        from .cpu.backend import CpuBackend
+
+        ctx["_backend"] = CpuBackend(ctx, w)
+    if w.is_cuda:
+        torch.cuda.synchronize(dev)
+    w.host_barrier()
+    return ctx
+
+
+class Buffer:
+    """Communication buffer of one EP rank (see module docstring)."""
+
+    def __init__(
+        self,
+        S: int,
+        H: int,
+        K: int,
+        E: int,
+        num_ep_ranks: int,
+        num_sms: int | None = None,
+        token_padding: int = 128,
+        B: int | None = None,
+        group=None,
+        comm_stream_priority: int = -1,
+        enable_pdl: bool = True,
+        explicitly_destroy: bool = False,
+        *,
+        world: World | None = None,
+    ):
+        self.explicitly_destroy = explicitly_destroy
+        self.comm_stream_priority = comm_stream_priority
+        self.enable_pdl = enable_pdl
+        self._comm_stream = None
+        self._destroyed = False
+        self._ctx = _create_context(
+            S, H, K, E, num_ep_ranks, num_sms=num_sms, token_padding=token_padding, B=B, group=group, world=world
+        )
+        w = self._ctx["world"]
+        if w.is_cuda:
+            max_sms = torch.cuda.get_device_properties(w.device).multi_processor_count
+            self._ctx["num_sms_dedup"] = config.num_sms_dedup(max_sms)
+            assert 1 <= self._ctx["num_sms"] <= max_sms, f"num_sms must be in [1, {max_sms}]"
+        self._comm_stream = w.comm_stream(comm_stream_priority)
+
+    # -- lifetime ----------------------------------------------------------------
+    @property
+    def destroyed(self) -> bool:
+        return self._destroyed
+
+    def _require_ctx(self) -> dict:
+        assert not self._destroyed, "Buffer has been destroyed"
+        return self._ctx
+
+    def destroy(self) -> None:
+        """Collective: wait for outstanding work on every rank, then free the symmetric memory."""
+        if self._destroyed:
+            return
+        ctx = self._ctx
+        self._destroyed = True
+        if ctx is None:
+            return
+        w = ctx["world"]
+        if w.is_cuda:
+            if self._comm_stream is not None:
+                self._comm_stream.synchronize()
+            torch.cuda.synchronize(w.device)
+        w.host_barrier()
+        ctx["_backend"].destroy()
+        for key in ("hidden_buf", "meta_buf", "hidden_buf_local", "weights_buf_local"):
+            ctx.pop(key, None)
+        for st in ctx.pop("_symm", []):
+            w.free_symmetric(st)
+        ctx.clear()
+        self._ctx = None
+        self._comm_stream = None
+
+    def __del__(self):
+        if getattr(self, "_destroyed", True):
+            return
+        if getattr(self, "explicitly_destroy", False):
+            warnings.warn("Buffer was not destroyed explicitly.", ResourceWarning)
+            return
+        try:
+            self.destroy()
+        except Exception as exc:  # noqa: BLE001 - never raise from a destructor
+            warnings.warn(f"Buffer destructor failed: {exc!r}", ResourceWarning)
+
+    def check_status(self) -> None:
+        """Raise ``MoonEPTimeoutError`` if a device-side wait of an earlier operation ran out."""
+        self._require_ctx()["_backend"].check_status()
+
+    def stats(self) -> dict:
+        """Counters of the last operations (rows sent, duplicates, waits that timed out)."""
+        return self._require_ctx()["_backend"].stats()
+
+    # -- stream helpers ------------------------------------------------------------
+    def _on_comm_stream(self, tensors, fn):
+        """Run ``fn`` on the communication stream after the current stream's work; return its event."""
+        comm = self._comm_stream
+        if comm is None:  # CPU backend: nothing is asynchronous
+            fn()
+            return _DoneEvent()
+        for t in tensors:
+            if t is not None:
+                t.record_stream(comm)
+        comm.wait_event(torch.cuda.current_stream().record_event())
+        with torch.cuda.stream(comm):
+            fn()
+            return comm.record_event()
+
+    # -- dispatch ---------------------------------------------------------------------
+    def _run_dispatch(self, ctx, hidden_sh, route_weights_sk, planning_args, plan, hidden_nvsh, route_weights_nvs,
+                      *, inter_rank_sync, zero_copy):  # fmt: skip
+        be = ctx["_backend"]
+        wait = None
+        if planning_args is not None:
+            topk_flat, tpe, cu_seqlens = planning_args
+            be.plan_publish(tpe)
+            be.plan_compute(topk_flat, tpe, cu_seqlens, plan)
+            wait = FLAG_PLAN
+        elif inter_rank_sync:
+            be.signal(FLAG_READY)
+            wait = FLAG_READY
+        be.dispatch_send(hidden_sh, route_weights_sk, plan, planning_args is not None, wait=wait)
+        be.dispatch_expand(plan, hidden_nvsh, route_weights_nvs, zero_copy)
+
+    def dispatch(
+        self,
+        hidden_sh,
+        route_weights_sk=None,
+        topk_experts_sk=None,
+        tokens_per_expert=None,
+        plan=None,
+        async_finish=False,
+        *,
+        inter_rank_sync=True,
+        zero_copy=False,
+    ):
+        """Send every token to the ranks that will run its experts.
+
+        Returns ``(hidden_nvsh[NvS,H], route_weights_nvs[NvS] | None, cu_seqlens[E+B] | None, plan)``
+        plus a completion event if ``async_finish``.  With ``plan`` given, the
+        routing of that plan is replayed (no planning, ``cu_seqlens`` is None).
+        """
+        ctx = self._require_ctx()
+        S, H, K, NvS = ctx["S"], ctx["H"], ctx["K"], ctx["NvS"]
+        dev = ctx["device"]
+        assert hidden_sh.dtype == torch.bfloat16 and hidden_sh.is_contiguous(), "hidden_sh must be contiguous bf16"
+        assert tuple(hidden_sh.shape) == (S, H), "hidden_sh shape mismatch"
+        if route_weights_sk is not None:
+            assert route_weights_sk.dtype == torch.float32 and route_weights_sk.is_contiguous(), (
+                "route_weights_sk must be contiguous fp32"
+            )
+            assert tuple(route_weights_sk.shape) == (S, K), "route_weights_sk shape mismatch"
+        if plan is None:
+            assert topk_experts_sk is not None and tokens_per_expert is not None, (
+                "a fresh dispatch needs topk_experts_sk and tokens_per_expert"
+            )
+            assert topk_experts_sk.numel() == S * K, "topk_experts_sk shape mismatch"
+            topk_flat = topk_experts_sk.reshape(-1).to(torch.int32).contiguous()
+            tpe = tokens_per_expert.to(torch.int32).contiguous()
+            assert tpe.numel() in (ctx["E"], ctx["R"] * ctx["E"]), "tokens_per_expert must be [E] or [R, E]"
+            plan, cu_seqlens = allocate_planning_outputs(ctx)
+            check_planning_outputs(ctx, cu_seqlens, plan)
+            planning_args = (topk_flat, tpe, cu_seqlens)
+        else:
+            check_plan_for_ctx(ctx, plan, dev)
+            cu_seqlens, planning_args = None, None
+        if zero_copy:
+            hidden_nvsh = ctx["hidden_buf_local"]
+            route_weights_nvs = ctx["weights_buf_local"].view(torch.float32) if route_weights_sk is not None else None
+        else:
+            hidden_nvsh = torch.empty(NvS, H, dtype=torch.bfloat16, device=dev)
+            route_weights_nvs = (
+                torch.empty(NvS, dtype=torch.float32, device=dev) if route_weights_sk is not None else None
+            )
+
+        def run():
+            self._run_dispatch(
+                ctx, hidden_sh, route_weights_sk, planning_args, plan, hidden_nvsh, route_weights_nvs,
+                inter_rank_sync=inter_rank_sync, zero_copy=zero_copy,
+            )  # fmt: skip
+
+        if not async_finish:
+            run()
+            return hidden_nvsh, route_weights_nvs, cu_seqlens, plan
+        tensors = [hidden_sh, route_weights_sk, hidden_nvsh, route_weights_nvs, *plan.tensors()]
+        if planning_args is not None:
+            tensors.extend(planning_args)
+        done = self._on_comm_stream(tensors, run)
+        return hidden_nvsh, route_weights_nvs, cu_seqlens, plan, done
+
+    # -- expert weights ---------------------------------------------------------------
+    def prefetch_weight(
+        self, plan=None, async_finish=False, *, full_gate_weight=None, full_up_weight=None, full_down_weight=None
+    ):
+        """Copy the remote experts this rank was assigned into its slots ``[E, E+B)`` of each weight."""
+        ctx = self._require_ctx()
+        assert isinstance(plan, MoonEPCommPlan), "prefetch_weight: plan is required"
+        weights = (full_gate_weight, full_up_weight, full_down_weight)
+        assert all(w is not None for w in weights), "prefetch_weight needs gate, up and down weights"
+
+        def run():
+            ctx["_backend"].prefetch(weights, plan.experts_to_copy)
+
+        if not async_finish:
+            run()
+            return None
+        return self._on_comm_stream((plan.experts_to_copy, *weights), run)
+
+    # -- combine ------------------------------------------------------------------------
+    def _run_combine(self, ctx, hidden_sh, plan, hidden_nvsh, route_weights_nvs, route_weights_sk,
+                     *, inter_rank_sync, zero_copy):  # fmt: skip
+        be = ctx["_backend"]
+        wait = None
+        if inter_rank_sync:
+            be.signal(FLAG_READY)
+            wait = FLAG_READY
+        be.combine_prologue(plan, hidden_nvsh, route_weights_nvs, zero_copy, wait=wait)
+        be.combine_pull(plan.dst, hidden_sh, route_weights_sk)
+
+    def combine(
+        self,
+        plan=None,
+        hidden_nvsh=None,
+        route_weights_nvs=None,
+        async_finish=False,
+        inter_rank_sync=True,
+        *,
+        zero_copy=False,
+    ):
+        """Bring expert outputs home: ``out[token] = bf16(sum_k row(token, k))`` (unweighted).
+
+        Returns ``(hidden_sh[S,H], route_weights_sk[S,K] | None, event | None)``.
+        """
+        ctx = self._require_ctx()
+        S, H, K, NvS = ctx["S"], ctx["H"], ctx["K"], ctx["NvS"]
+        assert isinstance(plan, MoonEPCommPlan), "Buffer.combine: plan is required"
+        check_plan_for_ctx(ctx, plan, ctx["device"])
+        assert hidden_nvsh is not None, "Buffer.combine: hidden_nvsh is required"
+        assert hidden_nvsh.dtype == torch.bfloat16 and hidden_nvsh.is_contiguous()
+        assert tuple(hidden_nvsh.shape) == (NvS, H), "hidden_nvsh shape mismatch"
+        if route_weights_nvs is not None:
+            assert route_weights_nvs.dtype == torch.float32 and route_weights_nvs.is_contiguous()
+            assert tuple(route_weights_nvs.shape) == (NvS,), "route_weights_nvs shape mismatch"
+        if zero_copy:
+            assert hidden_nvsh.data_ptr() == ctx["hidden_buf_local"].data_ptr(), (
+                "combine(zero_copy=True): hidden_nvsh must alias the shard view returned by dispatch(zero_copy=True)"
+            )
+            if route_weights_nvs is not None:
+                assert route_weights_nvs.data_ptr() == ctx["weights_buf_local"].data_ptr(), (
+                    "combine(zero_copy=True): route_weights_nvs must alias the weights view "
+                    "returned by dispatch(zero_copy=True)"
+                )
+        dev = hidden_nvsh.device
+        hidden_sh = torch.empty(S, H, dtype=torch.bfloat16, device=dev)
+        route_weights_sk = torch.empty(S, K, dtype=torch.float32, device=dev) if route_weights_nvs is not None else None
+
+        def run():
+            self._run_combine(
+                ctx, hidden_sh, plan, hidden_nvsh, route_weights_nvs, route_weights_sk,
+                inter_rank_sync=inter_rank_sync, zero_copy=zero_copy,
+            )  # fmt: skip
+
+        if not async_finish:
+            run()
+            return hidden_sh, route_weights_sk, None
+        done = self._on_comm_stream((hidden_sh, *plan.tensors(), hidden_nvsh, route_weights_nvs, route_weights_sk), run)
+        return hidden_sh, route_weights_sk, done
+
+    # -- gradients ----------------------------------------------------------------------
+    def reduce_grad(
+        self,
+        plan=None,
+        async_finish=False,
+        full_gate_grad=None,
+        full_up_grad=None,
+        full_down_grad=None,
+        gate_reduce_buffer=None,
+        up_reduce_buffer=None,
+        down_reduce_buffer=None,
+    ):
+        """Add the gradients of prefetched expert copies back into their owners' gradients."""
+        ctx = self._require_ctx()
+        assert isinstance(plan, MoonEPCommPlan), "reduce_grad: plan is required"
+        grads = (full_gate_grad, full_up_grad, full_down_grad)
+        bufs = (gate_reduce_buffer, up_reduce_buffer, down_reduce_buffer)
+        assert all(t is not None for t in (*grads, *bufs)), "reduce_grad needs three gradients and three reduce buffers"
+
+        def run():
+            E = ctx["E"]
+            ctx["_backend"].reduce_grad(plan.experts_to_copy, [g[:E] for g in grads], list(bufs))
+
+        if not async_finish:
+            run()
+            return None
+        return self._on_comm_stream((plan.experts_to_copy, *grads, *bufs), run)
+
+
+class _DoneEvent:
+    """Stand-in for a CUDA event on the CPU backend."""
+
+    def synchronize(self):
+        pass
+
+    def wait(self, stream=None):
+        pass
+
+    def query(self):
+        return True

@@ -1,0 +1,56 @@
+"""Environment toggles.
+
+MOONEP_PLANNER        ``gpu`` (default) or ``cpu``: run the planner kernels or the host planner.
+MOONEP_TIMEOUT_MS     budget of every device-side wait (default 10000).
+MOONEP_COPY_PATH      ``bulk`` (default: TMA bulk copies through shared memory) or ``ldst``
+                      (plain 16-byte loads/stores) for dispatch/combine/prefetch.
+MOONEP_NUM_SMS_DEDUP  number of SMs the dedup builder may use (validated, 1..SM count).
+MOONEP_DEBUG          ``1`` enables device-side index checks that record a status instead of faulting.
+
+Parity: reference ``moonep_td/_pipeline.py:1-14``, ``moonep_td/api.py:40-47``,
+``moonep_td/_planning_gpu.py:14-16`` (``MOONEP_TD_PLANNING_TRITON`` is accepted as an alias).
+"""
+
+from __future__ import annotations
+
+import os
+
+from .constants import DEFAULT_TIMEOUT_MS
+
+_FALSE = ("0", "false", "False", "")
+
+
+def planner_on_gpu() -> bool:
+    raw = os.environ.get("MOONEP_PLANNER")
+    if raw is not None:
+        return raw.lower() != "cpu"
+    return os.environ.get("MOONEP_TD_PLANNING_TRITON", "1") not in _FALSE
+
+
+def timeout_ms() -> int:
+    return max(1, int(os.environ.get("MOONEP_TIMEOUT_MS", DEFAULT_TIMEOUT_MS)))
+
+
+def copy_path() -> str:
+    raw = os.environ.get("MOONEP_COPY_PATH", "bulk").lower()
+    if raw not in ("bulk", "ldst"):
+        raise ValueError(f"MOONEP_COPY_PATH must be 'bulk' or 'ldst', got {raw!r}")
+    return raw
+
+
+def debug() -> bool:
+    return os.environ.get("MOONEP_DEBUG", "0") not in _FALSE
+
+
+def pipeline_enabled() -> bool:
+    return os.environ.get("MOONEP_TD_PIPELINE", "0") not in _FALSE
+
+
+def num_sms_dedup(max_sms: int) -> int:
+    raw = os.environ.get("MOONEP_NUM_SMS_DEDUP")
+    if raw is None or raw == "":
+        return max_sms
+    value = int(raw)
+    if not (1 <= value <= max_sms):
+        raise ValueError(f"MOONEP_NUM_SMS_DEDUP must be in [1, {max_sms}], got {value}")
+    return value

@@ -1,0 +1,264 @@
+// Combine for sm_100a: fold duplicate rows on the expert side, then pull every token's
+// primary rows home over NVLink peer memory and sum them.
+//
+//   combine_prologue  (optionally waits for FLAG_READY) for every duplicate group of the
+//                     local shard: primary = bf16(f32(primary) + sum f32(duplicates)), in the
+//                     stored order; the last CTA signals FLAG_COMB.
+//   combine_pull      waits for every peer's FLAG_COMB; tokens are handed out in batches from an
+//                     atomic counter; per token the primary rows (one per destination rank) are
+//                     read from the peers with 16-byte loads, several rows in flight per lane,
+//                     accumulated in fp32 in ascending k and stored as bf16; all K gate weights
+//                     are read back from the rows' weight slots.
+//
+// Parity: reference moonep_td/combine_prologue.py:19-40 and moonep_td/combine.py:22-68 (which
+// re-reads and re-decodes dst for each of the H/128 column chunks of a token).
+#include "common.cuh"
+#include "host.h"
+
+namespace moonep {
+
+namespace {
+
+constexpr int kTokenBatch = 2;
+constexpr int kPullVec = 4;     // int4 per lane per row chunk (2 KB per warp and row)
+constexpr int kPullRows = 4;    // rows whose loads are issued before the first add
+constexpr int kGroupVec = 8;
+
+__device__ __forceinline__ void acc_add(float* acc, const int4& v) {
+  acc[0] += bf16lo((unsigned)v.x);
+  acc[1] += bf16hi((unsigned)v.x);
+  acc[2] += bf16lo((unsigned)v.y);
+  acc[3] += bf16hi((unsigned)v.y);
+  acc[4] += bf16lo((unsigned)v.z);
+  acc[5] += bf16hi((unsigned)v.z);
+  acc[6] += bf16lo((unsigned)v.w);
+  acc[7] += bf16hi((unsigned)v.w);
+}
+
+__device__ __forceinline__ int4 acc_pack(const float* acc) {
+  int4 o;
+  o.x = (int)pack_bf16(acc[0], acc[1]);
+  o.y = (int)pack_bf16(acc[2], acc[3]);
+  o.z = (int)pack_bf16(acc[4], acc[5]);
+  o.w = (int)pack_bf16(acc[6], acc[7]);
+  return o;
+}
+
+__device__ __forceinline__ float bf16_to_f32(uint16_t u) { return __uint_as_float(((unsigned)u) << 16); }
+__device__ __forceinline__ uint16_t f32_to_bf16(float f) {
+  __nv_bfloat16 b = __float2bfloat16_rn(f);
+  return *reinterpret_cast<uint16_t*>(&b);
+}
+
+__global__ void __launch_bounds__(512)
+    combine_prologue_kernel(const MoonepDevCtx c, const int* __restrict__ dup_groups, const int* __restrict__ dup_loffs,
+                            const int* __restrict__ dup_counts, int wait_family, int wait_epoch, int signal_epoch,
+                            int vec_ok) {
+  const bool ok = block_wait_flags(c, wait_family, wait_epoch, MOONEP_K_COMBINE_PROLOGUE);
+  if (ok) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int H = c.H;
+    int ngroups = dup_counts[0];
+    if (ngroups < 0 || ngroups > c.NvS) ngroups = 0;
+    uint16_t* shard = c.hidden_peer[c.rank];
+    for (int g = blockIdx.x * nwarps + warp; g < ngroups; g += gridDim.x * nwarps) {
+      const int primary = dup_groups[3 * g];
+      const int ds = dup_groups[3 * g + 1];
+      const int dn = dup_groups[3 * g + 2];
+      if (primary < 0 || primary >= c.NvS || ds < 0 || dn < 0 || ds + dn > c.NvS) continue;
+      uint16_t* prow = shard + (long long)primary * H;
+      if (vec_ok) {
+        const int nvec = H / 8;
+        int4* p4 = reinterpret_cast<int4*>(prow);
+        for (int c0 = 0; c0 < nvec; c0 += 32 * kGroupVec) {
+          float acc[kGroupVec][8];
+#pragma unroll
+          for (int j = 0; j < kGroupVec; ++j) {
+            const int i = c0 + j * 32 + lane;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) acc[j][q] = 0.f;
+            if (i < nvec) acc_add(acc[j], ld16(p4 + i));
+          }
+          for (int q = 0; q < dn; ++q) {
+            const int row = dup_loffs[ds + q];
+            if (row < 0 || row >= c.NvS) continue;
+            const int4* r4 = reinterpret_cast<const int4*>(shard + (long long)row * H);
+            int4 v[kGroupVec];
+#pragma unroll
+            for (int j = 0; j < kGroupVec; ++j) {
+              const int i = c0 + j * 32 + lane;
+              if (i < nvec) v[j] = ld16(r4 + i);
+            }
+#pragma unroll
+            for (int j = 0; j < kGroupVec; ++j) {
+              const int i = c0 + j * 32 + lane;
+              if (i < nvec) acc_add(acc[j], v[j]);
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < kGroupVec; ++j) {
+            const int i = c0 + j * 32 + lane;
+            if (i < nvec) st16(p4 + i, acc_pack(acc[j]));
+          }
+        }
+      } else {
+        for (int i = lane; i < H; i += 32) {
+          float acc = bf16_to_f32(prow[i]);
+          for (int q = 0; q < dn; ++q) {
+            const int row = dup_loffs[ds + q];
+            if (row < 0 || row >= c.NvS) continue;
+            acc += bf16_to_f32(shard[(long long)row * H + i]);
+          }
+          prow[i] = f32_to_bf16(acc);
+        }
+      }
+    }
+  }
+  grid_tail_signal(c, MOONEP_K_COMBINE_PROLOGUE, ok ? MOONEP_FLAG_COMB : -1, signal_epoch);
+}
+
+__global__ void __launch_bounds__(512)
+    combine_pull_kernel(const MoonepDevCtx c, const int* __restrict__ dst, uint16_t* __restrict__ out,
+                        float* __restrict__ out_w, int wait_epoch, int vec_ok) {
+  const bool ok = block_wait_flags(c, MOONEP_FLAG_COMB, wait_epoch, MOONEP_K_COMBINE_PULL);
+  const int lane = threadIdx.x & 31;
+  int* work = c.counters + MOONEP_NUM_KERNEL_IDS + 1;
+  if (ok) {
+    const int H = c.H, K = c.K, S = c.S, NvS = c.NvS;
+    for (;;) {
+      int b0 = 0;
+      if (lane == 0) b0 = atomicAdd(work, kTokenBatch);
+      b0 = __shfl_sync(0xffffffffu, b0, 0);
+      if (b0 >= S) break;
+      const int b1 = min(S, b0 + kTokenBatch);
+      for (int token = b0; token < b1; ++token) {
+        int d = 0, dest = 0, loff = 0;
+        bool valid = false;
+        if (lane < K) {
+          d = dst[token * K + lane];
+          const int raw = d < 0 ? -d - 1 : d;
+          dest = raw / NvS;
+          loff = raw - dest * NvS;
+          valid = dest >= 0 && dest < c.R && loff >= 0 && loff < NvS;
+          if (!valid) record_status(c, MOONEP_STATUS_BAD_INDEX, MOONEP_K_COMBINE_PULL, 6, d, token, lane);
+          if (out_w != nullptr) {
+            const float* w = reinterpret_cast<const float*>(c.meta_peer[valid ? dest : c.rank] + c.weights_off);
+            out_w[token * K + lane] = valid ? w[loff] : 0.f;
+          }
+        }
+        const unsigned prim = __ballot_sync(0xffffffffu, valid && d >= 0);
+        // row pointers of the primaries, compacted into the low lanes
+        const int my_pos = __popc(prim & ((1u << lane) - 1u));
+        const int nprim = __popc(prim);
+        const uint16_t* my_row = (valid && d >= 0) ? c.hidden_peer[dest] + (long long)loff * H : nullptr;
+        unsigned long long rows_compact = 0;
+        {
+          // lane p receives the pointer of the p-th primary (ascending k)
+          unsigned m = prim;
+          int p = 0;
+          while (m) {
+            const int kk = __ffs(m) - 1;
+            m &= m - 1;
+            const unsigned long long ptr = __shfl_sync(0xffffffffu, (unsigned long long)my_row, kk);
+            if (lane == p) rows_compact = ptr;
+            ++p;
+          }
+        }
+        (void)my_pos;
+        uint16_t* orow = out + (long long)token * H;
+        if (vec_ok) {
+          const int nvec = H / 8;
+          for (int c0 = 0; c0 < nvec; c0 += 32 * kPullVec) {
+            float acc[kPullVec][8];
+#pragma unroll
+            for (int j = 0; j < kPullVec; ++j)
+#pragma unroll
+              for (int q = 0; q < 8; ++q) acc[j][q] = 0.f;
+            for (int p0 = 0; p0 < nprim; p0 += kPullRows) {
+              int4 v[kPullRows][kPullVec];
+#pragma unroll
+              for (int r = 0; r < kPullRows; ++r) {
+                const unsigned long long ptr = __shfl_sync(0xffffffffu, rows_compact, (p0 + r) & 31);
+                if (p0 + r < nprim) {
+                  const int4* r4 = reinterpret_cast<const int4*>(ptr);
+#pragma unroll
+                  for (int j = 0; j < kPullVec; ++j) {
+                    const int i = c0 + j * 32 + lane;
+                    if (i < nvec) v[r][j] = ld16(r4 + i);
+                  }
+                }
+              }
+#pragma unroll
+              for (int r = 0; r < kPullRows; ++r) {
+                if (p0 + r < nprim) {
+#pragma unroll
+                  for (int j = 0; j < kPullVec; ++j) {
+                    const int i = c0 + j * 32 + lane;
+                    if (i < nvec) acc_add(acc[j], v[r][j]);
+                  }
+                }
+              }
+            }
+            int4* o4 = reinterpret_cast<int4*>(orow);
+#pragma unroll
+            for (int j = 0; j < kPullVec; ++j) {
+              const int i = c0 + j * 32 + lane;
+              if (i < nvec) st16(o4 + i, acc_pack(acc[j]));
+            }
+          }
+        } else {
+          for (int i = lane; i < H; i += 32) {
+            float acc = 0.f;
+            for (int p = 0; p < nprim; ++p) {
+              const unsigned long long ptr = __shfl_sync(0xffffffffu, rows_compact, p);
+              acc += bf16_to_f32(reinterpret_cast<const uint16_t*>(ptr)[i]);
+            }
+            orow[i] = f32_to_bf16(acc);
+          }
+        }
+      }
+    }
+  }
+  __shared__ int s_last;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int arrived = atomicAdd(c.counters + MOONEP_K_COMBINE_PULL, 1);
+    s_last = arrived == (int)gridDim.x - 1;
+    if (s_last) {
+      c.counters[MOONEP_K_COMBINE_PULL] = 0;
+      *work = 0;
+      __threadfence();
+    }
+  }
+}
+
+}  // namespace
+
+}  // namespace moonep
+
+using namespace moonep;
+
+extern "C" int moonep_combine_prologue(void* ctx, const int* dup_groups, const int* dup_loffs, const int* dup_counts,
+                                       const void* in_hidden, const float* in_weights, int wait_family, int wait_epoch,
+                                       int signal_epoch_comb, void* stream) {
+  (void)in_hidden;
+  (void)in_weights;
+  auto* h = (HostCtx*)ctx;
+  const MoonepDevCtx& c = h->dev;
+  const int grid = imax(1, imin(c.num_sms, h->sm_count));
+  combine_prologue_kernel<<<grid, 512, 0, (cudaStream_t)stream>>>(c, dup_groups, dup_loffs, dup_counts, wait_family,
+                                                                 wait_epoch, signal_epoch_comb, (c.H % 8 == 0) ? 1 : 0);
+  return check_launch("combine_prologue_kernel");
+}
+
+extern "C" int moonep_combine_pull(void* ctx, const int* dst, void* out_hidden, float* out_weights, int wait_epoch_comb,
+                                   int path, void* stream) {
+  (void)path;
+  auto* h = (HostCtx*)ctx;
+  const MoonepDevCtx& c = h->dev;
+  const int grid = imax(1, imin(c.num_sms, h->sm_count));
+  const int vec_ok = (c.H % 8 == 0) && ((reinterpret_cast<uintptr_t>(out_hidden) & 15u) == 0);
+  combine_pull_kernel<<<grid, 512, 0, (cudaStream_t)stream>>>(c, dst, (uint16_t*)out_hidden, out_weights,
+                                                             wait_epoch_comb, vec_ok);
+  return check_launch("combine_pull_kernel");
+}

@@ -1,0 +1,161 @@
+// moonep_b200 native library: C API and the device-side context.
+//
+// One shared object (libmoonep_b200.so) built for sm_100a holds every kernel of the
+// library plus the CUDA-VMM symmetric allocator.  Python talks to it through ctypes:
+// plain C functions, raw device pointers, a cudaStream_t.  No function here allocates
+// device memory except moonep_ctx_create / the VMM calls; operations only launch
+// kernels on the stream they are given and never synchronise with the host.
+//
+// Parity: the kernels replace the reference's Triton kernels K1-K17
+// (moonep_td/_common.py, _planning_gpu.py, _dedup_builder.py, dispatch.py,
+// dispatch_epilogue.py, combine_prologue.py, combine.py, prefetch.py, grad_reduce.py);
+// the allocator replaces its NVSHMEM heap (moonep_td/buffer.py:86-109).
+#pragma once
+
+#include <cstdint>
+
+#define MOONEP_VERSION 1
+
+// Packed encodings (must match moonep_b200/constants.py).
+#define MOONEP_KIDX_BITS 7
+#define MOONEP_NVS_BITS 24
+#define MOONEP_NVS_MASK ((1 << MOONEP_NVS_BITS) - 1)
+#define MOONEP_MAX_TOPK 32
+#define MOONEP_MAX_RANKS 128
+
+// Flag families (one int32 per source rank and family in every meta chunk).
+#define MOONEP_FLAG_READY 0
+#define MOONEP_FLAG_TPE 1
+#define MOONEP_FLAG_PLAN 2
+#define MOONEP_FLAG_SENT 3
+#define MOONEP_FLAG_COMB 4
+#define MOONEP_FLAG_GRAD_READY 5
+#define MOONEP_FLAG_GRAD_DONE 6
+#define MOONEP_NUM_FLAG_FAMILIES 8
+
+// Status block (int32 words, device memory, zero = healthy).
+#define MOONEP_ST_CODE 0      // 0 ok, 1 wait timed out, 2 index out of range
+#define MOONEP_ST_KERNEL 1    // id of the kernel that recorded it
+#define MOONEP_ST_FAMILY 2    // flag family waited on / kind of index
+#define MOONEP_ST_PEER 3      // rank waited on / offending value
+#define MOONEP_ST_EXPECT 4    // epoch expected
+#define MOONEP_ST_SEEN 5      // value seen
+#define MOONEP_ST_WORDS 8
+
+#define MOONEP_STATUS_OK 0
+#define MOONEP_STATUS_TIMEOUT 1
+#define MOONEP_STATUS_BAD_INDEX 2
+
+// Kernel ids for the status block.
+#define MOONEP_K_SIGNAL 1
+#define MOONEP_K_PLAN_PUBLISH 2
+#define MOONEP_K_PLAN_TABLES 3
+#define MOONEP_K_PLAN_TOKENS 4
+#define MOONEP_K_DISPATCH_SEND 5
+#define MOONEP_K_DISPATCH_EXPAND 6
+#define MOONEP_K_COMBINE_PROLOGUE 7
+#define MOONEP_K_COMBINE_PULL 8
+#define MOONEP_K_PREFETCH 9
+#define MOONEP_K_GRAD_ACCUM 10
+#define MOONEP_K_GRAD_CLEAR 11
+#define MOONEP_K_WAIT 12
+#define MOONEP_NUM_KERNEL_IDS 16
+
+// Routing entries per planner block (whole tokens, at most this many entries).
+#define MOONEP_PLAN_BLOCK 512
+
+// Copy paths of dispatch/combine/prefetch.
+#define MOONEP_PATH_LDST 0  // 16-byte loads/stores from registers
+#define MOONEP_PATH_BULK 1  // cp.async.bulk through shared memory (mbarrier pipeline)
+
+// Everything a kernel needs to know about one Buffer; passed by value.
+struct MoonepDevCtx {
+  int rank, R, E, S, K, H, B, N;
+  int NvS, epn, token_padding, num_sms;
+  long long nvs_padded;   // rows per hidden chunk
+  long long meta_stride;  // int32 words per meta chunk
+  int weights_off, tpe_off, plan_off, src_info_off, sync_off, r32;
+  int debug;
+  int pad0;
+  unsigned long long timeout_ns;
+  // Peer tables: base address of every rank's chunk as seen from this GPU.
+  uint16_t* const* hidden_peer;  // [R] -> bf16 [nvs_padded, H]
+  int* const* meta_peer;         // [R] -> int32 [meta_stride]
+  // Local scratch.
+  int* status;        // [MOONEP_ST_WORDS]
+  int* counters;      // [MOONEP_NUM_KERNEL_IDS] arrival counters of kernel tails
+  int* alloc_cum;     // [E, R]   inclusive cumsum of alloc over destination ranks
+  int* expert_off;    // [R, E]   first row of expert e on destination d
+  int* tpe_prev;      // [E]      tokens of expert e on source ranks < rank
+  int* tables;        // planner work area, see planner.cu
+  int* primary_packed;  // [R*S]
+  int* kmask;           // [R*S]
+  int* kidx_to_loff;    // [R*S*K]
+  long long* stats;     // [16] counters (rows sent, duplicates, ...)
+};
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+int moonep_version(void);
+const char* moonep_last_error(void);
+int moonep_sizeof_devctx(void);
+// Number of int32 words of planner work area needed for (R, E, B).
+long long moonep_planner_table_words(int R, int E, int B);
+
+// ctx: params is an int64 array in the order of MoonepDevCtx's integer fields (see runtime.cu),
+// followed by the scratch pointers.  Returns an opaque handle or null.
+void* moonep_ctx_create(const long long* params, int nparams, const unsigned long long* hidden_peers,
+                        const unsigned long long* meta_peers);
+void moonep_ctx_destroy(void* ctx);
+int moonep_ctx_set_timeout_ms(void* ctx, long long ms);
+
+// Cross-rank flags.  signal: store `epoch` into flag[family][rank] of every peer.
+// wait: spin (bounded) until every peer's flag[wait_family] >= wait_epoch.  Either part
+// may be skipped by passing family < 0.
+int moonep_signal_wait(void* ctx, int signal_family, int signal_epoch, int wait_family, int wait_epoch,
+                       void* stream);
+
+// Planner.  tpe is [E] (pushed to all peers) or [R, E] (tpe_is_2d, used as is).
+int moonep_plan_publish(void* ctx, const int* tpe, int tpe_is_2d, int epoch_tpe, void* stream);
+int moonep_plan_compute(void* ctx, const int* topk, const int* tpe2d, int* dst, int* cu_seqlens,
+                        int* experts_to_copy, int* zero_fill, int* remote_stats, int wait_epoch_tpe,
+                        int signal_epoch_plan, void* stream);
+
+// Dispatch.
+int moonep_dispatch_send(void* ctx, const void* hidden, const float* weights, const int* dst,
+                         const int* zero_fill, int* dup_groups, int* dup_loffs, int* dup_counts,
+                         int build_dedup, int wait_family, int wait_epoch, int signal_epoch_sent, int path,
+                         void* stream);
+int moonep_dispatch_expand(void* ctx, const int* dup_groups, const int* dup_loffs, const int* dup_counts,
+                           void* out_hidden, float* out_weights, int wait_epoch_sent, int path, void* stream);
+
+// Combine.
+int moonep_combine_prologue(void* ctx, const int* dup_groups, const int* dup_loffs, const int* dup_counts,
+                            const void* in_hidden, const float* in_weights, int wait_family, int wait_epoch,
+                            int signal_epoch_comb, void* stream);
+int moonep_combine_pull(void* ctx, const int* dst, void* out_hidden, float* out_weights, int wait_epoch_comb,
+                        int path, void* stream);
+
+// Expert weights: w[3] are [E+B, H, Hp] bf16 tensors whose first E experts are peer mapped.
+int moonep_prefetch(void* ctx, void* const* w3, int n_tensors, const int* experts_to_copy_row, long long elems,
+                    int path, void* stream);
+// grads[i]: [E, H, Hp] fp32 (local), reduce[i]: [R, B, H, Hp] fp32 (slot (src, b) lives on rank src).
+int moonep_grad_reduce(void* ctx, float* const* grads, float* const* reduce, int n_tensors,
+                       const int* experts_to_copy, int Bcols, long long elems, int epoch_ready, int epoch_done,
+                       int phase, void* stream);
+
+// CUDA VMM symmetric allocator (driver API through cudaGetDriverEntryPoint).
+int moonep_vmm_granularity(int device, unsigned long long* gran);
+int moonep_vmm_create(int device, unsigned long long bytes, unsigned long long* handle, int* fd);
+int moonep_vmm_import(int fd, unsigned long long* handle);
+int moonep_vmm_reserve(unsigned long long bytes, unsigned long long align, unsigned long long* va);
+int moonep_vmm_map(unsigned long long va, unsigned long long bytes, unsigned long long handle, int device);
+int moonep_vmm_unmap(unsigned long long va, unsigned long long bytes);
+int moonep_vmm_release(unsigned long long handle);
+int moonep_vmm_free_va(unsigned long long va, unsigned long long bytes);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,272 @@
+// Expert-weight traffic for sm_100a: prefetch of remote experts and reduction of their
+// gradients back to the owners, plus the stand-alone signal/wait kernel.
+//
+//   prefetch     for every slot b of this rank with experts_to_copy[rank][b] = e >= 0, copy expert e
+//                (physically on its owner, reached through the peer-mapped part of the weight
+//                tensor) into local slot E+b.  Gate, up and down go in one launch; persistent CTAs
+//                stride over 16 KB pieces with eight 16-byte loads in flight per lane.
+//   grad_accum   the owner of expert e adds every slot (src, b) with experts_to_copy[src][b] == e
+//                to its local gradient, in ascending src*B+b order starting from the local value,
+//                so results are bitwise reproducible.  Waits for FLAG_GRAD_READY, signals
+//                FLAG_GRAD_DONE.
+//   grad_clear   after every peer's FLAG_GRAD_DONE each rank zeroes the slots it produced.
+//
+// Parity: reference moonep_td/prefetch.py:22-64, moonep_td/grad_reduce.py:14-178 (host prescan with
+// argsort/bincount and a host sync per tensor, two barriers and two kernels per tensor).
+#include "common.cuh"
+#include "host.h"
+
+namespace moonep {
+
+namespace {
+
+constexpr int kMaxTensors = 3;
+constexpr int kMaxSlots = 4096;     // R*B entries owned by one rank that grad_accum can list
+constexpr int kMaxLocalExperts = 2048;
+constexpr int kPieceVec = 1024;     // 16-byte vectors per work item (16 KB)
+
+struct TensorSet {
+  void* p[kMaxTensors];
+  void* q[kMaxTensors];
+  int n;
+};
+
+__global__ void __launch_bounds__(256)
+    signal_wait_kernel(const MoonepDevCtx c, int signal_family, int signal_epoch, int wait_family, int wait_epoch) {
+  if (signal_family >= 0 && !poisoned(c)) {
+    if (threadIdx.x == 0) fence_sys();
+    __syncthreads();
+    for (int r = threadIdx.x; r < c.R; r += blockDim.x)
+      st_release_sys(flag_ptr(c, r, signal_family, c.rank), signal_epoch);
+  }
+  if (wait_family >= 0) block_wait_flags(c, wait_family, wait_epoch, MOONEP_K_WAIT);
+}
+
+__global__ void __launch_bounds__(512)
+    prefetch_kernel(const MoonepDevCtx c, const TensorSet w, const int* __restrict__ experts, long long elems) {
+  if (poisoned(c)) return;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const long long nvec = elems / 8;  // bf16: 8 elements per 16 bytes
+  const long long pieces = (nvec + kPieceVec - 1) / kPieceVec;
+  const long long total = (long long)w.n * c.B * pieces;
+  for (long long item = (long long)blockIdx.x * nwarps + warp; item < total; item += (long long)gridDim.x * nwarps) {
+    const long long piece = item % pieces;
+    const int b = (int)((item / pieces) % c.B);
+    const int t = (int)(item / (pieces * c.B));
+    const int e = experts[b];
+    if (e < 0) continue;
+    if (e >= c.E) {
+      record_status(c, MOONEP_STATUS_BAD_INDEX, MOONEP_K_PREFETCH, 7, e, b, t);
+      continue;
+    }
+    const int4* src = reinterpret_cast<const int4*>(w.p[t]) + (long long)e * nvec;
+    int4* dstp = reinterpret_cast<int4*>(w.p[t]) + (long long)(c.E + b) * nvec;
+    const long long v0 = piece * kPieceVec;
+    const long long v1 = v0 + kPieceVec < nvec ? v0 + kPieceVec : nvec;
+    for (long long i0 = v0; i0 < v1; i0 += 32 * 8) {
+      int4 v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const long long i = i0 + j * 32 + lane;
+        if (i < v1) v[j] = ld16(src + i);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const long long i = i0 + j * 32 + lane;
+        if (i < v1) st16(dstp + i, v[j]);
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ float4 ld16f(const float4* p) {
+  int4 v = ld16(p);
+  return make_float4(__int_as_float(v.x), __int_as_float(v.y), __int_as_float(v.z), __int_as_float(v.w));
+}
+
+__device__ __forceinline__ void st16f(float4* p, const float4& f) {
+  st16(p, make_int4(__float_as_int(f.x), __float_as_int(f.y), __float_as_int(f.z), __float_as_int(f.w)));
+}
+
+__global__ void __launch_bounds__(512)
+    grad_accum_kernel(const MoonepDevCtx c, const TensorSet ts, const int* __restrict__ etc, int Bcols, long long elems,
+                      int wait_epoch, int signal_epoch) {
+  __shared__ int s_rb[kMaxSlots];
+  __shared__ short s_le[kMaxSlots];
+  __shared__ short s_active[kMaxLocalExperts];
+  __shared__ unsigned char s_has[kMaxLocalExperts];
+  __shared__ int s_n, s_nactive;
+  const bool ok = block_wait_flags(c, MOONEP_FLAG_GRAD_READY, wait_epoch, MOONEP_K_GRAD_ACCUM);
+  if (ok) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int epn = c.epn, owner0 = c.rank * epn, nslots = c.R * Bcols;
+    for (int i = threadIdx.x; i < epn; i += blockDim.x) s_has[i] = 0;
+    __syncthreads();
+    if (warp == 0) {
+      int n = 0;
+      for (int base = 0; base < nslots; base += 32) {
+        const int rb = base + lane;
+        const int e = rb < nslots ? etc[rb] : -1;
+        const bool mine = e >= owner0 && e < owner0 + epn;
+        const unsigned m = __ballot_sync(0xffffffffu, mine);
+        if (mine) {
+          const int pos = n + __popc(m & ((1u << lane) - 1u));
+          if (pos < kMaxSlots) {
+            s_rb[pos] = rb;
+            s_le[pos] = (short)(e - owner0);
+          }
+          s_has[e - owner0] = 1;
+        }
+        n += __popc(m);
+      }
+      __syncwarp();
+      int na = 0;
+      for (int base = 0; base < epn; base += 32) {
+        const int le = base + lane;
+        const bool has = le < epn && s_has[le];
+        const unsigned m = __ballot_sync(0xffffffffu, has);
+        if (has) s_active[na + __popc(m & ((1u << lane) - 1u))] = (short)le;
+        na += __popc(m);
+      }
+      if (lane == 0) {
+        s_n = n < kMaxSlots ? n : kMaxSlots;
+        s_nactive = na;
+        if (n > kMaxSlots) record_status(c, MOONEP_STATUS_BAD_INDEX, MOONEP_K_GRAD_ACCUM, 8, n, kMaxSlots, 0);
+      }
+    }
+    __syncthreads();
+    const int n = s_n, na = s_nactive;
+    const long long nvec = elems / 4;  // fp32: 4 elements per 16 bytes
+    const long long pieces = (nvec + kPieceVec - 1) / kPieceVec;
+    const long long total = (long long)ts.n * na * pieces;
+    for (long long item = (long long)blockIdx.x * nwarps + warp; item < total; item += (long long)gridDim.x * nwarps) {
+      const long long piece = item % pieces;
+      const int ai = (int)((item / pieces) % na);
+      const int t = (int)(item / (pieces * na));
+      const int le = s_active[ai];
+      float4* g = reinterpret_cast<float4*>(ts.p[t]) + (long long)(owner0 + le) * nvec;
+      const float4* red = reinterpret_cast<const float4*>(ts.q[t]);
+      const long long v0 = piece * kPieceVec;
+      const long long v1 = v0 + kPieceVec < nvec ? v0 + kPieceVec : nvec;
+      for (long long i0 = v0; i0 < v1; i0 += 32 * 4) {
+        float4 acc[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const long long i = i0 + j * 32 + lane;
+          if (i < v1) acc[j] = ld16f(g + i);
+        }
+        for (int s = 0; s < n; ++s) {
+          if (s_le[s] != le) continue;
+          const float4* src = red + (long long)s_rb[s] * nvec;
+          float4 v[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const long long i = i0 + j * 32 + lane;
+            if (i < v1) v[j] = ld16f(src + i);
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const long long i = i0 + j * 32 + lane;
+            if (i < v1) {
+              acc[j].x += v[j].x;
+              acc[j].y += v[j].y;
+              acc[j].z += v[j].z;
+              acc[j].w += v[j].w;
+            }
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const long long i = i0 + j * 32 + lane;
+          if (i < v1) st16f(g + i, acc[j]);
+        }
+      }
+    }
+  }
+  grid_tail_signal(c, MOONEP_K_GRAD_ACCUM, ok ? MOONEP_FLAG_GRAD_DONE : -1, signal_epoch);
+}
+
+__global__ void __launch_bounds__(512)
+    grad_clear_kernel(const MoonepDevCtx c, const TensorSet ts, const int* __restrict__ etc, int Bcols, long long elems,
+                      int wait_epoch) {
+  if (!block_wait_flags(c, MOONEP_FLAG_GRAD_DONE, wait_epoch, MOONEP_K_GRAD_CLEAR)) return;
+  const long long nvec = elems / 4;
+  const long long total = (long long)ts.n * Bcols * nvec;
+  const int4 z = make_int4(0, 0, 0, 0);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long v = i % nvec;
+    const int b = (int)((i / nvec) % Bcols);
+    const int t = (int)(i / (nvec * Bcols));
+    if (etc[c.rank * Bcols + b] < 0) continue;
+    st16(reinterpret_cast<int4*>(ts.q[t]) + ((long long)c.rank * Bcols + b) * nvec + v, z);
+  }
+}
+
+}  // namespace
+
+}  // namespace moonep
+
+using namespace moonep;
+
+extern "C" int moonep_signal_wait(void* ctx, int signal_family, int signal_epoch, int wait_family, int wait_epoch,
+                                  void* stream) {
+  auto* h = (HostCtx*)ctx;
+  signal_wait_kernel<<<1, 128, 0, (cudaStream_t)stream>>>(h->dev, signal_family, signal_epoch, wait_family, wait_epoch);
+  return check_launch("signal_wait_kernel");
+}
+
+extern "C" int moonep_prefetch(void* ctx, void* const* w3, int n_tensors, const int* experts_to_copy_row,
+                               long long elems, int path, void* stream) {
+  (void)path;
+  auto* h = (HostCtx*)ctx;
+  const MoonepDevCtx& c = h->dev;
+  if (n_tensors < 1 || n_tensors > kMaxTensors || elems % 8 != 0) {
+    set_error("moonep_prefetch: 1..3 tensors with H*Hp a multiple of 8 expected");
+    return 1;
+  }
+  if (c.B == 0) return 0;
+  TensorSet w;
+  w.n = n_tensors;
+  for (int i = 0; i < kMaxTensors; ++i) {
+    w.p[i] = i < n_tensors ? w3[i] : nullptr;
+    w.q[i] = nullptr;
+  }
+  const int grid = imax(1, imin(c.num_sms, h->sm_count));
+  prefetch_kernel<<<grid, 512, 0, (cudaStream_t)stream>>>(c, w, experts_to_copy_row, elems);
+  return check_launch("prefetch_kernel");
+}
+
+extern "C" int moonep_grad_reduce(void* ctx, float* const* grads, float* const* reduce, int n_tensors,
+                                  const int* experts_to_copy, int Bcols, long long elems, int epoch_ready,
+                                  int epoch_done, int phase, void* stream) {
+  auto* h = (HostCtx*)ctx;
+  const MoonepDevCtx& c = h->dev;
+  if (n_tensors < 1 || n_tensors > kMaxTensors || elems % 4 != 0) {
+    set_error("moonep_grad_reduce: 1..3 tensors with H*Hp a multiple of 4 expected");
+    return 1;
+  }
+  if (c.epn > kMaxLocalExperts) {
+    set_error("moonep_grad_reduce: more than 2048 experts per rank");
+    return 1;
+  }
+  TensorSet ts;
+  ts.n = n_tensors;
+  for (int i = 0; i < kMaxTensors; ++i) {
+    ts.p[i] = i < n_tensors ? (void*)grads[i] : nullptr;
+    ts.q[i] = i < n_tensors ? (void*)reduce[i] : nullptr;
+  }
+  const int grid = imax(1, imin(c.num_sms, h->sm_count));
+  cudaStream_t st = (cudaStream_t)stream;
+  if (phase == 1) {
+    grad_accum_kernel<<<grid, 512, 0, st>>>(c, ts, experts_to_copy, Bcols, elems, epoch_ready, epoch_done);
+    return check_launch("grad_accum_kernel");
+  }
+  if (phase == 2) {
+    if (Bcols == 0) return 0;
+    grad_clear_kernel<<<grid, 512, 0, st>>>(c, ts, experts_to_copy, Bcols, elems, epoch_done);
+    return check_launch("grad_clear_kernel");
+  }
+  set_error("moonep_grad_reduce: phase must be 1 (accumulate) or 2 (clear)");
+  return 1;
+}

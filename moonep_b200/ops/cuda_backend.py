@@ -1,0 +1,280 @@
+"""CUDA backend: launches the sm_100a kernels of ``libmoonep_b200.so`` for one Buffer.
+
+Every method enqueues kernels on the current CUDA stream and returns; nothing
+here synchronises with the host.  Cross-rank ordering is carried by epoch flags
+in the meta chunks: ``self.epoch[family]`` counts the signals of a family, and
+since all ranks issue the same sequence of operations the counters agree
+without communication.  ``world.step()`` is a no-op for real multi-GPU worlds
+and a thread barrier for in-process emulation (it keeps the emulated ranks'
+launches in phase order on their shared stream).
+
+Parity: plays the role of the reference's ``launch_*`` functions
+(``moonep_td/dispatch.py:126``, ``combine.py:77``, ``prefetch.py:73``,
+``grad_reduce.py:183``, ``_planning_gpu.py:523``).
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+import torch
+
+from .. import config
+from ..constants import (
+    FLAG_COMB,
+    FLAG_GRAD_DONE,
+    FLAG_GRAD_READY,
+    FLAG_PLAN,
+    FLAG_READY,
+    FLAG_SENT,
+    FLAG_TPE,
+    NUM_FLAG_FAMILIES,
+    STATUS_BAD_INDEX,
+    STATUS_TIMEOUT,
+)
+from ..errors import MoonEPIndexError, MoonEPTimeoutError
+from . import _lib
+
+_PATHS = {"ldst": 0, "bulk": 1}
+_KERNEL_NAMES = {
+    1: "signal", 2: "plan_publish", 3: "plan_tables", 4: "plan_tokens", 5: "dispatch_send", 6: "dispatch_expand",
+    7: "combine_prologue", 8: "combine_pull", 9: "prefetch", 10: "grad_accum", 11: "grad_clear", 12: "wait",
+}  # fmt: skip
+_FAMILY_NAMES = {0: "READY", 1: "TPE", 2: "PLAN", 3: "SENT", 4: "COMB", 5: "GRAD_READY", 6: "GRAD_DONE"}
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+class CudaBackend:
+    name = "cuda"
+
+    def __init__(self, ctx: dict, world):
+        self.ctx = ctx
+        self.world = world
+        self.lib = _lib.load()
+        dev = ctx["device"]
+        c = ctx
+        R, E, S, K, B = c["R"], c["E"], c["S"], c["K"], c["B"]
+        self.epoch = [0] * NUM_FLAG_FAMILIES
+        self.path = _PATHS[config.copy_path()]
+
+        def i32(n):
+            return torch.zeros(max(int(n), 1), dtype=torch.int32, device=dev)
+
+        self.status = i32(8)
+        self.counters = i32(64)
+        self.alloc_cum = i32(E * R)
+        self.expert_off = i32(R * E)
+        self.tpe_prev = i32(E)
+        self.tables = i32(self.lib.moonep_planner_table_words(R, E, B))
+        self.stats_buf = torch.zeros(16, dtype=torch.int64, device=dev)
+        c["alloc"] = self.tables[2 * E : 2 * E + R * E]  # planner's alloc[d*E+e]
+
+        hid_base = c["hidden_buf"].data_ptr()
+        meta_base = c["meta_buf"].data_ptr()
+        hp = (ctypes.c_ulonglong * R)(*[hid_base + r * c["NvS_padded"] * c["H"] * 2 for r in range(R)])
+        mp = (ctypes.c_ulonglong * R)(*[meta_base + r * c["meta_chunk_padded"] * 4 for r in range(R)])
+        params = [
+            c["rank"], R, E, S, K, c["H"], B, c["N"], c["NvS"], c["epn"], c["token_padding"], c["num_sms"],
+            c["NvS_padded"], c["meta_chunk_padded"], c["WEIGHTS_OFF"], c["TPE_OFF"], c["PLAN_OFF"], c["SRC_INFO_OFF"],
+            c["SYNC_OFF"], c["R32"], int(config.debug()), config.timeout_ms(),
+            self.status.data_ptr(), self.counters.data_ptr(), self.alloc_cum.data_ptr(), self.expert_off.data_ptr(),
+            self.tpe_prev.data_ptr(), self.tables.data_ptr(), c["primary_packed"].data_ptr(), c["kmask"].data_ptr(),
+            c["kidx_to_loff"].data_ptr(), self.stats_buf.data_ptr(),
+        ]  # fmt: skip
+        arr = (ctypes.c_longlong * len(params))(*params)
+        with torch.cuda.device(dev):
+            self.handle = self.lib.moonep_ctx_create(arr, len(params), hp, mp)
+        if not self.handle:
+            raise _lib.NativeError("moonep_ctx_create failed: " + self.lib.moonep_last_error().decode())
+
+    # -- housekeeping ------------------------------------------------------------------
+    def destroy(self):
+        if self.handle:
+            self.lib.moonep_ctx_destroy(self.handle)
+            self.handle = None
+
+    def set_timeout_ms(self, ms: int):
+        _lib.check(self.lib.moonep_ctx_set_timeout_ms(self.handle, int(ms)), "set_timeout_ms")
+
+    def check_status(self):
+        st = self.status.cpu().tolist()
+        if st[0] == 0:
+            return
+        self.status.zero_()
+        kern = _KERNEL_NAMES.get(st[1], str(st[1]))
+        if st[0] == STATUS_TIMEOUT:
+            raise MoonEPTimeoutError(
+                f"rank {self.ctx['rank']}: kernel {kern} gave up waiting for flag "
+                f"{_FAMILY_NAMES.get(st[2], st[2])} of rank {st[3]} (expected epoch {st[4]}, saw {st[5]})",
+                kernel=kern, family=st[2], peer=st[3], expected=st[4], seen=st[5],
+            )  # fmt: skip
+        if st[0] == STATUS_BAD_INDEX:
+            raise MoonEPIndexError(
+                f"rank {self.ctx['rank']}: kernel {kern} met an out-of-range index (kind {st[2]}, value {st[3]}, "
+                f"limit {st[4]}, at {st[5]})"
+            )
+        raise RuntimeError(f"unknown device status {st}")
+
+    def stats(self) -> dict:
+        return {"epochs": list(self.epoch), "status": self.status.cpu().tolist()}
+
+    def _next(self, family: int) -> int:
+        self.epoch[family] += 1
+        return self.epoch[family]
+
+    def _call(self, name, *args):
+        with torch.cuda.device(self.ctx["device"]):
+            _lib.check(getattr(self.lib, name)(self.handle, *args), name)
+
+    # -- flags ---------------------------------------------------------------------------
+    def signal(self, family: int):
+        self._call("moonep_signal_wait", family, self._next(family), -1, 0, _stream())
+        self.world.step()
+
+    def wait(self, family: int):
+        self._call("moonep_signal_wait", -1, 0, family, self.epoch[family], _stream())
+
+    def barrier(self):
+        self.signal(FLAG_READY)
+        self.wait(FLAG_READY)
+
+    # -- planning ------------------------------------------------------------------------
+    def plan_publish(self, tpe: torch.Tensor):
+        is2d = int(tpe.dim() == 2)
+        self._call("moonep_plan_publish", _ptr(tpe), is2d, self._next(FLAG_TPE), _stream())
+        self.world.step()
+
+    def plan_compute(self, topk_flat, tpe, cu_seqlens, plan):
+        if not config.planner_on_gpu():
+            return self._plan_compute_host(topk_flat, tpe, cu_seqlens, plan)
+        tpe2d = _ptr(tpe) if tpe.dim() == 2 else None
+        self._call(
+            "moonep_plan_compute", _ptr(topk_flat), tpe2d, _ptr(plan.dst), _ptr(cu_seqlens),
+            _ptr(plan.experts_to_copy), _ptr(plan.zero_fill_ranges), _ptr(plan.remote_stats),
+            self.epoch[FLAG_TPE], self._next(FLAG_PLAN), _stream(),
+        )  # fmt: skip
+        self.world.step()
+
+    def _plan_compute_host(self, topk_flat, tpe, cu_seqlens, plan):
+        """MOONEP_PLANNER=cpu: the host planner on device data (synchronises; for debugging)."""
+        from ..cpu import planner as P
+
+        c = self.ctx
+        rank, R, E, S, K, NvS, ms = c["rank"], c["R"], c["E"], c["S"], c["K"], c["NvS"], c["meta_chunk_padded"]
+        self.wait(FLAG_TPE)
+        meta = c["meta_buf"]
+        if tpe.dim() == 2:
+            tpe_np = tpe.cpu().numpy()
+        else:
+            tpe_np = meta[rank * ms + c["TPE_OFF"] : rank * ms + c["TPE_OFF"] + R * E].cpu().numpy().reshape(R, E)
+        tabs = P.global_tables(tpe_np, S=S, K=K, B=c["B"], token_padding=c["token_padding"], NvS=NvS)
+        dst_pos = P.local_destinations(topk_flat.cpu().numpy().reshape(-1), rank, tabs, NvS)
+        dst = P.mark_duplicates(dst_pos, S, K, NvS)
+        dev = c["device"]
+
+        def put(t, a):
+            t.copy_(torch.from_numpy(np.ascontiguousarray(a)).to(torch.int32).reshape(t.shape).to(dev))
+
+        put(plan.dst, dst)
+        put(cu_seqlens, tabs["cu_seqlens"][rank])
+        put(plan.experts_to_copy, tabs["experts_to_copy"])
+        put(plan.remote_stats, tabs["remote_stats"][rank])
+        put(plan.zero_fill_ranges, tabs["zero_fill"][rank])
+        dest = dst_pos // NvS
+        loff = dst_pos - dest * NvS
+        idx = torch.from_numpy(dest * ms + c["SRC_INFO_OFF"] + loff).to(dev)
+        meta[idx] = torch.from_numpy(rank * NvS + np.arange(S * K)).to(torch.int32).to(dev)
+        self._call("moonep_signal_wait", FLAG_PLAN, self._next(FLAG_PLAN), -1, 0, _stream())
+        self.world.step()
+
+    # -- dispatch ------------------------------------------------------------------------
+    def dispatch_send(self, hidden_sh, route_weights_sk, plan, build_dedup_map, wait=None):
+        wf = -1 if wait is None else int(wait)
+        we = 0 if wait is None else self.epoch[wf]
+        self._call(
+            "moonep_dispatch_send", _ptr(hidden_sh), _ptr(route_weights_sk), _ptr(plan.dst),
+            _ptr(plan.zero_fill_ranges), _ptr(plan.dup_groups), _ptr(plan.dup_loffs), _ptr(plan.dup_counts),
+            int(bool(build_dedup_map)), wf, we, self._next(FLAG_SENT), self.path, _stream(),
+        )  # fmt: skip
+        self.world.step()
+
+    def dispatch_expand(self, plan, out_hidden, out_weights, zero_copy):
+        self._call(
+            "moonep_dispatch_expand", _ptr(plan.dup_groups), _ptr(plan.dup_loffs), _ptr(plan.dup_counts),
+            None, None, self.epoch[FLAG_SENT], self.path, _stream(),
+        )  # fmt: skip
+        if not zero_copy:
+            out_hidden.copy_(self.ctx["hidden_buf_local"])
+            if out_weights is not None:
+                out_weights.copy_(self.ctx["weights_buf_local"].view(torch.float32))
+
+    # -- combine -------------------------------------------------------------------------
+    def combine_prologue(self, plan, hidden_nvsh, route_weights_nvs, zero_copy, wait=None):
+        wf = -1 if wait is None else int(wait)
+        if not zero_copy:
+            if wait is not None:
+                self.wait(wf)  # peers must be done reading the shard before it is overwritten
+                wf = -1
+            self.ctx["hidden_buf_local"].copy_(hidden_nvsh)
+            if route_weights_nvs is not None:
+                self.ctx["weights_buf_local"].copy_(route_weights_nvs.view(torch.int32))
+        we = 0 if wf < 0 else self.epoch[wf]
+        self._call(
+            "moonep_combine_prologue", _ptr(plan.dup_groups), _ptr(plan.dup_loffs), _ptr(plan.dup_counts),
+            None, None, wf, we, self._next(FLAG_COMB), _stream(),
+        )  # fmt: skip
+        self.world.step()
+
+    def combine_pull(self, plan_dst, out_hidden, out_weights_sk):
+        self._call(
+            "moonep_combine_pull", _ptr(plan_dst), _ptr(out_hidden), _ptr(out_weights_sk), self.epoch[FLAG_COMB],
+            self.path, _stream(),
+        )  # fmt: skip
+
+    # -- expert weights --------------------------------------------------------------------
+    def prefetch(self, weights, experts_to_copy):
+        c = self.ctx
+        E, B = c["E"], c["B"]
+        ws = [w for w in weights if w is not None]
+        if B == 0 or not ws or experts_to_copy.numel() == 0:
+            return
+        H, Hp = int(ws[0].shape[1]), int(ws[0].shape[2])
+        for w in ws:
+            assert w.dtype == torch.bfloat16 and w.is_contiguous(), "weights must be contiguous bf16"
+            assert tuple(w.shape) == (E + B, H, Hp), f"weight shape {tuple(w.shape)} != {(E + B, H, Hp)}"
+        assert H % 128 == 0 and Hp % 128 == 0, f"H and H' must be multiples of 128, got ({H}, {Hp})"
+        assert experts_to_copy.dtype == torch.int32 and experts_to_copy.is_contiguous()
+        arr = (ctypes.c_void_p * len(ws))(*[w.data_ptr() for w in ws])
+        row = experts_to_copy[c["rank"]]
+        self._call("moonep_prefetch", arr, len(ws), _ptr(row), H * Hp, self.path, _stream())
+
+    def reduce_grad(self, experts_to_copy, grads, reduce_buffers):
+        c = self.ctx
+        R, E = c["R"], c["E"]
+        if experts_to_copy.numel() == 0 or any(r.numel() == 0 for r in reduce_buffers):
+            return
+        Bc = int(experts_to_copy.shape[1])
+        H, Hp = int(grads[0].shape[1]), int(grads[0].shape[2])
+        assert experts_to_copy.dtype == torch.int32 and experts_to_copy.is_contiguous()
+        assert tuple(experts_to_copy.shape) == (R, Bc)
+        for g, r in zip(grads, reduce_buffers):
+            assert g.dtype == torch.float32 and g.is_contiguous() and g.ndim == 3
+            assert r.dtype == torch.float32 and r.is_contiguous() and r.ndim == 4
+            assert tuple(g.shape) == (E, H, Hp) and tuple(r.shape) == (R, Bc, H, Hp)
+        assert H % 128 == 0 and Hp % 128 == 0, f"H and H' must be multiples of 128, got ({H}, {Hp})"
+        n = len(grads)
+        ga = (ctypes.c_void_p * n)(*[g.data_ptr() for g in grads])
+        ra = (ctypes.c_void_p * n)(*[r.data_ptr() for r in reduce_buffers])
+        self.signal(FLAG_GRAD_READY)
+        ready, done = self.epoch[FLAG_GRAD_READY], self._next(FLAG_GRAD_DONE)
+        self._call("moonep_grad_reduce", ga, ra, n, _ptr(experts_to_copy), Bc, H * Hp, ready, done, 1, _stream())
+        self.world.step()
+        self._call("moonep_grad_reduce", ga, ra, n, _ptr(experts_to_copy), Bc, H * Hp, ready, done, 2, _stream())
