@@ -1,0 +1,260 @@
+"""Headline benchmark: expert-parallel dispatch + combine round trip.
+
+Config (DeepSeek-V3 shaped EP): S=4096 tokens per rank, H=7168 bf16, K=8, E=256 experts,
+router logits ~ N(0,1) with softmax top-8 gates, num_sms=32, token_padding=128,
+identity expert, synthetic data, weak scaling (S per rank fixed).
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 8 --steps 20 --warmup 5
+
+Rank 0 prints one JSON line.  ``value`` is aggregate tokens per second through one
+fresh-plan dispatch plus one combine (device-timed with CUDA events, max over ranks, L2
+flushed between timed steps).  ``e2e`` is the same step through the public API including
+the per-step host-to-device copy of the inputs from pinned memory and the device-to-host
+read of a checksum of the result.  ``--impl reference`` runs the reference package from
+``baseline/_ref`` if its runtime (triton_dist + nvshmem4py) can be imported.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def parse_args():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=20)
+    p.add_argument("--warmup", type=int, default=5)
+    p.add_argument("--impl", default="ours", choices=["ours", "reference", "nccl"])
+    p.add_argument("--S", type=int, default=4096)
+    p.add_argument("--H", type=int, default=7168)
+    p.add_argument("--K", type=int, default=8)
+    p.add_argument("--E", type=int, default=256)
+    p.add_argument("--num-sms", type=int, default=32)
+    p.add_argument("--token-padding", type=int, default=128)
+    p.add_argument("--routing", default="softmax")
+    p.add_argument("--staged", action="store_true", help="use the copying (non zero-copy) API paths")
+    return p.parse_args()
+
+
+def init_dist(n):
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local)
+    if n > 1:
+        import torch.distributed as dist
+
+        assert world == n, f"--gpus {n} but WORLD_SIZE={world}; launch with torch.distributed.run"
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29500")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return rank, local, world
+
+
+def max_over_ranks(x: float, n: int) -> float:
+    if n == 1:
+        return x
+    import torch.distributed as dist
+
+    t = torch.tensor([x], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def barrier_sync(n):
+    torch.cuda.synchronize()
+    if n > 1:
+        import torch.distributed as dist
+
+        dist.barrier(device_ids=[torch.cuda.current_device()])
+        torch.cuda.synchronize()
+
+
+def reference_arm(args):
+    out = {"impl": "reference"}
+    sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
+    try:
+        import moonep_td  # noqa: F401
+    except Exception as exc:  # noqa: BLE001
+        out["unavailable"] = f"reference package not installed under baseline/_ref: {exc!r}"
+        print(json.dumps(out))
+        return
+    try:
+        import nvshmem.core  # noqa: F401
+        import triton_dist  # noqa: F401
+    except Exception as exc:  # noqa: BLE001
+        out["unavailable"] = (
+            "reference needs triton_dist (Triton-distributed) and nvshmem4py, neither is in this image "
+            f"and there is no network: {exc!r}"
+        )
+        print(json.dumps(out))
+        return
+    # Both runtimes import: run the reference's own Buffer on the same config.
+    from moonep_td import Buffer as RefBuffer
+
+    rank, local, world = init_dist(args.gpus)
+    res = run_steps(args, RefBuffer, rank, world, reference=True)
+    if rank == 0:
+        res["impl"] = "reference"
+        print(json.dumps(res))
+
+
+def run_steps(args, BufferCls, rank, n, reference=False):
+    from moonep_b200.models.routing import make_routing
+    from moonep_b200.utils.clocks import ClockSampler
+
+    S, H, K, E = args.S, args.H, args.K, args.E
+    dev = torch.device("cuda", torch.cuda.current_device())
+    buf = BufferCls(S, H, K, E, n, num_sms=args.num_sms, token_padding=args.token_padding)
+    zero_copy = not args.staged
+    topk_h, tpe_h, gates_h = make_routing(args.routing, S, K, E, n, rank, seed=2026)
+    g = torch.Generator().manual_seed(7 + rank)
+    x_h = torch.randn(S, H, generator=g).to(torch.bfloat16)
+    pinned = [t.pin_memory() for t in (x_h, gates_h, topk_h, tpe_h)]
+    x, gates, topk, tpe = (t.to(dev) for t in pinned)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)  # > 126 MB L2
+
+    def step(x, gates, topk, tpe):
+        xn, wn, cu, plan = buf.dispatch(x, gates, topk, tpe, zero_copy=zero_copy)
+        out, wb, _ = buf.combine(plan, xn, wn, zero_copy=zero_copy)
+        return out, wb, plan
+
+    lib = None
+    if not reference:
+        from moonep_b200.ops import _lib
+
+        lib = _lib.load()
+
+    for _ in range(max(args.warmup, 3)):
+        out, wb, plan = step(x, gates, topk, tpe)
+    torch.cuda.synchronize()
+    if hasattr(buf, "check_status"):
+        buf.check_status()
+    # correctness spot check: identity expert gives K * x up to two bf16 roundings
+    err = (out.float() - K * x.float()).abs().max().item()
+    ok = err <= 0.25 and torch.equal(wb, gates)
+
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    launches0 = lib.moonep_launch_count() if lib else 0
+    barrier_sync(n)
+    with ClockSampler(torch.cuda.current_device()) as clocks:
+        for i in range(args.steps):
+            flush.zero_()
+            ev[i][0].record()
+            xn, wn, cu, plan = buf.dispatch(x, gates, topk, tpe, zero_copy=zero_copy)
+            ev[i][1].record()
+            out, wb, _ = buf.combine(plan, xn, wn, zero_copy=zero_copy)
+            ev[i][2].record()
+        barrier_sync(n)
+    launches = (lib.moonep_launch_count() - launches0) if lib else 0
+    t_disp = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps
+    t_comb = sum(e[1].elapsed_time(e[2]) for e in ev) / args.steps
+    t_step = sum(e[0].elapsed_time(e[2]) for e in ev) / args.steps
+    t_disp, t_comb, t_step = (max_over_ranks(t, n) for t in (t_disp, t_comb, t_step))
+
+    # end to end: inputs come from pinned host memory every step, a checksum goes back
+    cs_h = torch.empty(1, dtype=torch.float32).pin_memory()
+    dev_in = [torch.empty_like(t, device=dev) for t in pinned]
+    e2e_ev = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(args.steps)]
+    for i in range(2 + args.steps):
+        timed = i >= 2
+        if timed:
+            flush.zero_()
+            e2e_ev[i - 2][0].record()
+        for d, h in zip(dev_in, pinned):
+            d.copy_(h, non_blocking=True)
+        out, wb, plan = step(*dev_in)
+        cs_h.copy_(out.float().abs().mean().reshape(1), non_blocking=True)
+        if timed:
+            e2e_ev[i - 2][1].record()
+        torch.cuda.synchronize()
+    barrier_sync(n)
+    t_e2e = max_over_ranks(sum(e[0].elapsed_time(e[1]) for e in e2e_ev) / args.steps, n)
+    h2d = sum(t.numel() * t.element_size() for t in pinned)
+
+    # bytes that cross to other ranks (primary rows only) for the bandwidth figures
+    dst = plan.dst
+    NvS = plan.NvS
+    dest = torch.where(dst < 0, -dst - 1, dst) // NvS
+    remote_rows = int(((dst >= 0) & (dest != rank)).sum().item())
+    total_rows = int((dst >= 0).sum().item())
+    row_bytes = H * 2
+    if hasattr(buf, "check_status"):
+        buf.check_status()
+    buf.destroy()
+    res = {
+        "metric": "ep_dispatch_combine_tokens_per_s",
+        "value": n * S / (t_step / 1e3),
+        "unit": "tokens/s",
+        "n_gpus": n,
+        "steps": args.steps,
+        "warmup": max(args.warmup, 3),
+        "ms_per_step": t_step,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic (N(0,1) activations, N(0,1) router logits, softmax top-k gates, identity expert)",
+        "config": {
+            "model": "DeepSeek-V3-shaped EP dispatch+combine",
+            "S_per_rank": S, "H": H, "K": K, "E": E, "global_batch": n * S, "seq_len": S,
+            "parallelism": f"ep{n}", "num_sms": args.num_sms, "token_padding": args.token_padding,
+            "routing": args.routing, "zero_copy": zero_copy, "l2": "flushed between timed steps (256 MB write)",
+        },
+        "dispatch_us": t_disp * 1e3,
+        "combine_us": t_comb * 1e3,
+        "rows_sent_per_rank": total_rows,
+        "remote_rows_per_rank": remote_rows,
+        "dispatch_nvlink_GBps_per_rank": remote_rows * row_bytes / (t_disp / 1e3) / 1e9,
+        "combine_nvlink_GBps_per_rank": remote_rows * row_bytes / (t_comb / 1e3) / 1e9,
+        "dispatch_payload_GBps_per_rank": total_rows * row_bytes / (t_disp / 1e3) / 1e9,
+        "combine_payload_GBps_per_rank": total_rows * row_bytes / (t_comb / 1e3) / 1e9,
+        "correct": bool(ok),
+        "max_abs_err": err,
+        "clocks": clocks.summary(),
+        "e2e": {
+            "value": n * S / (t_e2e / 1e3), "unit": "tokens/s", "ms_per_step": t_e2e,
+            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
+        },
+        "gpu_launches": int(launches),
+    }  # fmt: skip
+    return res
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+    rank, local, world = init_dist(args.gpus)
+    if args.impl == "nccl":
+        from moonep_b200.bench.nccl_baseline import run_nccl_baseline
+
+        res = run_nccl_baseline(args, rank, args.gpus)
+    else:
+        from moonep_b200 import Buffer
+
+        res = run_steps(args, Buffer, rank, args.gpus)
+    if rank == 0:
+        res["impl"] = args.impl
+        print(json.dumps(res))
+    if args.gpus > 1:
+        import torch.distributed as dist
+
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    t0 = time.time()
+    main()

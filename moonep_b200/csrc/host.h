@@ -19,7 +19,12 @@ struct HostCtx {
 void set_error(const std::string& s);
 int check_cuda(cudaError_t e, const char* what);
 
-inline int check_launch(const char* what) { return check_cuda(cudaGetLastError(), what); }
+// Every kernel launch of the library goes through check_launch, which also counts it.
+extern long long g_launch_count;
+inline int check_launch(const char* what) {
+  ++g_launch_count;
+  return check_cuda(cudaGetLastError(), what);
+}
 
 inline int imin(int a, int b) { return a < b ? a : b; }
 inline int imax(int a, int b) { return a > b ? a : b; }

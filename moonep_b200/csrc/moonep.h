@@ -101,6 +101,8 @@ extern "C" {
 int moonep_version(void);
 const char* moonep_last_error(void);
 int moonep_sizeof_devctx(void);
+// Number of kernels this library has launched in the calling process.
+long long moonep_launch_count(void);
 // Number of int32 words of planner work area needed for (R, E, B).
 long long moonep_planner_table_words(int R, int E, int B);
 

@@ -26,6 +26,7 @@
 namespace moonep {
 
 static thread_local std::string g_last_error;
+long long g_launch_count = 0;
 
 void set_error(const std::string& s) { g_last_error = s; }
 
@@ -42,6 +43,7 @@ using namespace moonep;
 extern "C" int moonep_version(void) { return MOONEP_VERSION; }
 extern "C" const char* moonep_last_error(void) { return g_last_error.c_str(); }
 extern "C" int moonep_sizeof_devctx(void) { return (int)sizeof(MoonepDevCtx); }
+extern "C" long long moonep_launch_count(void) { return g_launch_count; }
 
 // ---- context ----------------------------------------------------------------------------------
 

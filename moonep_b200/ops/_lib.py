@@ -99,6 +99,7 @@ _SIGNATURES = {
     "moonep_version": (_i, []),
     "moonep_last_error": (ctypes.c_char_p, []),
     "moonep_sizeof_devctx": (_i, []),
+    "moonep_launch_count": (_ll, []),
     "moonep_planner_table_words": (_ll, [_i, _i, _i]),
     "moonep_ctx_create": (_vp, [ctypes.POINTER(_ll), _i, ctypes.POINTER(_ull), ctypes.POINTER(_ull)]),
     "moonep_ctx_destroy": (None, [_vp]),

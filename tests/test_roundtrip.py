@@ -1,0 +1,89 @@
+"""Dispatch -> expert -> combine on emulated worlds: CPU backend (always) and the sm_100a
+kernels on one GPU with R emulated ranks (marked gpu).
+
+Checks (parity: reference tests/test_dispatch.py:200-342, tests/test_combine.py:201-257):
+planner outputs equal the host planner; every (source, token, k) row and weight landed where
+dst says; pad rows are zero after the shard was poisoned; the dedup map equals the oracle's as
+a set of groups; combine returns the K-sum with the library's two roundings; gate weights come
+back bit-exact.
+"""
+
+import pytest
+import torch
+
+from tests.cases import PLANNING_CASES, ROUNDTRIP_CASES
+from tests.harness import assert_within_ulp, check_dispatch_records, expected_combine, run_round_trip
+
+DEVICES = ["cpu", pytest.param("cuda", marks=pytest.mark.gpu)]
+
+
+def _check(case, R, device, **kw):
+    recs = run_round_trip(case, R, device, **kw)
+    tabs, dst_pos, dst, src_info = check_dispatch_records(case, R, recs)
+    return recs, tabs, dst_pos
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("R", [1, 2, 4])
+@pytest.mark.parametrize("case", ROUNDTRIP_CASES, ids=lambda c: c.name)
+def test_identity_round_trip(case, R, device):
+    if not case.supports(R):
+        pytest.skip("world size not supported by this case")
+    recs, tabs, dst_pos = _check(case, R, device)
+    want = expected_combine(case, R, recs, dst_pos)
+    for r in range(R):
+        assert_within_ulp(recs[r]["out"], want[r], max_ulps=0 if device == "cpu" else 1, what=f"rank {r} combine")
+        assert torch.equal(recs[r]["weights_back"], recs[r]["w"]), f"rank {r}: weights did not round-trip"
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("R", [2, 4])
+@pytest.mark.parametrize("case", ROUNDTRIP_CASES[:4] + ROUNDTRIP_CASES[7:8], ids=lambda c: c.name)
+def test_zero_copy_scaled_expert_round_trip(case, R, device):
+    """Expert stage multiplies every received row by (row index % 5 + 1); zero-copy buffers."""
+    if not case.supports(R):
+        pytest.skip("world size not supported by this case")
+
+    def scale(rec, r, E):
+        n = rec["hidden_nvsh"].shape[0]
+        return (torch.arange(n) % 5 + 1).float()
+
+    recs, tabs, dst_pos = _check(case, R, device, zero_copy=True, expert_scale=scale)
+    NvS = recs[0]["layout"]["NvS"]
+    scale_rows = [(torch.arange(NvS) % 5 + 1).float() for _ in range(R)]
+    want = expected_combine(case, R, recs, dst_pos, scale_rows)
+    for r in range(R):
+        assert_within_ulp(recs[r]["out"], want[r], max_ulps=0 if device == "cpu" else 1, what=f"rank {r} combine")
+        assert torch.equal(recs[r]["weights_back"], recs[r]["w"])
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("R", [1, 2, 4])
+@pytest.mark.parametrize("case", PLANNING_CASES, ids=lambda c: c.name)
+def test_planning_cases_through_dispatch(case, R, device):
+    """The planner matrix, checked through a full dispatch (plan equality + landed rows)."""
+    if not case.supports(R):
+        pytest.skip("world size not supported by this case")
+    if device == "cpu" and case.S * case.K * R > 20000:
+        pytest.skip("slow on the CPU backend")
+    _check(case, R, device)
+
+
+@pytest.mark.parametrize("device", DEVICES)
+def test_async_finish_matches_sync(device):
+    case = ROUNDTRIP_CASES[1]
+    a = run_round_trip(case, 2, device, async_finish=False)
+    b = run_round_trip(case, 2, device, async_finish=True)
+    for r in range(2):
+        assert torch.equal(a[r]["out"], b[r]["out"])
+        assert torch.equal(a[r]["dst"], b[r]["dst"])
+        assert torch.equal(a[r]["weights_back"], b[r]["weights_back"])
+
+
+@pytest.mark.parametrize("device", DEVICES)
+def test_hidden_only_dispatch_without_weights(device):
+    case = ROUNDTRIP_CASES[0]
+    recs = run_round_trip(case, 2, device, with_weights=False)
+    check_dispatch_records(case, 2, recs)
+    for r in range(2):
+        assert recs[r]["weights_nvs"] is None and recs[r]["weights_back"] is None
