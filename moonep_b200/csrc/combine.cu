@@ -207,13 +207,15 @@ __global__ void __launch_bounds__(512)
             }
           }
         } else {
-          for (int i = lane; i < H; i += 32) {
+          // every lane runs the same number of iterations: the shuffles need the whole warp
+          for (int i0 = 0; i0 < H; i0 += 32) {
+            const int i = i0 + lane;
             float acc = 0.f;
             for (int p = 0; p < nprim; ++p) {
               const unsigned long long ptr = __shfl_sync(0xffffffffu, rows_compact, p);
-              acc += bf16_to_f32(reinterpret_cast<const uint16_t*>(ptr)[i]);
+              if (i < H) acc += bf16_to_f32(reinterpret_cast<const uint16_t*>(ptr)[i]);
             }
-            orow[i] = f32_to_bf16(acc);
+            if (i < H) orow[i] = f32_to_bf16(acc);
           }
         }
       }
