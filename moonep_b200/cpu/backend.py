@@ -219,6 +219,12 @@ class CpuBackend:
                 if e >= 0:
                     w[E + b].copy_(w[e])
 
+    def prefetch_launch(self, remote_experts, prefetch_buffers, experts_row):
+        for src, dst in zip(remote_experts, prefetch_buffers):
+            for b, e in enumerate(experts_row.tolist()):
+                if e >= 0:
+                    dst[b].copy_(src[e])
+
     def reduce_grad(self, experts_to_copy, grads, reduce_buffers):
         c = self.ctx
         E, R, rank = c["E"], c["R"], c["rank"]

@@ -140,9 +140,9 @@ int moonep_combine_prologue(void* ctx, const int* dup_groups, const int* dup_lof
 int moonep_combine_pull(void* ctx, const int* dst, void* out_hidden, float* out_weights, int wait_epoch_comb,
                         int path, void* stream);
 
-// Expert weights: w[3] are [E+B, H, Hp] bf16 tensors whose first E experts are peer mapped.
-int moonep_prefetch(void* ctx, void* const* w3, int n_tensors, const int* experts_to_copy_row, long long elems,
-                    int path, void* stream);
+// Expert weights: src[i] is [nexperts, H, Hp] bf16 (peer mapped), dst[i] is [nslots, H, Hp] bf16 (local).
+int moonep_prefetch(void* ctx, void* const* src3, void* const* dst3, int n_tensors, const int* experts_to_copy_row,
+                    long long elems, int nslots, int nexperts, int path, void* stream);
 // grads[i]: [E, H, Hp] fp32 (local), reduce[i]: [R, B, H, Hp] fp32 (slot (src, b) lives on rank src).
 int moonep_grad_reduce(void* ctx, float* const* grads, float* const* reduce, int n_tensors,
                        const int* experts_to_copy, int Bcols, long long elems, int epoch_ready, int epoch_done,

@@ -3,7 +3,7 @@
 //
 //   prefetch     for every slot b of this rank with experts_to_copy[rank][b] = e >= 0, copy expert e
 //                (physically on its owner, reached through the peer-mapped part of the weight
-//                tensor) into local slot E+b.  Gate, up and down go in one launch; persistent CTAs
+//                tensor) into local slot b of the prefetch buffers (slot E+b of the full weight).  Gate, up and down go in one launch; persistent CTAs
 //                stride over 16 KB pieces with eight 16-byte loads in flight per lane.
 //   grad_accum   the owner of expert e adds every slot (src, b) with experts_to_copy[src][b] == e
 //                to its local gradient, in ascending src*B+b order starting from the local value,
@@ -43,24 +43,25 @@ __global__ void __launch_bounds__(256)
 }
 
 __global__ void __launch_bounds__(512)
-    prefetch_kernel(const MoonepDevCtx c, const TensorSet w, const int* __restrict__ experts, long long elems) {
+    prefetch_kernel(const MoonepDevCtx c, const TensorSet w, const int* __restrict__ experts, long long elems,
+                    int nslots, int nexperts) {
   if (poisoned(c)) return;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const long long nvec = elems / 8;  // bf16: 8 elements per 16 bytes
   const long long pieces = (nvec + kPieceVec - 1) / kPieceVec;
-  const long long total = (long long)w.n * c.B * pieces;
+  const long long total = (long long)w.n * nslots * pieces;
   for (long long item = (long long)blockIdx.x * nwarps + warp; item < total; item += (long long)gridDim.x * nwarps) {
     const long long piece = item % pieces;
-    const int b = (int)((item / pieces) % c.B);
-    const int t = (int)(item / (pieces * c.B));
+    const int b = (int)((item / pieces) % nslots);
+    const int t = (int)(item / (pieces * nslots));
     const int e = experts[b];
     if (e < 0) continue;
-    if (e >= c.E) {
+    if (e >= nexperts) {
       record_status(c, MOONEP_STATUS_BAD_INDEX, MOONEP_K_PREFETCH, 7, e, b, t);
       continue;
     }
     const int4* src = reinterpret_cast<const int4*>(w.p[t]) + (long long)e * nvec;
-    int4* dstp = reinterpret_cast<int4*>(w.p[t]) + (long long)(c.E + b) * nvec;
+    int4* dstp = reinterpret_cast<int4*>(w.q[t]) + (long long)b * nvec;
     const long long v0 = piece * kPieceVec;
     const long long v1 = v0 + kPieceVec < nvec ? v0 + kPieceVec : nvec;
     for (long long i0 = v0; i0 < v1; i0 += 32 * 8) {
@@ -216,8 +217,9 @@ extern "C" int moonep_signal_wait(void* ctx, int signal_family, int signal_epoch
   return check_launch("signal_wait_kernel");
 }
 
-extern "C" int moonep_prefetch(void* ctx, void* const* w3, int n_tensors, const int* experts_to_copy_row,
-                               long long elems, int path, void* stream) {
+extern "C" int moonep_prefetch(void* ctx, void* const* src3, void* const* dst3, int n_tensors,
+                               const int* experts_to_copy_row, long long elems, int nslots, int nexperts, int path,
+                               void* stream) {
   (void)path;
   auto* h = (HostCtx*)ctx;
   const MoonepDevCtx& c = h->dev;
@@ -225,15 +227,15 @@ extern "C" int moonep_prefetch(void* ctx, void* const* w3, int n_tensors, const 
     set_error("moonep_prefetch: 1..3 tensors with H*Hp a multiple of 8 expected");
     return 1;
   }
-  if (c.B == 0) return 0;
+  if (nslots <= 0) return 0;
   TensorSet w;
   w.n = n_tensors;
   for (int i = 0; i < kMaxTensors; ++i) {
-    w.p[i] = i < n_tensors ? w3[i] : nullptr;
-    w.q[i] = nullptr;
+    w.p[i] = i < n_tensors ? src3[i] : nullptr;
+    w.q[i] = i < n_tensors ? dst3[i] : nullptr;
   }
   const int grid = imax(1, imin(c.num_sms, h->sm_count));
-  prefetch_kernel<<<grid, 512, 0, (cudaStream_t)stream>>>(c, w, experts_to_copy_row, elems);
+  prefetch_kernel<<<grid, 512, 0, (cudaStream_t)stream>>>(c, w, experts_to_copy_row, elems, nslots, nexperts);
   return check_launch("prefetch_kernel");
 }
 

@@ -111,7 +111,7 @@ _SIGNATURES = {
     "moonep_dispatch_expand": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp]),
     "moonep_combine_prologue": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "moonep_combine_pull": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp]),
-    "moonep_prefetch": (_i, [_vp, ctypes.POINTER(_vp), _i, _vp, _ll, _i, _vp]),
+    "moonep_prefetch": (_i, [_vp, ctypes.POINTER(_vp), ctypes.POINTER(_vp), _i, _vp, _ll, _i, _i, _i, _vp]),
     "moonep_grad_reduce": (_i, [_vp, ctypes.POINTER(_vp), ctypes.POINTER(_vp), _i, _vp, _i, _ll, _i, _i, _i, _vp]),
     "moonep_vmm_granularity": (_i, [_i, ctypes.POINTER(_ull)]),
     "moonep_vmm_create": (_i, [_i, _ull, ctypes.POINTER(_ull), ctypes.POINTER(_i)]),

@@ -252,9 +252,24 @@ class CudaBackend:
             assert tuple(w.shape) == (E + B, H, Hp), f"weight shape {tuple(w.shape)} != {(E + B, H, Hp)}"
         assert H % 128 == 0 and Hp % 128 == 0, f"H and H' must be multiples of 128, got ({H}, {Hp})"
         assert experts_to_copy.dtype == torch.int32 and experts_to_copy.is_contiguous()
-        arr = (ctypes.c_void_p * len(ws))(*[w.data_ptr() for w in ws])
         row = experts_to_copy[c["rank"]]
-        self._call("moonep_prefetch", arr, len(ws), _ptr(row), H * Hp, self.path, _stream())
+        self.prefetch_launch([w[:E] for w in ws], [w[E:] for w in ws], row)
+
+    def prefetch_launch(self, remote_experts, prefetch_buffers, experts_row):
+        """Launch-level form: ``remote_experts[i]`` is ``[E', H, Hp]``, ``prefetch_buffers[i]`` ``[B', H, Hp]``."""
+        n = len(remote_experts)
+        nexp, H, Hp = (int(v) for v in remote_experts[0].shape)
+        nslots = int(prefetch_buffers[0].shape[0])
+        if nslots == 0 or experts_row.numel() == 0:
+            return
+        for s, d in zip(remote_experts, prefetch_buffers):
+            assert s.dtype == torch.bfloat16 and s.is_contiguous() and d.dtype == torch.bfloat16 and d.is_contiguous()
+            assert tuple(s.shape) == (nexp, H, Hp) and tuple(d.shape) == (nslots, H, Hp)
+        assert experts_row.dtype == torch.int32 and experts_row.is_contiguous() and experts_row.numel() == nslots
+        assert H % 128 == 0 and Hp % 128 == 0, f"H and H' must be multiples of 128, got ({H}, {Hp})"
+        src = (ctypes.c_void_p * n)(*[t.data_ptr() for t in remote_experts])
+        dst = (ctypes.c_void_p * n)(*[t.data_ptr() for t in prefetch_buffers])
+        self._call("moonep_prefetch", src, dst, n, _ptr(experts_row), H * Hp, nslots, nexp, self.path, _stream())
 
     def reduce_grad(self, experts_to_copy, grads, reduce_buffers):
         c = self.ctx

@@ -71,56 +71,21 @@ def create_nvl_single_owner_tensor(shape, dtype, owner_rank: int, world: World) 
     return view
 
 
-def create_full_expert_weight(E: int, B: int, H: int, Hp: int, world: World, dtype=torch.bfloat16):
-    """Weight tensor ``[E+B, H, Hp]``: experts sharded over their owners, then B local prefetch slots.
+def create_full_expert_weight(E: int, B: int, H: int, Hp: int, world: World, dtype=torch.bfloat16) -> torch.Tensor:
+    """Collective.  Weight tensor ``[E+B, H, Hp]``: experts ``[0, E)`` live on their owners
+    (rank r holds experts ``[r*E/R, (r+1)*E/R)``), slots ``[E, E+B)`` are local.
 
-    Returns ``(full, handle)``; pass ``handle`` to ``release_full_expert_weight``.  On CUDA
-    worlds with more than one process the two parts are mapped back to back in one address
-    range; elsewhere the tensor is simply the concatenation inside one allocation.
+    On a multi-process CUDA world the peers' experts and the local slots are mapped back to
+    back in one address range (``E/R * H * Hp`` elements must fill whole VMM granules).  On
+    emulated and host worlds there is no peer mapping: a plain local tensor is returned and
+    the caller fills ``[:E]`` with all experts.
     """
     R = world.size
     assert E % R == 0
-    epn = E // R
     if world.is_cuda and not world.emulated and R > 1:
         from .vmm import VmmAllocator
 
-        return VmmAllocator.get(world).alloc_expert_weight(epn, B, H, Hp, dtype)
-    # host / emulated / single rank: one allocation per rank view, shared expert part
-    chunk = epn * H * Hp
-    st = world.alloc_symmetric(chunk, dtype, 128)
-    experts = st.full.view(E, H, Hp)
-    if world.emulated and R > 1 or not world.is_cuda:
-        # a rank-private tail cannot follow shared storage contiguously without VMM, so the
-        # emulated layouts keep [E+B] per rank with the first E rows copied on refresh
-        full = torch.zeros(E + B, H, Hp, dtype=dtype, device=world.device)
-        return full, _EmulatedWeight(st, experts, full, world, epn)
-    full = torch.zeros(E + B, H, Hp, dtype=dtype, device=world.device)
-    return full, _EmulatedWeight(st, experts, full, world, epn)
-
-
-class _EmulatedWeight:
-    """Expert weights of an emulated or single-rank world.
-
-    ``publish()`` copies this rank's own experts into the shared storage;
-    ``refresh()`` (after all ranks published and stepped) copies all experts into the
-    rank's private ``[E+B]`` tensor so that ``full[:E]`` reads what a peer mapping would.
-    """
-
-    def __init__(self, st, experts, full, world, epn):
-        self.st, self.experts, self.full, self.world, self.epn = st, experts, full, world, epn
-
-    def publish(self):
-        r, epn = self.world.rank, self.epn
-        self.experts[r * epn : (r + 1) * epn].copy_(self.full[r * epn : (r + 1) * epn])
-        self.world.step()
-
-    def refresh(self):
-        self.full[: self.experts.shape[0]].copy_(self.experts)
-        self.world.step()
-
-    def release(self):
-        self.st.release()
-
-
-def release_full_expert_weight(handle) -> None:
-    handle.release()
+        full, st = VmmAllocator.get(world).alloc_expert_weight(E // R, B, H, Hp, dtype)
+        _LIVE[full.data_ptr()] = st
+        return full
+    return torch.zeros(E + B, H, Hp, dtype=dtype, device=world.device)

@@ -100,7 +100,8 @@ class VmmAllocator:
             _lib.check(self.lib.moonep_vmm_granularity(self.dev_index, ctypes.byref(g)), "moonep_vmm_granularity")
         self.granularity = int(g.value)
 
-    def alloc(self, chunk_numel: int, dtype: torch.dtype) -> SymmetricTensor:
+    def alloc(self, chunk_numel: int, dtype: torch.dtype, tail_numel: int = 0) -> SymmetricTensor:
+        """Map all ranks' chunks back to back, optionally followed by ``tail_numel`` rank-private elements."""
         w, lib = self.world, self.lib
         R, rank = w.size, w.rank
         itemsize = torch.empty(0, dtype=dtype).element_size()
@@ -113,8 +114,10 @@ class VmmAllocator:
             _lib.check(lib.moonep_vmm_create(self.dev_index, chunk_bytes, ctypes.byref(handle), ctypes.byref(fd)),
                        "moonep_vmm_create")  # fmt: skip
             fds = exchange_fds(w.group, rank, R, fd.value)
+            tail_bytes = -(-tail_numel * itemsize // self.granularity) * self.granularity
             va = ctypes.c_ulonglong(0)
-            _lib.check(lib.moonep_vmm_reserve(R * chunk_bytes, self.granularity, ctypes.byref(va)), "moonep_vmm_reserve")
+            _lib.check(lib.moonep_vmm_reserve(R * chunk_bytes + tail_bytes, self.granularity, ctypes.byref(va)),
+                       "moonep_vmm_reserve")  # fmt: skip
             handles = []
             for r in range(R):
                 if r == rank:
@@ -128,17 +131,43 @@ class VmmAllocator:
             for f in fds:
                 if f >= 0:
                     os.close(f)
-        full = tensor_from_ptr(va.value, R * chunk_numel, dtype, w.device)
-        base, total = va.value, R * chunk_bytes
+            tail_handle = None
+            if tail_bytes:
+                th, tfd = ctypes.c_ulonglong(0), ctypes.c_int(-1)
+                _lib.check(lib.moonep_vmm_create(self.dev_index, tail_bytes, ctypes.byref(th), ctypes.byref(tfd)),
+                           "moonep_vmm_create(tail)")  # fmt: skip
+                os.close(tfd.value)
+                _lib.check(lib.moonep_vmm_map(va.value + R * chunk_bytes, tail_bytes, th.value, self.dev_index),
+                           "moonep_vmm_map(tail)")  # fmt: skip
+                tail_handle = th.value
+        full = tensor_from_ptr(va.value, R * chunk_numel + tail_numel, dtype, w.device)
+        base, total = va.value, R * chunk_bytes + tail_bytes
 
         def release():
             torch.cuda.synchronize(w.device)
             for r in range(R):
                 lib.moonep_vmm_unmap(base + r * chunk_bytes, chunk_bytes)
                 lib.moonep_vmm_release(handles[r])
+            if tail_handle is not None:
+                lib.moonep_vmm_unmap(base + R * chunk_bytes, tail_bytes)
+                lib.moonep_vmm_release(tail_handle)
             lib.moonep_vmm_free_va(base, total)
 
         full[rank * chunk_numel : (rank + 1) * chunk_numel].zero_()
+        if tail_numel:
+            full[R * chunk_numel :].zero_()
         torch.cuda.synchronize(w.device)
         dist.barrier(group=w.group, device_ids=[self.dev_index])
         return SymmetricTensor(full, chunk_numel, on_release=release)
+
+    def alloc_expert_weight(self, epn: int, B: int, H: int, Hp: int, dtype: torch.dtype):
+        """``[R*epn + B, H, Hp]``: every owner's experts mapped in rank order, then B local slots."""
+        per = H * Hp
+        itemsize = torch.empty(0, dtype=dtype).element_size()
+        assert (epn * per * itemsize) % self.granularity == 0, (
+            f"experts per rank * H * H' * {itemsize} bytes must be a multiple of the VMM granularity "
+            f"({self.granularity}); got {epn}*{H}*{Hp}"
+        )
+        st = self.alloc(epn * per, dtype, tail_numel=B * per)
+        full = st.full.view(self.world.size * epn + B, H, Hp)
+        return full, st

@@ -148,58 +148,61 @@ def assert_within_ulp(actual, expected, max_ulps=1, atol=0.0, what=""):
     assert not bool(bad.any()), f"{what}: {int(bad.sum())} elements differ, max err {float(diff.max())}"
 
 
-def run_round_trip(case: Case, R: int, device: str, *, zero_copy=False, expert_scale=None, with_weights=True,
-                   poison=True, async_finish=False):  # fmt: skip
-    """Fresh dispatch -> per-row expert function -> combine on a LocalWorld; returns per-rank records."""
-    lw = LocalWorld(R, device)
-    bufs = make_buffers(case, lw)
+def round_trip_rank(buf, case: Case, R: int, r: int, step, *, zero_copy=False, expert_scale=None, with_weights=True,
+                    poison=True, async_finish=False):  # fmt: skip
+    """One rank's part of: fresh dispatch -> per-row expert function -> combine.  ``step()`` is a host
+    rendezvous of all ranks (thread barrier or dist.barrier)."""
+    ctx = buf._require_ctx()
+    dev = ctx["device"]
     E = case.E(R)
-
-    def body(r):
-        buf = bufs[r]
-        ctx = buf._require_ctx()
-        dev = ctx["device"]
-        topk, tpe, _ = routing_for(case, R, r, device=dev)
-        x = traceable_hidden(case.S, case.H, r, dev)
-        w = traceable_weights(case.S, case.K, r, dev) if with_weights else None
-        if poison:
-            ctx["hidden_buf_local"].fill_(7.0)
-            ctx["weights_buf_local"].fill_(0x55555555)
-            lw.view(r).step()
-        res = buf.dispatch(x, w, topk, tpe, async_finish=async_finish, zero_copy=zero_copy)
-        if async_finish:
-            res[-1].synchronize() if dev.type == "cpu" else torch.cuda.current_stream().wait_event(res[-1])
-        xn, wn, cu, plan = res[:4]
-        rec = {
-            "topk": topk.cpu(), "tpe": tpe.cpu(), "x": x.cpu(), "w": None if w is None else w.cpu(),
-            "hidden_nvsh": xn.detach().cpu().clone(), "weights_nvs": None if wn is None else wn.detach().cpu().clone(),
-            "cu_seqlens": cu.cpu(), "dst": plan.dst.cpu(), "experts_to_copy": plan.experts_to_copy.cpu(),
-            "zero_fill": plan.zero_fill_ranges.cpu(), "remote_stats": plan.remote_stats.cpu(),
-            "dup_groups": plan.dup_groups.cpu(), "dup_loffs": plan.dup_loffs.cpu(), "dup_counts": plan.dup_counts.cpu(),
-            "src_info": ctx["meta_buf"][r * ctx["meta_chunk_padded"] + ctx["SRC_INFO_OFF"]:][: ctx["NvS"]].cpu().clone(),
-            "layout": {k: v for k, v in ctx.items() if isinstance(v, int)},
-        }  # fmt: skip
-        # expert stage: y = scale(group) * x, applied row-wise on the received rows
-        if expert_scale is not None:
-            scale = expert_scale(rec, r, E).to(dev)
-            y = (xn.float() * scale[:, None]).to(torch.bfloat16)
-            if zero_copy:
-                xn.copy_(y)
-                y = xn
-        else:
-            y = xn
-        out, wb, ev = buf.combine(plan, y, wn, async_finish=async_finish, zero_copy=zero_copy)
-        if async_finish and dev.type == "cuda":
-            torch.cuda.current_stream().wait_event(ev)
-        rec["out"] = out.cpu()
-        rec["weights_back"] = None if wb is None else wb.cpu()
+    topk, tpe, _ = routing_for(case, R, r, device=dev)
+    x = traceable_hidden(case.S, case.H, r, dev)
+    w = traceable_weights(case.S, case.K, r, dev) if with_weights else None
+    if poison:
+        ctx["hidden_buf_local"].fill_(7.0)
+        ctx["weights_buf_local"].fill_(0x55555555)
         if dev.type == "cuda":
             torch.cuda.synchronize()
-            buf.check_status()
-        return rec
+        step()
+    res = buf.dispatch(x, w, topk, tpe, async_finish=async_finish, zero_copy=zero_copy)
+    if async_finish:
+        res[-1].synchronize() if dev.type == "cpu" else torch.cuda.current_stream().wait_event(res[-1])
+    xn, wn, cu, plan = res[:4]
+    rec = {
+        "topk": topk.cpu(), "tpe": tpe.cpu(), "x": x.cpu(), "w": None if w is None else w.cpu(),
+        "hidden_nvsh": xn.detach().cpu().clone(), "weights_nvs": None if wn is None else wn.detach().cpu().clone(),
+        "cu_seqlens": cu.cpu(), "dst": plan.dst.cpu(), "experts_to_copy": plan.experts_to_copy.cpu(),
+        "zero_fill": plan.zero_fill_ranges.cpu(), "remote_stats": plan.remote_stats.cpu(),
+        "dup_groups": plan.dup_groups.cpu(), "dup_loffs": plan.dup_loffs.cpu(), "dup_counts": plan.dup_counts.cpu(),
+        "src_info": ctx["meta_buf"][r * ctx["meta_chunk_padded"] + ctx["SRC_INFO_OFF"]:][: ctx["NvS"]].cpu().clone(),
+        "layout": {k: v for k, v in ctx.items() if isinstance(v, int)},
+    }  # fmt: skip
+    # expert stage: y = scale(row) * x, applied row-wise on the received rows
+    if expert_scale is not None:
+        scale = expert_scale(rec, r, E).to(dev)
+        y = (xn.float() * scale[:, None]).to(torch.bfloat16)
+        if zero_copy:
+            xn.copy_(y)
+            y = xn
+    else:
+        y = xn
+    out, wb, ev = buf.combine(plan, y, wn, async_finish=async_finish, zero_copy=zero_copy)
+    if async_finish and dev.type == "cuda":
+        torch.cuda.current_stream().wait_event(ev)
+    rec["out"] = out.cpu()
+    rec["weights_back"] = None if wb is None else wb.cpu()
+    if dev.type == "cuda":
+        torch.cuda.synchronize()
+        buf.check_status()
+    return rec
 
+
+def run_round_trip(case: Case, R: int, device: str, **kw):
+    """``round_trip_rank`` on a LocalWorld; returns the per-rank records."""
+    lw = LocalWorld(R, device)
+    bufs = make_buffers(case, lw)
     try:
-        return lw.run(body)
+        return lw.run(lambda r: round_trip_rank(bufs[r], case, R, r, lw.view(r).step, **kw))
     finally:
         destroy_buffers(lw, bufs)
 

@@ -1,0 +1,33 @@
+"""One process per rank over torch.distributed: gloo + /dev/shm on CPU, NCCL + CUDA VMM on GPUs."""
+
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run_worker(nproc, backend, port, timeout, extra_env=None):
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MOONEP_TIMEOUT_MS=os.environ.get("MOONEP_TIMEOUT_MS", "5000"))
+    env.update(extra_env or {})
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "mp_worker.py"), "--backend", backend]  # fmt: skip
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env, cwd=ROOT)
+    assert out.returncode == 0, f"worker failed:\n{out.stdout[-4000:]}\n{out.stderr[-6000:]}"
+    assert out.stdout.count("WORKER OK") == nproc, out.stdout[-4000:]
+
+
+def test_cpu_backend_two_gloo_processes():
+    _run_worker(2, "gloo", 29621, 600)
+
+
+@pytest.mark.gpu
+def test_cuda_backend_nccl_processes():
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    # NVLS off: a rank that dies while bound to an NVLink multicast object can fault its peers
+    _run_worker(min(n, 4), "nccl", 29631, 900, {"NCCL_NVLS_ENABLE": "0"})
