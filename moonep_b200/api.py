@@ -192,7 +192,7 @@ class Buffer:
         wait = None
         if planning_args is not None:
             topk_flat, tpe, cu_seqlens = planning_args
-            be.plan_publish(tpe)
+            be.plan_publish(tpe, topk_flat)
             be.plan_compute(topk_flat, tpe, cu_seqlens, plan)
             wait = FLAG_PLAN
         elif inter_rank_sync:

@@ -4,6 +4,8 @@ MOONEP_PLANNER        ``gpu`` (default) or ``cpu``: run the planner kernels or t
 MOONEP_TIMEOUT_MS     budget of every device-side wait (default 10000).
 MOONEP_COPY_PATH      ``bulk`` (default: TMA bulk copies through shared memory) or ``ldst``
                       (plain 16-byte loads/stores) for dispatch/combine/prefetch.
+MOONEP_LOCAL_SMS      CTAs of the kernels that only touch local memory (default: all SMs); ``num_sms`` of
+                      the Buffer bounds the kernels that move data between ranks.
 MOONEP_NUM_SMS_DEDUP  number of SMs the dedup builder may use (validated, 1..SM count).
 MOONEP_DEBUG          ``1`` enables device-side index checks that record a status instead of faulting.
 
@@ -36,6 +38,14 @@ def copy_path() -> str:
     if raw not in ("bulk", "ldst"):
         raise ValueError(f"MOONEP_COPY_PATH must be 'bulk' or 'ldst', got {raw!r}")
     return raw
+
+
+def local_sms(sm_count: int) -> int:
+    """CTAs for kernels that only touch local memory (planner, dedup expansion, duplicate folding)."""
+    raw = os.environ.get("MOONEP_LOCAL_SMS")
+    if raw is None or raw == "":
+        return sm_count
+    return max(1, min(int(raw), sm_count))
 
 
 def debug() -> bool:

@@ -26,6 +26,9 @@ BARRIER_SLOTS = 3
 # many (token, k) entries; blocks are aligned to whole tokens.
 BLOCK_SIZE_P2 = 2048
 
+# Planner kernels work on blocks of whole tokens with at most this many routing entries.
+PLAN_BLOCK = 512
+
 # Vestigial tags of the reference's grid barrier; the flag protocol here uses
 # monotonically increasing epochs instead.
 GRID_SYNC_TAG = 0x80000000

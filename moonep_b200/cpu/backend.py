@@ -75,7 +75,7 @@ class CpuBackend:
         return {}
 
     # -- planning ------------------------------------------------------------
-    def plan_publish(self, tokens_per_expert: torch.Tensor):
+    def plan_publish(self, tokens_per_expert: torch.Tensor, topk_flat=None):
         c = self.ctx
         rank, R, E = c["rank"], c["R"], c["E"]
         self._meta(rank, c["SRC_INFO_OFF"], c["NvS"]).fill_(-1)
@@ -109,12 +109,14 @@ class CpuBackend:
         dest = dst_pos // NvS
         loff = dst_pos - dest * NvS
         src_val = torch.from_numpy(rank * NvS + np.arange(S * K)).to(torch.int32)
+        link = torch.from_numpy(P.link_words(dst_pos, S, K, NvS)).to(torch.int32)
         loff_t = torch.from_numpy(loff)
         dest_t = torch.from_numpy(dest)
         for d in range(R):
             m = dest_t == d
             if bool(m.any()):
                 self._meta(d, c["SRC_INFO_OFF"], NvS)[loff_t[m]] = src_val[m]
+                self._meta(d, c["LINK_OFF"], NvS)[loff_t[m]] = link[m]
         self.world.step()
 
     def build_dedup(self, plan):

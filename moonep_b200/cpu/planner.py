@@ -190,6 +190,28 @@ def mark_duplicates(dst_pos: np.ndarray, S: int, K: int, NvS: int) -> np.ndarray
     return np.where(is_dup, -d - 1, d).reshape(-1)
 
 
+LINK_PRIMARY = 1 << 30
+LINK_HAS_NEXT = 1 << 29
+
+
+def link_words(dst_pos: np.ndarray, S: int, K: int, NvS: int) -> np.ndarray:
+    """Per local entry, the word its source pushes beside src_info: primary bit, and the row of the
+    next entry (higher k) of the same token on the same destination rank."""
+    d = dst_pos.reshape(S, K)
+    dest = d // NvS
+    loff = d - dest * NvS
+    same = dest[:, :, None] == dest[:, None, :]  # [S, k, k']
+    earlier = np.tril(np.ones((K, K), dtype=bool), k=-1)
+    later = np.triu(np.ones((K, K), dtype=bool), k=1)
+    is_dup = (same & earlier[None]).any(axis=2)
+    cand = same & later[None]
+    has_next = cand.any(axis=2)
+    nxt_k = cand.argmax(axis=2)  # first later k' on the same destination
+    nxt = np.take_along_axis(loff, nxt_k, axis=1)
+    words = np.where(is_dup, 0, LINK_PRIMARY) | np.where(has_next, LINK_HAS_NEXT | nxt, 0)
+    return words.reshape(-1)
+
+
 def build_dedup(src_info: np.ndarray, *, S: int, K: int, NvS: int):
     """Destination side: duplicate groups from the src_info of the landed rows.
 

@@ -247,7 +247,7 @@ extern "C" int moonep_combine_prologue(void* ctx, const int* dup_groups, const i
   (void)in_weights;
   auto* h = (HostCtx*)ctx;
   const MoonepDevCtx& c = h->dev;
-  const int grid = imax(1, imin(c.num_sms, h->sm_count));
+  const int grid = imax(1, imin(c.local_sms, h->sm_count));
   combine_prologue_kernel<<<grid, 512, 0, (cudaStream_t)stream>>>(c, dup_groups, dup_loffs, dup_counts, wait_family,
                                                                  wait_epoch, signal_epoch_comb, (c.H % 8 == 0) ? 1 : 0);
   return check_launch("combine_prologue_kernel");

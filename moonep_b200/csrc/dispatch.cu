@@ -13,8 +13,8 @@
 //                            bulk groups); no register traffic, one instruction per 14 KB row.
 //                      ldst: 16-byte loads into registers, 16-byte stores to every destination.
 //                    Meanwhile the pad rows of the local shard are zero-filled and, for a fresh
-//                    plan, the last CTA builds dup_groups/dup_loffs/dup_counts from the src_info
-//                    the peers pushed during planning.  The last CTA to finish signals FLAG_SENT.
+//                    plan, dup_groups/dup_loffs/dup_counts are built from the link words the
+//                    peers pushed during planning (all CTAs share the rows).  The last CTA to finish signals FLAG_SENT.
 //   dispatch_expand  waits for every peer's FLAG_SENT, then copies each primary row to its
 //                    duplicate rows inside the local shard.
 //
@@ -59,62 +59,41 @@ __device__ __forceinline__ void decode_dst(int d, int NvS, int& dest, int& loff)
   loff = raw - dest * NvS;
 }
 
-// ---- destination-side dedup builder (one CTA) ----------------------------------------------
-
-__device__ void build_dedup_block(const MoonepDevCtx& c, const SendArgs& a) {
-  const int tid = threadIdx.x, nth = blockDim.x, lane = tid & 31;
-  const int R = c.R, S = c.S, K = c.K, NvS = c.NvS;
+// ---- destination-side dedup builder (all CTAs share the rows) ----------------------------------
+//
+// During planning every source pushed, next to src_info, a link word per landed row: whether the
+// row is the first of its (source, token) on this rank and which row holds the next entry of the
+// same token.  A primary row that has a successor opens a group; walking the chain lists its
+// duplicates in ascending k.  Rows are independent, so any number of threads can share them; groups
+// and duplicate rows are numbered with one pair of atomics per warp.  dup_counts is zeroed by the
+// host wrapper before the launch.
+__device__ void build_dedup_rows(const MoonepDevCtx& c, const SendArgs& a, int gthread, int gthreads) {
+  const int lane = threadIdx.x & 31;
+  const int NvS = c.NvS;
   const int* src_info = c.meta_peer[c.rank] + c.src_info_off;
-  const int nkeys = R * S;
-  if (tid < 2) a.dup_counts[tid] = 0;
-  for (int i = tid; i < nkeys; i += nth) {
-    c.primary_packed[i] = INT_MAX;
-    c.kmask[i] = 0;
-  }
-  for (int i = tid; i < NvS; i += nth) {
-    a.dup_loffs[i] = 0;
-    a.dup_groups[3 * i] = 0;
-    a.dup_groups[3 * i + 1] = 0;
-    a.dup_groups[3 * i + 2] = 0;
-  }
-  __syncthreads();
-  for (int loff = tid; loff < NvS; loff += nth) {
-    const int info = src_info[loff];
-    if (info < 0) continue;
-    const int src = info / NvS;
-    const int slot = info - src * NvS;
-    const int token = slot / K;
-    const int kidx = slot - token * K;
-    if (src >= R || token >= S) {
-      record_status(c, MOONEP_STATUS_BAD_INDEX, MOONEP_K_DISPATCH_SEND, 5, info, loff, 0);
-      continue;
-    }
-    const int key = src * S + token;
-    atomicMin(c.primary_packed + key, (kidx << MOONEP_NVS_BITS) | loff);
-    atomicOr(c.kmask + key, 1 << kidx);
-    c.kidx_to_loff[(long long)key * K + kidx] = loff;
-  }
-  __syncthreads();
-  const int rounds = (NvS + nth - 1) / nth;
+  const int* link = c.meta_peer[c.rank] + c.link_off;
+  const int rounds = (NvS + gthreads - 1) / gthreads;
   for (int it = 0; it < rounds; ++it) {
-    const int loff = it * nth + tid;
-    int dup_n = 0, key = 0, pk = 0;
-    unsigned mask = 0;
-    if (loff < NvS) {
-      const int info = src_info[loff];
-      if (info >= 0) {
-        const int src = info / NvS;
-        const int token = (info - src * NvS) / K;
-        if (src < R && token < S) {
-          key = src * S + token;
-          const int packed = c.primary_packed[key];
-          mask = (unsigned)c.kmask[key];
-          pk = packed >> MOONEP_NVS_BITS;
-          if ((packed & MOONEP_NVS_MASK) == loff) dup_n = __popc(mask) - 1;
+    const int loff = it * gthreads + gthread;
+    int dup_n = 0, first = -1;
+    if (loff < NvS && src_info[loff] >= 0) {
+      const int l = link[loff];
+      if ((l & MOONEP_LINK_PRIMARY) && (l & MOONEP_LINK_HAS_NEXT)) {
+        first = l & MOONEP_NVS_MASK;
+        int cur = first;
+        while (dup_n < MOONEP_MAX_TOPK) {
+          if (cur < 0 || cur >= NvS) {
+            record_status(c, MOONEP_STATUS_BAD_INDEX, MOONEP_K_DISPATCH_SEND, 5, cur, loff, 0);
+            dup_n = 0;
+            break;
+          }
+          ++dup_n;
+          const int l2 = link[cur];
+          if (!(l2 & MOONEP_LINK_HAS_NEXT)) break;
+          cur = l2 & MOONEP_NVS_MASK;
         }
       }
     }
-    // one pair of atomics per warp: groups and duplicate rows are numbered by warp scans
     const unsigned has = __ballot_sync(0xffffffffu, dup_n > 0);
     if (has == 0) continue;
     int incl = dup_n;
@@ -134,14 +113,15 @@ __device__ void build_dedup_block(const MoonepDevCtx& c, const SendArgs& a) {
     if (dup_n > 0) {
       const int g = gbase + __popc(has & ((1u << lane) - 1u));
       int ds = dbase + incl - dup_n;
-      a.dup_groups[3 * g] = loff;
-      a.dup_groups[3 * g + 1] = ds;
-      a.dup_groups[3 * g + 2] = dup_n;
-      unsigned m = mask & ~(1u << pk);
-      while (m) {
-        const int kk = __ffs(m) - 1;
-        m &= m - 1;
-        a.dup_loffs[ds++] = c.kidx_to_loff[(long long)key * K + kk];
+      if (g < NvS && ds + dup_n <= NvS) {
+        a.dup_groups[3 * g] = loff;
+        a.dup_groups[3 * g + 1] = ds;
+        a.dup_groups[3 * g + 2] = dup_n;
+        int cur = first;
+        for (int q = 0; q < dup_n; ++q) {
+          a.dup_loffs[ds + q] = cur;
+          cur = link[cur] & MOONEP_NVS_MASK;
+        }
       }
     }
   }
@@ -201,7 +181,7 @@ __global__ void __launch_bounds__(kSendThreadsLdst) dispatch_send_ldst_kernel(co
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   int* work = c.counters + MOONEP_NUM_KERNEL_IDS;  // token counter of this kernel
   if (ok) {
-    if (a.build_dedup && blockIdx.x == gridDim.x - 1) build_dedup_block(c, a);
+    if (a.build_dedup) build_dedup_rows(c, a, blockIdx.x * blockDim.x + threadIdx.x, gridDim.x * blockDim.x);
     zero_fill_rows(c, a, blockIdx.x * nwarps + warp, gridDim.x * nwarps, lane);
     const int H = c.H, K = c.K, S = c.S;
     for (;;) {
@@ -289,10 +269,12 @@ __global__ void __launch_bounds__(kSendThreadsBulk) dispatch_send_bulk_kernel(co
   const bool ok = block_wait_flags(c, a.wait_family, a.wait_epoch, MOONEP_K_DISPATCH_SEND);
   int* work = c.counters + MOONEP_NUM_KERNEL_IDS;
   if (ok) {
-    if (a.build_dedup && blockIdx.x == gridDim.x - 1) build_dedup_block(c, a);
     if (warp >= kBulkWarps) {
-      // helper warps: pad rows
+      // helper warps: duplicate map and pad rows
       const int hw = nwarps - kBulkWarps;
+      const int hthreads = hw * 32;
+      if (a.build_dedup)
+        build_dedup_rows(c, a, blockIdx.x * hthreads + (threadIdx.x - kBulkWarps * 32), gridDim.x * hthreads);
       zero_fill_rows(c, a, blockIdx.x * hw + (warp - kBulkWarps), gridDim.x * hw, lane);
     } else {
       const int H = c.H, K = c.K, S = c.S;
@@ -502,6 +484,10 @@ extern "C" int moonep_dispatch_send(void* ctx, const void* hidden, const float* 
   a.chunk_bytes = (int)((cb + 15) / 16 * 16);
   const int grid = imax(1, imin(c.num_sms, h->sm_count));
   cudaStream_t st = (cudaStream_t)stream;
+  if (build_dedup) {
+    if (int rc = check_cuda(cudaMemsetAsync(dup_counts, 0, 2 * sizeof(int), st), "cudaMemsetAsync(dup_counts)"))
+      return rc;
+  }
   if (path == MOONEP_PATH_BULK && a.vec_ok) {
     const size_t smem = (size_t)kBulkWarps * kBulkStages * a.chunk_bytes;
     if ((int)smem + 4096 <= h->max_smem_optin) {
@@ -525,7 +511,7 @@ extern "C" int moonep_dispatch_expand(void* ctx, const int* dup_groups, const in
   (void)path;
   auto* h = (HostCtx*)ctx;
   const MoonepDevCtx& c = h->dev;
-  const int grid = imax(1, imin(c.num_sms, h->sm_count));
+  const int grid = imax(1, imin(c.local_sms, h->sm_count));
   dispatch_expand_kernel<<<grid, 512, 0, (cudaStream_t)stream>>>(c, dup_groups, dup_loffs, dup_counts, wait_epoch_sent,
                                                                 (c.H % 8 == 0) ? 1 : 0);
   return check_launch("dispatch_expand_kernel");

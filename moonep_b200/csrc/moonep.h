@@ -61,6 +61,10 @@
 #define MOONEP_K_WAIT 12
 #define MOONEP_NUM_KERNEL_IDS 16
 
+// link word of a landed row (pushed by the source rank during planning).
+#define MOONEP_LINK_PRIMARY (1 << 30)
+#define MOONEP_LINK_HAS_NEXT (1 << 29)
+
 // Routing entries per planner block (whole tokens, at most this many entries).
 #define MOONEP_PLAN_BLOCK 512
 
@@ -75,6 +79,8 @@ struct MoonepDevCtx {
   long long nvs_padded;   // rows per hidden chunk
   long long meta_stride;  // int32 words per meta chunk
   int weights_off, tpe_off, plan_off, src_info_off, sync_off, r32;
+  int link_off;   // [NvS] per landed row: LINK_PRIMARY | LINK_HAS_NEXT | next row of the same (source, token)
+  int local_sms;  // CTAs used by kernels that only touch local memory
   int debug;
   int pad0;
   unsigned long long timeout_ns;
@@ -88,6 +94,7 @@ struct MoonepDevCtx {
   int* expert_off;    // [R, E]   first row of expert e on destination d
   int* tpe_prev;      // [E]      tokens of expert e on source ranks < rank
   int* tables;        // planner work area, see planner.cu
+  int* block_hist;    // [planner blocks, E] per-block expert histograms of the local routing
   int* primary_packed;  // [R*S]
   int* kmask;           // [R*S]
   int* kidx_to_loff;    // [R*S*K]
@@ -120,7 +127,7 @@ int moonep_signal_wait(void* ctx, int signal_family, int signal_epoch, int wait_
                        void* stream);
 
 // Planner.  tpe is [E] (pushed to all peers) or [R, E] (tpe_is_2d, used as is).
-int moonep_plan_publish(void* ctx, const int* tpe, int tpe_is_2d, int epoch_tpe, void* stream);
+int moonep_plan_publish(void* ctx, const int* topk, const int* tpe, int tpe_is_2d, int epoch_tpe, void* stream);
 int moonep_plan_compute(void* ctx, const int* topk, const int* tpe2d, int* dst, int* cu_seqlens,
                         int* experts_to_copy, int* zero_fill, int* remote_stats, int wait_epoch_tpe,
                         int signal_epoch_plan, void* stream);

@@ -97,22 +97,40 @@ __device__ inline void warp_argmin_first(const int* v, int n, int lane, int& bes
   }
 }
 
-__global__ void __launch_bounds__(256) plan_publish_kernel(const MoonepDevCtx c, const int* __restrict__ tpe,
-                                                           int tpe_is_2d, int epoch_tpe) {
-  if (poisoned(c)) return;
-  const int tid = blockIdx.x * blockDim.x + threadIdx.x;
-  const int nth = gridDim.x * blockDim.x;
-  int* src_info = c.meta_peer[c.rank] + c.src_info_off;
-  for (int i = tid; i < c.NvS; i += nth) src_info[i] = -1;
-  if (!tpe_is_2d) {
-    const int total = c.R * c.E;
-    for (int i = tid; i < total; i += nth) {
-      const int d = i / c.E;
-      const int e = i - d * c.E;
-      c.meta_peer[d][c.tpe_off + c.rank * c.E + e] = tpe[e];
+// One CTA per planner block of whole tokens.  Besides the exchange, each CTA counts the experts
+// of its block (block_hist[block][e]); plan_tokens turns these into in-order indices.
+__global__ void __launch_bounds__(kTokensThreads)
+    plan_publish_kernel(const MoonepDevCtx c, const int* __restrict__ topk, const int* __restrict__ tpe, int tpe_is_2d,
+                        int tokens_per_block, int epoch_tpe) {
+  extern __shared__ int s_hist[];  // [E]
+  const bool live = !poisoned(c);
+  if (live) {
+    const int tid = blockIdx.x * blockDim.x + threadIdx.x;
+    const int nth = gridDim.x * blockDim.x;
+    int* src_info = c.meta_peer[c.rank] + c.src_info_off;
+    for (int i = tid; i < c.NvS; i += nth) src_info[i] = -1;
+    if (!tpe_is_2d) {
+      const int total = c.R * c.E;
+      for (int i = tid; i < total; i += nth) {
+        const int d = i / c.E;
+        const int e = i - d * c.E;
+        c.meta_peer[d][c.tpe_off + c.rank * c.E + e] = tpe[e];
+      }
     }
+    const int E = c.E;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) s_hist[e] = 0;
+    __syncthreads();
+    const int start = blockIdx.x * tokens_per_block * c.K;
+    const int end = min(c.N, start + tokens_per_block * c.K);
+    for (int i = start + threadIdx.x; i < end; i += blockDim.x) {
+      const int e = topk[i];
+      if (e >= 0 && e < E) atomicAdd(s_hist + e, 1);
+    }
+    __syncthreads();
+    int* out = c.block_hist + (long long)blockIdx.x * E;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) out[e] = s_hist[e];
   }
-  grid_tail_signal(c, MOONEP_K_PLAN_PUBLISH, MOONEP_FLAG_TPE, epoch_tpe);
+  grid_tail_signal(c, MOONEP_K_PLAN_PUBLISH, live ? MOONEP_FLAG_TPE : -1, epoch_tpe);
 }
 
 __global__ void __launch_bounds__(kTablesThreads)
@@ -297,38 +315,29 @@ __global__ void __launch_bounds__(kTokensThreads)
   const int nent = live ? (t1 - t0) * K : 0;
 
   if (live) {
+    // entries of earlier blocks: sum of their per-block histograms
     for (int e = tid; e < E; e += blockDim.x) s_hist[e] = 0;
     __syncthreads();
-    // entries of earlier blocks
-    for (int base = (tid & ~31); base < start; base += blockDim.x) {
-      const int i = base + lane;
-      int e = i < start ? topk[i] : -1;
-      if (e < 0 || e >= E) e = -1 - lane;
-      const unsigned m = __match_any_sync(0xffffffffu, e);
-      if (e >= 0 && lane == __ffs(m) - 1) atomicAdd(s_hist + e, __popc(m));
+    {
+      const long long total = (long long)blockIdx.x * E;  // rows of the blocks before this one
+      for (long long idx = tid; idx < total; idx += blockDim.x) {
+        const int v = c.block_hist[idx];
+        if (v) atomicAdd(s_hist + (int)(idx % E), v);
+      }
+    }
+    for (int i = tid; i < nent; i += blockDim.x) {
+      const int e = topk[start + i];
+      const bool valid = e >= 0 && e < E;
+      if (!valid) record_status(c, MOONEP_STATUS_BAD_INDEX, MOONEP_K_PLAN_TOKENS, 2, e, E, start + i);
+      s_e[i] = valid ? e : -1;
     }
     __syncthreads();
-    // in-order index inside this block
-    if (tid < 32) {
-      for (int base = 0; base < nent; base += 32) {
-        const int i = base + lane;
-        int e = i < nent ? topk[start + i] : -1;
-        const bool valid = e >= 0 && e < E;
-        if (i < nent && !valid) record_status(c, MOONEP_STATUS_BAD_INDEX, MOONEP_K_PLAN_TOKENS, 2, e, E, start + i);
-        if (!valid) e = -1 - lane;
-        const unsigned m = __match_any_sync(0xffffffffu, e);
-        const int leader = __ffs(m) - 1;
-        int old = 0;
-        if (valid && lane == leader) {
-          old = s_hist[e];
-          s_hist[e] = old + __popc(m);
-        }
-        old = __shfl_sync(0xffffffffu, old, leader);
-        if (i < nent) {
-          s_e[i] = valid ? e : -1;
-          s_lc[i] = old + __popc(m & ((1u << lane) - 1u));
-        }
-      }
+    // in-order index inside this block: entries before i with the same expert
+    for (int i = tid; i < nent; i += blockDim.x) {
+      const int e = s_e[i];
+      int cnt = 0;
+      for (int j = 0; j < i; ++j) cnt += (s_e[j] == e) ? 1 : 0;
+      s_lc[i] = (e >= 0 ? s_hist[e] : 0) + cnt;
     }
     __syncthreads();
     for (int i = tid; i < nent; i += blockDim.x) {
@@ -372,8 +381,14 @@ __global__ void __launch_bounds__(kTokensThreads)
       const int k = i % K;
       bool dup = false;
       for (int kk = 0; kk < k; ++kk) dup |= (s_dest[i - k + kk] == dest);
+      int next = -1;
+      for (int kk = K - 1; kk > k; --kk)
+        if (s_dest[i - k + kk] == dest) next = s_dst[i - k + kk] - dest * NvS;
       dst_out[start + i] = dup ? -dstv - 1 : dstv;
-      c.meta_peer[dest][c.src_info_off + (dstv - dest * NvS)] = c.rank * NvS + start + i;
+      const int loff = dstv - dest * NvS;
+      int* meta = c.meta_peer[dest];
+      meta[c.src_info_off + loff] = c.rank * NvS + start + i;
+      meta[c.link_off + loff] = (dup ? 0 : MOONEP_LINK_PRIMARY) | (next >= 0 ? (MOONEP_LINK_HAS_NEXT | next) : 0);
     }
   }
   grid_tail_signal(c, MOONEP_K_PLAN_TOKENS, live ? MOONEP_FLAG_PLAN : -1, epoch_plan);
@@ -390,13 +405,24 @@ extern "C" long long moonep_planner_table_words(int R, int E, int B) {
   return table_words(R, E);
 }
 
-extern "C" int moonep_plan_publish(void* ctx, const int* tpe, int tpe_is_2d, int epoch_tpe, void* stream) {
+static int hist_smem_ok(HostCtx* h, const void* kernel, size_t smem, const char* what) {
+  if (smem <= 48 * 1024) return 0;
+  if ((int)smem + 8192 > h->max_smem_optin) {
+    set_error(std::string(what) + ": E too large for the shared-memory histogram");
+    return 1;
+  }
+  return check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), what);
+}
+
+extern "C" int moonep_plan_publish(void* ctx, const int* topk, const int* tpe, int tpe_is_2d, int epoch_tpe,
+                                   void* stream) {
   auto* h = (HostCtx*)ctx;
   const MoonepDevCtx& c = h->dev;
-  const long long work = (long long)c.NvS + (tpe_is_2d ? 0 : (long long)c.R * c.E);
-  int grid = (int)((work + 256 * 8 - 1) / (256 * 8));
-  grid = imax(1, imin(grid, imin(c.num_sms, h->sm_count)));
-  plan_publish_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(c, tpe, tpe_is_2d, epoch_tpe);
+  const int tpb = imax(1, MOONEP_PLAN_BLOCK / c.K);
+  const int grid = (c.S + tpb - 1) / tpb;
+  const size_t smem = (size_t)c.E * sizeof(int);
+  if (int rc = hist_smem_ok(h, (const void*)plan_publish_kernel, smem, "plan_publish_kernel")) return rc;
+  plan_publish_kernel<<<grid, kTokensThreads, smem, (cudaStream_t)stream>>>(c, topk, tpe, tpe_is_2d, tpb, epoch_tpe);
   return check_launch("plan_publish_kernel");
 }
 
@@ -412,16 +438,7 @@ extern "C" int moonep_plan_compute(void* ctx, const int* topk, const int* tpe2d,
   const int tpb = imax(1, MOONEP_PLAN_BLOCK / c.K);
   const int grid = (c.S + tpb - 1) / tpb;
   const size_t smem = (size_t)c.E * sizeof(int);
-  if (smem > 48 * 1024) {
-    if ((int)smem + 8192 > h->max_smem_optin) {
-      set_error("plan_tokens_kernel: E too large for the shared-memory histogram");
-      return 1;
-    }
-    if (int rc = check_cuda(cudaFuncSetAttribute(plan_tokens_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 (int)smem),
-                            "cudaFuncSetAttribute(plan_tokens_kernel)"))
-      return rc;
-  }
+  if (int rc = hist_smem_ok(h, (const void*)plan_tokens_kernel, smem, "plan_tokens_kernel")) return rc;
   plan_tokens_kernel<<<grid, kTokensThreads, smem, st>>>(c, topk, dst, tpb, signal_epoch_plan);
   return check_launch("plan_tokens_kernel");
 }

@@ -49,9 +49,10 @@ extern "C" long long moonep_launch_count(void) { return g_launch_count; }
 
 enum ParamIndex {
   P_RANK = 0, P_R, P_E, P_S, P_K, P_H, P_B, P_N, P_NVS, P_EPN, P_TOKEN_PADDING, P_NUM_SMS, P_NVS_PADDED,
-  P_META_STRIDE, P_WEIGHTS_OFF, P_TPE_OFF, P_PLAN_OFF, P_SRC_INFO_OFF, P_SYNC_OFF, P_R32, P_DEBUG, P_TIMEOUT_MS,
+  P_META_STRIDE, P_WEIGHTS_OFF, P_TPE_OFF, P_PLAN_OFF, P_SRC_INFO_OFF, P_SYNC_OFF, P_R32, P_LINK_OFF, P_LOCAL_SMS,
+  P_DEBUG, P_TIMEOUT_MS,
   P_PTR_STATUS, P_PTR_COUNTERS, P_PTR_ALLOC_CUM, P_PTR_EXPERT_OFF, P_PTR_TPE_PREV, P_PTR_TABLES,
-  P_PTR_PRIMARY_PACKED, P_PTR_KMASK, P_PTR_KIDX_TO_LOFF, P_PTR_STATS, P_COUNT
+  P_PTR_PRIMARY_PACKED, P_PTR_KMASK, P_PTR_KIDX_TO_LOFF, P_PTR_STATS, P_PTR_BLOCK_HIST, P_COUNT
 };
 
 extern "C" void* moonep_ctx_create(const long long* p, int nparams, const unsigned long long* hidden_peers,
@@ -69,6 +70,7 @@ extern "C" void* moonep_ctx_create(const long long* p, int nparams, const unsign
   d.nvs_padded = p[P_NVS_PADDED]; d.meta_stride = p[P_META_STRIDE];
   d.weights_off = (int)p[P_WEIGHTS_OFF]; d.tpe_off = (int)p[P_TPE_OFF]; d.plan_off = (int)p[P_PLAN_OFF];
   d.src_info_off = (int)p[P_SRC_INFO_OFF]; d.sync_off = (int)p[P_SYNC_OFF]; d.r32 = (int)p[P_R32];
+  d.link_off = (int)p[P_LINK_OFF]; d.local_sms = (int)p[P_LOCAL_SMS];
   d.debug = (int)p[P_DEBUG];
   d.timeout_ns = (unsigned long long)p[P_TIMEOUT_MS] * 1000000ull;
   d.status = (int*)p[P_PTR_STATUS]; d.counters = (int*)p[P_PTR_COUNTERS];
@@ -76,6 +78,7 @@ extern "C" void* moonep_ctx_create(const long long* p, int nparams, const unsign
   d.tpe_prev = (int*)p[P_PTR_TPE_PREV]; d.tables = (int*)p[P_PTR_TABLES];
   d.primary_packed = (int*)p[P_PTR_PRIMARY_PACKED]; d.kmask = (int*)p[P_PTR_KMASK];
   d.kidx_to_loff = (int*)p[P_PTR_KIDX_TO_LOFF]; d.stats = (long long*)p[P_PTR_STATS];
+  d.block_hist = (int*)p[P_PTR_BLOCK_HIST];
   if (d.R < 1 || d.R > MOONEP_MAX_RANKS || d.K < 1 || d.K > MOONEP_MAX_TOPK) {
     set_error("moonep_ctx_create: R or K out of range");
     delete h;

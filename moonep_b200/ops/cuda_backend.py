@@ -22,6 +22,7 @@ import torch
 
 from .. import config
 from ..constants import (
+    PLAN_BLOCK,
     FLAG_COMB,
     FLAG_GRAD_DONE,
     FLAG_GRAD_READY,
@@ -75,6 +76,9 @@ class CudaBackend:
         self.tpe_prev = i32(E)
         self.tables = i32(self.lib.moonep_planner_table_words(R, E, B))
         self.stats_buf = torch.zeros(16, dtype=torch.int64, device=dev)
+        tokens_per_block = max(1, PLAN_BLOCK // K)
+        self.block_hist = i32(-(-S // tokens_per_block) * E)
+        sm_count = torch.cuda.get_device_properties(dev).multi_processor_count
         c["alloc"] = self.tables[2 * E : 2 * E + R * E]  # planner's alloc[d*E+e]
 
         hid_base = c["hidden_buf"].data_ptr()
@@ -84,10 +88,10 @@ class CudaBackend:
         params = [
             c["rank"], R, E, S, K, c["H"], B, c["N"], c["NvS"], c["epn"], c["token_padding"], c["num_sms"],
             c["NvS_padded"], c["meta_chunk_padded"], c["WEIGHTS_OFF"], c["TPE_OFF"], c["PLAN_OFF"], c["SRC_INFO_OFF"],
-            c["SYNC_OFF"], c["R32"], int(config.debug()), config.timeout_ms(),
+            c["SYNC_OFF"], c["R32"], c["LINK_OFF"], config.local_sms(sm_count), int(config.debug()), config.timeout_ms(),
             self.status.data_ptr(), self.counters.data_ptr(), self.alloc_cum.data_ptr(), self.expert_off.data_ptr(),
             self.tpe_prev.data_ptr(), self.tables.data_ptr(), c["primary_packed"].data_ptr(), c["kmask"].data_ptr(),
-            c["kidx_to_loff"].data_ptr(), self.stats_buf.data_ptr(),
+            c["kidx_to_loff"].data_ptr(), self.stats_buf.data_ptr(), self.block_hist.data_ptr(),
         ]  # fmt: skip
         arr = (ctypes.c_longlong * len(params))(*params)
         with torch.cuda.device(dev):
@@ -147,9 +151,10 @@ class CudaBackend:
         self.wait(FLAG_READY)
 
     # -- planning ------------------------------------------------------------------------
-    def plan_publish(self, tpe: torch.Tensor):
+    def plan_publish(self, tpe: torch.Tensor, topk_flat: torch.Tensor):
+        self._topk = topk_flat
         is2d = int(tpe.dim() == 2)
-        self._call("moonep_plan_publish", _ptr(tpe), is2d, self._next(FLAG_TPE), _stream())
+        self._call("moonep_plan_publish", _ptr(self._topk), _ptr(tpe), is2d, self._next(FLAG_TPE), _stream())
         self.world.step()
 
     def plan_compute(self, topk_flat, tpe, cu_seqlens, plan):
@@ -192,6 +197,8 @@ class CudaBackend:
         loff = dst_pos - dest * NvS
         idx = torch.from_numpy(dest * ms + c["SRC_INFO_OFF"] + loff).to(dev)
         meta[idx] = torch.from_numpy(rank * NvS + np.arange(S * K)).to(torch.int32).to(dev)
+        idx = torch.from_numpy(dest * ms + c["LINK_OFF"] + loff).to(dev)
+        meta[idx] = torch.from_numpy(P.link_words(dst_pos, S, K, NvS)).to(torch.int32).to(dev)
         self._call("moonep_signal_wait", FLAG_PLAN, self._next(FLAG_PLAN), -1, 0, _stream())
         self.world.step()
 

@@ -1,68 +1,81 @@
-"""Sample SM clocks and throttle reasons with nvidia-smi while a benchmark runs (read-only)."""
+"""Sample SM clocks and throttle reasons while a benchmark runs (read-only NVML queries)."""
 
 from __future__ import annotations
 
 import statistics
-import subprocess
 import threading
+import time
 
-_QUERY = (
-    "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-    "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-    "clocks_event_reasons.sw_power_cap"
-)
-_REASONS = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+_REASON_BITS = {
+    "hw_slowdown": 0x8,
+    "sw_power_cap": 0x4,
+    "sw_thermal_slowdown": 0x20,
+    "hw_thermal_slowdown": 0x40,
+}
+
+
+def _physical_index(index: int) -> int:
+    import os
+
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        ids = [v.strip() for v in vis.split(",") if v.strip()]
+        if index < len(ids) and ids[index].isdigit():
+            return int(ids[index])
+    return index
 
 
 class ClockSampler:
-    """``with ClockSampler(gpu_index) as cs: ...; cs.summary()``."""
+    """``with ClockSampler(gpu_index) as cs: ...; cs.summary()`` — samples every ``period_ms``."""
 
-    def __init__(self, index: int = 0, period_ms: int = 100):
-        self.index, self.period_ms = index, period_ms
-        self.samples: list[tuple[float, float, float, tuple[bool, ...]]] = []
-        self._proc = None
+    def __init__(self, index: int = 0, period_ms: int = 10):
+        self.index, self.period = _physical_index(index), period_ms / 1e3
+        self.samples: list[tuple[int, int, float, int]] = []
+        self._stop = threading.Event()
         self._thread = None
+        self._nvml = None
+        self._handle = None
 
     def __enter__(self):
         try:
-            self._proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={_QUERY}", "--format=csv,noheader,nounits", "-i", str(self.index),
-                 "-lms", str(self.period_ms)],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
-            )  # fmt: skip
-        except OSError:
-            self._proc = None
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+        except Exception:  # noqa: BLE001 - sampling is best effort
+            self._nvml = None
             return self
-        self._thread = threading.Thread(target=self._read, daemon=True)
+        self._thread = threading.Thread(target=self._run, daemon=True)
         self._thread.start()
         return self
 
-    def _read(self):
-        for line in self._proc.stdout:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 7:
-                continue
+    def _run(self):
+        nv, h = self._nvml, self._handle
+        while not self._stop.is_set():
             try:
-                sm, mx, pw = float(parts[0]), float(parts[1]), float(parts[2])
-            except ValueError:
-                continue
-            self.samples.append((sm, mx, pw, tuple(p.lower() == "active" for p in parts[3:7])))
+                sm = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+                mx = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+                pw = nv.nvmlDeviceGetPowerUsage(h) / 1e3
+                try:
+                    rs = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+                except AttributeError:
+                    rs = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                self.samples.append((sm, mx, pw, int(rs)))
+            except Exception:  # noqa: BLE001
+                pass
+            time.sleep(self.period)
 
     def __exit__(self, *exc):
-        if self._proc is not None:
-            self._proc.terminate()
-            try:
-                self._proc.wait(timeout=5)
-            except subprocess.TimeoutExpired:
-                self._proc.kill()
+        self._stop.set()
         if self._thread is not None:
-            self._thread.join(timeout=5)
+            self._thread.join(timeout=2)
         return False
 
     def summary(self) -> dict:
         if not self.samples:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        reasons = [name for i, name in enumerate(_REASONS) if any(s[3][i] for s in self.samples)]
+        reasons = [name for name, bit in _REASON_BITS.items() if any(s[3] & bit for s in self.samples)]
         return {
             "sm_mhz": statistics.median(s[0] for s in self.samples),
             "sm_max_mhz": max(s[1] for s in self.samples),

@@ -175,6 +175,7 @@ def round_trip_rank(buf, case: Case, R: int, r: int, step, *, zero_copy=False, e
         "zero_fill": plan.zero_fill_ranges.cpu(), "remote_stats": plan.remote_stats.cpu(),
         "dup_groups": plan.dup_groups.cpu(), "dup_loffs": plan.dup_loffs.cpu(), "dup_counts": plan.dup_counts.cpu(),
         "src_info": ctx["meta_buf"][r * ctx["meta_chunk_padded"] + ctx["SRC_INFO_OFF"]:][: ctx["NvS"]].cpu().clone(),
+        "link": ctx["meta_buf"][r * ctx["meta_chunk_padded"] + ctx["LINK_OFF"]:][: ctx["NvS"]].cpu().clone(),
         "layout": {k: v for k, v in ctx.items() if isinstance(v, int)},
     }  # fmt: skip
     # expert stage: y = scale(row) * x, applied row-wise on the received rows
@@ -213,7 +214,12 @@ def check_dispatch_records(case: Case, R: int, recs):
     NvS, S, K, H = lay["NvS"], case.S, case.K, case.H
     tabs, dst_pos, dst = host_plan_all(case, R, [r["topk"] for r in recs], [r["tpe"] for r in recs], lay)
     src_info = expected_src_info(R, NvS, dst_pos)
+    link = np.zeros((R, NvS), dtype=np.int64)
+    for r in range(R):
+        link[dst_pos[r] // NvS, dst_pos[r] % NvS] = P.link_words(dst_pos[r], S, K, NvS)
     for r, rec in enumerate(recs):
+        occ = src_info[r] >= 0
+        assert np.array_equal(rec["link"].numpy()[occ], link[r][occ]), f"rank {r}: link words differ"
         assert np.array_equal(rec["dst"].numpy(), dst[r]), f"rank {r}: dst differs from the host planner"
         assert np.array_equal(rec["cu_seqlens"].numpy(), tabs["cu_seqlens"][r]), f"rank {r}: cu_seqlens"
         assert np.array_equal(rec["experts_to_copy"].numpy(), tabs["experts_to_copy"]), f"rank {r}: experts_to_copy"
