@@ -44,6 +44,7 @@ def parse_args():
     p.add_argument("--token-padding", type=int, default=128)
     p.add_argument("--routing", default="softmax")
     p.add_argument("--staged", action="store_true", help="use the copying (non zero-copy) API paths")
+    p.add_argument("--profile-phases", action="store_true", help="add per-kernel device times (phases_us)")
     return p.parse_args()
 
 
@@ -163,6 +164,16 @@ def run_steps(args, BufferCls, rank, n, reference=False):
     t_step = sum(e[0].elapsed_time(e[2]) for e in ev) / args.steps
     t_disp, t_comb, t_step = (max_over_ranks(t, n) for t in (t_disp, t_comb, t_step))
 
+    phases = None
+    if args.profile_phases and not reference:
+        be = buf._require_ctx()["_backend"]
+        be.profile(True)
+        for _ in range(10):
+            flush.zero_()
+            step(x, gates, topk, tpe)
+        phases = {k: round(max_over_ranks(v, n), 1) for k, v in sorted(be.phase_times().items())}
+        be.profile(False)
+
     # end to end: inputs come from pinned host memory every step, a checksum goes back
     cs_h = torch.empty(1, dtype=torch.float32).pin_memory()
     dev_in = [torch.empty_like(t, device=dev) for t in pinned]
@@ -229,6 +240,8 @@ def run_steps(args, BufferCls, rank, n, reference=False):
         },
         "gpu_launches": int(launches),
     }  # fmt: skip
+    if phases is not None:
+        res["phases_us"] = phases
     return res
 
 

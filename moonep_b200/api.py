@@ -290,7 +290,9 @@ class Buffer:
                      *, inter_rank_sync, zero_copy):  # fmt: skip
         be = ctx["_backend"]
         wait = None
-        if inter_rank_sync:
+        # The barrier protects the shard from being rewritten while a peer still pulls from it.  A
+        # dispatch that waited for all peers since the last pull already gives that guarantee.
+        if inter_rank_sync and not be.shard_quiesced():
             be.signal(FLAG_READY)
             wait = FLAG_READY
         be.combine_prologue(plan, hidden_nvsh, route_weights_nvs, zero_copy, wait=wait)

@@ -71,6 +71,9 @@ class CpuBackend:
     def check_status(self):
         pass
 
+    def shard_quiesced(self) -> bool:
+        return False
+
     def stats(self) -> dict:
         return {}
 

@@ -234,6 +234,193 @@ __global__ void __launch_bounds__(512)
   }
 }
 
+// ---- pull kernel, bulk-copy path ---------------------------------------------------------------------
+//
+// Warp 0 is the producer: per (token, row piece) it takes a free slot of a shared-memory ring and
+// lets one lane issue one cp.async.bulk per primary row (peer global -> shared, completion counted
+// in bytes on the slot's "full" mbarrier).  Warps 1..8 are consumers, warp w taking every 8th item:
+// it waits for the slot, adds the rows in fp32 in ascending k, stores the bf16 result with 16-byte
+// stores and releases the slot through its "empty" mbarrier.  Remote reads are therefore issued back to back without waiting for data,
+// which keeps the NVLink request queue full with few SMs.
+
+constexpr int kPullConsumerWarps = 8;
+constexpr int kPullBulkThreads = 32 * (1 + kPullConsumerWarps);
+constexpr int kPullMaxSlots = 8;
+
+struct PullBulkArgs {
+  const int* dst;
+  uint16_t* out;
+  float* out_w;
+  int wait_epoch;
+  int chunk_bytes;  // bytes of one row piece (multiple of 16)
+  int nsplit;       // pieces per row
+  int kp;           // rows a slot can hold: min(K, R)
+  int nslots;
+};
+
+__device__ __forceinline__ int4 lds16(const void* p) {
+  int4 v;
+  asm volatile("ld.shared.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(smem_u32(p)));
+  return v;
+}
+
+__global__ void __launch_bounds__(kPullBulkThreads) combine_pull_bulk_kernel(const MoonepDevCtx c, const PullBulkArgs a) {
+  extern __shared__ __align__(128) unsigned char s_slots[];  // [nslots][kp][chunk_bytes]
+  __shared__ __align__(8) unsigned long long s_full[kPullMaxSlots];
+  __shared__ __align__(8) unsigned long long s_empty[kPullMaxSlots];
+  __shared__ int s_tok[kPullMaxSlots], s_split[kPullMaxSlots], s_np[kPullMaxSlots];
+  __shared__ int s_fail;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x < a.nslots) {
+    mbar_init(s_full + threadIdx.x, 1);
+    mbar_init(s_empty + threadIdx.x, 1);
+  }
+  if (threadIdx.x == 0) s_fail = 0;
+  fence_barrier_init();
+  const bool ok = block_wait_flags(c, MOONEP_FLAG_COMB, a.wait_epoch, MOONEP_K_COMBINE_PULL);
+  int* work = c.counters + MOONEP_NUM_KERNEL_IDS + 1;
+  const long long row_bytes = (long long)c.H * 2;
+  const size_t slot_bytes = (size_t)a.kp * a.chunk_bytes;
+  if (ok) {
+    if (warp == 0) {
+      // ---------------- producer ----------------
+      const int K = c.K, S = c.S, NvS = c.NvS;
+      int item = 0;
+      bool failed = false;
+      auto acquire_slot = [&](int slot, int use) -> bool {
+        int got = 1;
+        if (use > 0 && lane == 0) got = mbar_wait(s_empty + slot, (unsigned)((use - 1) & 1), c.timeout_ns) ? 1 : 0;
+        got = __shfl_sync(0xffffffffu, got, 0);
+        if (!got && lane == 0) {
+          record_status(c, MOONEP_STATUS_TIMEOUT, MOONEP_K_COMBINE_PULL, 101, slot, use, 0);
+          s_fail = 1;
+        }
+        return got != 0;
+      };
+      for (;;) {
+        int b0 = 0;
+        if (lane == 0) b0 = atomicAdd(work, kTokenBatch);
+        b0 = __shfl_sync(0xffffffffu, b0, 0);
+        if (b0 >= S || failed) break;
+        const int b1 = min(S, b0 + kTokenBatch);
+        for (int token = b0; token < b1 && !failed; ++token) {
+          int d = 0, dest = 0, loff = 0;
+          bool valid = false;
+          if (lane < K) {
+            d = a.dst[token * K + lane];
+            const int raw = d < 0 ? -d - 1 : d;
+            dest = raw / NvS;
+            loff = raw - dest * NvS;
+            valid = dest >= 0 && dest < c.R && loff >= 0 && loff < NvS;
+            if (!valid) record_status(c, MOONEP_STATUS_BAD_INDEX, MOONEP_K_COMBINE_PULL, 6, d, token, lane);
+            if (a.out_w != nullptr) {
+              const float* w = reinterpret_cast<const float*>(c.meta_peer[valid ? dest : c.rank] + c.weights_off);
+              a.out_w[token * K + lane] = valid ? w[loff] : 0.f;
+            }
+          }
+          const unsigned prim = __ballot_sync(0xffffffffu, valid && d >= 0);
+          int nprim = __popc(prim);
+          if (nprim > a.kp) nprim = a.kp;
+          const unsigned char* my_row =
+              (valid && d >= 0) ? reinterpret_cast<const unsigned char*>(c.hidden_peer[dest]) + (long long)loff * row_bytes
+                                : nullptr;
+          unsigned long long rows_compact = 0;
+          {
+            unsigned m = prim;
+            int p = 0;
+            while (m) {
+              const int kk = __ffs(m) - 1;
+              m &= m - 1;
+              const unsigned long long ptr = __shfl_sync(0xffffffffu, (unsigned long long)my_row, kk);
+              if (lane == p) rows_compact = ptr;
+              ++p;
+            }
+          }
+          for (int split = 0; split < a.nsplit; ++split) {
+            const int slot = item % a.nslots, use = item / a.nslots;
+            if (!acquire_slot(slot, use)) {
+              failed = true;
+              break;
+            }
+            const long long off = (long long)split * a.chunk_bytes;
+            const unsigned len = (unsigned)((row_bytes - off) < a.chunk_bytes ? (row_bytes - off) : a.chunk_bytes);
+            if (lane == 0) {
+              s_tok[slot] = token;
+              s_split[slot] = split;
+              s_np[slot] = nprim;
+              if (nprim > 0)
+                mbar_expect_tx(s_full + slot, (unsigned)nprim * len);
+              else
+                mbar_arrive(s_full + slot);
+            }
+            for (int p = 0; p < nprim; ++p) {
+              const unsigned long long ptr = __shfl_sync(0xffffffffu, rows_compact, p);
+              if (lane == 0)
+                bulk_g2s(s_slots + slot * slot_bytes + (size_t)p * a.chunk_bytes,
+                         reinterpret_cast<const unsigned char*>(ptr) + off, len, s_full + slot);
+            }
+            ++item;
+          }
+        }
+      }
+      // end markers: one for each consumer warp (warp w takes the items congruent to w)
+      for (int q = 0; q < kPullConsumerWarps && !failed; ++q, ++item) {
+        const int slot = item % a.nslots, use = item / a.nslots;
+        if (!acquire_slot(slot, use)) break;
+        if (lane == 0) {
+          s_tok[slot] = -1;
+          mbar_arrive(s_full + slot);
+        }
+      }
+    } else {
+      // ---------------- consumers ----------------
+      // each consumer warp owns every kPullConsumerWarps-th item, so several slots are reduced at once
+      for (int item = warp - 1;; item += kPullConsumerWarps) {
+        const int slot = item % a.nslots, use = item / a.nslots;
+        bool got = mbar_try_wait(s_full + slot, (unsigned)(use & 1));
+        if (!got) {
+          const unsigned long long t0 = globaltimer_ns();
+          unsigned spins = 0;
+          while (!(got = mbar_try_wait(s_full + slot, (unsigned)(use & 1)))) {
+            if ((++spins & 255u) == 0 && (*(volatile int*)&s_fail || globaltimer_ns() - t0 > c.timeout_ns)) break;
+          }
+        }
+        if (!got) {
+          if (!*(volatile int*)&s_fail) record_status(c, MOONEP_STATUS_TIMEOUT, MOONEP_K_COMBINE_PULL, 102, slot, use, 0);
+          break;
+        }
+        const int token = s_tok[slot];
+        if (token < 0) break;
+        const int split = s_split[slot], np = s_np[slot];
+        const long long off = (long long)split * a.chunk_bytes;
+        const int len = (int)((row_bytes - off) < a.chunk_bytes ? (row_bytes - off) : a.chunk_bytes);
+        const unsigned char* base = s_slots + slot * slot_bytes;
+        unsigned char* orow = reinterpret_cast<unsigned char*>(a.out) + (long long)token * row_bytes + off;
+        for (int v = lane; v < len / 16; v += 32) {
+          float acc[8];
+#pragma unroll
+          for (int q = 0; q < 8; ++q) acc[q] = 0.f;
+          for (int p = 0; p < np; ++p) acc_add(acc, lds16(base + (size_t)p * a.chunk_bytes + (size_t)v * 16));
+          st16(orow + (size_t)v * 16, acc_pack(acc));
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(s_empty + slot);
+      }
+    }
+  }
+  __shared__ int s_last;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int arrived = atomicAdd(c.counters + MOONEP_K_COMBINE_PULL, 1);
+    s_last = arrived == (int)gridDim.x - 1;
+    if (s_last) {
+      c.counters[MOONEP_K_COMBINE_PULL] = 0;
+      *work = 0;
+      __threadfence();
+    }
+  }
+}
+
 }  // namespace
 
 }  // namespace moonep
@@ -255,11 +442,40 @@ extern "C" int moonep_combine_prologue(void* ctx, const int* dup_groups, const i
 
 extern "C" int moonep_combine_pull(void* ctx, const int* dst, void* out_hidden, float* out_weights, int wait_epoch_comb,
                                    int path, void* stream) {
-  (void)path;
   auto* h = (HostCtx*)ctx;
   const MoonepDevCtx& c = h->dev;
   const int grid = imax(1, imin(c.num_sms, h->sm_count));
   const int vec_ok = (c.H % 8 == 0) && ((reinterpret_cast<uintptr_t>(out_hidden) & 15u) == 0);
+  if (path == MOONEP_PATH_BULK && vec_ok) {
+    PullBulkArgs a;
+    a.dst = dst;
+    a.out = (uint16_t*)out_hidden;
+    a.out_w = out_weights;
+    a.wait_epoch = wait_epoch_comb;
+    a.kp = imin(c.K, c.R);
+    const long long row_bytes = (long long)c.H * 2;
+    const long long slot_budget = 28 * 1024;
+    a.nsplit = 1;
+    for (;;) {
+      long long cb = (row_bytes + a.nsplit - 1) / a.nsplit;
+      cb = (cb + 15) / 16 * 16;
+      a.chunk_bytes = (int)cb;
+      if (cb * a.kp <= slot_budget || cb <= 512) break;
+      ++a.nsplit;
+    }
+    const long long slot_bytes = (long long)a.kp * a.chunk_bytes;
+    a.nslots = (int)((h->max_smem_optin - 8192) / slot_bytes);
+    if (a.nslots > kPullMaxSlots) a.nslots = kPullMaxSlots;
+    if (a.nslots >= 2) {
+      const size_t smem = (size_t)a.nslots * slot_bytes;
+      if (int rc = check_cuda(cudaFuncSetAttribute(combine_pull_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   (int)smem),
+                              "cudaFuncSetAttribute(combine_pull_bulk_kernel)"))
+        return rc;
+      combine_pull_bulk_kernel<<<grid, kPullBulkThreads, smem, (cudaStream_t)stream>>>(c, a);
+      return check_launch("combine_pull_bulk_kernel");
+    }
+  }
   combine_pull_kernel<<<grid, 512, 0, (cudaStream_t)stream>>>(c, dst, (uint16_t*)out_hidden, out_weights,
                                                              wait_epoch_comb, vec_ok);
   return check_launch("combine_pull_kernel");

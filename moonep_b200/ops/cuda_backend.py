@@ -65,6 +65,8 @@ class CudaBackend:
         R, E, S, K, B = c["R"], c["E"], c["S"], c["K"], c["B"]
         self.epoch = [0] * NUM_FLAG_FAMILIES
         self.path = _PATHS[config.copy_path()]
+        self._profile = None
+        self._quiesced = False  # every peer is known to be past its last pull from this rank's shard
 
         def i32(n):
             return torch.zeros(max(int(n), 1), dtype=torch.int32, device=dev)
@@ -134,9 +136,31 @@ class CudaBackend:
         self.epoch[family] += 1
         return self.epoch[family]
 
-    def _call(self, name, *args):
+    def _call(self, name, *args, tag=None):
         with torch.cuda.device(self.ctx["device"]):
+            if self._profile is None:
+                _lib.check(getattr(self.lib, name)(self.handle, *args), name)
+                return
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
             _lib.check(getattr(self.lib, name)(self.handle, *args), name)
+            e1.record()
+            self._profile.append((tag or name.replace("moonep_", ""), e0, e1))
+
+    def profile(self, on: bool = True):
+        """Start (or stop) timing every native call with CUDA events; read with ``phase_times()``."""
+        self._profile = [] if on else None
+
+    def phase_times(self) -> dict:
+        """Mean device time in microseconds per kind of native call since ``profile(True)``; synchronises."""
+        if not self._profile:
+            return {}
+        torch.cuda.synchronize(self.ctx["device"])
+        acc: dict[str, list[float]] = {}
+        for name, e0, e1 in self._profile:
+            acc.setdefault(name, []).append(e0.elapsed_time(e1) * 1e3)
+        self._profile = []
+        return {k: sum(v) / len(v) for k, v in acc.items()}
 
     # -- flags ---------------------------------------------------------------------------
     def signal(self, family: int):
@@ -211,6 +235,8 @@ class CudaBackend:
             _ptr(plan.zero_fill_ranges), _ptr(plan.dup_groups), _ptr(plan.dup_loffs), _ptr(plan.dup_counts),
             int(bool(build_dedup_map)), wf, we, self._next(FLAG_SENT), self.path, _stream(),
         )  # fmt: skip
+        if wait is not None:
+            self._quiesced = True
         self.world.step()
 
     def dispatch_expand(self, plan, out_hidden, out_weights, zero_copy):
@@ -240,7 +266,11 @@ class CudaBackend:
         )  # fmt: skip
         self.world.step()
 
+    def shard_quiesced(self) -> bool:
+        return self._quiesced
+
     def combine_pull(self, plan_dst, out_hidden, out_weights_sk):
+        self._quiesced = False
         self._call(
             "moonep_combine_pull", _ptr(plan_dst), _ptr(out_hidden), _ptr(out_weights_sk), self.epoch[FLAG_COMB],
             self.path, _stream(),
