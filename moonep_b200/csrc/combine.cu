@@ -297,33 +297,42 @@ __global__ void __launch_bounds__(kPullBulkThreads) combine_pull_bulk_kernel(con
         }
         return got != 0;
       };
+      // A batch is as many tokens as fit their K routing entries into the 32 lanes: one coalesced
+      // load of dst and one round of weight gathers serve the whole batch.
+      const int TB = K <= 32 ? 32 / K : 1;
+      const int tl = lane / K, kl = lane - tl * K;
       for (;;) {
         int b0 = 0;
-        if (lane == 0) b0 = atomicAdd(work, kTokenBatch);
+        if (lane == 0) b0 = atomicAdd(work, TB);
         b0 = __shfl_sync(0xffffffffu, b0, 0);
         if (b0 >= S || failed) break;
-        const int b1 = min(S, b0 + kTokenBatch);
-        for (int token = b0; token < b1 && !failed; ++token) {
-          int d = 0, dest = 0, loff = 0;
-          bool valid = false;
-          if (lane < K) {
-            d = a.dst[token * K + lane];
-            const int raw = d < 0 ? -d - 1 : d;
-            dest = raw / NvS;
-            loff = raw - dest * NvS;
-            valid = dest >= 0 && dest < c.R && loff >= 0 && loff < NvS;
-            if (!valid) record_status(c, MOONEP_STATUS_BAD_INDEX, MOONEP_K_COMBINE_PULL, 6, d, token, lane);
-            if (a.out_w != nullptr) {
-              const float* w = reinterpret_cast<const float*>(c.meta_peer[valid ? dest : c.rank] + c.weights_off);
-              a.out_w[token * K + lane] = valid ? w[loff] : 0.f;
-            }
+        const int my_token = b0 + tl;
+        const bool have = tl < TB && my_token < S;
+        int d = 0, dest = 0, loff = 0;
+        bool valid = false;
+        if (have) {
+          d = a.dst[my_token * K + kl];
+          const int raw = d < 0 ? -d - 1 : d;
+          dest = raw / NvS;
+          loff = raw - dest * NvS;
+          valid = dest >= 0 && dest < c.R && loff >= 0 && loff < NvS;
+          if (!valid) record_status(c, MOONEP_STATUS_BAD_INDEX, MOONEP_K_COMBINE_PULL, 6, d, my_token, kl);
+          if (a.out_w != nullptr) {
+            const float* w = reinterpret_cast<const float*>(c.meta_peer[valid ? dest : c.rank] + c.weights_off);
+            a.out_w[my_token * K + kl] = valid ? w[loff] : 0.f;
           }
-          const unsigned prim = __ballot_sync(0xffffffffu, valid && d >= 0);
+        }
+        const unsigned prim_all = __ballot_sync(0xffffffffu, have && valid && d >= 0);
+        const unsigned long long my_row =
+            (have && valid && d >= 0)
+                ? (unsigned long long)(reinterpret_cast<const unsigned char*>(c.hidden_peer[dest]) + (long long)loff * row_bytes)
+                : 0ull;
+        const int ntok = min(TB, S - b0);
+        for (int tt = 0; tt < ntok && !failed; ++tt) {
+          const int token = b0 + tt;
+          const unsigned prim = (K >= 32) ? prim_all : ((prim_all >> (tt * K)) & ((1u << K) - 1u));
           int nprim = __popc(prim);
           if (nprim > a.kp) nprim = a.kp;
-          const unsigned char* my_row =
-              (valid && d >= 0) ? reinterpret_cast<const unsigned char*>(c.hidden_peer[dest]) + (long long)loff * row_bytes
-                                : nullptr;
           unsigned long long rows_compact = 0;
           {
             unsigned m = prim;
@@ -331,7 +340,7 @@ __global__ void __launch_bounds__(kPullBulkThreads) combine_pull_bulk_kernel(con
             while (m) {
               const int kk = __ffs(m) - 1;
               m &= m - 1;
-              const unsigned long long ptr = __shfl_sync(0xffffffffu, (unsigned long long)my_row, kk);
+              const unsigned long long ptr = __shfl_sync(0xffffffffu, my_row, tt * K + kk);
               if (lane == p) rows_compact = ptr;
               ++p;
             }

@@ -154,6 +154,33 @@ __device__ void zero_fill_rows(const MoonepDevCtx& c, const SendArgs& a, int war
   }
 }
 
+// Same with bulk stores: lane 0 of each warp writes whole row pieces from a zeroed shared buffer.
+__device__ void zero_fill_rows_bulk(const MoonepDevCtx& c, const SendArgs& a, int warp_global, int warps_total, int lane,
+                                    const unsigned char* zero_buf) {
+  if (lane != 0) return;
+  unsigned char* shard = reinterpret_cast<unsigned char*>(c.hidden_peer[c.rank]);
+  float* wbuf = reinterpret_cast<float*>(c.meta_peer[c.rank] + c.weights_off);
+  const int ngroups = c.E + c.B;
+  const long long row_bytes = (long long)c.H * 2;
+  for (int g = 0; g < ngroups; ++g) {
+    const int n_pad = a.zero_fill[2 * g + 1];
+    if (n_pad <= 0) continue;
+    const int start = a.zero_fill[2 * g];
+    for (int r = warp_global; r < n_pad; r += warps_total) {
+      const int row = start + r;
+      if (row < 0 || row >= c.NvS) continue;
+      for (int ch = 0; ch < a.nchunks; ++ch) {
+        const long long off = (long long)ch * a.chunk_bytes;
+        const long long rest = row_bytes - off;
+        bulk_s2g(shard + (long long)row * row_bytes + off, zero_buf, (unsigned)(rest < a.chunk_bytes ? rest : a.chunk_bytes));
+      }
+      if (a.weights != nullptr) wbuf[row] = 0.f;
+    }
+  }
+  bulk_commit();
+  bulk_wait<0>();
+}
+
 // Grab the next batch of tokens; lane-uniform result.
 __device__ __forceinline__ int grab_tokens(int* counter, int lane) {
   int b = 0;
@@ -261,7 +288,7 @@ __global__ void __launch_bounds__(kSendThreadsLdst) dispatch_send_ldst_kernel(co
 // ---- send kernel, bulk-copy path -----------------------------------------------------------------
 
 __global__ void __launch_bounds__(kSendThreadsBulk) dispatch_send_bulk_kernel(const MoonepDevCtx c, const SendArgs a) {
-  extern __shared__ __align__(128) unsigned char s_ring[];  // [kBulkWarps][kBulkStages][chunk_bytes]
+  extern __shared__ __align__(128) unsigned char s_ring[];  // [kBulkWarps][kBulkStages][chunk_bytes] + zero piece
   __shared__ __align__(8) unsigned long long s_bar[kBulkWarps][kBulkStages];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   if (threadIdx.x < kBulkWarps * kBulkStages) mbar_init(&s_bar[0][0] + threadIdx.x, 1);
@@ -275,7 +302,13 @@ __global__ void __launch_bounds__(kSendThreadsBulk) dispatch_send_bulk_kernel(co
       const int hthreads = hw * 32;
       if (a.build_dedup)
         build_dedup_rows(c, a, blockIdx.x * hthreads + (threadIdx.x - kBulkWarps * 32), gridDim.x * hthreads);
-      zero_fill_rows(c, a, blockIdx.x * hw + (warp - kBulkWarps), gridDim.x * hw, lane);
+      // pad rows: bulk stores from a zeroed piece of shared memory, one instruction per row piece
+      unsigned char* zero_buf = s_ring + (size_t)kBulkWarps * kBulkStages * a.chunk_bytes;
+      for (int i = threadIdx.x - kBulkWarps * 32; i < a.chunk_bytes / 16; i += hthreads)
+        reinterpret_cast<int4*>(zero_buf)[i] = make_int4(0, 0, 0, 0);
+      fence_proxy_async();
+      asm volatile("bar.sync 1, %0;" ::"r"(hthreads) : "memory");
+      zero_fill_rows_bulk(c, a, blockIdx.x * hw + (warp - kBulkWarps), gridDim.x * hw, lane, zero_buf);
     } else {
       const int H = c.H, K = c.K, S = c.S;
       const long long row_bytes = (long long)H * 2;
@@ -489,7 +522,7 @@ extern "C" int moonep_dispatch_send(void* ctx, const void* hidden, const float* 
       return rc;
   }
   if (path == MOONEP_PATH_BULK && a.vec_ok) {
-    const size_t smem = (size_t)kBulkWarps * kBulkStages * a.chunk_bytes;
+    const size_t smem = (size_t)(kBulkWarps * kBulkStages + 1) * a.chunk_bytes;  // ring + one zeroed piece
     if ((int)smem + 4096 <= h->max_smem_optin) {
       if (int rc = check_cuda(cudaFuncSetAttribute(dispatch_send_bulk_kernel,
                                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),

@@ -1,0 +1,438 @@
+// Grouped expert GEMM for sm_100a: tcgen05 tensor cores, TMEM accumulators, TMA-fed shared memory.
+//
+//   Y[rows of group g, :] = X[rows of group g, :] @ W[g]^T        X: [rows, K] bf16, W: [G, N, K] bf16
+//
+// Groups are the padded row segments of a dispatched shard: cu_seqlens[g] is the inclusive end of
+// group g and every non-empty segment is a multiple of 128 rows, so each 128-row block belongs to
+// exactly one group.  The number of row blocks is read from cu_seqlens on the device; the host never
+// synchronises.
+//
+// Persistent kernel, one CTA per SM, 192 threads:
+//   warp 0      TMA producer: per 64-wide K block one 128x64 tile of X and two 128x64 tiles of W
+//               (cp.async.bulk.tensor.2d, 128-byte swizzle, no multicast) into a 4-stage ring; the
+//               transaction bytes complete the stage's "full" mbarrier.
+//   warp 1      allocates 512 TMEM columns (two 128x256 fp32 accumulators) and issues the MMAs from
+//               one lane: four tcgen05.mma (M=128, N=256, K=16, bf16 -> fp32) per stage;
+//               tcgen05.commit releases the stage and, after the last K block, publishes the
+//               accumulator to the epilogue.
+//   warps 2..5  epilogue: tcgen05.ld 32 columns at a time from their 32 TMEM lanes, apply the
+//               epilogue, convert to bf16, store.  While they drain one accumulator the MMA warp
+//               fills the other.
+// Epilogues: PLAIN  y = acc                                   (256 output columns per tile)
+//            SWIGLU y = silu(acc[:, :128]) * acc[:, 128:]      (W tiles come from W_gate and W_up;
+//                                                              128 output columns per tile)
+//            SCALE  y = acc * row_scale[row]                   (down projection times the gate
+//                                                              weight carried with the row)
+// Every mbarrier wait is bounded; on expiry the role records a status word and leaves its loop, the
+// CTA still frees its TMEM before it returns.
+//
+// The reference has no GEMM; this kernel serves the MoE-layer benchmark configuration (dispatch ->
+// prefetch_weight -> grouped GEMM -> combine) named beside the reference's Buffer API
+// (reference README.md:46-48).
+#include <cuda.h>
+
+#include "common.cuh"
+#include "host.h"
+
+namespace moonep {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int kStages = 4;
+constexpr int kGemmThreads = 192;
+constexpr int kTmemCols = 512;
+constexpr unsigned kATileBytes = BM * BK * 2;        // 16 KB
+constexpr unsigned kBHalfBytes = 128 * BK * 2;       // 16 KB
+constexpr unsigned kStageBytes = kATileBytes + 2 * kBHalfBytes;  // 48 KB
+
+enum GemmMode { kPlain = 0, kSwiglu = 1, kScale = 2 };
+
+struct GemmArgs {
+  uint16_t* out;           // [rows, ldo] bf16
+  const float* row_scale;  // [rows] or null
+  const int* cu_seqlens;   // [G] inclusive padded ends
+  int* status;             // [MOONEP_ST_WORDS] or null
+  unsigned long long timeout_ns;
+  int G;
+  int n_per_group;   // rows of W per group (N)
+  int n_tiles;       // output column tiles per row block
+  int k_blocks;      // K / 64
+  int ldo;           // row stride of out in elements
+  int mode;
+  int rows_cap;      // rows of X
+};
+
+__device__ __forceinline__ void gemm_fail(const GemmArgs& a, int where, int x, int y) {
+  if (a.status != nullptr && atomicCAS(a.status + MOONEP_ST_CODE, 0, MOONEP_STATUS_TIMEOUT) == 0) {
+    a.status[MOONEP_ST_KERNEL] = 13;
+    a.status[MOONEP_ST_FAMILY] = where;
+    a.status[MOONEP_ST_PEER] = x;
+    a.status[MOONEP_ST_EXPECT] = y;
+    __threadfence();
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* tmap, int c0, int c1,
+                                            unsigned long long* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(reinterpret_cast<unsigned long long>(tmap)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(unsigned* smem_dst, unsigned ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(unsigned taddr, unsigned ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_bf16(unsigned d_tmem, unsigned long long adesc, unsigned long long bdesc,
+                                          unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,"
+      "%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile stored with the 128-byte swizzle: rows are
+// 128 bytes apart, groups of eight rows 1024 bytes apart.
+__device__ __forceinline__ unsigned long long make_smem_desc(const void* tile) {
+  const unsigned addr = smem_u32(tile);
+  unsigned long long d = 0;
+  d |= (unsigned long long)((addr & 0x3FFFFu) >> 4);  // start address, 16-byte units
+  d |= (unsigned long long)1 << 16;                   // leading byte offset (unused for this layout)
+  d |= (unsigned long long)(1024 >> 4) << 32;         // stride byte offset: 8 rows * 128 bytes
+  d |= (unsigned long long)1 << 46;                   // descriptor version of sm_100
+  d |= (unsigned long long)2 << 61;                   // 128-byte swizzle
+  return d;
+}
+
+// kind::f16 instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, M x N.
+__host__ __device__ constexpr unsigned make_idesc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b0,
+                        const __grid_constant__ CUtensorMap tmap_b1, const GemmArgs a) {
+  extern __shared__ unsigned char s_raw[];
+  __shared__ __align__(8) unsigned long long s_full[kStages], s_empty[kStages], s_tfull[2], s_tempty[2];
+  __shared__ unsigned s_tmem_base;
+  unsigned char* s_tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(s_raw) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(s_full + s, 1);
+      mbar_init(s_empty + s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(s_tfull + b, 1);
+      mbar_init(s_tempty + b, 4);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&s_tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const unsigned tmem_base = s_tmem_base;
+
+  const int total_rows = min(a.cu_seqlens[a.G - 1], a.rows_cap);
+  const int row_blocks = total_rows / BM;
+  const long long num_tiles = (long long)row_blocks * a.n_tiles;
+  const int b_rows_per_tile = (a.mode == kSwiglu) ? 128 : 256;  // W rows consumed per output tile and tensor map
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      unsigned phase = 0;
+      bool failed = false;
+      for (long long t = blockIdx.x; t < num_tiles && !failed; t += gridDim.x) {
+        const int mb = (int)(t / a.n_tiles), nb = (int)(t % a.n_tiles);
+        const int row0 = mb * BM;
+        int lo = 0, hi = a.G - 1;  // first group whose end is beyond row0
+        while (lo < hi) {
+          const int mid = (lo + hi) >> 1;
+          if (a.cu_seqlens[mid] > row0) hi = mid; else lo = mid + 1;
+        }
+        const int wrow0 = lo * a.n_per_group + nb * b_rows_per_tile;
+        for (int kb = 0; kb < a.k_blocks; ++kb) {
+          if (!mbar_wait(s_empty + stage, phase ^ 1u, a.timeout_ns)) {
+            gemm_fail(a, 1, stage, kb);
+            failed = true;
+            break;
+          }
+          unsigned char* st = s_tiles + (size_t)stage * kStageBytes;
+          mbar_expect_tx(s_full + stage, kStageBytes);
+          tma_load_2d(st, &tmap_a, kb * BK, row0, s_full + stage);
+          tma_load_2d(st + kATileBytes, &tmap_b0, kb * BK, wrow0, s_full + stage);
+          if (a.mode == kSwiglu)
+            tma_load_2d(st + kATileBytes + kBHalfBytes, &tmap_b1, kb * BK, wrow0, s_full + stage);
+          else
+            tma_load_2d(st + kATileBytes + kBHalfBytes, &tmap_b0, kb * BK, wrow0 + 128, s_full + stage);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr unsigned idesc = make_idesc(BM, BN);
+      int stage = 0;
+      unsigned phase = 0;
+      unsigned tphase[2] = {0, 0};
+      int it = 0;
+      bool failed = false;
+      for (long long t = blockIdx.x; t < num_tiles && !failed; t += gridDim.x, ++it) {
+        const int buf = it & 1;
+        if (!mbar_wait(s_tempty + buf, tphase[buf] ^ 1u, a.timeout_ns)) {
+          gemm_fail(a, 2, buf, it);
+          break;
+        }
+        tphase[buf] ^= 1u;
+        tc_fence_after();
+        const unsigned d_tmem = tmem_base + (unsigned)(buf * BN);
+        for (int kb = 0; kb < a.k_blocks; ++kb) {
+          if (!mbar_wait(s_full + stage, phase, a.timeout_ns)) {
+            gemm_fail(a, 3, stage, kb);
+            failed = true;
+            break;
+          }
+          tc_fence_after();
+          const unsigned char* st = s_tiles + (size_t)stage * kStageBytes;
+          const unsigned long long adesc = make_smem_desc(st);
+          const unsigned long long bdesc = make_smem_desc(st + kATileBytes);
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            // 16 bf16 = 32 bytes further along K inside the swizzled 128-byte rows
+            umma_bf16(d_tmem, adesc + (unsigned long long)(kk * 2), bdesc + (unsigned long long)(kk * 2), idesc,
+                      (kb | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit(s_empty + stage);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!failed) umma_commit(s_tfull + buf);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- epilogue (warps 2..5) ----------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    unsigned tphase[2] = {0, 0};
+    int it = 0;
+    for (long long t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+      const int buf = it & 1;
+      const int mb = (int)(t / a.n_tiles), nb = (int)(t % a.n_tiles);
+      int got = 1;
+      if (lane == 0) got = mbar_wait(s_tfull + buf, tphase[buf], a.timeout_ns) ? 1 : 0;
+      got = __shfl_sync(0xffffffffu, got, 0);
+      if (!got) {
+        if (lane == 0) gemm_fail(a, 4, buf, it);
+        break;
+      }
+      tphase[buf] ^= 1u;
+      tc_fence_after();
+      const int row = mb * BM + q * 32 + lane;
+      const unsigned taddr = tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)(buf * BN);
+      if (a.mode == kSwiglu) {
+        uint16_t* orow = a.out + (long long)row * a.ldo + (long long)nb * 128;
+#pragma unroll 1
+        for (int c0 = 0; c0 < 128; c0 += 32) {
+          unsigned g[32], u[32];
+          tmem_ld32(taddr + (unsigned)c0, g);
+          tmem_ld32(taddr + (unsigned)(128 + c0), u);
+          tmem_ld_wait();
+          unsigned o[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float y0 = silu(__uint_as_float(g[2 * j])) * __uint_as_float(u[2 * j]);
+            const float y1 = silu(__uint_as_float(g[2 * j + 1])) * __uint_as_float(u[2 * j + 1]);
+            o[j] = pack_bf16(y0, y1);
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            st16(orow + c0 + j * 8, make_int4((int)o[4 * j], (int)o[4 * j + 1], (int)o[4 * j + 2], (int)o[4 * j + 3]));
+        }
+      } else {
+        const float scale = (a.mode == kScale && a.row_scale != nullptr) ? a.row_scale[row] : 1.f;
+        uint16_t* orow = a.out + (long long)row * a.ldo + (long long)nb * BN;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          unsigned v[32];
+          tmem_ld32(taddr + (unsigned)c0, v);
+          tmem_ld_wait();
+          unsigned o[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            o[j] = pack_bf16(__uint_as_float(v[2 * j]) * scale, __uint_as_float(v[2 * j + 1]) * scale);
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            st16(orow + c0 + j * 8, make_int4((int)o[4 * j], (int)o[4 * j + 1], (int)o[4 * j + 2], (int)o[4 * j + 3]));
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_tempty + buf);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace
+
+// ---- host side --------------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+    else
+      cudaGetLastError();
+  }
+  return fn;
+}
+
+// 2-D bf16 row-major [rows, cols] tensor, box = 64 columns x box_rows rows, 128-byte swizzle.
+static int make_tmap(CUtensorMap* m, const void* base, unsigned long long rows, unsigned long long cols,
+                     unsigned box_rows) {
+  EncodeTiledFn fn = encode_tiled();
+  if (fn == nullptr) {
+    set_error("cuTensorMapEncodeTiled is not available (no CUDA driver?)");
+    return 1;
+  }
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with CUresult " + std::to_string((int)r));
+    return (int)r;
+  }
+  return 0;
+}
+
+}  // namespace moonep
+
+using namespace moonep;
+
+// x: [rows_cap, K] bf16.  w0 (and w1 for SwiGLU): [G, n_per_group, K] bf16.  out: [rows_cap, n_out] bf16 with
+// n_out = n_per_group (plain, scale) or n_per_group (swiglu: gate and up each have n_per_group rows).
+// cu_seqlens: [G] int32 inclusive padded ends (multiples of 128).  mode: 0 plain, 1 swiglu, 2 scale by row_scale.
+extern "C" int moonep_grouped_gemm(const void* x, const void* w0, const void* w1, void* out, const float* row_scale,
+                                   const int* cu_seqlens, int G, int rows_cap, int K, int n_per_group, int mode,
+                                   int* status, long long timeout_ms, int num_sms, void* stream) {
+  if (K % BK != 0 || K <= 0) {
+    set_error("moonep_grouped_gemm: K must be a positive multiple of 64");
+    return 1;
+  }
+  const int tile_n = (mode == kSwiglu) ? 128 : BN;
+  if (n_per_group % tile_n != 0 || n_per_group <= 0) {
+    set_error("moonep_grouped_gemm: N per group must be a multiple of " + std::to_string(tile_n));
+    return 1;
+  }
+  if (mode == kSwiglu && w1 == nullptr) {
+    set_error("moonep_grouped_gemm: SwiGLU needs the up-projection weights");
+    return 1;
+  }
+  CUtensorMap ta, tb0, tb1;
+  if (int rc = make_tmap(&ta, x, (unsigned long long)rows_cap, (unsigned long long)K, BM)) return rc;
+  if (int rc = make_tmap(&tb0, w0, (unsigned long long)G * n_per_group, (unsigned long long)K, 128)) return rc;
+  if (int rc = make_tmap(&tb1, mode == kSwiglu ? w1 : w0, (unsigned long long)G * n_per_group, (unsigned long long)K, 128))
+    return rc;
+  GemmArgs a;
+  a.out = (uint16_t*)out;
+  a.row_scale = row_scale;
+  a.cu_seqlens = cu_seqlens;
+  a.status = status;
+  a.timeout_ns = (unsigned long long)(timeout_ms > 0 ? timeout_ms : 10000) * 1000000ull;
+  a.G = G;
+  a.n_per_group = n_per_group;
+  a.n_tiles = n_per_group / tile_n;
+  a.k_blocks = K / BK;
+  a.ldo = n_per_group;
+  a.mode = mode;
+  a.rows_cap = rows_cap;
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int grid = imax(1, num_sms > 0 ? imin(num_sms, sms) : sms);
+  const size_t smem = (size_t)kStages * kStageBytes + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (int rc = check_cuda(cudaFuncSetAttribute(grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 (int)smem),
+                            "cudaFuncSetAttribute(grouped_gemm_kernel)"))
+      return rc;
+    attr_set = true;
+  }
+  grouped_gemm_kernel<<<grid, kGemmThreads, smem, (cudaStream_t)stream>>>(ta, tb0, tb1, a);
+  return check_launch("grouped_gemm_kernel");
+}

@@ -113,6 +113,7 @@ _SIGNATURES = {
     "moonep_combine_pull": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp]),
     "moonep_prefetch": (_i, [_vp, ctypes.POINTER(_vp), ctypes.POINTER(_vp), _i, _vp, _ll, _i, _i, _i, _vp]),
     "moonep_grad_reduce": (_i, [_vp, ctypes.POINTER(_vp), ctypes.POINTER(_vp), _i, _vp, _i, _ll, _i, _i, _i, _vp]),
+    "moonep_grouped_gemm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _ll, _i, _vp]),
     "moonep_vmm_granularity": (_i, [_i, ctypes.POINTER(_ull)]),
     "moonep_vmm_create": (_i, [_i, _ull, ctypes.POINTER(_ull), ctypes.POINTER(_i)]),
     "moonep_vmm_import": (_i, [_i, ctypes.POINTER(_ull)]),
