@@ -3,7 +3,8 @@
 MOONEP_PLANNER        ``gpu`` (default) or ``cpu``: run the planner kernels or the host planner.
 MOONEP_TIMEOUT_MS     budget of every device-side wait (default 10000).
 MOONEP_COPY_PATH      ``bulk`` (default: TMA bulk copies through shared memory) or ``ldst``
-                      (plain 16-byte loads/stores) for dispatch/combine/prefetch.
+                      (plain 16-byte loads/stores) for dispatch/combine/prefetch;
+                      ``MOONEP_SEND_PATH`` / ``MOONEP_PULL_PATH`` set one direction only.
 MOONEP_LOCAL_SMS      CTAs of the kernels that only touch local memory (default: all SMs); ``num_sms`` of
                       the Buffer bounds the kernels that move data between ranks.
 MOONEP_NUM_SMS_DEDUP  number of SMs the dedup builder may use (validated, 1..SM count).
@@ -33,10 +34,17 @@ def timeout_ms() -> int:
     return max(1, int(os.environ.get("MOONEP_TIMEOUT_MS", DEFAULT_TIMEOUT_MS)))
 
 
-def copy_path() -> str:
-    raw = os.environ.get("MOONEP_COPY_PATH", "bulk").lower()
+def copy_path(which: str = "") -> str:
+    """Copy path of the send (``which="send"``) or pull (``"pull"``) kernel.
+
+    ``MOONEP_SEND_PATH`` / ``MOONEP_PULL_PATH`` override ``MOONEP_COPY_PATH`` for one direction.
+    """
+    raw = os.environ.get(f"MOONEP_{which.upper()}_PATH") if which else None
+    if not raw:
+        raw = os.environ.get("MOONEP_COPY_PATH", "bulk")
+    raw = raw.lower()
     if raw not in ("bulk", "ldst"):
-        raise ValueError(f"MOONEP_COPY_PATH must be 'bulk' or 'ldst', got {raw!r}")
+        raise ValueError(f"copy path must be 'bulk' or 'ldst', got {raw!r}")
     return raw
 
 

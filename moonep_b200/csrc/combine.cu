@@ -67,6 +67,7 @@ __global__ void __launch_bounds__(512)
       const int dn = dup_groups[3 * g + 2];
       if (primary < 0 || primary >= c.NvS || ds < 0 || dn < 0 || ds + dn > c.NvS) continue;
       uint16_t* prow = shard + (long long)primary * H;
+      const int my_dup = (lane < dn && lane < 32) ? dup_loffs[ds + lane] : -1;  // lane q: q-th duplicate row
       if (vec_ok) {
         const int nvec = H / 8;
         int4* p4 = reinterpret_cast<int4*>(prow);
@@ -79,8 +80,8 @@ __global__ void __launch_bounds__(512)
             for (int q = 0; q < 8; ++q) acc[j][q] = 0.f;
             if (i < nvec) acc_add(acc[j], ld16(p4 + i));
           }
-          for (int q = 0; q < dn; ++q) {
-            const int row = dup_loffs[ds + q];
+          for (int q = 0; q < dn && q < 32; ++q) {
+            const int row = __shfl_sync(0xffffffffu, my_dup, q);
             if (row < 0 || row >= c.NvS) continue;
             const int4* r4 = reinterpret_cast<const int4*>(shard + (long long)row * H);
             int4 v[kGroupVec];
@@ -238,7 +239,7 @@ __global__ void __launch_bounds__(512)
 //
 // Warp 0 is the producer: per (token, row piece) it takes a free slot of a shared-memory ring and
 // lets one lane issue one cp.async.bulk per primary row (peer global -> shared, completion counted
-// in bytes on the slot's "full" mbarrier).  Warps 1..8 are consumers, warp w taking every 8th item:
+// in bytes on the slot's "full" mbarrier).  Warps 1..nslots are consumers, warp w owning slot w-1:
 // it waits for the slot, adds the rows in fp32 in ascending k, stores the bf16 result with 16-byte
 // stores and releases the slot through its "empty" mbarrier.  Remote reads are therefore issued back to back without waiting for data,
 // which keeps the NVLink request queue full with few SMs.
@@ -301,27 +302,53 @@ __global__ void __launch_bounds__(kPullBulkThreads) combine_pull_bulk_kernel(con
       // load of dst and one round of weight gathers serve the whole batch.
       const int TB = K <= 32 ? 32 / K : 1;
       const int tl = lane / K, kl = lane - tl * K;
+      // Three batches are in flight so that no load is used in the iteration that issued it:
+      // N has its dst load outstanding, Q its weight gather, P is complete and gets its rows fetched.
+      struct Batch {
+        int b0, d, dest, loff;
+        bool valid;
+        float w;
+      };
+      auto stage1 = [&](Batch& n) {
+        int b = 0;
+        if (lane == 0) b = atomicAdd(work, TB);
+        n.b0 = __shfl_sync(0xffffffffu, b, 0);
+        n.d = 0;
+        const int tok = n.b0 + tl;
+        if (tl < TB && tok < S) n.d = a.dst[tok * K + kl];
+      };
+      auto stage2 = [&](Batch& q) {
+        q.valid = false;
+        q.dest = 0;
+        q.loff = 0;
+        q.w = 0.f;
+        const int tok = q.b0 + tl;
+        if (q.b0 < S && tl < TB && tok < S) {
+          const int raw = q.d < 0 ? -q.d - 1 : q.d;
+          q.dest = raw / NvS;
+          q.loff = raw - q.dest * NvS;
+          q.valid = q.dest >= 0 && q.dest < c.R && q.loff >= 0 && q.loff < NvS;
+          if (!q.valid) record_status(c, MOONEP_STATUS_BAD_INDEX, MOONEP_K_COMBINE_PULL, 6, q.d, tok, kl);
+          if (a.out_w != nullptr && q.valid)
+            q.w = reinterpret_cast<const float*>(c.meta_peer[q.dest] + c.weights_off)[q.loff];
+        }
+      };
+      Batch P, Q, N;
+      stage1(Q);
+      stage2(Q);
+      stage1(N);
       for (;;) {
-        int b0 = 0;
-        if (lane == 0) b0 = atomicAdd(work, TB);
-        b0 = __shfl_sync(0xffffffffu, b0, 0);
-        if (b0 >= S || failed) break;
+        P = Q;
+        Q = N;
+        if (P.b0 >= S || failed) break;
+        stage2(Q);
+        stage1(N);
+        const int b0 = P.b0;
         const int my_token = b0 + tl;
         const bool have = tl < TB && my_token < S;
-        int d = 0, dest = 0, loff = 0;
-        bool valid = false;
-        if (have) {
-          d = a.dst[my_token * K + kl];
-          const int raw = d < 0 ? -d - 1 : d;
-          dest = raw / NvS;
-          loff = raw - dest * NvS;
-          valid = dest >= 0 && dest < c.R && loff >= 0 && loff < NvS;
-          if (!valid) record_status(c, MOONEP_STATUS_BAD_INDEX, MOONEP_K_COMBINE_PULL, 6, d, my_token, kl);
-          if (a.out_w != nullptr) {
-            const float* w = reinterpret_cast<const float*>(c.meta_peer[valid ? dest : c.rank] + c.weights_off);
-            a.out_w[my_token * K + kl] = valid ? w[loff] : 0.f;
-          }
-        }
+        const int d = P.d, dest = P.dest, loff = P.loff;
+        const bool valid = P.valid;
+        if (have && a.out_w != nullptr) a.out_w[my_token * K + kl] = valid ? P.w : 0.f;
         const unsigned prim_all = __ballot_sync(0xffffffffu, have && valid && d >= 0);
         const unsigned long long my_row =
             (have && valid && d >= 0)
@@ -372,8 +399,8 @@ __global__ void __launch_bounds__(kPullBulkThreads) combine_pull_bulk_kernel(con
           }
         }
       }
-      // end markers: one for each consumer warp (warp w takes the items congruent to w)
-      for (int q = 0; q < kPullConsumerWarps && !failed; ++q, ++item) {
+      // end markers: one for each consumer warp (one per slot)
+      for (int q = 0; q < a.nslots && !failed; ++q, ++item) {
         const int slot = item % a.nslots, use = item / a.nslots;
         if (!acquire_slot(slot, use)) break;
         if (lane == 0) {
@@ -383,8 +410,10 @@ __global__ void __launch_bounds__(kPullBulkThreads) combine_pull_bulk_kernel(con
       }
     } else {
       // ---------------- consumers ----------------
-      // each consumer warp owns every kPullConsumerWarps-th item, so several slots are reduced at once
-      for (int item = warp - 1;; item += kPullConsumerWarps) {
+      // Consumer warp w owns slot w-1 and therefore the items w-1, w-1+nslots, ...: it has always
+      // finished use u-1 of its slot before it waits for use u, which the parity wait relies on
+      // (a warp that could run a whole phase ahead would take the previous fill for its own).
+      for (int item = warp - 1; warp <= a.nslots; item += a.nslots) {
         const int slot = item % a.nslots, use = item / a.nslots;
         bool got = mbar_try_wait(s_full + slot, (unsigned)(use & 1));
         if (!got) {
@@ -474,7 +503,7 @@ extern "C" int moonep_combine_pull(void* ctx, const int* dst, void* out_hidden, 
     }
     const long long slot_bytes = (long long)a.kp * a.chunk_bytes;
     a.nslots = (int)((h->max_smem_optin - 8192) / slot_bytes);
-    if (a.nslots > kPullMaxSlots) a.nslots = kPullMaxSlots;
+    if (a.nslots > kPullConsumerWarps) a.nslots = kPullConsumerWarps;  // one consumer warp per slot
     if (a.nslots >= 2) {
       const size_t smem = (size_t)a.nslots * slot_bytes;
       if (int rc = check_cuda(cudaFuncSetAttribute(combine_pull_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,

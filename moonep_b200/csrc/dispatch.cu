@@ -12,11 +12,11 @@
 //                            cp.async.bulk (global->shared on an mbarrier, shared->peer global in
 //                            bulk groups); no register traffic, one instruction per 14 KB row.
 //                      ldst: 16-byte loads into registers, 16-byte stores to every destination.
-//                    Meanwhile the pad rows of the local shard are zero-filled and, for a fresh
+//                    Meanwhile, for a fresh
 //                    plan, dup_groups/dup_loffs/dup_counts are built from the link words the
 //                    peers pushed during planning (all CTAs share the rows).  The last CTA to finish signals FLAG_SENT.
-//   dispatch_expand  waits for every peer's FLAG_SENT, then copies each primary row to its
-//                    duplicate rows inside the local shard.
+//   dispatch_expand  all SMs: zero-fills the pad rows of the local shard, waits for every peer's
+//                    FLAG_SENT, then copies each primary row to its duplicate rows inside the shard.
 //
 // Parity: reference moonep_td/dispatch.py:42-117 (dispatch_kernel, zero_fill_kernel),
 // moonep_td/_dedup_builder.py:23-108 (three dedup kernels), moonep_td/dispatch_epilogue.py:21-40.
@@ -129,56 +129,44 @@ __device__ void build_dedup_rows(const MoonepDevCtx& c, const SendArgs& a, int g
 
 // ---- zero fill of pad rows ---------------------------------------------------------------------
 
+// Reads the (start, count) pairs of 32 groups at a time, then spreads the pad rows of every
+// non-empty range over all participating warps.
 __device__ void zero_fill_rows(const MoonepDevCtx& c, const SendArgs& a, int warp_global, int warps_total, int lane) {
   uint16_t* shard = c.hidden_peer[c.rank];
   float* wbuf = reinterpret_cast<float*>(c.meta_peer[c.rank] + c.weights_off);
   const int ngroups = c.E + c.B;
   const int H = c.H;
-  for (int g = 0; g < ngroups; ++g) {
-    const int n_pad = a.zero_fill[2 * g + 1];
-    if (n_pad <= 0) continue;
-    const int start = a.zero_fill[2 * g];
-    for (int r = warp_global; r < n_pad; r += warps_total) {
-      const int row = start + r;
-      if (row < 0 || row >= c.NvS) continue;
-      uint16_t* p = shard + (long long)row * H;
-      if (a.vec_ok) {
-        const int nvec = H / 8;
-        const int4 z = make_int4(0, 0, 0, 0);
-        for (int i = lane; i < nvec; i += 32) st16(reinterpret_cast<int4*>(p) + i, z);
-      } else {
-        for (int i = lane; i < H; i += 32) p[i] = 0;
+  int seen = 0;  // pad rows of the ranges before this one: rows are dealt round-robin across ranges
+  for (int base = 0; base < ngroups; base += 32) {
+    const int g = base + lane;
+    int n_pad = 0, start = 0;
+    if (g < ngroups) {
+      n_pad = a.zero_fill[2 * g + 1];
+      start = a.zero_fill[2 * g];
+    }
+    unsigned m = __ballot_sync(0xffffffffu, n_pad > 0);
+    while (m) {
+      const int src = __ffs(m) - 1;
+      m &= m - 1;
+      const int s0 = __shfl_sync(0xffffffffu, start, src);
+      const int np = __shfl_sync(0xffffffffu, n_pad, src);
+      const int first = ((warp_global - seen) % warps_total + warps_total) % warps_total;
+      seen = (seen + np) % warps_total;
+      for (int r = first; r < np; r += warps_total) {
+        const int row = s0 + r;
+        if (row < 0 || row >= c.NvS) continue;
+        uint16_t* p = shard + (long long)row * H;
+        if (a.vec_ok) {
+          const int nvec = H / 8;
+          const int4 z = make_int4(0, 0, 0, 0);
+          for (int i = lane; i < nvec; i += 32) st16(reinterpret_cast<int4*>(p) + i, z);
+        } else {
+          for (int i = lane; i < H; i += 32) p[i] = 0;
+        }
+        if (a.weights != nullptr && lane == 0) wbuf[row] = 0.f;
       }
-      if (a.weights != nullptr && lane == 0) wbuf[row] = 0.f;
     }
   }
-}
-
-// Same with bulk stores: lane 0 of each warp writes whole row pieces from a zeroed shared buffer.
-__device__ void zero_fill_rows_bulk(const MoonepDevCtx& c, const SendArgs& a, int warp_global, int warps_total, int lane,
-                                    const unsigned char* zero_buf) {
-  if (lane != 0) return;
-  unsigned char* shard = reinterpret_cast<unsigned char*>(c.hidden_peer[c.rank]);
-  float* wbuf = reinterpret_cast<float*>(c.meta_peer[c.rank] + c.weights_off);
-  const int ngroups = c.E + c.B;
-  const long long row_bytes = (long long)c.H * 2;
-  for (int g = 0; g < ngroups; ++g) {
-    const int n_pad = a.zero_fill[2 * g + 1];
-    if (n_pad <= 0) continue;
-    const int start = a.zero_fill[2 * g];
-    for (int r = warp_global; r < n_pad; r += warps_total) {
-      const int row = start + r;
-      if (row < 0 || row >= c.NvS) continue;
-      for (int ch = 0; ch < a.nchunks; ++ch) {
-        const long long off = (long long)ch * a.chunk_bytes;
-        const long long rest = row_bytes - off;
-        bulk_s2g(shard + (long long)row * row_bytes + off, zero_buf, (unsigned)(rest < a.chunk_bytes ? rest : a.chunk_bytes));
-      }
-      if (a.weights != nullptr) wbuf[row] = 0.f;
-    }
-  }
-  bulk_commit();
-  bulk_wait<0>();
 }
 
 // Grab the next batch of tokens; lane-uniform result.
@@ -209,7 +197,6 @@ __global__ void __launch_bounds__(kSendThreadsLdst) dispatch_send_ldst_kernel(co
   int* work = c.counters + MOONEP_NUM_KERNEL_IDS;  // token counter of this kernel
   if (ok) {
     if (a.build_dedup) build_dedup_rows(c, a, blockIdx.x * blockDim.x + threadIdx.x, gridDim.x * blockDim.x);
-    zero_fill_rows(c, a, blockIdx.x * nwarps + warp, gridDim.x * nwarps, lane);
     const int H = c.H, K = c.K, S = c.S;
     for (;;) {
       const int b0 = grab_tokens(work, lane);
@@ -288,7 +275,7 @@ __global__ void __launch_bounds__(kSendThreadsLdst) dispatch_send_ldst_kernel(co
 // ---- send kernel, bulk-copy path -----------------------------------------------------------------
 
 __global__ void __launch_bounds__(kSendThreadsBulk) dispatch_send_bulk_kernel(const MoonepDevCtx c, const SendArgs a) {
-  extern __shared__ __align__(128) unsigned char s_ring[];  // [kBulkWarps][kBulkStages][chunk_bytes] + zero piece
+  extern __shared__ __align__(128) unsigned char s_ring[];  // [kBulkWarps][kBulkStages][chunk_bytes]
   __shared__ __align__(8) unsigned long long s_bar[kBulkWarps][kBulkStages];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   if (threadIdx.x < kBulkWarps * kBulkStages) mbar_init(&s_bar[0][0] + threadIdx.x, 1);
@@ -297,18 +284,11 @@ __global__ void __launch_bounds__(kSendThreadsBulk) dispatch_send_bulk_kernel(co
   int* work = c.counters + MOONEP_NUM_KERNEL_IDS;
   if (ok) {
     if (warp >= kBulkWarps) {
-      // helper warps: duplicate map and pad rows
+      // helper warps: duplicate map
       const int hw = nwarps - kBulkWarps;
       const int hthreads = hw * 32;
       if (a.build_dedup)
         build_dedup_rows(c, a, blockIdx.x * hthreads + (threadIdx.x - kBulkWarps * 32), gridDim.x * hthreads);
-      // pad rows: bulk stores from a zeroed piece of shared memory, one instruction per row piece
-      unsigned char* zero_buf = s_ring + (size_t)kBulkWarps * kBulkStages * a.chunk_bytes;
-      for (int i = threadIdx.x - kBulkWarps * 32; i < a.chunk_bytes / 16; i += hthreads)
-        reinterpret_cast<int4*>(zero_buf)[i] = make_int4(0, 0, 0, 0);
-      fence_proxy_async();
-      asm volatile("bar.sync 1, %0;" ::"r"(hthreads) : "memory");
-      zero_fill_rows_bulk(c, a, blockIdx.x * hw + (warp - kBulkWarps), gridDim.x * hw, lane, zero_buf);
     } else {
       const int H = c.H, K = c.K, S = c.S;
       const long long row_bytes = (long long)H * 2;
@@ -438,10 +418,19 @@ __global__ void __launch_bounds__(kSendThreadsBulk) dispatch_send_bulk_kernel(co
 // ---- duplicate expansion --------------------------------------------------------------------------
 
 __global__ void __launch_bounds__(512)
-    dispatch_expand_kernel(const MoonepDevCtx c, const int* __restrict__ dup_groups, const int* __restrict__ dup_loffs,
+    dispatch_expand_kernel(const MoonepDevCtx c, const int* __restrict__ zero_fill, int with_weights,
+                           const int* __restrict__ dup_groups, const int* __restrict__ dup_loffs,
                            const int* __restrict__ dup_counts, int wait_epoch, int vec_ok) {
-  if (!block_wait_flags(c, MOONEP_FLAG_SENT, wait_epoch, MOONEP_K_DISPATCH_EXPAND)) return;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  if (!poisoned(c) && zero_fill != nullptr) {
+    // pad rows belong to this rank alone, so they are cleared while the peers' rows are still arriving
+    SendArgs z;
+    z.zero_fill = zero_fill;
+    z.vec_ok = vec_ok;
+    z.weights = with_weights ? reinterpret_cast<const float*>(zero_fill) : nullptr;  // only tested for null
+    zero_fill_rows(c, z, blockIdx.x * nwarps + warp, gridDim.x * nwarps, lane);
+  }
+  if (!block_wait_flags(c, MOONEP_FLAG_SENT, wait_epoch, MOONEP_K_DISPATCH_EXPAND)) return;
   const int H = c.H;
   int ngroups = dup_counts[0];
   if (ngroups < 0 || ngroups > c.NvS) ngroups = 0;
@@ -452,6 +441,8 @@ __global__ void __launch_bounds__(512)
     const int dn = dup_groups[3 * g + 2];
     if (primary < 0 || primary >= c.NvS || ds < 0 || dn < 0 || ds + dn > c.NvS) continue;
     const uint16_t* src = shard + (long long)primary * H;
+    // lane q holds the q-th duplicate row (a group has fewer than 32 duplicates)
+    const int my_dup = (lane < dn && lane < 32) ? dup_loffs[ds + lane] : -1;
     if (vec_ok) {
       const int nvec = H / 8;
       const int4* s4 = reinterpret_cast<const int4*>(src);
@@ -462,8 +453,8 @@ __global__ void __launch_bounds__(512)
           const int i = c0 + j * 32 + lane;
           if (i < nvec) v[j] = ld16(s4 + i);
         }
-        for (int q = 0; q < dn; ++q) {
-          const int row = dup_loffs[ds + q];
+        for (int q = 0; q < dn && q < 32; ++q) {
+          const int row = __shfl_sync(0xffffffffu, my_dup, q);
           if (row < 0 || row >= c.NvS) continue;
           int4* o4 = reinterpret_cast<int4*>(shard + (long long)row * H);
 #pragma unroll
@@ -522,7 +513,7 @@ extern "C" int moonep_dispatch_send(void* ctx, const void* hidden, const float* 
       return rc;
   }
   if (path == MOONEP_PATH_BULK && a.vec_ok) {
-    const size_t smem = (size_t)(kBulkWarps * kBulkStages + 1) * a.chunk_bytes;  // ring + one zeroed piece
+    const size_t smem = (size_t)kBulkWarps * kBulkStages * a.chunk_bytes;
     if ((int)smem + 4096 <= h->max_smem_optin) {
       if (int rc = check_cuda(cudaFuncSetAttribute(dispatch_send_bulk_kernel,
                                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
@@ -536,16 +527,12 @@ extern "C" int moonep_dispatch_send(void* ctx, const void* hidden, const float* 
   return check_launch("dispatch_send_ldst_kernel");
 }
 
-extern "C" int moonep_dispatch_expand(void* ctx, const int* dup_groups, const int* dup_loffs, const int* dup_counts,
-                                      void* out_hidden, float* out_weights, int wait_epoch_sent, int path,
-                                      void* stream) {
-  (void)out_hidden;
-  (void)out_weights;
-  (void)path;
+extern "C" int moonep_dispatch_expand(void* ctx, const int* zero_fill, int with_weights, const int* dup_groups,
+                                      const int* dup_loffs, const int* dup_counts, int wait_epoch_sent, void* stream) {
   auto* h = (HostCtx*)ctx;
   const MoonepDevCtx& c = h->dev;
   const int grid = imax(1, imin(c.local_sms, h->sm_count));
-  dispatch_expand_kernel<<<grid, 512, 0, (cudaStream_t)stream>>>(c, dup_groups, dup_loffs, dup_counts, wait_epoch_sent,
-                                                                (c.H % 8 == 0) ? 1 : 0);
+  dispatch_expand_kernel<<<grid, 512, 0, (cudaStream_t)stream>>>(c, zero_fill, with_weights, dup_groups, dup_loffs,
+                                                                dup_counts, wait_epoch_sent, (c.H % 8 == 0) ? 1 : 0);
   return check_launch("dispatch_expand_kernel");
 }

@@ -137,8 +137,8 @@ int moonep_dispatch_send(void* ctx, const void* hidden, const float* weights, co
                          const int* zero_fill, int* dup_groups, int* dup_loffs, int* dup_counts,
                          int build_dedup, int wait_family, int wait_epoch, int signal_epoch_sent, int path,
                          void* stream);
-int moonep_dispatch_expand(void* ctx, const int* dup_groups, const int* dup_loffs, const int* dup_counts,
-                           void* out_hidden, float* out_weights, int wait_epoch_sent, int path, void* stream);
+int moonep_dispatch_expand(void* ctx, const int* zero_fill, int with_weights, const int* dup_groups,
+                           const int* dup_loffs, const int* dup_counts, int wait_epoch_sent, void* stream);
 
 // Combine.
 int moonep_combine_prologue(void* ctx, const int* dup_groups, const int* dup_loffs, const int* dup_counts,

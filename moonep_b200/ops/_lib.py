@@ -108,7 +108,7 @@ _SIGNATURES = {
     "moonep_plan_publish": (_i, [_vp, _vp, _vp, _i, _i, _vp]),
     "moonep_plan_compute": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp]),
     "moonep_dispatch_send": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
-    "moonep_dispatch_expand": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp]),
+    "moonep_dispatch_expand": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _i, _vp]),
     "moonep_combine_prologue": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "moonep_combine_pull": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp]),
     "moonep_prefetch": (_i, [_vp, ctypes.POINTER(_vp), ctypes.POINTER(_vp), _i, _vp, _ll, _i, _i, _i, _vp]),

@@ -65,6 +65,8 @@ class CudaBackend:
         R, E, S, K, B = c["R"], c["E"], c["S"], c["K"], c["B"]
         self.epoch = [0] * NUM_FLAG_FAMILIES
         self.path = _PATHS[config.copy_path()]
+        self.send_path = _PATHS[config.copy_path("send")]
+        self.pull_path = _PATHS[config.copy_path("pull")]
         self._profile = None
         self._quiesced = False  # every peer is known to be past its last pull from this rank's shard
 
@@ -233,16 +235,17 @@ class CudaBackend:
         self._call(
             "moonep_dispatch_send", _ptr(hidden_sh), _ptr(route_weights_sk), _ptr(plan.dst),
             _ptr(plan.zero_fill_ranges), _ptr(plan.dup_groups), _ptr(plan.dup_loffs), _ptr(plan.dup_counts),
-            int(bool(build_dedup_map)), wf, we, self._next(FLAG_SENT), self.path, _stream(),
+            int(bool(build_dedup_map)), wf, we, self._next(FLAG_SENT), self.send_path, _stream(),
         )  # fmt: skip
         if wait is not None:
             self._quiesced = True
+        self._sent_weights = route_weights_sk is not None
         self.world.step()
 
     def dispatch_expand(self, plan, out_hidden, out_weights, zero_copy):
         self._call(
-            "moonep_dispatch_expand", _ptr(plan.dup_groups), _ptr(plan.dup_loffs), _ptr(plan.dup_counts),
-            None, None, self.epoch[FLAG_SENT], self.path, _stream(),
+            "moonep_dispatch_expand", _ptr(plan.zero_fill_ranges), int(self._sent_weights), _ptr(plan.dup_groups),
+            _ptr(plan.dup_loffs), _ptr(plan.dup_counts), self.epoch[FLAG_SENT], _stream(),
         )  # fmt: skip
         if not zero_copy:
             out_hidden.copy_(self.ctx["hidden_buf_local"])
@@ -273,7 +276,7 @@ class CudaBackend:
         self._quiesced = False
         self._call(
             "moonep_combine_pull", _ptr(plan_dst), _ptr(out_hidden), _ptr(out_weights_sk), self.epoch[FLAG_COMB],
-            self.path, _stream(),
+            self.pull_path, _stream(),
         )  # fmt: skip
 
     # -- expert weights --------------------------------------------------------------------
