@@ -41,7 +41,8 @@ def copy_path(which: str = "") -> str:
     """
     raw = os.environ.get(f"MOONEP_{which.upper()}_PATH") if which else None
     if not raw:
-        raw = os.environ.get("MOONEP_COPY_PATH", "bulk")
+        # measured on 8 B200: bulk stores win for the send, register loads for the pull
+        raw = os.environ.get("MOONEP_COPY_PATH", "ldst" if which == "pull" else "bulk")
     raw = raw.lower()
     if raw not in ("bulk", "ldst"):
         raise ValueError(f"copy path must be 'bulk' or 'ldst', got {raw!r}")

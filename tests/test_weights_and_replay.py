@@ -1,0 +1,209 @@
+"""prefetch_weight, reduce_grad, plan replay and failure reporting on emulated worlds
+(CPU backend always; the sm_100a kernels with R emulated ranks on one GPU when marked gpu).
+
+Parity: reference tests/test_prefetch.py:45-156 (holes, duplicates, empty plan, sentinel slots),
+tests/test_grad_reduce.py:232-350 (bitwise order, fan-in, empty plan, repeated launch) and
+tests/test_dispatch.py:345-411 (hidden-only dispatch with a saved plan).
+"""
+
+import dataclasses
+
+import pytest
+import torch
+
+from moonep_b200 import Buffer
+from moonep_b200.models.routing import make_routing
+from moonep_b200.parallel.world import LocalWorld
+
+DEVICES = ["cpu", pytest.param("cuda", marks=pytest.mark.gpu)]
+
+
+def _world(R, device, S=32, H=64, K=2, epn=4, B=3, num_sms=5):
+    lw = LocalWorld(R, device)
+    bufs = lw.run(lambda r: Buffer(S, H, K, R * epn, R, num_sms=num_sms, token_padding=8, B=B, world=lw.view(r)))
+    return lw, bufs
+
+
+def _plans(lw, bufs, R, S, H, K, E, device):
+    def body(r):
+        topk, tpe, gates = make_routing("biased", S, K, E, R, r, bias=1.5, seed=5, device=device)
+        x = torch.randn(S, H, device=device).to(torch.bfloat16)
+        return bufs[r].dispatch(x, gates, topk, tpe)[3]
+
+    return lw.run(body)
+
+
+TABLES = {
+    "holes_and_duplicates": lambda R, B, E, epn: [[(-1 if b == 1 else ((r + 1) % R) * epn) for b in range(B)] for r in range(R)],
+    "empty": lambda R, B, E, epn: [[-1] * B for _ in range(R)],
+    "fan_in": lambda R, B, E, epn: [[(0 if r != 0 else epn) for _ in range(B)] for r in range(R)],
+    "random": None,
+}
+
+
+def _table(name, R, B, E, epn):
+    if TABLES[name] is not None:
+        return torch.tensor(TABLES[name](R, B, E, epn), dtype=torch.int32)
+    g = torch.Generator().manual_seed(17)
+    t = torch.randint(-1, E, (R, B), generator=g).to(torch.int32)
+    return t
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("table", list(TABLES))
+@pytest.mark.parametrize("R", [2, 4])
+def test_prefetch_and_reduce_grad(device, table, R):
+    S, H, K, epn, B = 32, 64, 2, 4, 3
+    E, Hw, Hp = R * epn, 128, 256
+    lw, bufs = _world(R, device, S, H, K, epn, B)
+    plans = _plans(lw, bufs, R, S, H, K, E, device)
+    etc = _table(table, R, B, E, epn)
+
+    def expert(t, e):
+        return torch.full((Hw, Hp), float(10 * t + e % 7), dtype=torch.bfloat16)
+
+    def slot(t, src, b):
+        return torch.randn(Hw, Hp, generator=torch.Generator().manual_seed(1000 * t + src * B + b))
+
+    def grad0(t, e):
+        return torch.randn(Hw, Hp, generator=torch.Generator().manual_seed(77000 + 100 * t + e))
+
+    shared_red = [torch.zeros(R, B, Hw, Hp, dtype=torch.float32, device=device) for _ in range(3)]
+
+    def body(r):
+        plan = dataclasses.replace(plans[r], experts_to_copy=etc.to(device))
+        fulls = []
+        for t in range(3):
+            full = torch.stack([expert(t, e) for e in range(E)] + [torch.full((Hw, Hp), -123.0, dtype=torch.bfloat16)] * B)
+            fulls.append(full.to(device).contiguous())
+        bufs[r].prefetch_weight(plan, full_gate_weight=fulls[0], full_up_weight=fulls[1], full_down_weight=fulls[2])
+        grads = [torch.stack([grad0(t, e) for e in range(E)] + [torch.zeros(Hw, Hp)] * B).to(device) for t in range(3)]
+        for t in range(3):
+            for b in range(B):
+                shared_red[t][r, b].copy_(slot(t, r, b))
+        if device == "cuda":
+            torch.cuda.synchronize()
+        lw.view(r).step()
+        for _rep in range(2):  # the second call finds the consumed slots cleared and must add zeros
+            bufs[r].reduce_grad(plan, False, grads[0], grads[1], grads[2], shared_red[0], shared_red[1], shared_red[2])
+        if device == "cuda":
+            torch.cuda.synchronize()
+            bufs[r].check_status()
+        lw.view(r).step()
+        return [f.cpu() for f in fulls], [g.cpu() for g in grads]
+
+    res = lw.run(body)
+    for r in range(R):
+        fulls, grads = res[r]
+        for t in range(3):
+            for b in range(B):
+                e = int(etc[r, b])
+                want = expert(t, e) if e >= 0 else torch.full((Hw, Hp), -123.0, dtype=torch.bfloat16)
+                assert torch.equal(fulls[t][E + b], want), f"rank {r} tensor {t} slot {b}"
+            for e in range(E):
+                want = grad0(t, e)
+                if e // epn == r:
+                    for src in range(R):
+                        for b in range(B):
+                            if int(etc[src, b]) == e:
+                                want = want + slot(t, src, b)
+                assert torch.equal(grads[t][e], want), f"rank {r} tensor {t} expert {e}: reduce_grad not bitwise equal"
+    for t in range(3):
+        red = shared_red[t].cpu()
+        for r in range(R):
+            for b in range(B):
+                if int(etc[r, b]) >= 0:
+                    assert not bool(red[r, b].abs().max() > 0), "consumed slot not cleared"
+                else:
+                    assert torch.equal(red[r, b], slot(t, r, b)), "unused slot modified"
+    lw.run(lambda r: bufs[r].destroy())
+
+
+@pytest.mark.parametrize("device", DEVICES)
+def test_saved_plan_replay_leaves_weights_and_dedup_untouched(device):
+    R, S, H, K, epn, B = 2, 48, 32, 4, 2, 1
+    E = R * epn
+    lw, bufs = _world(R, device, S, H, K, epn, B)
+
+    def body(r):
+        buf = bufs[r]
+        ctx = buf._require_ctx()
+        topk, tpe, gates = make_routing("biased", S, K, E, R, r, bias=2.0, seed=9, device=device)
+        x = torch.randn(S, H, device=device).to(torch.bfloat16)
+        xn, wn, cu, plan = buf.dispatch(x, gates, topk, tpe)
+        snap = plan.clone()
+        wbuf = ctx["weights_buf_local"].clone()
+        x2 = (x.float() * 3).to(torch.bfloat16)
+        xn2, wn2, cu2, plan2 = buf.dispatch(x2, None, plan=snap)
+        assert wn2 is None and cu2 is None and plan2 is snap
+        occ = ctx["meta_buf"][r * ctx["meta_chunk_padded"] + ctx["SRC_INFO_OFF"]:][: ctx["NvS"]] >= 0
+        ok_rows = torch.equal((xn.float() * 3).to(torch.bfloat16)[occ], xn2[occ])
+        ok_w = torch.equal(ctx["weights_buf_local"], wbuf)
+        ok_plan = all(torch.equal(getattr(plan, f), getattr(snap, f)) for f in ("dst", "dup_groups", "dup_loffs", "dup_counts"))
+        o1, _, _ = buf.combine(snap, xn2, None)
+        o2, _, _ = buf.combine(snap, xn2, None, inter_rank_sync=True)
+        if device == "cuda":
+            torch.cuda.synchronize()
+            buf.check_status()
+        return ok_rows, ok_w, ok_plan, torch.equal(o1, o2)
+
+    for r, flags in enumerate(lw.run(body)):
+        assert all(flags), f"rank {r}: rows/weights/plan/combine checks {flags}"
+    lw.run(lambda r: bufs[r].destroy())
+
+
+@pytest.mark.parametrize("device", DEVICES)
+def test_api_rejects_bad_arguments(device):
+    lw, bufs = _world(1, device, S=8, H=16, K=2, epn=4, B=1)
+    buf = bufs[0]
+    topk, tpe, gates = make_routing("balanced", 8, 2, 4, 1, 0, device=device)
+    x = torch.randn(8, 16, device=device).to(torch.bfloat16)
+    with pytest.raises(AssertionError):
+        buf.dispatch(x.float(), gates, topk, tpe)
+    with pytest.raises(AssertionError):
+        buf.dispatch(x[:, :8], gates, topk, tpe)
+    with pytest.raises(AssertionError):
+        buf.dispatch(x, gates[:, :1].contiguous(), topk, tpe)
+    with pytest.raises(AssertionError):
+        buf.dispatch(x)  # neither routing nor plan
+    xn, wn, cu, plan = buf.dispatch(x, gates, topk, tpe)
+    with pytest.raises(AssertionError):
+        buf.combine(None, xn, wn)
+    with pytest.raises(AssertionError):
+        buf.combine(plan, xn[:-1], wn)
+    with pytest.raises(AssertionError):
+        buf.combine(plan, xn, wn, zero_copy=True)  # not the shard view
+    with pytest.raises(TypeError):
+        buf.combine(plan, xn, wn, hidden_sh=x)
+    buf.destroy()
+    assert buf.destroyed
+    with pytest.raises(AssertionError):
+        buf.dispatch(x, gates, topk, tpe)
+
+
+@pytest.mark.gpu
+def test_wait_that_nothing_satisfies_reports_timeout_and_buffer_recovers():
+    """A flag that no rank sets: the wait gives up after its budget, the kernel returns, the host
+    reads the status; after check_status() the same Buffer works again."""
+    from moonep_b200.constants import FLAG_GRAD_DONE
+    from moonep_b200.errors import MoonEPTimeoutError
+
+    lw, bufs = _world(1, "cuda", S=16, H=32, K=2, epn=4, B=1)
+    buf = bufs[0]
+    be = buf._require_ctx()["_backend"]
+    be.set_timeout_ms(200)
+    be.epoch[FLAG_GRAD_DONE] += 1  # an epoch nobody will ever signal
+    be.wait(FLAG_GRAD_DONE)
+    torch.cuda.synchronize()
+    with pytest.raises(MoonEPTimeoutError) as ei:
+        buf.check_status()
+    assert ei.value.kernel == "wait" and ei.value.peer == 0
+    be.epoch[FLAG_GRAD_DONE] -= 1
+    topk, tpe, gates = make_routing("balanced", 16, 2, 4, 1, 0, device="cuda")
+    x = torch.randn(16, 32, device="cuda").to(torch.bfloat16)
+    xn, wn, cu, plan = buf.dispatch(x, gates, topk, tpe)
+    out, wb, _ = buf.combine(plan, xn, wn)
+    torch.cuda.synchronize()
+    buf.check_status()
+    assert torch.equal(wb, gates)
+    buf.destroy()
