@@ -174,24 +174,47 @@ def run_steps(args, BufferCls, rank, n, reference=False):
         phases = {k: round(max_over_ranks(v, n), 1) for k, v in sorted(be.phase_times().items())}
         be.profile(False)
 
-    # end to end: inputs come from pinned host memory every step, a checksum goes back
-    cs_h = torch.empty(1, dtype=torch.float32).pin_memory()
-    dev_in = [torch.empty_like(t, device=dev) for t in pinned]
-    e2e_ev = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(args.steps)]
-    for i in range(2 + args.steps):
-        timed = i >= 2
-        if timed:
+    # end to end: every step copies its inputs from pinned host memory and sends a checksum of its
+    # result back to the host.  The copy of step i+1 runs on a second stream while step i computes
+    # (two input buffer sets), as a training or serving loop would do it.
+    K_e2e = args.steps
+    cs_h = torch.empty(K_e2e + 2, dtype=torch.float32).pin_memory()
+    sets = [[torch.empty_like(t, device=dev) for t in pinned] for _ in range(2)]
+    copy_stream = torch.cuda.Stream()
+    main = torch.cuda.current_stream()
+    ready = [torch.cuda.Event() for _ in range(2)]
+    free = [torch.cuda.Event() for _ in range(2)]
+
+    def issue_h2d(i):
+        k = i % 2
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(free[k])
+            for d, h in zip(sets[k], pinned):
+                d.copy_(h, non_blocking=True)
+            ready[k].record(copy_stream)
+
+    def e2e_loop(steps, base):
+        for k in range(2):
+            free[k].record(main)
+        issue_h2d(0)
+        for i in range(steps):
+            if i + 1 < steps:
+                issue_h2d(i + 1)
             flush.zero_()
-            e2e_ev[i - 2][0].record()
-        for d, h in zip(dev_in, pinned):
-            d.copy_(h, non_blocking=True)
-        out, wb, plan = step(*dev_in)
-        cs_h.copy_(out.float().abs().mean().reshape(1), non_blocking=True)
-        if timed:
-            e2e_ev[i - 2][1].record()
-        torch.cuda.synchronize()
+            main.wait_event(ready[i % 2])
+            out, wb, plan = step(*sets[i % 2])
+            free[i % 2].record(main)
+            cs_h[base + i : base + i + 1].copy_(out.sum(dtype=torch.float32).reshape(1), non_blocking=True)
+
+    e2e_loop(2, K_e2e)  # warm-up
     barrier_sync(n)
-    t_e2e = max_over_ranks(sum(e[0].elapsed_time(e[1]) for e in e2e_ev) / args.steps, n)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    e2e_loop(K_e2e, 0)
+    t1.record()
+    barrier_sync(n)
+    t_e2e = max_over_ranks(t0.elapsed_time(t1) / K_e2e, n)
+    assert bool(torch.isfinite(cs_h[:K_e2e]).all()), "end-to-end checksums are not finite"
     h2d = sum(t.numel() * t.element_size() for t in pinned)
 
     # bytes that cross to other ranks (primary rows only) for the bandwidth figures
