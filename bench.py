@@ -45,6 +45,11 @@ def parse_args():
     p.add_argument("--routing", default="softmax")
     p.add_argument("--staged", action="store_true", help="use the copying (non zero-copy) API paths")
     p.add_argument("--profile-phases", action="store_true", help="add per-kernel device times (phases_us)")
+    p.add_argument("--config", default="headline", choices=["headline", "skew", "sweep", "moe_step"],
+                   help="headline: S=4096,H=7168,K=8,E=256 softmax routing; skew: S=8192,H=4096,E=64,K=6 Zipf(1.2); "
+                        "sweep: S in {128..16384} with uniform routing, ours and NCCL; moe_step: SwiGLU MoE layer "
+                        "forward+backward+SGD with intermediate size --inter")  # fmt: skip
+    p.add_argument("--inter", type=int, default=2048)
     return p.parse_args()
 
 
@@ -268,12 +273,101 @@ def run_steps(args, BufferCls, rank, n, reference=False):
     return res
 
 
+def run_moe_step(args, rank, n):
+    """SwiGLU MoE layer training step: dispatch -> prefetch -> grouped GEMMs -> combine, backward with the
+    plan replayed, reduce_grad, SGD on the owned experts.  Device-timed, max over ranks."""
+    from moonep_b200 import Buffer
+    from moonep_b200.models.moe_layer import ExpertParallelMoE
+    from moonep_b200.models.routing import make_routing
+    from moonep_b200.utils.clocks import ClockSampler
+
+    S, H, K, E, inter = args.S, args.H, args.K, args.E, args.inter
+    dev = torch.device("cuda", torch.cuda.current_device())
+    buf = Buffer(S, H, K, E, n, num_sms=args.num_sms, token_padding=128)
+    layer = ExpertParallelMoE(buf, inter, init_std=0.02, seed=1)
+    topk, tpe, gates = make_routing(args.routing, S, K, E, n, rank, seed=2026, device=dev)
+    g = torch.Generator().manual_seed(7 + rank)
+    x = torch.randn(S, H, generator=g).to(torch.bfloat16).to(dev)
+    go = (torch.randn(S, H, generator=g) * 0.1).to(torch.bfloat16).to(dev)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+
+    def step():
+        out, saved = layer.forward(x, gates, topk, tpe)
+        mid.record()
+        dx, dg = layer.backward(saved, go)
+        layer.sgd_step(1e-3)
+        layer.zero_grad()
+        return out
+
+    mid = torch.cuda.Event(enable_timing=True)
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    buf.check_status()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    barrier_sync(n)
+    with ClockSampler(torch.cuda.current_device()) as clocks:
+        for i in range(args.steps):
+            flush.zero_()
+            ev[i][0].record()
+            mid = ev[i][1]
+            out = step()
+            ev[i][2].record()
+        barrier_sync(n)
+    t_f = max_over_ranks(sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps, n)
+    t_all = max_over_ranks(sum(e[0].elapsed_time(e[2]) for e in ev) / args.steps, n)
+    buf.check_status()
+    flops_fwd = 2.0 * S * K * H * inter * 3  # per rank, real rows
+    return {
+        "metric": "moe_layer_train_tokens_per_s", "value": n * S / (t_all / 1e3), "unit": "tokens/s", "n_gpus": n,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": t_all, "forward_ms": t_f,
+        "backward_ms": t_all - t_f, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic, random-init weights ~N(0,0.02)",
+        "config": {"model": "SwiGLU MoE layer (dispatch->prefetch->grouped GEMM->combine, backward with reduce_grad)",
+                   "S_per_rank": S, "H": H, "K": K, "E": E, "inter": inter, "parallelism": f"ep{n}",
+                   "routing": args.routing, "backward_gemms": "torch matmul per group (bf16)"},
+        "forward_tflops_per_gpu": flops_fwd / (t_f / 1e3) / 1e12, "finite": bool(torch.isfinite(out.float()).all()),
+        "clocks": clocks.summary(),
+    }  # fmt: skip
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
         reference_arm(args)
         return
     rank, local, world = init_dist(args.gpus)
+    if args.config == "skew":
+        args.S, args.H, args.E, args.K, args.routing = 8192, 4096, 64, 6, "zipf"
+    if args.config == "moe_step":
+        res = run_moe_step(args, rank, args.gpus)
+        if rank == 0:
+            res["impl"] = "ours"
+            print(json.dumps(res))
+        if args.gpus > 1:
+            import torch.distributed as dist
+
+            dist.destroy_process_group()
+        return
+    if args.config == "sweep":
+        from moonep_b200 import Buffer
+        from moonep_b200.bench.nccl_baseline import run_nccl_baseline
+
+        for S in (128, 512, 2048, 8192, 16384):
+            args.S = S
+            args.routing = "softmax"
+            ours = run_steps(args, Buffer, rank, args.gpus)
+            base = run_nccl_baseline(args, rank, args.gpus)
+            if rank == 0:
+                print(json.dumps({"S": S, "n_gpus": args.gpus, "ours_dispatch_us": ours["dispatch_us"],
+                                  "ours_combine_us": ours["combine_us"], "nccl_dispatch_us": base["dispatch_us"],
+                                  "nccl_combine_us": base["combine_us"],
+                                  "speedup_round_trip": base["ms_per_step"] / ours["ms_per_step"]}))  # fmt: skip
+        if args.gpus > 1:
+            import torch.distributed as dist
+
+            dist.destroy_process_group()
+        return
     if args.impl == "nccl":
         from moonep_b200.bench.nccl_baseline import run_nccl_baseline
 

@@ -358,8 +358,15 @@ class Buffer:
         gate_reduce_buffer=None,
         up_reduce_buffer=None,
         down_reduce_buffer=None,
+        *,
+        owner_local=False,
     ):
-        """Add the gradients of prefetched expert copies back into their owners' gradients."""
+        """Add the gradients of prefetched expert copies back into their owners' gradients.
+
+        ``full_*_grad`` are ``[>=E, H, H']`` fp32 indexed by global expert id (only this rank's experts
+        are touched).  With ``owner_local=True`` they are ``[E/R, H, H']`` and hold this rank's experts
+        only, which saves the memory of the other ranks' rows.
+        """
         ctx = self._require_ctx()
         assert isinstance(plan, MoonEPCommPlan), "reduce_grad: plan is required"
         grads = (full_gate_grad, full_up_grad, full_down_grad)
@@ -368,7 +375,8 @@ class Buffer:
 
         def run():
             E = ctx["E"]
-            ctx["_backend"].reduce_grad(plan.experts_to_copy, [g[:E] for g in grads], list(bufs))
+            gs = list(grads) if owner_local else [g[:E] for g in grads]
+            ctx["_backend"].reduce_grad(plan.experts_to_copy, gs, list(bufs), local=owner_local)
 
         if not async_finish:
             run()

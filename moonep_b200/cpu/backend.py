@@ -230,10 +230,11 @@ class CpuBackend:
                 if e >= 0:
                     dst[b].copy_(src[e])
 
-    def reduce_grad(self, experts_to_copy, grads, reduce_buffers):
+    def reduce_grad(self, experts_to_copy, grads, reduce_buffers, local=False):
         c = self.ctx
         E, R, rank = c["E"], c["R"], c["rank"]
         epn = E // R
+        off = rank * epn if local else 0
         etc = experts_to_copy.tolist()
         Bn = experts_to_copy.shape[1]
         self.world.step()
@@ -242,7 +243,7 @@ class CpuBackend:
                 for b in range(Bn):
                     e = etc[src][b]
                     if e >= 0 and rank * epn <= e < (rank + 1) * epn:
-                        grad[e] += red[src, b]
+                        grad[e - off] += red[src, b]
         self.world.step()
         for red in reduce_buffers:
             for b in range(Bn):

@@ -44,6 +44,7 @@ class ExpertParallelMoE:
         self.w_up = create_full_expert_weight(E, B, I, H, w)
         self.w_down = create_full_expert_weight(E, B, H, I, w)
         self.mapped = w.is_cuda and not w.emulated and w.size > 1
+        self.matmul_dtype = torch.bfloat16 if w.is_cuda else torch.float32
         dev = ctx["device"]
         for t, (wt, shape) in enumerate(((self.w_gate, (I, H)), (self.w_up, (I, H)), (self.w_down, (H, I)))):
             for e in range(E):
@@ -51,10 +52,11 @@ class ExpertParallelMoE:
                     continue  # a peer's expert: its owner initialises it
                 g = torch.Generator().manual_seed(seed * 1_000_003 + t * 10_007 + e)
                 wt[e].copy_((torch.randn(*shape, generator=g) * init_std).to(torch.bfloat16).to(dev))
-        # fp32 gradients of every group this rank can compute, and the slots that travel to the owners
-        self.g_gate = torch.zeros(E + B, I, H, dtype=torch.float32, device=dev)
-        self.g_up = torch.zeros(E + B, I, H, dtype=torch.float32, device=dev)
-        self.g_down = torch.zeros(E + B, H, I, dtype=torch.float32, device=dev)
+        # fp32 gradients of the groups this rank computes: its own experts [0, epn), then the B prefetch slots
+        n_g = self.epn + B
+        self.g_gate = torch.zeros(n_g, I, H, dtype=torch.float32, device=dev)
+        self.g_up = torch.zeros(n_g, I, H, dtype=torch.float32, device=dev)
+        self.g_down = torch.zeros(n_g, H, I, dtype=torch.float32, device=dev)
         self._red_full = [create_nvl_dist_tensor([B, d0, d1], torch.float32, w, pad_dim0=False)
                           for d0, d1 in ((I, H), (I, H), (H, I))]  # fmt: skip
         self.red = [view_nvl_dist_rows(t, self.R, B) for t in self._red_full]
@@ -82,32 +84,49 @@ class ExpertParallelMoE:
         dgate_nvs = torch.zeros_like(w_nvs)
         ends = cu.tolist()
         start = 0
+        own0 = self.rank * self.epn
         for g in range(E + B):
             end = int(ends[g])
             if end > start:
-                xs, dy = x_nvs[start:end].float(), dy_nvs[start:end].float()
-                wg, wu, wd = self.w_gate[g].float(), self.w_up[g].float(), self.w_down[g].float()
-                a, u = xs @ wg.t(), xs @ wu.t()
+                if g >= E:
+                    gi = self.epn + (g - E)
+                elif own0 <= g < own0 + self.epn:
+                    gi = g - own0
+                else:
+                    raise NotImplementedError(
+                        "a remote expert without a prefetch slot received tokens (more remote experts than B); "
+                        "its weight gradient has no way home — raise B"
+                    )
+                md = self.matmul_dtype  # bf16 tensor-core matmuls on CUDA, fp32 on the host
+
+                def mm(p, q):
+                    return (p.to(md) @ q.to(md)).float()
+
+                xs, dy = x_nvs[start:end], dy_nvs[start:end].float()
+                wg, wu, wd = self.w_gate[g], self.w_up[g], self.w_down[g]
+                a, u = mm(xs, wg.t()), mm(xs, wu.t())
                 hs = torch.nn.functional.silu(a) * u
-                y = hs @ wd.t()
+                y = mm(hs, wd.t())
                 wr = w_nvs[start:end, None]
                 dgate_nvs[start:end] = (dy * y).sum(dim=1)
                 dys = dy * wr
-                self.g_down[g] += dys.t() @ hs
-                dh = dys @ wd
+                self.g_down[gi] += mm(dys.t(), hs)
+                dh = mm(dys, wd)
                 sig = torch.sigmoid(a)
                 da = dh * u * (sig * (1 + a * (1 - sig)))
                 du = dh * (a * sig)
-                self.g_gate[g] += da.t() @ xs
-                self.g_up[g] += du.t() @ xs
-                dx_nvs[start:end] = (da @ wg + du @ wu).to(torch.bfloat16)
+                self.g_gate[gi] += mm(da.t(), xs)
+                self.g_up[gi] += mm(du.t(), xs)
+                dx_nvs[start:end] = (mm(da, wg) + mm(du, wu)).to(torch.bfloat16)
             start = max(start, end)
         dx, dgates, _ = buf.combine(plan, dx_nvs, dgate_nvs, zero_copy=False)
         # gradients of prefetched copies go home
+        epn = self.epn
         for red, g in zip(self.red, (self.g_gate, self.g_up, self.g_down)):
-            red[self.rank].copy_(g[E:])
-            g[E:].zero_()
-        buf.reduce_grad(plan, False, self.g_gate, self.g_up, self.g_down, self.red[0], self.red[1], self.red[2])
+            red[self.rank].copy_(g[epn:])
+            g[epn:].zero_()
+        buf.reduce_grad(plan, False, self.g_gate[:epn], self.g_up[:epn], self.g_down[:epn], self.red[0], self.red[1],
+                        self.red[2], owner_local=True)  # fmt: skip
         return dx, dgates
 
     def zero_grad(self):
@@ -116,14 +135,13 @@ class ExpertParallelMoE:
 
     def owner_grads(self):
         """fp32 gradients of the experts this rank owns: three tensors ``[E/R, ...]``."""
-        s = slice(self.rank * self.epn, (self.rank + 1) * self.epn)
-        return self.g_gate[s], self.g_up[s], self.g_down[s]
+        return self.g_gate[: self.epn], self.g_up[: self.epn], self.g_down[: self.epn]
 
     def sgd_step(self, lr: float):
         """Plain SGD on the owned experts (enough for a benchmark step)."""
         s = slice(self.rank * self.epn, (self.rank + 1) * self.epn)
         for w, g in ((self.w_gate, self.g_gate), (self.w_up, self.g_up), (self.w_down, self.g_down)):
-            w[s].add_((-lr * g[s]).to(torch.bfloat16))
+            w[s].add_((-lr * g[: self.epn]).to(torch.bfloat16))
 
 
 def dense_reference(x, gates, topk, w_gate, w_up, w_down):

@@ -286,11 +286,12 @@ class CudaBackend:
         ws = [w for w in weights if w is not None]
         if B == 0 or not ws or experts_to_copy.numel() == 0:
             return
-        H, Hp = int(ws[0].shape[1]), int(ws[0].shape[2])
+        per = int(ws[0].shape[1]) * int(ws[0].shape[2])
         for w in ws:
             assert w.dtype == torch.bfloat16 and w.is_contiguous(), "weights must be contiguous bf16"
-            assert tuple(w.shape) == (E + B, H, Hp), f"weight shape {tuple(w.shape)} != {(E + B, H, Hp)}"
-        assert H % 128 == 0 and Hp % 128 == 0, f"H and H' must be multiples of 128, got ({H}, {Hp})"
+            assert w.ndim == 3 and w.shape[0] == E + B, f"weight shape {tuple(w.shape)}: dim 0 must be E+B={E + B}"
+            assert int(w.shape[1]) * int(w.shape[2]) == per, "gate, up and down must have equally sized experts"
+            assert w.shape[1] % 128 == 0 and w.shape[2] % 128 == 0, f"H and H' must be multiples of 128, got {tuple(w.shape[1:])}"
         assert experts_to_copy.dtype == torch.int32 and experts_to_copy.is_contiguous()
         row = experts_to_copy[c["rank"]]
         self.prefetch_launch([w[:E] for w in ws], [w[E:] for w in ws], row)
@@ -304,16 +305,19 @@ class CudaBackend:
             return
         for s, d in zip(remote_experts, prefetch_buffers):
             assert s.dtype == torch.bfloat16 and s.is_contiguous() and d.dtype == torch.bfloat16 and d.is_contiguous()
-            assert tuple(s.shape) == (nexp, H, Hp) and tuple(d.shape) == (nslots, H, Hp)
+            assert s.shape[0] == nexp and d.shape[0] == nslots and s.shape[1:] == d.shape[1:]
+            assert int(s.shape[1]) * int(s.shape[2]) == H * Hp, "all tensors must have equally sized experts"
         assert experts_row.dtype == torch.int32 and experts_row.is_contiguous() and experts_row.numel() == nslots
         assert H % 128 == 0 and Hp % 128 == 0, f"H and H' must be multiples of 128, got ({H}, {Hp})"
         src = (ctypes.c_void_p * n)(*[t.data_ptr() for t in remote_experts])
         dst = (ctypes.c_void_p * n)(*[t.data_ptr() for t in prefetch_buffers])
         self._call("moonep_prefetch", src, dst, n, _ptr(experts_row), H * Hp, nslots, nexp, self.path, _stream())
 
-    def reduce_grad(self, experts_to_copy, grads, reduce_buffers):
+    def reduce_grad(self, experts_to_copy, grads, reduce_buffers, local=False):
+        """``local=True``: ``grads[i]`` holds only this rank's experts, ``[E/R, H, H']``."""
         c = self.ctx
         R, E = c["R"], c["E"]
+        n_grad_experts = c["epn"] if local else E
         if experts_to_copy.numel() == 0 or any(r.numel() == 0 for r in reduce_buffers):
             return
         Bc = int(experts_to_copy.shape[1])
@@ -323,10 +327,14 @@ class CudaBackend:
         for g, r in zip(grads, reduce_buffers):
             assert g.dtype == torch.float32 and g.is_contiguous() and g.ndim == 3
             assert r.dtype == torch.float32 and r.is_contiguous() and r.ndim == 4
-            assert tuple(g.shape) == (E, H, Hp) and tuple(r.shape) == (R, Bc, H, Hp)
-        assert H % 128 == 0 and Hp % 128 == 0, f"H and H' must be multiples of 128, got ({H}, {Hp})"
+            assert g.shape[0] == n_grad_experts and tuple(r.shape[:2]) == (R, Bc) and g.shape[1:] == r.shape[2:]
+            assert int(g.shape[1]) * int(g.shape[2]) == H * Hp, "all tensors must have equally sized experts"
+            assert g.shape[1] % 128 == 0 and g.shape[2] % 128 == 0, f"H and H' must be multiples of 128, got {tuple(g.shape[1:])}"
         n = len(grads)
-        ga = (ctypes.c_void_p * n)(*[g.data_ptr() for g in grads])
+        # the kernel indexes gradients by global expert id but only touches this rank's experts, so an
+        # owner-local tensor is passed with its base moved back by the experts of the lower ranks
+        shift = c["rank"] * c["epn"] * H * Hp * 4 if local else 0
+        ga = (ctypes.c_void_p * n)(*[g.data_ptr() - shift for g in grads])
         ra = (ctypes.c_void_p * n)(*[r.data_ptr() for r in reduce_buffers])
         self.signal(FLAG_GRAD_READY)
         ready, done = self.epoch[FLAG_GRAD_READY], self._next(FLAG_GRAD_DONE)
