@@ -283,7 +283,8 @@ def run_moe_step(args, rank, n):
 
     S, H, K, E, inter = args.S, args.H, args.K, args.E, args.inter
     dev = torch.device("cuda", torch.cuda.current_device())
-    buf = Buffer(S, H, K, E, n, num_sms=args.num_sms, token_padding=128)
+    slots = min(E // n, 32)  # prefetch slots per rank; bounds weights + gradients + reduce buffers to ~25 GB
+    buf = Buffer(S, H, K, E, n, num_sms=args.num_sms, token_padding=128, B=slots)
     layer = ExpertParallelMoE(buf, inter, init_std=0.02, seed=1)
     topk, tpe, gates = make_routing(args.routing, S, K, E, n, rank, seed=2026, device=dev)
     g = torch.Generator().manual_seed(7 + rank)

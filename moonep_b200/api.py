@@ -12,8 +12,8 @@ Typical training step::
 Parity: reference ``moonep_td/api.py:187-498`` (constructor signature, return
 tuples, ``async_finish`` events, ``zero_copy`` aliasing rules, ``destroy``).
 Differences by design: a fresh dispatch needs no separate inter-rank barrier
-(the planner's first exchange doubles as one), no host synchronisation happens
-inside any operation, and the non-zero-copy paths copy only rows that hold data.
+(the planner's first exchange doubles as one) and no host synchronisation happens
+inside any operation.
 """
 
 from __future__ import annotations

@@ -204,10 +204,70 @@ def scenario_weights(rank, R, dev):
         print("  prefetch + reduce_grad ok", flush=True)
 
 
+def scenario_moe_layer(rank, R, dev):
+    """SwiGLU MoE layer forward/backward on real peer-mapped weights against a dense fp32 reference."""
+    from moonep_b200.models.moe_layer import ExpertParallelMoE, dense_reference
+    from moonep_b200.models.routing import make_routing
+
+    S, H, I, K, epn, B = 96, 256, 256, 2, 16, 8
+    E = R * epn
+    buf = Buffer(S, H, K, E, R, num_sms=8, token_padding=128, B=B)
+    layer = ExpertParallelMoE(buf, I, init_std=0.05, seed=3)
+    data = []
+    for r in range(R):
+        topk, tpe, gates = make_routing("biased", S, K, E, R, r, bias=2.0, seed=11)
+        g = torch.Generator().manual_seed(100 + r)
+        x = (torch.randn(S, H, generator=g) * 0.5).to(torch.bfloat16)
+        go = (torch.randn(S, H, generator=g) * 0.5).to(torch.bfloat16)
+        data.append((x, gates, topk, tpe, go))
+    x, gates, topk, tpe, go = (t.to(dev) for t in data[rank])
+    for it in range(2):  # second pass: same inputs, gradients were zeroed, weights unchanged
+        out, saved = layer.forward(x, gates, topk, tpe)
+        dx, dgates = layer.backward(saved, go)
+        barrier(dev)
+        if dev.type == "cuda":
+            buf.check_status()
+        grads = [g.cpu().clone() for g in layer.owner_grads()]
+        layer.zero_grad()
+        barrier(dev)
+    mine = (out.cpu(), dx.cpu(), dgates.cpu(), grads)
+    # every rank holds (or maps) all experts: take the full weights for the reference
+    wg = layer.w_gate[:E].float().cpu().requires_grad_(True)
+    wu = layer.w_up[:E].float().cpu().requires_grad_(True)
+    wd = layer.w_down[:E].float().cpu().requires_grad_(True)
+    if dev.type == "cpu":  # host worlds have no peer mapping: every rank initialised all experts itself
+        pass
+    ref = None
+    for r in range(R):
+        xr = data[r][0].float().requires_grad_(True)
+        gr = data[r][1].clone().requires_grad_(True)
+        o = dense_reference(xr, gr, data[r][2], wg, wu, wd)
+        o.backward(data[r][4].float())
+        if r == rank:
+            ref = (o.detach(), xr.grad, gr.grad)
+
+    def close(a, b, what, tol=4e-2):
+        err = (a.float() - b.float()).abs().max().item()
+        scale = max(1e-3, b.float().abs().max().item())
+        assert err <= tol * scale, f"moe layer rank {rank} {what}: max abs err {err} vs scale {scale}"
+
+    close(mine[0], ref[0], "output")
+    close(mine[1], ref[1], "grad_x")
+    close(mine[2], ref[2], "grad_gates")
+    sl = slice(rank * epn, (rank + 1) * epn)
+    close(mine[3][0], wg.grad[sl], "grad W_gate")
+    close(mine[3][1], wu.grad[sl], "grad W_up")
+    close(mine[3][2], wd.grad[sl], "grad W_down")
+    barrier(dev)
+    buf.destroy()
+    if rank == 0:
+        print("  moe layer ok", flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--backend", default="gloo", choices=["gloo", "nccl"])
-    ap.add_argument("--scenarios", default="round_trips,plan_reuse,weights")
+    ap.add_argument("--scenarios", default="round_trips,plan_reuse,weights,moe_layer")
     args = ap.parse_args()
     rank = int(os.environ["RANK"])
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -227,6 +287,8 @@ def main():
         scenario_plan_reuse(rank, R, dev)
     if "weights" in todo:
         scenario_weights(rank, R, dev)
+    if "moe_layer" in todo:
+        scenario_moe_layer(rank, R, dev)
     barrier(dev)
     print(f"WORKER OK rank {rank}", flush=True)
     dist.destroy_process_group()
