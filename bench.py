@@ -296,7 +296,7 @@ def run_moe_step(args, rank, n):
         out, saved = layer.forward(x, gates, topk, tpe)
         mid.record()
         dx, dg = layer.backward(saved, go)
-        layer.sgd_step(1e-3)
+        layer.sgd_step(1e-5)
         layer.zero_grad()
         return out
 
@@ -326,7 +326,7 @@ def run_moe_step(args, rank, n):
         "data": "synthetic, random-init weights ~N(0,0.02)",
         "config": {"model": "SwiGLU MoE layer (dispatch->prefetch->grouped GEMM->combine, backward with reduce_grad)",
                    "S_per_rank": S, "H": H, "K": K, "E": E, "inter": inter, "parallelism": f"ep{n}",
-                   "routing": args.routing, "backward_gemms": "torch matmul per group (bf16)"},
+                   "routing": args.routing, "backward_gemms": "activation grads: tcgen05 grouped GEMM; weight grads: torch matmul per group (bf16)"},
         "forward_tflops_per_gpu": flops_fwd / (t_f / 1e3) / 1e12, "finite": bool(torch.isfinite(out.float()).all()),
         "clocks": clocks.summary(),
     }  # fmt: skip

@@ -64,6 +64,8 @@ struct GemmArgs {
   int ldo;           // row stride of out in elements
   int mode;
   int rows_cap;      // rows of X
+  const int* group_map;  // [G] weight slot of every group, or null for the identity
+  int w_slots;           // number of weight slots (rows of W = w_slots * n_per_group)
 };
 
 __device__ __forceinline__ void gemm_fail(const GemmArgs& a, int where, int x, int y) {
@@ -197,7 +199,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           const int mid = (lo + hi) >> 1;
           if (a.cu_seqlens[mid] > row0) hi = mid; else lo = mid + 1;
         }
-        const int wrow0 = lo * a.n_per_group + nb * b_rows_per_tile;
+        int wslot = a.group_map != nullptr ? a.group_map[lo] : lo;
+        if (wslot < 0 || wslot >= a.w_slots) wslot = 0;  // a group without weights here: result is meaningless but in bounds
+        const int wrow0 = wslot * a.n_per_group + nb * b_rows_per_tile;
         for (int kb = 0; kb < a.k_blocks; ++kb) {
           if (!mbar_wait(s_empty + stage, phase ^ 1u, a.timeout_ns)) {
             gemm_fail(a, 1, stage, kb);
@@ -386,9 +390,12 @@ using namespace moonep;
 // x: [rows_cap, K] bf16.  w0 (and w1 for SwiGLU): [G, n_per_group, K] bf16.  out: [rows_cap, n_out] bf16 with
 // n_out = n_per_group (plain, scale) or n_per_group (swiglu: gate and up each have n_per_group rows).
 // cu_seqlens: [G] int32 inclusive padded ends (multiples of 128).  mode: 0 plain, 1 swiglu, 2 scale by row_scale.
+// group_map (optional): [G] int32, weight slot of every group when w holds only w_slots < G experts.
 extern "C" int moonep_grouped_gemm(const void* x, const void* w0, const void* w1, void* out, const float* row_scale,
                                    const int* cu_seqlens, int G, int rows_cap, int K, int n_per_group, int mode,
-                                   int* status, long long timeout_ms, int num_sms, void* stream) {
+                                   int* status, long long timeout_ms, int num_sms, const int* group_map, int w_slots,
+                                   void* stream) {
+  if (group_map == nullptr || w_slots <= 0) w_slots = G;
   if (K % BK != 0 || K <= 0) {
     set_error("moonep_grouped_gemm: K must be a positive multiple of 64");
     return 1;
@@ -404,8 +411,9 @@ extern "C" int moonep_grouped_gemm(const void* x, const void* w0, const void* w1
   }
   CUtensorMap ta, tb0, tb1;
   if (int rc = make_tmap(&ta, x, (unsigned long long)rows_cap, (unsigned long long)K, BM)) return rc;
-  if (int rc = make_tmap(&tb0, w0, (unsigned long long)G * n_per_group, (unsigned long long)K, 128)) return rc;
-  if (int rc = make_tmap(&tb1, mode == kSwiglu ? w1 : w0, (unsigned long long)G * n_per_group, (unsigned long long)K, 128))
+  if (int rc = make_tmap(&tb0, w0, (unsigned long long)w_slots * n_per_group, (unsigned long long)K, 128)) return rc;
+  if (int rc = make_tmap(&tb1, mode == kSwiglu ? w1 : w0, (unsigned long long)w_slots * n_per_group,
+                         (unsigned long long)K, 128))
     return rc;
   GemmArgs a;
   a.out = (uint16_t*)out;
@@ -420,6 +428,8 @@ extern "C" int moonep_grouped_gemm(const void* x, const void* w0, const void* w1
   a.ldo = n_per_group;
   a.mode = mode;
   a.rows_cap = rows_cap;
+  a.group_map = group_map;
+  a.w_slots = w_slots;
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

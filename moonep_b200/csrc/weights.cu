@@ -191,16 +191,17 @@ __global__ void __launch_bounds__(512)
     grad_clear_kernel(const MoonepDevCtx c, const TensorSet ts, const int* __restrict__ etc, int Bcols, long long elems,
                       int wait_epoch) {
   if (!block_wait_flags(c, MOONEP_FLAG_GRAD_DONE, wait_epoch, MOONEP_K_GRAD_CLEAR)) return;
+  // one (tensor, slot) pair at a time; inside a slot the CTAs stride over 16-byte vectors, so there is no
+  // 64-bit division per element and every CTA streams contiguous memory
   const long long nvec = elems / 4;
-  const long long total = (long long)ts.n * Bcols * nvec;
   const int4 z = make_int4(0, 0, 0, 0);
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-       i += (long long)gridDim.x * blockDim.x) {
-    const long long v = i % nvec;
-    const int b = (int)((i / nvec) % Bcols);
-    const int t = (int)(i / (nvec * Bcols));
-    if (etc[c.rank * Bcols + b] < 0) continue;
-    st16(reinterpret_cast<int4*>(ts.q[t]) + ((long long)c.rank * Bcols + b) * nvec + v, z);
+  for (int t = 0; t < ts.n; ++t) {
+    for (int b = 0; b < Bcols; ++b) {
+      if (etc[c.rank * Bcols + b] < 0) continue;
+      int4* base = reinterpret_cast<int4*>(ts.q[t]) + ((long long)c.rank * Bcols + b) * nvec;
+      for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += (long long)gridDim.x * blockDim.x)
+        st16(base + v, z);
+    }
   }
 }
 
@@ -266,7 +267,9 @@ extern "C" int moonep_grad_reduce(void* ctx, float* const* grads, float* const* 
   }
   if (phase == 2) {
     if (Bcols == 0) return 0;
-    grad_clear_kernel<<<grid, 512, 0, st>>>(c, ts, experts_to_copy, Bcols, elems, epoch_done);
+    // the slots are this rank's own memory: all SMs may help
+    grad_clear_kernel<<<imax(1, imin(c.local_sms, h->sm_count)), 512, 0, st>>>(c, ts, experts_to_copy, Bcols, elems,
+                                                                            epoch_done);
     return check_launch("grad_clear_kernel");
   }
   set_error("moonep_grad_reduce: phase must be 1 (accumulate) or 2 (clear)");

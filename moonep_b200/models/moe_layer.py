@@ -19,7 +19,8 @@ prefetch slot ``b``.  On multi-GPU worlds ``[:E]`` is peer mapped (``create_full
 remote expert that did not get a prefetch slot is read in place over NVLink.
 
 Usage pattern of the reference's Buffer API: reference ``README.md:46-48`` and ``tests/test_e2e.py:201-431``.
-The backward GEMMs run as per-group torch matmuls in this version.
+In the backward pass the activation gradients run on the same grouped GEMM (with per-call K-major copies of
+the local experts); the weight gradients are per-group matmuls.
 """
 
 from __future__ import annotations
@@ -28,6 +29,7 @@ import torch
 
 from ..api import Buffer
 from ..ops.grouped_gemm import grouped_gemm
+from ..ops.moe_ops import sgd_update, swiglu_bwd, transpose_experts
 from ..parallel.symm import create_full_expert_weight, create_nvl_dist_tensor, view_nvl_dist_rows
 
 
@@ -45,6 +47,10 @@ class ExpertParallelMoE:
         self.w_down = create_full_expert_weight(E, B, H, I, w)
         self.mapped = w.is_cuda and not w.emulated and w.size > 1
         self.matmul_dtype = torch.bfloat16 if w.is_cuda else torch.float32
+        gm = torch.full((E + B,), -1, dtype=torch.int32)
+        gm[self.rank * self.epn : (self.rank + 1) * self.epn] = torch.arange(self.epn, dtype=torch.int32)
+        gm[E:] = self.epn + torch.arange(B, dtype=torch.int32)
+        self.group_map = gm.to(ctx["device"])  # group -> index among (own experts, prefetch slots)
         dev = ctx["device"]
         for t, (wt, shape) in enumerate(((self.w_gate, (I, H)), (self.w_up, (I, H)), (self.w_down, (H, I)))):
             for e in range(E):
@@ -52,11 +58,13 @@ class ExpertParallelMoE:
                     continue  # a peer's expert: its owner initialises it
                 g = torch.Generator().manual_seed(seed * 1_000_003 + t * 10_007 + e)
                 wt[e].copy_((torch.randn(*shape, generator=g) * init_std).to(torch.bfloat16).to(dev))
-        # fp32 gradients of the groups this rank computes: its own experts [0, epn), then the B prefetch slots
-        n_g = self.epn + B
+        # fp32 gradients of the experts this rank owns; gradients of prefetched copies are written into the
+        # reduce buffers and added to their owners' gradients by reduce_grad
+        n_g = self.epn
         self.g_gate = torch.zeros(n_g, I, H, dtype=torch.float32, device=dev)
         self.g_up = torch.zeros(n_g, I, H, dtype=torch.float32, device=dev)
         self.g_down = torch.zeros(n_g, H, I, dtype=torch.float32, device=dev)
+        self._fresh = True
         self._red_full = [create_nvl_dist_tensor([B, d0, d1], torch.float32, w, pad_dim0=False)
                           for d0, d1 in ((I, H), (I, H), (H, I))]  # fmt: skip
         self.red = [view_nvl_dist_rows(t, self.R, B) for t in self._red_full]
@@ -75,73 +83,102 @@ class ExpertParallelMoE:
         return out, saved
 
     # -- backward ------------------------------------------------------------------------------
+    def _local_transposed(self, weights):
+        """K-major copies of the experts this rank owns and of its prefetch slots for the activation-gradient
+        GEMMs: ``[epn+B, d1, sum(d0)]`` with the transposes of ``weights`` side by side along the last axis."""
+        E, epn, own0, B = self.E, self.epn, self.rank * self.epn, self.B
+        d1 = int(weights[0].shape[2])
+        width = sum(int(w.shape[1]) for w in weights)
+        out = torch.empty(epn + B, d1, width, dtype=weights[0].dtype, device=weights[0].device)
+        col = 0
+        for w in weights:
+            transpose_experts(w[own0 : own0 + epn], out[:epn], col)
+            if B:
+                transpose_experts(w[E:], out[epn:], col)
+            col += int(w.shape[1])
+        return out
+
+    def _grad_target(self, t, g):
+        """Where the weight gradient of group ``g`` of tensor ``t`` goes: this rank's gradient for an owned
+        expert, the reduce-buffer slot that travels to the owner for a prefetched copy."""
+        epn, own0 = self.epn, self.rank * self.epn
+        if g >= self.E:
+            return self.red[t][self.rank, g - self.E], True
+        if own0 <= g < own0 + epn:
+            return (self.g_gate, self.g_up, self.g_down)[t][g - own0], False
+        raise NotImplementedError(
+            "a remote expert without a prefetch slot received tokens (more remote experts than B); "
+            "its weight gradient has no way home — raise B"
+        )
+
     def backward(self, saved, grad_out):
-        """Returns ``(grad_x[S,H], grad_gates[S,K])`` and accumulates the weight gradients."""
-        buf, E, B = self.buffer, self.E, self.B
-        plan, cu, x_nvs, w_nvs, h = saved["plan"], saved["cu"], saved["x_nvs"], saved["w_nvs"], saved["h"]
+        """Returns ``(grad_x[S,H], grad_gates[S,K])`` and accumulates the weight gradients.
+
+        Activation gradients and the recomputed pre-activations run on the grouped GEMM (K-major copies of
+        the local experts are rebuilt per call because the weights change every step); the weight gradients,
+        whose contraction runs over the rows of a group, are per-group matmuls written straight into the
+        gradient of an owned expert or into the reduce-buffer slot of a prefetched copy.
+        """
+        buf, E, B, epn, I = self.buffer, self.E, self.B, self.epn, self.I
+        ctx = buf._require_ctx()
+        plan, cu, x_nvs, w_nvs = saved["plan"], saved["cu"], saved["x_nvs"], saved["w_nvs"]
         dy_nvs, _, _, _ = buf.dispatch(grad_out.contiguous(), None, plan=plan, zero_copy=True)
-        dx_nvs = dy_nvs  # rewritten in place, group by group
-        dgate_nvs = torch.zeros_like(w_nvs)
+        gmap = self.group_map
+        rows = int(x_nvs.shape[0])
+        dev = x_nvs.device
+        a = grouped_gemm(x_nvs, self.w_gate, cu)
+        u = grouped_gemm(x_nvs, self.w_up, cu)
+        g = grouped_gemm(dy_nvs, self._local_transposed([self.w_down]), cu, group_map=gmap)  # dy @ W_down, unscaled
+        dadu = torch.empty(rows, 2 * I, dtype=torch.bfloat16, device=dev)
+        hsw = torch.empty(rows, I, dtype=torch.bfloat16, device=dev)
+        dgate_nvs = ctx["weights_buf_local"].view(torch.float32)  # gate gradients ride the weights channel home
+        swiglu_bwd(a, u, g, w_nvs, cu[-1:], dadu, hsw, dgate_nvs)
+        del a, u, g
         ends = cu.tolist()
         start = 0
-        own0 = self.rank * self.epn
-        for g in range(E + B):
-            end = int(ends[g])
+        md = self.matmul_dtype
+        visited = set()
+        for grp in range(E + B):
+            end = int(ends[grp])
             if end > start:
-                if g >= E:
-                    gi = self.epn + (g - E)
-                elif own0 <= g < own0 + self.epn:
-                    gi = g - own0
-                else:
-                    raise NotImplementedError(
-                        "a remote expert without a prefetch slot received tokens (more remote experts than B); "
-                        "its weight gradient has no way home — raise B"
-                    )
-                md = self.matmul_dtype  # bf16 tensor-core matmuls on CUDA, fp32 on the host
-
-                def mm(p, q):
-                    return (p.to(md) @ q.to(md)).float()
-
-                xs, dy = x_nvs[start:end], dy_nvs[start:end].float()
-                wg, wu, wd = self.w_gate[g], self.w_up[g], self.w_down[g]
-                a, u = mm(xs, wg.t()), mm(xs, wu.t())
-                hs = torch.nn.functional.silu(a) * u
-                y = mm(hs, wd.t())
-                wr = w_nvs[start:end, None]
-                dgate_nvs[start:end] = (dy * y).sum(dim=1)
-                dys = dy * wr
-                self.g_down[gi] += mm(dys.t(), hs)
-                dh = mm(dys, wd)
-                sig = torch.sigmoid(a)
-                da = dh * u * (sig * (1 + a * (1 - sig)))
-                du = dh * (a * sig)
-                self.g_gate[gi] += mm(da.t(), xs)
-                self.g_up[gi] += mm(du.t(), xs)
-                dx_nvs[start:end] = (mm(da, wg) + mm(du, wu)).to(torch.bfloat16)
+                sl = slice(start, end)
+                xs, dys = x_nvs[sl].to(md), dy_nvs[sl].to(md)
+                parts = (dadu[sl, :I].to(md).t() @ xs, dadu[sl, I:].to(md).t() @ xs, dys.t() @ hsw[sl].to(md))
+                for t, val in enumerate(parts):
+                    tgt, is_slot = self._grad_target(t, grp)
+                    if is_slot or self._fresh:
+                        tgt.copy_(val)
+                    else:
+                        tgt.add_(val)
+                if grp < E:
+                    visited.add(grp - self.rank * epn)
             start = max(start, end)
-        dx, dgates, _ = buf.combine(plan, dx_nvs, dgate_nvs, zero_copy=False)
-        # gradients of prefetched copies go home
-        epn = self.epn
-        for red, g in zip(self.red, (self.g_gate, self.g_up, self.g_down)):
-            red[self.rank].copy_(g[epn:])
-            g[epn:].zero_()
-        buf.reduce_grad(plan, False, self.g_gate[:epn], self.g_up[:epn], self.g_down[:epn], self.red[0], self.red[1],
-                        self.red[2], owner_local=True)  # fmt: skip
+        if self._fresh:  # zero_grad() only set a flag: clear the owned experts that got no rows
+            for le in range(epn):
+                if le not in visited:
+                    for gt in (self.g_gate, self.g_up, self.g_down):
+                        gt[le].zero_()
+            self._fresh = False
+        grouped_gemm(dadu, self._local_transposed([self.w_gate, self.w_up]), cu, group_map=gmap, out=dy_nvs)
+        dx, dgates, _ = buf.combine(plan, dy_nvs, dgate_nvs, zero_copy=True)
+        buf.reduce_grad(plan, False, self.g_gate, self.g_up, self.g_down, self.red[0], self.red[1], self.red[2],
+                        owner_local=True)  # fmt: skip
         return dx, dgates
 
     def zero_grad(self):
-        for g in (self.g_gate, self.g_up, self.g_down):
-            g.zero_()
+        """Lazy: the next backward overwrites (instead of adding to) the gradients of the experts it visits
+        and clears the others."""
+        self._fresh = True
 
     def owner_grads(self):
         """fp32 gradients of the experts this rank owns: three tensors ``[E/R, ...]``."""
-        return self.g_gate[: self.epn], self.g_up[: self.epn], self.g_down[: self.epn]
+        return self.g_gate, self.g_up, self.g_down
 
     def sgd_step(self, lr: float):
         """Plain SGD on the owned experts (enough for a benchmark step)."""
         s = slice(self.rank * self.epn, (self.rank + 1) * self.epn)
         for w, g in ((self.w_gate, self.g_gate), (self.w_up, self.g_up), (self.w_down, self.g_down)):
-            w[s].add_((-lr * g[: self.epn]).to(torch.bfloat16))
+            sgd_update(w[s], g, lr)
 
 
 def dense_reference(x, gates, topk, w_gate, w_up, w_down):

@@ -19,19 +19,22 @@ from . import _lib
 _MODES = {"plain": 0, "swiglu": 1, "scale": 2}
 
 
-def grouped_gemm_reference(x, w, cu_seqlens, *, w_up=None, row_scale=None, mode="plain"):
+def grouped_gemm_reference(x, w, cu_seqlens, *, w_up=None, row_scale=None, mode="plain", group_map=None):
     """Per-group fp32 matmul; the oracle of the kernel and the CPU path."""
-    G, N, K = w.shape
+    _, N, K = w.shape
+    G = cu_seqlens.numel()
     out = torch.zeros(x.shape[0], N, dtype=torch.bfloat16, device=x.device)
     ends = cu_seqlens.tolist()
+    gmap = list(range(G)) if group_map is None else group_map.tolist()
     start = 0
     for g in range(G):
         end = int(ends[g])
         if end > start:
             xs = x[start:end].float()
-            y = xs @ w[g].float().t()
+            ws = max(0, int(gmap[g]))
+            y = xs @ w[ws].float().t()
             if mode == "swiglu":
-                y = torch.nn.functional.silu(y) * (xs @ w_up[g].float().t())
+                y = torch.nn.functional.silu(y) * (xs @ w_up[ws].float().t())
             elif mode == "scale" and row_scale is not None:
                 y = y * row_scale[start:end, None]
             out[start:end] = y.to(torch.bfloat16)
@@ -45,21 +48,27 @@ def kernel_supports(x, w, mode: str) -> bool:
     return x.is_cuda and x.dtype == torch.bfloat16 and K % 64 == 0 and N % tile_n == 0 and x.shape[0] >= 128
 
 
-def grouped_gemm(x, w, cu_seqlens, *, w_up=None, row_scale=None, mode="plain", out=None, status=None, num_sms=0):
+def grouped_gemm(x, w, cu_seqlens, *, w_up=None, row_scale=None, mode="plain", out=None, status=None, num_sms=0,
+                 group_map=None):
     """See module docstring.  ``x``: ``[rows, K]`` bf16, ``w``: ``[G, N, K]`` bf16, returns ``[rows, N]`` bf16.
 
-    Rows beyond ``cu_seqlens[-1]`` are not written.  Group ends must be multiples of 128.
+    Rows beyond ``cu_seqlens[-1]`` are not written.  Group ends must be multiples of 128.  With
+    ``group_map`` (int32 ``[G]``) group ``g`` uses ``w[group_map[g]]`` and ``w`` may hold fewer experts
+    than there are groups (e.g. only the experts a rank owns or has prefetched).
     """
     assert mode in _MODES
-    G, N, K = (int(v) for v in w.shape)
-    assert x.dim() == 2 and x.shape[1] == K and cu_seqlens.numel() == G
+    W, N, K = (int(v) for v in w.shape)
+    G = int(cu_seqlens.numel())
+    assert x.dim() == 2 and x.shape[1] == K and (group_map is not None or W == G)
+    if group_map is not None:
+        assert group_map.dtype == torch.int32 and group_map.is_contiguous() and group_map.numel() == G
     if not kernel_supports(x, w, mode):
         if x.is_cuda and torch.cuda.is_available() and not _fallback_allowed():
             raise RuntimeError(
                 f"grouped_gemm: shapes rows={x.shape[0]}, K={K}, N={N} do not fit the tcgen05 kernel's tiling "
                 "(K % 64, N % 256 or 128 for swiglu, rows >= 128); set MOONEP_GEMM_FALLBACK=1 to use the reference"
             )
-        res = grouped_gemm_reference(x, w, cu_seqlens, w_up=w_up, row_scale=row_scale, mode=mode)
+        res = grouped_gemm_reference(x, w, cu_seqlens, w_up=w_up, row_scale=row_scale, mode=mode, group_map=group_map)
         if out is not None:
             out.copy_(res)
             return out
@@ -79,7 +88,7 @@ def grouped_gemm(x, w, cu_seqlens, *, w_up=None, row_scale=None, mode="plain", o
             x.data_ptr(), w.data_ptr(), None if w_up is None else w_up.data_ptr(), out.data_ptr(),
             None if row_scale is None else row_scale.data_ptr(), cu_seqlens.data_ptr(), G, int(x.shape[0]), K, N,
             _MODES[mode], None if status is None else status.data_ptr(), config.timeout_ms(), int(num_sms),
-            torch.cuda.current_stream().cuda_stream,
+            None if group_map is None else group_map.data_ptr(), W, torch.cuda.current_stream().cuda_stream,
         )  # fmt: skip
     _lib.check(rc, "moonep_grouped_gemm")
     return out

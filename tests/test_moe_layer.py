@@ -65,3 +65,38 @@ def test_moe_layer_forward_backward_matches_dense_reference(device, R, routing):
         close(res[r][3][1], wu.grad[s], f"rank {r} grad W_up")
         close(res[r][3][2], wd.grad[s], f"rank {r} grad W_down")
     lw.run(lambda r: bufs[r].destroy())
+
+
+@pytest.mark.parametrize("device", DEVICES)
+def test_moe_helper_ops_match_torch(device):
+    """Batched expert transpose, SwiGLU backward and the SGD update against plain torch."""
+    from moonep_b200.ops.moe_ops import sgd_update, swiglu_bwd, transpose_experts
+
+    g = torch.Generator().manual_seed(5)
+    src = torch.randn(3, 128, 192, generator=g).to(torch.bfloat16).to(device)
+    dst = torch.zeros(3, 192, 128 + 64, dtype=torch.bfloat16, device=device)
+    transpose_experts(src, dst, 64)
+    assert torch.equal(dst[:, :, 64:].cpu(), src.transpose(1, 2).cpu()) and not bool(dst[:, :, :64].abs().max() > 0)
+
+    rows, I, n = 70, 256, 50
+    a, u, gg = (torch.randn(rows, I, generator=g).to(torch.bfloat16).to(device) for _ in range(3))
+    w = torch.rand(rows, generator=g).to(device)
+    dadu = torch.zeros(rows, 2 * I, dtype=torch.bfloat16, device=device)
+    hsw = torch.zeros(rows, I, dtype=torch.bfloat16, device=device)
+    dgate = torch.zeros(rows, device=device)
+    swiglu_bwd(a, u, gg, w, torch.tensor([n], dtype=torch.int32, device=device), dadu, hsw, dgate)
+    af, uf, gf, wf = a.float().cpu(), u.float().cpu(), gg.float().cpu(), w.cpu()
+    s = torch.sigmoid(af)
+    h = af * s * uf
+    dh = gf * wf[:, None]
+    assert torch.allclose(dgate.cpu()[:n], (gf * h).sum(1)[:n], rtol=2e-3, atol=2e-2)
+    assert torch.allclose(dadu.float().cpu()[:n, :I], (dh * uf * s * (1 + af * (1 - s)))[:n], rtol=2e-2, atol=2e-2)
+    assert torch.allclose(dadu.float().cpu()[:n, I:], (dh * af * s)[:n], rtol=2e-2, atol=2e-2)
+    assert torch.allclose(hsw.float().cpu()[:n], (h * wf[:, None])[:n], rtol=2e-2, atol=2e-2)
+    assert not bool(dadu[n:].abs().max() > 0), "rows beyond the total were written"
+
+    wt = torch.randn(4, 128, 64, generator=g).to(torch.bfloat16).to(device)
+    gr = torch.randn(4, 128, 64, generator=g).to(device)
+    want = (wt.float() - 0.5 * gr).to(torch.bfloat16)
+    sgd_update(wt, gr, 0.5)
+    assert torch.allclose(wt.float().cpu(), want.float().cpu(), rtol=1e-2, atol=1e-2)
