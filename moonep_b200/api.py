@@ -166,9 +166,32 @@ class Buffer:
         """Raise ``MoonEPTimeoutError`` if a device-side wait of an earlier operation ran out."""
         self._require_ctx()["_backend"].check_status()
 
-    def stats(self) -> dict:
-        """Counters of the last operations (rows sent, duplicates, waits that timed out)."""
-        return self._require_ctx()["_backend"].stats()
+    def stats(self, plan: MoonEPCommPlan | None = None) -> dict:
+        """Runtime figures.  With ``plan``: rows this rank sends (primary entries), how many of them leave
+        the rank, duplicate entries saved by per-rank dedup, rows and duplicate groups received, remote experts
+        hosted here and ranks copying this rank's experts (``remote_stats``).  Reads the plan (synchronises).
+        Always: the backend's counters (flag epochs, status block, per-call device times when profiling)."""
+        ctx = self._require_ctx()
+        out = dict(ctx["_backend"].stats())
+        if plan is not None:
+            dst = plan.dst.cpu().to(torch.int64)
+            raw = torch.where(dst < 0, -dst - 1, dst)
+            dest = raw // plan.NvS
+            primary = dst >= 0
+            rs = plan.remote_stats.cpu().tolist()
+            dc = plan.dup_counts.cpu().tolist()
+            out.update({
+                "entries": int(dst.numel()),
+                "rows_sent": int(primary.sum()),
+                "rows_sent_remote": int((primary & (dest != ctx["rank"])).sum()),
+                "entries_deduplicated": int((~primary).sum()),
+                "dup_groups_received": int(dc[0]),
+                "dup_rows_received": int(dc[1]),
+                "remote_experts_hosted": int(rs[0]),
+                "ranks_copying_my_experts": int(rs[1]),
+                "bytes_sent_remote": int((primary & (dest != ctx["rank"])).sum()) * ctx["H"] * 2,
+            })  # fmt: skip
+        return out
 
     # -- stream helpers ------------------------------------------------------------
     def _on_comm_stream(self, tensors, fn):

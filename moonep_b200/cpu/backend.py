@@ -75,7 +75,7 @@ class CpuBackend:
         return False
 
     def stats(self) -> dict:
-        return {}
+        return {"backend": "cpu"}
 
     # -- planning ------------------------------------------------------------
     def plan_publish(self, tokens_per_expert: torch.Tensor, topk_flat=None):

@@ -135,12 +135,14 @@ __global__ void __launch_bounds__(kTokensThreads)
 
 __global__ void __launch_bounds__(kTablesThreads)
     plan_tables_kernel(const MoonepDevCtx c, const int* __restrict__ tpe2d, int* __restrict__ cu_out,
-                       int* __restrict__ etc_out, int* __restrict__ zf_out, int* __restrict__ rs_out, int wait_epoch) {
+                       int* __restrict__ etc_out, int* __restrict__ zf_out, int* __restrict__ rs_out, int wait_epoch,
+                       int work_in_smem) {
+  extern __shared__ int s_work[];  // the work tables, when they fit (the serial phases then run at shared-memory latency)
   if (!block_wait_flags(c, MOONEP_FLAG_TPE, wait_epoch, MOONEP_K_PLAN_TABLES)) return;
   const int R = c.R, E = c.E, B = c.B, epn = c.epn, P = c.token_padding;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
   const int* tpe = tpe2d ? tpe2d : (c.meta_peer[c.rank] + c.tpe_off);
-  Tables t = carve(c.tables, R, E);
+  Tables t = carve(work_in_smem ? s_work : c.tables, R, E);
   __shared__ int s_balance[MOONEP_MAX_RANKS];
   __shared__ int s_bad;
   if (tid == 0) s_bad = 0;
@@ -432,8 +434,21 @@ extern "C" int moonep_plan_compute(void* ctx, const int* topk, const int* tpe2d,
   auto* h = (HostCtx*)ctx;
   const MoonepDevCtx& c = h->dev;
   cudaStream_t st = (cudaStream_t)stream;
-  plan_tables_kernel<<<1, kTablesThreads, 0, st>>>(c, tpe2d, cu_seqlens, experts_to_copy, zero_fill, remote_stats,
-                                                  wait_epoch_tpe);
+  size_t work_bytes = (size_t)table_words(c.R, c.E) * sizeof(int);
+  int work_in_smem = 0;
+  if ((int)work_bytes + 8192 <= h->max_smem_optin) {
+    work_in_smem = 1;
+    if (work_bytes > 48 * 1024) {
+      if (int rc = check_cuda(cudaFuncSetAttribute(plan_tables_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   (int)work_bytes),
+                              "cudaFuncSetAttribute(plan_tables_kernel)"))
+        return rc;
+    }
+  } else {
+    work_bytes = 0;
+  }
+  plan_tables_kernel<<<1, kTablesThreads, work_bytes, st>>>(c, tpe2d, cu_seqlens, experts_to_copy, zero_fill, remote_stats,
+                                                           wait_epoch_tpe, work_in_smem);
   if (int rc = check_launch("plan_tables_kernel")) return rc;
   const int tpb = imax(1, MOONEP_PLAN_BLOCK / c.K);
   const int grid = (c.S + tpb - 1) / tpb;

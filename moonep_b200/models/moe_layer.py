@@ -74,8 +74,12 @@ class ExpertParallelMoE:
     def forward(self, x, gates, topk, tokens_per_expert):
         buf = self.buffer
         x_nvs, w_nvs, cu, plan = buf.dispatch(x, gates, topk, tokens_per_expert, zero_copy=True)
-        buf.prefetch_weight(plan, full_gate_weight=self.w_gate, full_up_weight=self.w_up, full_down_weight=self.w_down)
+        # the weight copies run on the communication stream while this stream saves the dispatched rows
+        fetched = buf.prefetch_weight(plan, async_finish=True, full_gate_weight=self.w_gate,
+                                      full_up_weight=self.w_up, full_down_weight=self.w_down)  # fmt: skip
         x_saved = x_nvs.clone()  # the shard is reused for the expert output
+        if hasattr(fetched, "wait") and x_nvs.is_cuda:
+            torch.cuda.current_stream().wait_event(fetched)
         h = grouped_gemm(x_saved, self.w_gate, cu, w_up=self.w_up, mode="swiglu")
         grouped_gemm(h, self.w_down, cu, row_scale=w_nvs, mode="scale", out=x_nvs)
         out, _, _ = buf.combine(plan, x_nvs, None, zero_copy=True)

@@ -132,7 +132,12 @@ class CudaBackend:
         raise RuntimeError(f"unknown device status {st}")
 
     def stats(self) -> dict:
-        return {"epochs": list(self.epoch), "status": self.status.cpu().tolist()}
+        out = {"backend": "cuda", "epochs": list(self.epoch), "status": self.status.cpu().tolist(),
+               "native_launches_in_process": int(self.lib.moonep_launch_count()),
+               "send_path": "bulk" if self.send_path else "ldst", "pull_path": "bulk" if self.pull_path else "ldst"}  # fmt: skip
+        if self._profile:
+            out["phase_times_us"] = self.phase_times()
+        return out
 
     def _next(self, family: int) -> int:
         self.epoch[family] += 1

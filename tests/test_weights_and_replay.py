@@ -207,3 +207,67 @@ def test_wait_that_nothing_satisfies_reports_timeout_and_buffer_recovers():
     buf.check_status()
     assert torch.equal(wb, gates)
     buf.destroy()
+
+
+@pytest.mark.gpu
+def test_prefetch_and_reduce_grad_with_offsets_beyond_2_31():
+    """Experts of 7168 x 3072 elements: byte and element offsets cross 2**31 (parity: reference
+    tests/test_prefetch.py:112-124 and tests/test_grad_reduce.py large-offset case)."""
+    R, S, H, K, epn, B = 2, 16, 32, 2, 52, 52
+    E, Hw, Hp = R * epn, 7168, 3072
+    per = Hw * Hp
+    lw, bufs = _world(R, "cuda", S, H, K, epn, B, num_sms=32)
+    plans = _plans(lw, bufs, R, S, H, K, E, "cuda")
+    etc = torch.full((R, B), -1, dtype=torch.int32)
+    etc[0, 51] = 103  # expert 103 of rank 1: source offset 103 * per * 2 bytes = 4.5 GB
+    etc[1, 50] = 3
+    # one shared pool of experts (emulated ranks see all of it) and per-rank slots
+    experts = torch.empty(E, Hw, Hp, dtype=torch.bfloat16, device="cuda")
+    experts[103].copy_(torch.arange(per, device="cuda").remainder(251).to(torch.bfloat16).view(Hw, Hp))
+    experts[3].fill_(3.0)
+    red = torch.zeros(R, B, Hw, Hp, dtype=torch.float32, device="cuda")  # slot (1, 50) starts at element 2.2e9
+    red[0, 51].fill_(0.5)
+    red[1, 50].copy_(torch.arange(per, device="cuda").remainder(127).float().view(Hw, Hp))
+
+    def body(r):
+        plan = dataclasses.replace(plans[r], experts_to_copy=etc.cuda())
+        slots = torch.full((B, Hw, Hp), -123.0, dtype=torch.bfloat16, device="cuda")
+        be = bufs[r]._require_ctx()["_backend"]
+        be.prefetch_launch([experts], [slots], etc[r].cuda().contiguous())
+        grad = torch.ones(epn, Hw, Hp, dtype=torch.float32, device="cuda")
+        lw.view(r).step()
+        be.reduce_grad(plan.experts_to_copy, [grad], [red], local=True)
+        torch.cuda.synchronize()
+        bufs[r].check_status()
+        lw.view(r).step()
+        if r == 0:
+            ok_pf = torch.equal(slots[51], experts[103]) and bool((slots[50] == -123.0).all())
+            want = torch.ones(Hw, Hp, device="cuda") + torch.arange(per, device="cuda").remainder(127).float().view(Hw, Hp)
+            ok_gr = torch.equal(grad[3], want) and bool((grad[4] == 1).all())
+        else:
+            ok_pf = torch.equal(slots[50], experts[3]) and bool((slots[51] == -123.0).all())
+            ok_gr = torch.equal(grad[103 - epn], torch.full((Hw, Hp), 1.5, device="cuda")) and bool((grad[0] == 1).all())
+        return ok_pf, ok_gr
+
+    for r, (ok_pf, ok_gr) in enumerate(lw.run(body)):
+        assert ok_pf, f"rank {r}: prefetch with large offsets wrong"
+        assert ok_gr, f"rank {r}: reduce_grad with large offsets wrong"
+    assert not bool(red[0, 51].abs().max() > 0) and not bool(red[1, 50].abs().max() > 0), "consumed slots not cleared"
+    lw.run(lambda r: bufs[r].destroy())
+
+
+@pytest.mark.parametrize("device", DEVICES)
+def test_stats_report_rows_and_dedup(device):
+    R, S, H, K, epn, B = 2, 32, 32, 4, 2, 1
+    lw, bufs = _world(R, device, S, H, K, epn, B)
+    plans = _plans(lw, bufs, R, S, H, K, R * epn, device)
+
+    def body(r):
+        return bufs[r].stats(plans[r])
+
+    st = lw.run(body)
+    for r in range(R):
+        assert st[r]["entries"] == S * K and st[r]["rows_sent"] + st[r]["entries_deduplicated"] == S * K
+        assert st[r]["rows_sent_remote"] <= st[r]["rows_sent"] and st[r]["bytes_sent_remote"] == st[r]["rows_sent_remote"] * H * 2
+    assert sum(s["entries_deduplicated"] for s in st) == sum(s["dup_rows_received"] for s in st)
+    lw.run(lambda r: bufs[r].destroy())
