@@ -45,7 +45,7 @@ def parse_args():
     p.add_argument("--routing", default="softmax")
     p.add_argument("--staged", action="store_true", help="use the copying (non zero-copy) API paths")
     p.add_argument("--profile-phases", action="store_true", help="add per-kernel device times (phases_us)")
-    p.add_argument("--config", default="headline", choices=["headline", "skew", "sweep", "moe_step"],
+    p.add_argument("--config", default="headline", choices=["headline", "skew", "sweep", "moe_step", "weights"],
                    help="headline: S=4096,H=7168,K=8,E=256 softmax routing; skew: S=8192,H=4096,E=64,K=6 Zipf(1.2); "
                         "sweep: S in {128..16384} with uniform routing, ours and NCCL; moe_step: SwiGLU MoE layer "
                         "forward+backward+SGD with intermediate size --inter")  # fmt: skip
@@ -332,6 +332,78 @@ def run_moe_step(args, rank, n):
     }  # fmt: skip
 
 
+def run_weights(args, rank, n):
+    """Worst-case expert-weight traffic: every rank prefetches B experts of the next rank (gate, up, down) and
+    every owner reduces B fp32 gradient slots per tensor from the previous rank.  Device-timed, max over ranks."""
+    import dataclasses
+
+    from moonep_b200 import Buffer
+    from moonep_b200.models.routing import make_routing
+    from moonep_b200.parallel.symm import create_full_expert_weight, create_nvl_dist_tensor, view_nvl_dist_rows
+
+    E, H, inter, S, K = args.E, args.H, args.inter, 512, args.K
+    epn = E // n
+    B = min(epn, 32)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    buf = Buffer(S, H, K, E, n, num_sms=args.num_sms, token_padding=128, B=B)
+    world = buf._require_ctx()["world"]
+    topk, tpe, gates = make_routing("softmax", S, K, E, n, rank, seed=1, device=dev)
+    x = torch.randn(S, H, device=dev).to(torch.bfloat16)
+    plan = buf.dispatch(x, gates, topk, tpe)[3]
+    etc = torch.full((n, B), -1, dtype=torch.int32)
+    for r in range(n):
+        src = (r + 1) % n
+        etc[r] = torch.arange(B, dtype=torch.int32) + src * epn
+    plan = dataclasses.replace(plan, experts_to_copy=etc.to(dev))
+    shapes = ((inter, H), (inter, H), (H, inter))
+    ws = [create_full_expert_weight(E, B, d0, d1, world) for d0, d1 in shapes]
+    mapped = n > 1
+    for w in ws:
+        (w[rank * epn : (rank + 1) * epn] if mapped else w[:E]).normal_(0, 0.02)
+    reds = [view_nvl_dist_rows(create_nvl_dist_tensor([B, d0, d1], torch.float32, world, pad_dim0=False), n, B)
+            for d0, d1 in shapes]  # fmt: skip
+    grads = [torch.zeros(epn, d0, d1, dtype=torch.float32, device=dev) for d0, d1 in shapes]
+    for r_ in reds:
+        r_[rank].fill_(1.0)
+    barrier_sync(n)
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        barrier_sync(n)
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+        for a_, b_ in ev:
+            a_.record()
+            fn()
+            b_.record()
+        barrier_sync(n)
+        return max_over_ranks(sum(a_.elapsed_time(b_) for a_, b_ in ev) / args.steps, n)
+
+    t_pf = timed(lambda: buf.prefetch_weight(plan, full_gate_weight=ws[0], full_up_weight=ws[1], full_down_weight=ws[2]))
+
+    def reduce_once():
+        for r_ in reds:
+            r_[rank].fill_(1.0)  # slots are cleared by every reduce; refill outside the kernel under test
+        buf.reduce_grad(plan, False, grads[0], grads[1], grads[2], reds[0], reds[1], reds[2], owner_local=True)
+
+    def fill_only():
+        for r_ in reds:
+            r_[rank].fill_(1.0)
+
+    t_red = timed(reduce_once) - timed(fill_only)
+    buf.check_status()
+    pf_bytes = 3 * B * H * inter * 2
+    red_bytes = 3 * B * H * inter * 4
+    return {
+        "metric": "expert_weight_traffic", "n_gpus": n, "B": B, "H": H, "inter": inter,
+        "prefetch_ms": t_pf, "prefetch_GB": pf_bytes / 1e9, "prefetch_GBps_per_rank": pf_bytes / (t_pf / 1e3) / 1e9,
+        "reduce_grad_ms": t_red, "reduce_grad_GB": red_bytes / 1e9,
+        "reduce_grad_pull_GBps_per_rank": red_bytes / (t_red / 1e3) / 1e9,
+        "note": "remote pulls over NVLink when n_gpus > 1, local HBM copies when n_gpus == 1; reduce_grad time "
+                "includes the accumulate kernel, the flag round and clearing the consumed slots",
+    }  # fmt: skip
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
@@ -340,8 +412,8 @@ def main():
     rank, local, world = init_dist(args.gpus)
     if args.config == "skew":
         args.S, args.H, args.E, args.K, args.routing = 8192, 4096, 64, 6, "zipf"
-    if args.config == "moe_step":
-        res = run_moe_step(args, rank, args.gpus)
+    if args.config in ("moe_step", "weights"):
+        res = run_moe_step(args, rank, args.gpus) if args.config == "moe_step" else run_weights(args, rank, args.gpus)
         if rank == 0:
             res["impl"] = "ours"
             print(json.dumps(res))

@@ -153,7 +153,7 @@ int moonep_prefetch(void* ctx, void* const* src3, void* const* dst3, int n_tenso
 // grads[i]: [E, H, Hp] fp32 (local), reduce[i]: [R, B, H, Hp] fp32 (slot (src, b) lives on rank src).
 int moonep_grad_reduce(void* ctx, float* const* grads, float* const* reduce, int n_tensors,
                        const int* experts_to_copy, int Bcols, long long elems, int epoch_ready, int epoch_done,
-                       int phase, void* stream);
+                       int phase, int path, void* stream);
 
 // CUDA VMM symmetric allocator (driver API through cudaGetDriverEntryPoint).
 int moonep_vmm_granularity(int device, unsigned long long* gran);

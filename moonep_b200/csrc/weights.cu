@@ -187,6 +187,172 @@ __global__ void __launch_bounds__(512)
   grid_tail_signal(c, MOONEP_K_GRAD_ACCUM, ok ? MOONEP_FLAG_GRAD_DONE : -1, signal_epoch);
 }
 
+// Bulk-copy variant of grad_accum: warp 0 streams the remote slots into a shared-memory ring with
+// cp.async.bulk (one 32 KB piece per stage, completion counted on the stage's "full" mbarrier) while
+// warps 1..8 hold the local gradient piece in registers, add the staged slots in ascending slot order
+// and write the piece back.  All consumer warps work on the same stage, so they advance in lockstep
+// and the parity waits stay unambiguous.  The deep ring keeps several hundred KB per SM in flight on
+// NVLink, which register loads cannot.
+constexpr int kAccConsumerWarps = 8;
+constexpr int kAccThreads = 32 * (1 + kAccConsumerWarps);
+constexpr int kAccPieceVec = 2048;  // 16-byte vectors per stage (32 KB)
+constexpr int kAccMaxStages = 8;
+
+__global__ void __launch_bounds__(kAccThreads)
+    grad_accum_bulk_kernel(const MoonepDevCtx c, const TensorSet ts, const int* __restrict__ etc, int Bcols,
+                           long long elems, int wait_epoch, int signal_epoch, int nstages) {
+  extern __shared__ __align__(128) unsigned char s_ring[];  // [nstages][kAccPieceVec * 16]
+  __shared__ __align__(8) unsigned long long s_full[kAccMaxStages], s_empty[kAccMaxStages];
+  __shared__ int s_rb[kMaxSlots];
+  __shared__ short s_le[kMaxSlots];
+  __shared__ short s_active[kMaxLocalExperts];
+  __shared__ unsigned char s_has[kMaxLocalExperts];
+  __shared__ int s_n, s_nactive, s_fail;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x < nstages) {
+    mbar_init(s_full + threadIdx.x, 1);
+    mbar_init(s_empty + threadIdx.x, kAccConsumerWarps);
+  }
+  if (threadIdx.x == 0) s_fail = 0;
+  fence_barrier_init();
+  const bool ok = block_wait_flags(c, MOONEP_FLAG_GRAD_READY, wait_epoch, MOONEP_K_GRAD_ACCUM);
+  if (ok) {
+    const int epn = c.epn, owner0 = c.rank * epn, nslots = c.R * Bcols;
+    for (int i = threadIdx.x; i < epn; i += blockDim.x) s_has[i] = 0;
+    __syncthreads();
+    if (warp == 0) {
+      int n = 0;
+      for (int base = 0; base < nslots; base += 32) {
+        const int rb = base + lane;
+        const int e = rb < nslots ? etc[rb] : -1;
+        const bool mine = e >= owner0 && e < owner0 + epn;
+        const unsigned m = __ballot_sync(0xffffffffu, mine);
+        if (mine) {
+          const int pos = n + __popc(m & ((1u << lane) - 1u));
+          if (pos < kMaxSlots) {
+            s_rb[pos] = rb;
+            s_le[pos] = (short)(e - owner0);
+          }
+          s_has[e - owner0] = 1;
+        }
+        n += __popc(m);
+      }
+      __syncwarp();
+      int na = 0;
+      for (int base = 0; base < epn; base += 32) {
+        const int le = base + lane;
+        const bool has = le < epn && s_has[le];
+        const unsigned m = __ballot_sync(0xffffffffu, has);
+        if (has) s_active[na + __popc(m & ((1u << lane) - 1u))] = (short)le;
+        na += __popc(m);
+      }
+      if (lane == 0) {
+        s_n = n < kMaxSlots ? n : kMaxSlots;
+        s_nactive = na;
+        if (n > kMaxSlots) record_status(c, MOONEP_STATUS_BAD_INDEX, MOONEP_K_GRAD_ACCUM, 8, n, kMaxSlots, 0);
+      }
+    }
+    __syncthreads();
+    const int n = s_n, na = s_nactive;
+    const long long nvec = elems / 4;
+    const long long pieces = (nvec + kAccPieceVec - 1) / kAccPieceVec;
+    const long long total = (long long)ts.n * na * pieces;
+    if (warp == 0) {
+      // ---------------- producer ----------------
+      if (lane == 0) {
+        long long k = 0;
+        bool failed = false;
+        for (long long item = blockIdx.x; item < total && !failed; item += gridDim.x) {
+          const long long piece = item % pieces;
+          const int ai = (int)((item / pieces) % na);
+          const int t = (int)(item / (pieces * na));
+          const int le = s_active[ai];
+          const long long v0 = piece * kAccPieceVec;
+          const unsigned bytes = (unsigned)((nvec - v0 < kAccPieceVec ? nvec - v0 : kAccPieceVec) * 16);
+          const unsigned char* red = reinterpret_cast<const unsigned char*>(ts.q[t]);
+          for (int s = 0; s < n && !failed; ++s) {
+            if (s_le[s] != le) continue;
+            const int stage = (int)(k % nstages);
+            const long long use = k / nstages;
+            if (use > 0 && !mbar_wait(s_empty + stage, (unsigned)((use - 1) & 1), c.timeout_ns)) {
+              record_status(c, MOONEP_STATUS_TIMEOUT, MOONEP_K_GRAD_ACCUM, 101, stage, (int)use, 0);
+              s_fail = 1;
+              failed = true;
+              break;
+            }
+            mbar_expect_tx(s_full + stage, bytes);
+            bulk_g2s(s_ring + (size_t)stage * kAccPieceVec * 16, red + ((long long)s_rb[s] * nvec + v0) * 16, bytes,
+                     s_full + stage);
+            ++k;
+          }
+        }
+      }
+      __syncwarp();
+    } else {
+      // ---------------- consumers ----------------
+      const int ctid = threadIdx.x - 32, cthreads = kAccConsumerWarps * 32;
+      constexpr int kPer = kAccPieceVec / (kAccConsumerWarps * 32);  // vectors per thread and piece
+      long long k = 0;
+      bool failed = false;
+      for (long long item = blockIdx.x; item < total && !failed; item += gridDim.x) {
+        const long long piece = item % pieces;
+        const int ai = (int)((item / pieces) % na);
+        const int t = (int)(item / (pieces * na));
+        const int le = s_active[ai];
+        const long long v0 = piece * kAccPieceVec;
+        const long long v1 = v0 + kAccPieceVec < nvec ? v0 + kAccPieceVec : nvec;
+        float4* g = reinterpret_cast<float4*>(ts.p[t]) + (long long)(owner0 + le) * nvec;
+        float4 acc[kPer];
+#pragma unroll
+        for (int j = 0; j < kPer; ++j) {
+          const long long i = v0 + j * cthreads + ctid;
+          if (i < v1) acc[j] = ld16f(g + i);
+        }
+        for (int s = 0; s < n && !failed; ++s) {
+          if (s_le[s] != le) continue;
+          const int stage = (int)(k % nstages);
+          const unsigned par = (unsigned)((k / nstages) & 1);
+          bool got = mbar_try_wait(s_full + stage, par);
+          if (!got) {
+            const unsigned long long t0 = globaltimer_ns();
+            unsigned spins = 0;
+            while (!(got = mbar_try_wait(s_full + stage, par))) {
+              if ((++spins & 255u) == 0 && (*(volatile int*)&s_fail || globaltimer_ns() - t0 > c.timeout_ns)) break;
+            }
+          }
+          if (!got) {
+            if (!*(volatile int*)&s_fail) record_status(c, MOONEP_STATUS_TIMEOUT, MOONEP_K_GRAD_ACCUM, 102, stage, 0, 0);
+            failed = true;
+            break;
+          }
+          const float4* st = reinterpret_cast<const float4*>(s_ring + (size_t)stage * kAccPieceVec * 16);
+#pragma unroll
+          for (int j = 0; j < kPer; ++j) {
+            const long long i = v0 + j * cthreads + ctid;
+            if (i < v1) {
+              const float4 v = st[j * cthreads + ctid];
+              acc[j].x += v.x;
+              acc[j].y += v.y;
+              acc[j].z += v.z;
+              acc[j].w += v.w;
+            }
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(s_empty + stage);
+          ++k;
+        }
+        if (failed) break;
+#pragma unroll
+        for (int j = 0; j < kPer; ++j) {
+          const long long i = v0 + j * cthreads + ctid;
+          if (i < v1) st16f(g + i, acc[j]);
+        }
+      }
+    }
+  }
+  grid_tail_signal(c, MOONEP_K_GRAD_ACCUM, ok ? MOONEP_FLAG_GRAD_DONE : -1, signal_epoch);
+}
+
 __global__ void __launch_bounds__(512)
     grad_clear_kernel(const MoonepDevCtx c, const TensorSet ts, const int* __restrict__ etc, int Bcols, long long elems,
                       int wait_epoch) {
@@ -242,7 +408,7 @@ extern "C" int moonep_prefetch(void* ctx, void* const* src3, void* const* dst3, 
 
 extern "C" int moonep_grad_reduce(void* ctx, float* const* grads, float* const* reduce, int n_tensors,
                                   const int* experts_to_copy, int Bcols, long long elems, int epoch_ready,
-                                  int epoch_done, int phase, void* stream) {
+                                  int epoch_done, int phase, int path, void* stream) {
   auto* h = (HostCtx*)ctx;
   const MoonepDevCtx& c = h->dev;
   if (n_tensors < 1 || n_tensors > kMaxTensors || elems % 4 != 0) {
@@ -262,6 +428,19 @@ extern "C" int moonep_grad_reduce(void* ctx, float* const* grads, float* const* 
   const int grid = imax(1, imin(c.num_sms, h->sm_count));
   cudaStream_t st = (cudaStream_t)stream;
   if (phase == 1) {
+    const size_t stage_bytes = (size_t)kAccPieceVec * 16;
+    int nstages = (int)((h->max_smem_optin - 40 * 1024) / (long long)stage_bytes);  // static tables take ~30 KB
+    if (nstages > kAccMaxStages) nstages = kAccMaxStages;
+    if (path == MOONEP_PATH_BULK && nstages >= 2) {
+      const size_t smem = (size_t)nstages * stage_bytes;
+      if (int rc = check_cuda(cudaFuncSetAttribute(grad_accum_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   (int)smem),
+                              "cudaFuncSetAttribute(grad_accum_bulk_kernel)"))
+        return rc;
+      grad_accum_bulk_kernel<<<grid, kAccThreads, smem, st>>>(c, ts, experts_to_copy, Bcols, elems, epoch_ready,
+                                                             epoch_done, nstages);
+      return check_launch("grad_accum_bulk_kernel");
+    }
     grad_accum_kernel<<<grid, 512, 0, st>>>(c, ts, experts_to_copy, Bcols, elems, epoch_ready, epoch_done);
     return check_launch("grad_accum_kernel");
   }

@@ -343,6 +343,8 @@ class CudaBackend:
         ra = (ctypes.c_void_p * n)(*[r.data_ptr() for r in reduce_buffers])
         self.signal(FLAG_GRAD_READY)
         ready, done = self.epoch[FLAG_GRAD_READY], self._next(FLAG_GRAD_DONE)
-        self._call("moonep_grad_reduce", ga, ra, n, _ptr(experts_to_copy), Bc, H * Hp, ready, done, 1, _stream())
+        self._call("moonep_grad_reduce", ga, ra, n, _ptr(experts_to_copy), Bc, H * Hp, ready, done, 1, self.path,
+                   _stream(), tag="grad_accum")  # fmt: skip
         self.world.step()
-        self._call("moonep_grad_reduce", ga, ra, n, _ptr(experts_to_copy), Bc, H * Hp, ready, done, 2, _stream())
+        self._call("moonep_grad_reduce", ga, ra, n, _ptr(experts_to_copy), Bc, H * Hp, ready, done, 2, self.path,
+                   _stream(), tag="grad_clear")  # fmt: skip
