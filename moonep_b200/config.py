@@ -4,7 +4,7 @@ MOONEP_PLANNER        ``gpu`` (default) or ``cpu``: run the planner kernels or t
 MOONEP_TIMEOUT_MS     budget of every device-side wait (default 10000).
 MOONEP_COPY_PATH      ``bulk`` (default: TMA bulk copies through shared memory) or ``ldst``
                       (plain 16-byte loads/stores) for dispatch/combine/prefetch;
-                      ``MOONEP_SEND_PATH`` / ``MOONEP_PULL_PATH`` set one direction only.
+                      ``MOONEP_SEND_PATH`` / ``MOONEP_PULL_PATH`` / ``MOONEP_GRAD_PATH`` set one kernel only.
 MOONEP_LOCAL_SMS      CTAs of the kernels that only touch local memory (default: all SMs); ``num_sms`` of
                       the Buffer bounds the kernels that move data between ranks.
 MOONEP_NUM_SMS_DEDUP  number of SMs the dedup builder may use (validated, 1..SM count).
@@ -42,7 +42,8 @@ def copy_path(which: str = "") -> str:
     raw = os.environ.get(f"MOONEP_{which.upper()}_PATH") if which else None
     if not raw:
         # measured on 8 B200: bulk stores win for the send, register loads for the pull
-        raw = os.environ.get("MOONEP_COPY_PATH", "ldst" if which == "pull" else "bulk")
+        # (bulk loads from peer memory measured below LSU loads, bulk stores to peer memory above LSU stores)
+        raw = os.environ.get("MOONEP_COPY_PATH", "ldst" if which in ("pull", "grad") else "bulk")
     raw = raw.lower()
     if raw not in ("bulk", "ldst"):
         raise ValueError(f"copy path must be 'bulk' or 'ldst', got {raw!r}")

@@ -89,7 +89,9 @@ __device__ __forceinline__ void st16f(float4* p, const float4& f) {
   st16(p, make_int4(__float_as_int(f.x), __float_as_int(f.y), __float_as_int(f.z), __float_as_int(f.w)));
 }
 
-__global__ void __launch_bounds__(512)
+constexpr int kAccLd = 8;  // 16-byte loads per lane and slot in flight (4 KB per warp)
+
+__global__ void __launch_bounds__(256, 3)
     grad_accum_kernel(const MoonepDevCtx c, const TensorSet ts, const int* __restrict__ etc, int Bcols, long long elems,
                       int wait_epoch, int signal_epoch) {
   __shared__ int s_rb[kMaxSlots];
@@ -149,24 +151,24 @@ __global__ void __launch_bounds__(512)
       const float4* red = reinterpret_cast<const float4*>(ts.q[t]);
       const long long v0 = piece * kPieceVec;
       const long long v1 = v0 + kPieceVec < nvec ? v0 + kPieceVec : nvec;
-      for (long long i0 = v0; i0 < v1; i0 += 32 * 4) {
-        float4 acc[4];
+      for (long long i0 = v0; i0 < v1; i0 += 32 * kAccLd) {
+        float4 acc[kAccLd];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < kAccLd; ++j) {
           const long long i = i0 + j * 32 + lane;
           if (i < v1) acc[j] = ld16f(g + i);
         }
         for (int s = 0; s < n; ++s) {
           if (s_le[s] != le) continue;
           const float4* src = red + (long long)s_rb[s] * nvec;
-          float4 v[4];
+          float4 v[kAccLd];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
+          for (int j = 0; j < kAccLd; ++j) {
             const long long i = i0 + j * 32 + lane;
             if (i < v1) v[j] = ld16f(src + i);
           }
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
+          for (int j = 0; j < kAccLd; ++j) {
             const long long i = i0 + j * 32 + lane;
             if (i < v1) {
               acc[j].x += v[j].x;
@@ -177,7 +179,7 @@ __global__ void __launch_bounds__(512)
           }
         }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < kAccLd; ++j) {
           const long long i = i0 + j * 32 + lane;
           if (i < v1) st16f(g + i, acc[j]);
         }
@@ -187,7 +189,8 @@ __global__ void __launch_bounds__(512)
   grid_tail_signal(c, MOONEP_K_GRAD_ACCUM, ok ? MOONEP_FLAG_GRAD_DONE : -1, signal_epoch);
 }
 
-// Bulk-copy variant of grad_accum: warp 0 streams the remote slots into a shared-memory ring with
+// Bulk-copy variant of grad_accum (selected with MOONEP_GRAD_PATH=bulk; measured slower than the register
+// path on B200 NVLink, where bulk loads from peer memory run below LSU loads): warp 0 streams the remote slots into a shared-memory ring with
 // cp.async.bulk (one 32 KB piece per stage, completion counted on the stage's "full" mbarrier) while
 // warps 1..8 hold the local gradient piece in registers, add the staged slots in ascending slot order
 // and write the piece back.  All consumer warps work on the same stage, so they advance in lockstep
@@ -294,19 +297,46 @@ __global__ void __launch_bounds__(kAccThreads)
       constexpr int kPer = kAccPieceVec / (kAccConsumerWarps * 32);  // vectors per thread and piece
       long long k = 0;
       bool failed = false;
-      for (long long item = blockIdx.x; item < total && !failed; item += gridDim.x) {
+      // the local gradient piece of the next item is loaded while the current one is being reduced
+      auto coords = [&](long long item, int& le, long long& v0, long long& v1, float4*& g) {
         const long long piece = item % pieces;
         const int ai = (int)((item / pieces) % na);
         const int t = (int)(item / (pieces * na));
-        const int le = s_active[ai];
-        const long long v0 = piece * kAccPieceVec;
-        const long long v1 = v0 + kAccPieceVec < nvec ? v0 + kAccPieceVec : nvec;
-        float4* g = reinterpret_cast<float4*>(ts.p[t]) + (long long)(owner0 + le) * nvec;
-        float4 acc[kPer];
+        le = s_active[ai];
+        v0 = piece * kAccPieceVec;
+        v1 = v0 + kAccPieceVec < nvec ? v0 + kAccPieceVec : nvec;
+        g = reinterpret_cast<float4*>(ts.p[t]) + (long long)(owner0 + le) * nvec;
+      };
+      float4 nxt[kPer];
+      if ((long long)blockIdx.x < total) {
+        int le0;
+        long long a0, a1;
+        float4* g0;
+        coords(blockIdx.x, le0, a0, a1, g0);
 #pragma unroll
         for (int j = 0; j < kPer; ++j) {
-          const long long i = v0 + j * cthreads + ctid;
-          if (i < v1) acc[j] = ld16f(g + i);
+          const long long i = a0 + j * cthreads + ctid;
+          if (i < a1) nxt[j] = ld16f(g0 + i);
+        }
+      }
+      for (long long item = blockIdx.x; item < total && !failed; item += gridDim.x) {
+        int le;
+        long long v0, v1;
+        float4* g;
+        coords(item, le, v0, v1, g);
+        float4 acc[kPer];
+#pragma unroll
+        for (int j = 0; j < kPer; ++j) acc[j] = nxt[j];
+        if (item + gridDim.x < total) {
+          int le2;
+          long long b0, b1;
+          float4* g2;
+          coords(item + gridDim.x, le2, b0, b1, g2);
+#pragma unroll
+          for (int j = 0; j < kPer; ++j) {
+            const long long i = b0 + j * cthreads + ctid;
+            if (i < b1) nxt[j] = ld16f(g2 + i);
+          }
         }
         for (int s = 0; s < n && !failed; ++s) {
           if (s_le[s] != le) continue;
@@ -441,7 +471,8 @@ extern "C" int moonep_grad_reduce(void* ctx, float* const* grads, float* const* 
                                                              epoch_done, nstages);
       return check_launch("grad_accum_bulk_kernel");
     }
-    grad_accum_kernel<<<grid, 512, 0, st>>>(c, ts, experts_to_copy, Bcols, elems, epoch_ready, epoch_done);
+    // three CTAs of 8 warps per SM: remote reads are latency bound, more resident warps mean more loads in flight
+    grad_accum_kernel<<<3 * grid, 256, 0, st>>>(c, ts, experts_to_copy, Bcols, elems, epoch_ready, epoch_done);
     return check_launch("grad_accum_kernel");
   }
   if (phase == 2) {

@@ -67,6 +67,7 @@ class CudaBackend:
         self.path = _PATHS[config.copy_path()]
         self.send_path = _PATHS[config.copy_path("send")]
         self.pull_path = _PATHS[config.copy_path("pull")]
+        self.grad_path = _PATHS[config.copy_path("grad")]
         self._profile = None
         self._quiesced = False  # every peer is known to be past its last pull from this rank's shard
 
@@ -343,7 +344,7 @@ class CudaBackend:
         ra = (ctypes.c_void_p * n)(*[r.data_ptr() for r in reduce_buffers])
         self.signal(FLAG_GRAD_READY)
         ready, done = self.epoch[FLAG_GRAD_READY], self._next(FLAG_GRAD_DONE)
-        self._call("moonep_grad_reduce", ga, ra, n, _ptr(experts_to_copy), Bc, H * Hp, ready, done, 1, self.path,
+        self._call("moonep_grad_reduce", ga, ra, n, _ptr(experts_to_copy), Bc, H * Hp, ready, done, 1, self.grad_path,
                    _stream(), tag="grad_accum")  # fmt: skip
         self.world.step()
         self._call("moonep_grad_reduce", ga, ra, n, _ptr(experts_to_copy), Bc, H * Hp, ready, done, 2, self.path,
