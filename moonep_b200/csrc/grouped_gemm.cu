@@ -9,7 +9,7 @@
 //
 // Persistent kernel, one CTA per SM, 192 threads:
 //   warp 0      TMA producer: per 64-wide K block one 128x64 tile of X and two 128x64 tiles of W
-//               (cp.async.bulk.tensor.2d, 128-byte swizzle, no multicast) into a 4-stage ring; the
+//               (cp.async.bulk.tensor.2d, 128-byte swizzle, every CTA loads its own tiles) into a 4-stage ring; the
 //               transaction bytes complete the stage's "full" mbarrier.
 //   warp 1      allocates 512 TMEM columns (two 128x256 fp32 accumulators) and issues the MMAs from
 //               one lane: four tcgen05.mma (M=128, N=256, K=16, bf16 -> fp32) per stage;

@@ -29,5 +29,5 @@ def test_cuda_backend_nccl_processes():
     n = torch.cuda.device_count()
     if n < 2:
         pytest.skip("needs at least two GPUs")
-    # NVLS off: a rank that dies while bound to an NVLink multicast object can fault its peers
+    # NVLS off: a rank that dies while its memory is bound to an in-switch reduction object can fault its peers
     _run_worker(min(n, 4), "nccl", 29631, 900, {"NCCL_NVLS_ENABLE": "0"})
