@@ -193,6 +193,19 @@ class Buffer:
             })  # fmt: skip
         return out
 
+    # -- CUDA graphs ---------------------------------------------------------------
+    def capture(self, fn, *, warmup: int = 1):
+        """Capture ``fn()`` — any sequence of this Buffer's operations on fixed tensors, plus whatever
+        else is capturable — into a CUDA graph and return a ``CapturedStep``; ``step.replay()`` then
+        runs the whole sequence with one launch.  Collective: every rank captures the same sequence and
+        replays it the same number of times.  ``fn`` runs ``warmup`` times for real before the capture
+        (lazy initialisation, allocator warm-up); its return value of the captured run is ``step.outputs``
+        (tensors that every replay overwrites).  Ordinary calls and replays can be mixed freely.
+        No counterpart in the reference, whose barriers are host-driven."""
+        ctx = self._require_ctx()
+        assert ctx["world"].is_cuda, "graph capture needs the CUDA backend"
+        return CapturedStep(self, fn, warmup)
+
     # -- stream helpers ------------------------------------------------------------
     def _on_comm_stream(self, tensors, fn):
         """Run ``fn`` on the communication stream after the current stream's work; return its event."""
@@ -405,6 +418,37 @@ class Buffer:
             run()
             return None
         return self._on_comm_stream((plan.experts_to_copy, *grads, *bufs), run)
+
+
+class CapturedStep:
+    """A CUDA graph of Buffer operations (see ``Buffer.capture``)."""
+
+    def __init__(self, buffer: Buffer, fn, warmup: int = 1):
+        self._buffer = buffer
+        be = buffer._require_ctx()["_backend"]
+        for _ in range(max(0, warmup)):
+            fn()
+        torch.cuda.synchronize(be.ctx["device"])
+        buffer.check_status()
+        self.graph = torch.cuda.CUDAGraph()
+        be.capture_begin()
+        try:
+            with torch.cuda.graph(self.graph):
+                self.outputs = fn()
+                self._end = be.capture_end()
+        except BaseException:
+            be.capture_abort()
+            raise
+        self.replays = 0
+
+    def replay(self):
+        """Enqueue one run of the captured sequence on the current stream; returns ``outputs``."""
+        be = self._buffer._require_ctx()["_backend"]
+        be.replay_prepare()
+        self.graph.replay()
+        be.replay_done(self._end)
+        self.replays += 1
+        return self.outputs
 
 
 class _DoneEvent:

@@ -11,6 +11,12 @@
 // miss a signal.  This replaces the reference's grid barrier + nvshmem_barrier_all pair
 // (moonep_td/_common.py:49-82), whose reset races with late spinners.
 //
+// Epoch arguments are relative: a kernel adds the per-family bias kept in device memory
+// (counters[MOONEP_BIAS_OFF + family]) to the epoch it was launched with.  The bias is zero
+// for ordinary launches; a captured CUDA graph carries small epochs relative to its capture
+// point and ends with a kernel that advances the bias by the epochs one replay consumes, so
+// the same graph can be replayed any number of times (moonep_epoch_bias in moonep.h).
+//
 // Every wait is bounded by ctx.timeout_ns of %globaltimer.  When it runs out the kernel
 // records {code, kernel, family, peer, expected, seen} in the status block and returns;
 // later kernels of the same Buffer see the non-zero status and return at once, so a
@@ -64,6 +70,11 @@ __device__ __forceinline__ void record_status(const MoonepDevCtx& c, int code, i
   }
 }
 
+// Absolute epoch of a launch argument: argument + this family's bias (see the header comment).
+__device__ __forceinline__ int abs_epoch(const MoonepDevCtx& c, int family, int epoch) {
+  return epoch + ld_volatile(c.counters + MOONEP_BIAS_OFF + family);
+}
+
 // True if an earlier kernel of this Buffer failed; the caller returns immediately.
 __device__ __forceinline__ bool poisoned(const MoonepDevCtx& c) { return ld_volatile(c.status + MOONEP_ST_CODE) != 0; }
 
@@ -74,6 +85,7 @@ __device__ __forceinline__ bool block_wait_flags(const MoonepDevCtx& c, int fami
   if (threadIdx.x == 0) s_ok = poisoned(c) ? 0 : 1;
   __syncthreads();
   if (family >= 0 && s_ok) {
+    epoch = abs_epoch(c, family, epoch);
     for (int r = threadIdx.x; r < c.R; r += blockDim.x) {
       const int* f = flag_ptr(c, c.rank, family, r);
       int v = ld_acquire_sys(f);
@@ -115,6 +127,7 @@ __device__ __forceinline__ void grid_tail_signal(const MoonepDevCtx& c, int coun
   }
   __syncthreads();
   if (s_last && family >= 0) {
+    epoch = abs_epoch(c, family, epoch);
     for (int r = threadIdx.x; r < c.R; r += blockDim.x) st_release_sys(flag_ptr(c, r, family, c.rank), epoch);
   }
 }

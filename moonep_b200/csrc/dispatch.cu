@@ -268,7 +268,7 @@ __global__ void __launch_bounds__(kSendThreadsLdst) dispatch_send_ldst_kernel(co
   __syncthreads();
   if (s_last && ok) {
     for (int r = threadIdx.x; r < c.R; r += blockDim.x)
-      st_release_sys(flag_ptr(c, r, MOONEP_FLAG_SENT, c.rank), a.signal_epoch);
+      st_release_sys(flag_ptr(c, r, MOONEP_FLAG_SENT, c.rank), abs_epoch(c, MOONEP_FLAG_SENT, a.signal_epoch));
   }
 }
 
@@ -411,7 +411,7 @@ __global__ void __launch_bounds__(kSendThreadsBulk) dispatch_send_bulk_kernel(co
   __syncthreads();
   if (s_last && ok) {
     for (int r = threadIdx.x; r < c.R; r += blockDim.x)
-      st_release_sys(flag_ptr(c, r, MOONEP_FLAG_SENT, c.rank), a.signal_epoch);
+      st_release_sys(flag_ptr(c, r, MOONEP_FLAG_SENT, c.rank), abs_epoch(c, MOONEP_FLAG_SENT, a.signal_epoch));
   }
 }
 

@@ -60,6 +60,8 @@
 #define MOONEP_K_GRAD_CLEAR 11
 #define MOONEP_K_WAIT 12
 #define MOONEP_NUM_KERNEL_IDS 16
+// counters[MOONEP_BIAS_OFF + family]: epoch bias added to every epoch argument of that family.
+#define MOONEP_BIAS_OFF 32
 
 // link word of a landed row (pushed by the source rank during planning).
 #define MOONEP_LINK_PRIMARY (1 << 30)
@@ -89,7 +91,7 @@ struct MoonepDevCtx {
   int* const* meta_peer;         // [R] -> int32 [meta_stride]
   // Local scratch.
   int* status;        // [MOONEP_ST_WORDS]
-  int* counters;      // [MOONEP_NUM_KERNEL_IDS] arrival counters of kernel tails
+  int* counters;      // [64] arrival counters of kernel tails, work counters, epoch biases
   int* alloc_cum;     // [E, R]   inclusive cumsum of alloc over destination ranks
   int* expert_off;    // [R, E]   first row of expert e on destination d
   int* tpe_prev;      // [E]      tokens of expert e on source ranks < rank
@@ -125,6 +127,12 @@ int moonep_ctx_set_timeout_ms(void* ctx, long long ms);
 // may be skipped by passing family < 0.
 int moonep_signal_wait(void* ctx, int signal_family, int signal_epoch, int wait_family, int wait_epoch,
                        void* stream);
+
+// Epoch bias (graph replay support).  Kernels add bias[family] to their epoch arguments.
+// mode 0: bias[f] = values[f]; mode 1: bias[f] += values[f], for f < MOONEP_NUM_FLAG_FAMILIES.
+// values is a host array read at call time.  Captured as the last node of a CUDA graph with
+// mode 1 and the epochs one replay consumes, it makes that graph replayable.
+int moonep_epoch_bias(void* ctx, const int* values, int mode, void* stream);
 
 // Planner.  tpe is [E] (pushed to all peers) or [R, E] (tpe_is_2d, used as is).
 int moonep_plan_publish(void* ctx, const int* topk, const int* tpe, int tpe_is_2d, int epoch_tpe, void* stream);

@@ -37,9 +37,18 @@ __global__ void __launch_bounds__(256)
     if (threadIdx.x == 0) fence_sys();
     __syncthreads();
     for (int r = threadIdx.x; r < c.R; r += blockDim.x)
-      st_release_sys(flag_ptr(c, r, signal_family, c.rank), signal_epoch);
+      st_release_sys(flag_ptr(c, r, signal_family, c.rank), abs_epoch(c, signal_family, signal_epoch));
   }
   if (wait_family >= 0) block_wait_flags(c, wait_family, wait_epoch, MOONEP_K_WAIT);
+}
+
+struct BiasValues {
+  int v[MOONEP_NUM_FLAG_FAMILIES];
+};
+
+__global__ void epoch_bias_kernel(const MoonepDevCtx c, const BiasValues b, int mode) {
+  const int f = threadIdx.x;
+  if (f < MOONEP_NUM_FLAG_FAMILIES) c.counters[MOONEP_BIAS_OFF + f] = (mode ? c.counters[MOONEP_BIAS_OFF + f] : 0) + b.v[f];
 }
 
 __global__ void __launch_bounds__(512)
@@ -412,6 +421,14 @@ extern "C" int moonep_signal_wait(void* ctx, int signal_family, int signal_epoch
   auto* h = (HostCtx*)ctx;
   signal_wait_kernel<<<1, 128, 0, (cudaStream_t)stream>>>(h->dev, signal_family, signal_epoch, wait_family, wait_epoch);
   return check_launch("signal_wait_kernel");
+}
+
+extern "C" int moonep_epoch_bias(void* ctx, const int* values, int mode, void* stream) {
+  auto* h = (HostCtx*)ctx;
+  BiasValues b;
+  for (int f = 0; f < MOONEP_NUM_FLAG_FAMILIES; ++f) b.v[f] = values[f];
+  epoch_bias_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(h->dev, b, mode);
+  return check_launch("epoch_bias_kernel");
 }
 
 extern "C" int moonep_prefetch(void* ctx, void* const* src3, void* const* dst3, int n_tensors,

@@ -64,6 +64,8 @@ class CudaBackend:
         c = ctx
         R, E, S, K, B = c["R"], c["E"], c["S"], c["K"], c["B"]
         self.epoch = [0] * NUM_FLAG_FAMILIES
+        self.bias = [0] * NUM_FLAG_FAMILIES  # host mirror of the device-side epoch bias (in stream order)
+        self._capture = None
         self.path = _PATHS[config.copy_path()]
         self.send_path = _PATHS[config.copy_path("send")]
         self.pull_path = _PATHS[config.copy_path("pull")]
@@ -141,8 +143,62 @@ class CudaBackend:
         return out
 
     def _next(self, family: int) -> int:
+        """Advance the family's epoch; return it as a launch argument (relative to the device-side bias)."""
         self.epoch[family] += 1
-        return self.epoch[family]
+        return self.epoch[family] - self.bias[family]
+
+    def _cur(self, family: int) -> int:
+        """The family's current epoch as a launch argument."""
+        return self.epoch[family] - self.bias[family]
+
+    # -- CUDA graph support ------------------------------------------------------------------
+    # Kernels add a per-family bias kept in device memory to their epoch arguments.  While a graph is
+    # captured the host bias is set to the current epochs, so the captured arguments are small numbers
+    # relative to the capture point; the graph's last node advances the device bias by the epochs one
+    # replay consumes.  Before a replay the device bias is set to the epochs reached so far (one tiny
+    # launch, skipped when replays follow each other), so graph replays and ordinary calls can be mixed.
+    def _bias_launch(self, values, mode):
+        arr = (ctypes.c_int * NUM_FLAG_FAMILIES)(*[int(v) for v in values])
+        with torch.cuda.device(self.ctx["device"]):
+            _lib.check(self.lib.moonep_epoch_bias(self.handle, arr, int(mode), _stream()), "moonep_epoch_bias")
+
+    def capture_begin(self):
+        assert self._capture is None, "a capture of this Buffer is already in progress"
+        assert self._profile is None, "stop profiling before capturing a graph"
+        assert self.world.size == 1 or not getattr(self.world, "emulated", False), (
+            "graph capture needs one process per rank (emulated ranks share a stream and cannot capture)"
+        )
+        self._capture = {"epoch": list(self.epoch), "bias": list(self.bias), "quiesced": self._quiesced}
+        self.bias = list(self.epoch)
+        self._quiesced = False  # a replay may follow anything: keep the barrier that protects the shard
+
+    def capture_end(self):
+        """Call inside the capture, after the captured work: adds the bias advance as the last graph node and
+        rolls the host state back (nothing ran).  Returns what ``replay_done`` needs."""
+        st = self._capture
+        delta = [e - e0 for e, e0 in zip(self.epoch, st["epoch"])]
+        self._bias_launch(delta, 1)
+        end = {"delta": delta, "quiesced": self._quiesced}
+        self.epoch, self.bias, self._quiesced = st["epoch"], st["bias"], st["quiesced"]
+        self._capture = None
+        return end
+
+    def capture_abort(self):
+        st = self._capture
+        if st is not None:
+            self.epoch, self.bias, self._quiesced = st["epoch"], st["bias"], st["quiesced"]
+            self._capture = None
+
+    def replay_prepare(self):
+        if self.bias != self.epoch:
+            self._bias_launch(self.epoch, 0)
+            self.bias = list(self.epoch)
+
+    def replay_done(self, end):
+        for f, d in enumerate(end["delta"]):
+            self.epoch[f] += d
+            self.bias[f] += d
+        self._quiesced = end["quiesced"]
 
     def _call(self, name, *args, tag=None):
         with torch.cuda.device(self.ctx["device"]):
@@ -176,7 +232,7 @@ class CudaBackend:
         self.world.step()
 
     def wait(self, family: int):
-        self._call("moonep_signal_wait", -1, 0, family, self.epoch[family], _stream())
+        self._call("moonep_signal_wait", -1, 0, family, self._cur(family), _stream())
 
     def barrier(self):
         self.signal(FLAG_READY)
@@ -196,7 +252,7 @@ class CudaBackend:
         self._call(
             "moonep_plan_compute", _ptr(topk_flat), tpe2d, _ptr(plan.dst), _ptr(cu_seqlens),
             _ptr(plan.experts_to_copy), _ptr(plan.zero_fill_ranges), _ptr(plan.remote_stats),
-            self.epoch[FLAG_TPE], self._next(FLAG_PLAN), _stream(),
+            self._cur(FLAG_TPE), self._next(FLAG_PLAN), _stream(),
         )  # fmt: skip
         self.world.step()
 
@@ -237,7 +293,7 @@ class CudaBackend:
     # -- dispatch ------------------------------------------------------------------------
     def dispatch_send(self, hidden_sh, route_weights_sk, plan, build_dedup_map, wait=None):
         wf = -1 if wait is None else int(wait)
-        we = 0 if wait is None else self.epoch[wf]
+        we = 0 if wait is None else self._cur(wf)
         self._call(
             "moonep_dispatch_send", _ptr(hidden_sh), _ptr(route_weights_sk), _ptr(plan.dst),
             _ptr(plan.zero_fill_ranges), _ptr(plan.dup_groups), _ptr(plan.dup_loffs), _ptr(plan.dup_counts),
@@ -251,7 +307,7 @@ class CudaBackend:
     def dispatch_expand(self, plan, out_hidden, out_weights, zero_copy):
         self._call(
             "moonep_dispatch_expand", _ptr(plan.zero_fill_ranges), int(self._sent_weights), _ptr(plan.dup_groups),
-            _ptr(plan.dup_loffs), _ptr(plan.dup_counts), self.epoch[FLAG_SENT], _stream(),
+            _ptr(plan.dup_loffs), _ptr(plan.dup_counts), self._cur(FLAG_SENT), _stream(),
         )  # fmt: skip
         if not zero_copy:
             out_hidden.copy_(self.ctx["hidden_buf_local"])
@@ -268,7 +324,7 @@ class CudaBackend:
             self.ctx["hidden_buf_local"].copy_(hidden_nvsh)
             if route_weights_nvs is not None:
                 self.ctx["weights_buf_local"].copy_(route_weights_nvs.view(torch.int32))
-        we = 0 if wf < 0 else self.epoch[wf]
+        we = 0 if wf < 0 else self._cur(wf)
         self._call(
             "moonep_combine_prologue", _ptr(plan.dup_groups), _ptr(plan.dup_loffs), _ptr(plan.dup_counts),
             None, None, wf, we, self._next(FLAG_COMB), _stream(),
@@ -281,7 +337,7 @@ class CudaBackend:
     def combine_pull(self, plan_dst, out_hidden, out_weights_sk):
         self._quiesced = False
         self._call(
-            "moonep_combine_pull", _ptr(plan_dst), _ptr(out_hidden), _ptr(out_weights_sk), self.epoch[FLAG_COMB],
+            "moonep_combine_pull", _ptr(plan_dst), _ptr(out_hidden), _ptr(out_weights_sk), self._cur(FLAG_COMB),
             self.pull_path, _stream(),
         )  # fmt: skip
 
@@ -343,7 +399,7 @@ class CudaBackend:
         ga = (ctypes.c_void_p * n)(*[g.data_ptr() - shift for g in grads])
         ra = (ctypes.c_void_p * n)(*[r.data_ptr() for r in reduce_buffers])
         self.signal(FLAG_GRAD_READY)
-        ready, done = self.epoch[FLAG_GRAD_READY], self._next(FLAG_GRAD_DONE)
+        ready, done = self._cur(FLAG_GRAD_READY), self._next(FLAG_GRAD_DONE)
         self._call("moonep_grad_reduce", ga, ra, n, _ptr(experts_to_copy), Bc, H * Hp, ready, done, 1, self.grad_path,
                    _stream(), tag="grad_accum")  # fmt: skip
         self.world.step()

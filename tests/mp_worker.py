@@ -264,10 +264,41 @@ def scenario_moe_layer(rank, R, dev):
         print("  moe layer ok", flush=True)
 
 
+def scenario_graph(rank, R, dev):
+    """A captured dispatch -> combine step replayed by every rank, mixed with ordinary calls."""
+    if dev.type != "cuda":
+        return
+    case = ROUNDTRIP_CASES[1]
+    buf = make_buffer(case, R)
+    topk, tpe, gates = routing_for(case, R, rank, device=dev)
+    x = torch.randn(case.S, case.H, device=dev).to(torch.bfloat16)
+
+    def step():
+        xn, wn, _, plan = buf.dispatch(x, gates, topk, tpe, zero_copy=True)
+        return buf.combine(plan, xn, wn, zero_copy=True)[:2]
+
+    def check(out, wb, what):
+        torch.cuda.synchronize()
+        buf.check_status()
+        assert torch.equal(out, (x.float() * case.K).to(torch.bfloat16)), f"{what}: identity round trip differs"
+        assert torch.equal(wb, gates), f"{what}: weights round trip differs"
+
+    graph_step = buf.capture(step)
+    for i in range(3):
+        x.copy_(torch.randn(case.S, case.H, device=dev).to(torch.bfloat16))
+        check(*graph_step.replay(), f"replay {i}")
+    check(*step(), "ordinary call after replays")
+    check(*graph_step.replay(), "replay after an ordinary call")
+    barrier(dev)
+    buf.destroy()
+    if rank == 0:
+        print("  graph capture ok", flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--backend", default="gloo", choices=["gloo", "nccl"])
-    ap.add_argument("--scenarios", default="round_trips,plan_reuse,weights,moe_layer")
+    ap.add_argument("--scenarios", default="round_trips,plan_reuse,weights,moe_layer,graph")
     args = ap.parse_args()
     rank = int(os.environ["RANK"])
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -289,6 +320,8 @@ def main():
         scenario_weights(rank, R, dev)
     if "moe_layer" in todo:
         scenario_moe_layer(rank, R, dev)
+    if "graph" in todo:
+        scenario_graph(rank, R, dev)
     barrier(dev)
     print(f"WORKER OK rank {rank}", flush=True)
     dist.destroy_process_group()
