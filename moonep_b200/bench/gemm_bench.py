@@ -2,8 +2,9 @@
 
     python -m moonep_b200.bench.gemm_bench [--rows 32768 --groups 40 --H 7168 --I 2048 --iters 10]
 
-Prints one JSON line per GEMM (SwiGLU gate/up, down projection) with TFLOP/s, the cuBLAS figure from
-MEASURED_PEAKS.json if present, and a torch per-group matmul baseline on the same data.
+Prints one JSON line per GEMM (SwiGLU gate/up, down projection, weight gradient of the down projection with
+and without the operand transposes) with TFLOP/s, the cuBLAS figure from MEASURED_PEAKS.json if present, and a
+torch batched-matmul baseline on the same data.
 """
 
 from __future__ import annotations
@@ -14,7 +15,8 @@ import os
 
 import torch
 
-from moonep_b200.ops.grouped_gemm import grouped_gemm
+from moonep_b200.ops.grouped_gemm import grouped_gemm, grouped_wgrad
+from moonep_b200.ops.moe_ops import transpose_experts
 
 
 def _time(fn, iters, flush):
@@ -88,6 +90,37 @@ def main():
             "tflops": round(f / t / 1e9, 1), "frac_of_measured_cublas_peak": round(f / t / 1e9 / peak, 3),
             "torch_bmm_plus_elementwise_ms": round(tr, 4), "speedup_vs_torch": round(tr / t, 2),
             "rel_err_vs_torch": round(err, 5), "measured_peak_tflops": peak,
+        }))  # fmt: skip
+
+    # weight gradient of the down projection: dW[g] (H x I, fp32) += dy_g^T h_g, contraction over the rows of a group
+    if total % 64 == 0 and a.H % 256 == 0 and a.I % 256 == 0:
+        dw = torch.zeros(a.groups, a.H, a.I, device=dev)
+        ptrs = torch.tensor([dw[g].data_ptr() for g in range(a.groups)], dtype=torch.int64, device=dev)
+        flags = torch.ones(a.groups, dtype=torch.int32, device=dev)  # accumulate, as in a training step
+        yt = torch.empty(1, a.H, total, dtype=torch.bfloat16, device=dev)
+        ht = torch.empty(1, a.I, total, dtype=torch.bfloat16, device=dev)
+
+        def transposes():
+            transpose_experts(y.unsqueeze(0), yt)
+            transpose_experts(h.unsqueeze(0), ht)
+
+        transposes()
+        t3 = _time(lambda: grouped_wgrad(yt[0], ht[0], ends, ptrs, flags, status=status), a.iters, flush)
+        t3t = _time(transposes, a.iters, flush)
+        assert status.tolist()[0] == 0, status.tolist()
+        ys = y.view(a.groups, per, a.H)
+        t3_ref = _time(lambda: torch.baddbmm(dw, ys.transpose(1, 2), hs, out=dw), a.iters, flush)
+        dw.zero_()
+        flags.zero_()
+        grouped_wgrad(yt[0], ht[0], ends, ptrs, flags, status=status)
+        ref3 = torch.bmm(ys[:2].transpose(1, 2).float(), hs[:2].float())
+        err3 = (dw[:2] - ref3).abs().max().item() / max(1e-6, ref3.abs().max().item())
+        print(json.dumps({
+            "gemm": "wgrad_down_accumulate", "rows": total, "groups": a.groups, "H": a.H, "I": a.I, "ms": round(t3, 4),
+            "tflops": round(f2 / t3 / 1e9, 1), "frac_of_measured_cublas_peak": round(f2 / t3 / 1e9 / peak, 3),
+            "operand_transposes_ms": round(t3t, 4), "torch_baddbmm_ms": round(t3_ref, 4),
+            "speedup_vs_torch": round(t3_ref / t3, 2), "speedup_vs_torch_with_transposes": round(t3_ref / (t3 + t3t), 2),
+            "rel_err_vs_torch": round(err3, 6), "measured_peak_tflops": peak,
         }))  # fmt: skip
 
 

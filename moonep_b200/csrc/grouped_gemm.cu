@@ -68,12 +68,12 @@ struct GemmArgs {
   int w_slots;           // number of weight slots (rows of W = w_slots * n_per_group)
 };
 
-__device__ __forceinline__ void gemm_fail(const GemmArgs& a, int where, int x, int y) {
-  if (a.status != nullptr && atomicCAS(a.status + MOONEP_ST_CODE, 0, MOONEP_STATUS_TIMEOUT) == 0) {
-    a.status[MOONEP_ST_KERNEL] = 13;
-    a.status[MOONEP_ST_FAMILY] = where;
-    a.status[MOONEP_ST_PEER] = x;
-    a.status[MOONEP_ST_EXPECT] = y;
+__device__ __forceinline__ void gemm_fail(int* status, int kernel, int where, int x, int y) {
+  if (status != nullptr && atomicCAS(status + MOONEP_ST_CODE, 0, MOONEP_STATUS_TIMEOUT) == 0) {
+    status[MOONEP_ST_KERNEL] = kernel;
+    status[MOONEP_ST_FAMILY] = where;
+    status[MOONEP_ST_PEER] = x;
+    status[MOONEP_ST_EXPECT] = y;
     __threadfence();
   }
 }
@@ -204,7 +204,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         const int wrow0 = wslot * a.n_per_group + nb * b_rows_per_tile;
         for (int kb = 0; kb < a.k_blocks; ++kb) {
           if (!mbar_wait(s_empty + stage, phase ^ 1u, a.timeout_ns)) {
-            gemm_fail(a, 1, stage, kb);
+            gemm_fail(a.status, 13, 1, stage, kb);
             failed = true;
             break;
           }
@@ -236,7 +236,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       for (long long t = blockIdx.x; t < num_tiles && !failed; t += gridDim.x, ++it) {
         const int buf = it & 1;
         if (!mbar_wait(s_tempty + buf, tphase[buf] ^ 1u, a.timeout_ns)) {
-          gemm_fail(a, 2, buf, it);
+          gemm_fail(a.status, 13, 2, buf, it);
           break;
         }
         tphase[buf] ^= 1u;
@@ -244,7 +244,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         const unsigned d_tmem = tmem_base + (unsigned)(buf * BN);
         for (int kb = 0; kb < a.k_blocks; ++kb) {
           if (!mbar_wait(s_full + stage, phase, a.timeout_ns)) {
-            gemm_fail(a, 3, stage, kb);
+            gemm_fail(a.status, 13, 3, stage, kb);
             failed = true;
             break;
           }
@@ -280,7 +280,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       if (lane == 0) got = mbar_wait(s_tfull + buf, tphase[buf], a.timeout_ns) ? 1 : 0;
       got = __shfl_sync(0xffffffffu, got, 0);
       if (!got) {
-        if (lane == 0) gemm_fail(a, 4, buf, it);
+        if (lane == 0) gemm_fail(a.status, 13, 4, buf, it);
         break;
       }
       tphase[buf] ^= 1u;
@@ -322,6 +322,228 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           for (int j = 0; j < 4; ++j)
             st16(orow + c0 + j * 8, make_int4((int)o[4 * j], (int)o[4 * j + 1], (int)o[4 * j + 2], (int)o[4 * j + 3]));
         }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_tempty + buf);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---- weight gradients: contraction over the rows of a group ----------------------------------------
+//
+//   dW[g] (P x Q, fp32) = L[rows of g, :P]^T  @  R[rows of g, :Q]
+//
+// The operands arrive transposed (Lt: [P, ld], Rt: [Q, ld], the row index contiguous), which makes
+// both K-major for the same TMA boxes, swizzle and MMA descriptors as the forward kernel; the K loop
+// of a tile runs over the group's rows (k0 = first row of the group, any multiple of 16 rows long; the
+// last 64-row block issues only the MMAs that lie inside the group).  One tile is 128 x 256 of one
+// group's dW.  Per group, flags[g] selects: 0 store (and store zeros if the group has no rows),
+// 1 add to what is there, 2 store, leave the target alone if the group has no rows.  A null
+// out_ptrs[g] skips the group; rows without a target are reported through the status block.
+struct WgradArgs {
+  float* const* out_ptrs;  // [G] device array
+  const int* flags;        // [G]
+  const int* cu_seqlens;   // [G] inclusive padded ends
+  int* status;
+  unsigned long long timeout_ns;
+  int G, P, Q, p_tiles, q_tiles, rows_cap;
+};
+
+struct WgradTile {
+  int g, pb, qb, k0, krows;
+  float* out;
+};
+
+__device__ __forceinline__ WgradTile wgrad_tile(const WgradArgs& a, long long t) {
+  WgradTile w;
+  const int per_group = a.p_tiles * a.q_tiles;
+  w.g = (int)(t / per_group);
+  const int rem = (int)(t % per_group);
+  w.pb = rem / a.q_tiles;
+  w.qb = rem % a.q_tiles;
+  const int start = w.g > 0 ? min(a.cu_seqlens[w.g - 1], a.rows_cap) : 0;
+  const int end = min(a.cu_seqlens[w.g], a.rows_cap);
+  w.k0 = start;
+  w.krows = end > start ? end - start : 0;
+  w.out = a.out_ptrs[w.g];
+  // the K coordinate of a TMA copy must be a multiple of 8 elements and the MMAs take 16 rows at a time:
+  // a group that does not start and end on a multiple of 16 is refused (reported as rows without a target)
+  if (((start | end) & 15) != 0) w.out = nullptr;
+  return w;
+}
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    grouped_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_l, const __grid_constant__ CUtensorMap tmap_r,
+                         const WgradArgs a) {
+  extern __shared__ unsigned char s_raw[];
+  __shared__ __align__(8) unsigned long long s_full[kStages], s_empty[kStages], s_tfull[2], s_tempty[2];
+  __shared__ unsigned s_tmem_base;
+  unsigned char* s_tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(s_raw) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(s_full + s, 1);
+      mbar_init(s_empty + s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(s_tfull + b, 1);
+      mbar_init(s_tempty + b, 4);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&s_tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const unsigned tmem_base = s_tmem_base;
+  const long long num_tiles = (long long)a.G * a.p_tiles * a.q_tiles;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      unsigned phase = 0;
+      bool failed = false;
+      for (long long t = blockIdx.x; t < num_tiles && !failed; t += gridDim.x) {
+        const WgradTile w = wgrad_tile(a, t);
+        if (w.krows == 0 || w.out == nullptr) continue;
+        const int kbs = (w.krows + BK - 1) / BK;
+        for (int kb = 0; kb < kbs; ++kb) {
+          if (!mbar_wait(s_empty + stage, phase ^ 1u, a.timeout_ns)) {
+            gemm_fail(a.status, 14, 1, stage, kb);
+            failed = true;
+            break;
+          }
+          unsigned char* st = s_tiles + (size_t)stage * kStageBytes;
+          mbar_expect_tx(s_full + stage, kStageBytes);
+          tma_load_2d(st, &tmap_l, w.k0 + kb * BK, w.pb * BM, s_full + stage);
+          tma_load_2d(st + kATileBytes, &tmap_r, w.k0 + kb * BK, w.qb * BN, s_full + stage);
+          tma_load_2d(st + kATileBytes + kBHalfBytes, &tmap_r, w.k0 + kb * BK, w.qb * BN + 128, s_full + stage);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr unsigned idesc = make_idesc(BM, BN);
+      int stage = 0;
+      unsigned phase = 0;
+      unsigned tphase[2] = {0, 0};
+      int it = 0;
+      bool failed = false;
+      for (long long t = blockIdx.x; t < num_tiles && !failed; t += gridDim.x) {
+        const WgradTile w = wgrad_tile(a, t);
+        if (w.krows == 0 || w.out == nullptr) continue;
+        const int buf = it & 1;
+        ++it;
+        if (!mbar_wait(s_tempty + buf, tphase[buf] ^ 1u, a.timeout_ns)) {
+          gemm_fail(a.status, 14, 2, buf, it);
+          break;
+        }
+        tphase[buf] ^= 1u;
+        tc_fence_after();
+        const unsigned d_tmem = tmem_base + (unsigned)(buf * BN);
+        const int kbs = (w.krows + BK - 1) / BK;
+        for (int kb = 0; kb < kbs; ++kb) {
+          if (!mbar_wait(s_full + stage, phase, a.timeout_ns)) {
+            gemm_fail(a.status, 14, 3, stage, kb);
+            failed = true;
+            break;
+          }
+          tc_fence_after();
+          const unsigned char* st = s_tiles + (size_t)stage * kStageBytes;
+          const unsigned long long adesc = make_smem_desc(st);
+          const unsigned long long bdesc = make_smem_desc(st + kATileBytes);
+          const int nkk = min(BK / UMMA_K, (w.krows - kb * BK) / UMMA_K);  // MMAs inside the group
+          for (int kk = 0; kk < nkk; ++kk)
+            umma_bf16(d_tmem, adesc + (unsigned long long)(kk * 2), bdesc + (unsigned long long)(kk * 2), idesc,
+                      (kb | kk) != 0 ? 1u : 0u);
+          umma_commit(s_empty + stage);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!failed) umma_commit(s_tfull + buf);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- epilogue (warps 2..5): one output row per thread ----------------
+    const int q = warp & 3;
+    unsigned tphase[2] = {0, 0};
+    int it = 0;
+    for (long long t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      const WgradTile w = wgrad_tile(a, t);
+      const int flag = a.flags[w.g];
+      if (w.out == nullptr) {
+        if (w.krows != 0 && q == 0 && lane == 0 && w.pb == 0 && w.qb == 0 && a.status != nullptr &&
+            atomicCAS(a.status + MOONEP_ST_CODE, 0, MOONEP_STATUS_BAD_INDEX) == 0) {
+          a.status[MOONEP_ST_KERNEL] = 14;
+          a.status[MOONEP_ST_FAMILY] = 100;  // kind: rows of a group whose gradient has no target
+          a.status[MOONEP_ST_PEER] = w.g;
+          a.status[MOONEP_ST_EXPECT] = 0;
+          a.status[MOONEP_ST_SEEN] = w.krows;
+          __threadfence();
+        }
+        continue;
+      }
+      float* orow = w.out + (long long)(w.pb * BM + q * 32 + lane) * a.Q + (long long)w.qb * BN;
+      if (w.krows == 0) {
+        if (flag == 0) {
+          const int4 z = make_int4(0, 0, 0, 0);
+#pragma unroll 4
+          for (int c = 0; c < BN; c += 4) st16(orow + c, z);
+        }
+        continue;
+      }
+      const int buf = it & 1;
+      ++it;
+      int got = 1;
+      if (lane == 0) got = mbar_wait(s_tfull + buf, tphase[buf], a.timeout_ns) ? 1 : 0;
+      got = __shfl_sync(0xffffffffu, got, 0);
+      if (!got) {
+        if (lane == 0) gemm_fail(a.status, 14, 4, buf, it);
+        break;
+      }
+      tphase[buf] ^= 1u;
+      tc_fence_after();
+      const unsigned taddr = tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)(buf * BN);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        unsigned v[32];
+        tmem_ld32(taddr + (unsigned)c0, v);
+        tmem_ld_wait();
+        if (flag == 1) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int4 old = ld16(orow + c0 + 4 * j);
+            v[4 * j] = __float_as_uint(__uint_as_float(v[4 * j]) + __int_as_float(old.x));
+            v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) + __int_as_float(old.y));
+            v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) + __int_as_float(old.z));
+            v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + __int_as_float(old.w));
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          st16(orow + c0 + 4 * j, make_int4((int)v[4 * j], (int)v[4 * j + 1], (int)v[4 * j + 2], (int)v[4 * j + 3]));
       }
       tc_fence_before();
       __syncwarp();
@@ -445,4 +667,51 @@ extern "C" int moonep_grouped_gemm(const void* x, const void* w0, const void* w1
   }
   grouped_gemm_kernel<<<grid, kGemmThreads, smem, (cudaStream_t)stream>>>(ta, tb0, tb1, a);
   return check_launch("grouped_gemm_kernel");
+}
+
+// lt: [P, ld] bf16 = L^T, rt: [Q, ld] bf16 = R^T (ld elements per row, a multiple of 8; the column index is the
+// row of the dispatched shard).  For every group g with rows [cu[g-1], cu[g]) (a multiple of 16 long):
+// out_ptrs[g][P, Q] fp32 = or += L_g^T R_g according to flags[g] (see the kernel).  out_ptrs and flags are
+// device arrays of G entries.  P % 128 == 0, Q % 256 == 0.
+extern "C" int moonep_grouped_wgrad(const void* lt, const void* rt, long long ld, int P, int Q, const int* cu_seqlens,
+                                    int G, void* const* out_ptrs, const int* flags, int rows_cap, int* status,
+                                    long long timeout_ms, int num_sms, void* stream) {
+  if (P <= 0 || Q <= 0 || P % BM != 0 || Q % BN != 0) {
+    set_error("moonep_grouped_wgrad: P must be a multiple of 128 and Q a multiple of 256");
+    return 1;
+  }
+  if (ld <= 0 || ld % 8 != 0 || rows_cap > ld) {
+    set_error("moonep_grouped_wgrad: ld must be a multiple of 8 and at least rows_cap");
+    return 1;
+  }
+  CUtensorMap tl, tr;
+  if (int rc = make_tmap(&tl, lt, (unsigned long long)P, (unsigned long long)ld, 128)) return rc;
+  if (int rc = make_tmap(&tr, rt, (unsigned long long)Q, (unsigned long long)ld, 128)) return rc;
+  WgradArgs a;
+  a.out_ptrs = (float* const*)out_ptrs;
+  a.flags = flags;
+  a.cu_seqlens = cu_seqlens;
+  a.status = status;
+  a.timeout_ns = (unsigned long long)(timeout_ms > 0 ? timeout_ms : 10000) * 1000000ull;
+  a.G = G;
+  a.P = P;
+  a.Q = Q;
+  a.p_tiles = P / BM;
+  a.q_tiles = Q / BN;
+  a.rows_cap = rows_cap;
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int grid = imax(1, num_sms > 0 ? imin(num_sms, sms) : sms);
+  const size_t smem = (size_t)kStages * kStageBytes + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (int rc = check_cuda(cudaFuncSetAttribute(grouped_wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 (int)smem),
+                            "cudaFuncSetAttribute(grouped_wgrad_kernel)"))
+      return rc;
+    attr_set = true;
+  }
+  grouped_wgrad_kernel<<<grid, kGemmThreads, smem, (cudaStream_t)stream>>>(tl, tr, a);
+  return check_launch("grouped_wgrad_kernel");
 }

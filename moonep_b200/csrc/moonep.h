@@ -163,6 +163,25 @@ int moonep_grad_reduce(void* ctx, float* const* grads, float* const* reduce, int
                        const int* experts_to_copy, int Bcols, long long elems, int epoch_ready, int epoch_done,
                        int phase, int path, void* stream);
 
+// Expert computation (tcgen05 tensor cores).  None of these has a counterpart in the reference, which has no GEMM.
+// y[rows of g] = x[rows of g] @ w[g]^T for the padded row groups of a dispatched shard; mode 0 plain, 1 SwiGLU
+// (w0 = gate, w1 = up), 2 scaled by row_scale.  See grouped_gemm.cu.
+int moonep_grouped_gemm(const void* x, const void* w0, const void* w1, void* out, const float* row_scale,
+                        const int* cu_seqlens, int G, int rows_cap, int K, int n_per_group, int mode, int* status,
+                        long long timeout_ms, int num_sms, const int* group_map, int w_slots, void* stream);
+// Weight gradients of all groups: out_ptrs[g][P, Q] fp32 (=, +=) L_g^T R_g with the contraction over the rows of
+// group g.  lt = L^T [P, ld], rt = R^T [Q, ld] bf16 (ld a multiple of 8, >= rows_cap).  flags[g]: 0 store (zeros for
+// an empty group), 1 accumulate, 2 store and leave empty groups alone.  out_ptrs, flags: device arrays [G].
+int moonep_grouped_wgrad(const void* lt, const void* rt, long long ld, int P, int Q, const int* cu_seqlens, int G,
+                         void* const* out_ptrs, const int* flags, int rows_cap, int* status, long long timeout_ms,
+                         int num_sms, void* stream);
+// Helpers of the MoE layer's backward pass and optimiser step, see moe_kernels.cu.
+int moonep_transpose_experts(const void* src, void* dst, int n, int d0, int d1, long long dst_ld,
+                             long long dst_expert_stride, int col0, void* stream);
+int moonep_swiglu_bwd(const void* a, const void* u, const void* g, const float* w, const int* total_rows, int rows_cap,
+                      int I, void* dadu, void* hsw, float* dgate, void* stream);
+int moonep_sgd_update(void* w, const float* g, long long n, float lr, void* stream);
+
 // CUDA VMM symmetric allocator (driver API through cudaGetDriverEntryPoint).
 int moonep_vmm_granularity(int device, unsigned long long* gran);
 int moonep_vmm_create(int device, unsigned long long bytes, unsigned long long* handle, int* fd);

@@ -20,7 +20,8 @@ remote expert that did not get a prefetch slot is read in place over NVLink.
 
 Usage pattern of the reference's Buffer API: reference ``README.md:46-48`` and ``tests/test_e2e.py:201-431``.
 In the backward pass the activation gradients run on the same grouped GEMM (with per-call K-major copies of
-the local experts); the weight gradients are per-group matmuls.
+the local experts); the weight gradients run on its sibling kernel whose contraction is over the rows of a
+group (per-group matmuls where the shapes do not fit its tiling, and on CPU).
 """
 
 from __future__ import annotations
@@ -28,7 +29,14 @@ from __future__ import annotations
 import torch
 
 from ..api import Buffer
-from ..ops.grouped_gemm import grouped_gemm
+from ..ops.grouped_gemm import (
+    WGRAD_ACCUMULATE,
+    WGRAD_STORE,
+    WGRAD_STORE_NONEMPTY,
+    grouped_gemm,
+    grouped_wgrad,
+    wgrad_kernel_supports,
+)
 from ..ops.moe_ops import sgd_update, swiglu_bwd, transpose_experts
 from ..parallel.symm import create_full_expert_weight, create_nvl_dist_tensor, view_nvl_dist_rows
 
@@ -68,6 +76,21 @@ class ExpertParallelMoE:
         self._red_full = [create_nvl_dist_tensor([B, d0, d1], torch.float32, w, pad_dim0=False)
                           for d0, d1 in ((I, H), (I, H), (H, I))]  # fmt: skip
         self.red = [view_nvl_dist_rows(t, self.R, B) for t in self._red_full]
+        # per group: where its weight gradient goes (0 = nowhere: a remote expert without a prefetch slot) and how
+        own0 = self.rank * self.epn
+        self._wgrad_ptrs, fresh, later = [], [], []
+        for t, gt in enumerate((self.g_gate, self.g_up, self.g_down)):
+            ptrs = [0] * (E + B)
+            for le in range(self.epn):
+                ptrs[own0 + le] = gt[le].data_ptr()
+            for b in range(B):
+                ptrs[E + b] = self.red[t][self.rank, b].data_ptr()
+            self._wgrad_ptrs.append(torch.tensor(ptrs, dtype=torch.int64).to(dev))
+        for g in range(E + B):
+            fresh.append(WGRAD_STORE if g < E else WGRAD_STORE_NONEMPTY)
+            later.append(WGRAD_ACCUMULATE if g < E else WGRAD_STORE_NONEMPTY)
+        self._wgrad_flags = {True: torch.tensor(fresh, dtype=torch.int32).to(dev),
+                             False: torch.tensor(later, dtype=torch.int32).to(dev)}  # fmt: skip
         w.host_barrier()
 
     # -- forward -------------------------------------------------------------------------------
@@ -120,8 +143,8 @@ class ExpertParallelMoE:
 
         Activation gradients and the recomputed pre-activations run on the grouped GEMM (K-major copies of
         the local experts are rebuilt per call because the weights change every step); the weight gradients,
-        whose contraction runs over the rows of a group, are per-group matmuls written straight into the
-        gradient of an owned expert or into the reduce-buffer slot of a prefetched copy.
+        whose contraction runs over the rows of a group, are written straight into the gradient of an owned
+        expert or into the reduce-buffer slot of a prefetched copy.
         """
         buf, E, B, epn, I = self.buffer, self.E, self.B, self.epn, self.I
         ctx = buf._require_ctx()
@@ -138,6 +161,12 @@ class ExpertParallelMoE:
         dgate_nvs = ctx["weights_buf_local"].view(torch.float32)  # gate gradients ride the weights channel home
         swiglu_bwd(a, u, g, w_nvs, cu[-1:], dadu, hsw, dgate_nvs)
         del a, u, g
+        if self._weight_grads_on_kernel(x_nvs, dy_nvs, dadu, hsw, cu):
+            grouped_gemm(dadu, self._local_transposed([self.w_gate, self.w_up]), cu, group_map=gmap, out=dy_nvs)
+            dx, dgates, _ = buf.combine(plan, dy_nvs, dgate_nvs, zero_copy=True)
+            buf.reduce_grad(plan, False, self.g_gate, self.g_up, self.g_down, self.red[0], self.red[1], self.red[2],
+                            owner_local=True)  # fmt: skip
+            return dx, dgates
         ends = cu.tolist()
         start = 0
         md = self.matmul_dtype
@@ -168,6 +197,34 @@ class ExpertParallelMoE:
         buf.reduce_grad(plan, False, self.g_gate, self.g_up, self.g_down, self.red[0], self.red[1], self.red[2],
                         owner_local=True)  # fmt: skip
         return dx, dgates
+
+    def _weight_grads_on_kernel(self, x_nvs, dy_nvs, dadu, hsw, cu) -> bool:
+        """All weight gradients with three launches of the grouped tcgen05 kernel (no host synchronisation):
+        the operands are transposed once so that the contraction over a group's rows is K-major, and every
+        group's result goes straight to the owner's gradient or to the reduce-buffer slot of a prefetched copy.
+        Returns False (nothing done) when the shapes do not fit the kernel."""
+        I, H = self.I, self.H
+        rows = int(x_nvs.shape[0]) // 64 * 64
+        dev = x_nvs.device
+        ok = (
+            x_nvs.is_cuda and rows >= 64 and self.buffer._require_ctx()["token_padding"] % 16 == 0
+            and wgrad_kernel_supports(I, H, rows, dev) and wgrad_kernel_supports(H, I, rows, dev)
+        )  # fmt: skip
+        if not ok:
+            return False
+
+        def transposed(t):
+            out = torch.empty(1, int(t.shape[1]), rows, dtype=torch.bfloat16, device=dev)
+            return transpose_experts(t[:rows].unsqueeze(0), out)[0]
+
+        xt, dadut, dyt, hswt = transposed(x_nvs), transposed(dadu), transposed(dy_nvs), transposed(hsw)
+        flags = self._wgrad_flags[bool(self._fresh)]
+        status = self.buffer._require_ctx()["_backend"].status
+        grouped_wgrad(dadut[:I], xt, cu, self._wgrad_ptrs[0], flags, status=status)  # dW_gate = da^T x
+        grouped_wgrad(dadut[I:], xt, cu, self._wgrad_ptrs[1], flags, status=status)  # dW_up   = du^T x
+        grouped_wgrad(dyt, hswt, cu, self._wgrad_ptrs[2], flags, status=status)  # dW_down = dy^T (h * gate weight)
+        self._fresh = False
+        return True
 
     def zero_grad(self):
         """Lazy: the next backward overwrites (instead of adding to) the gradients of the experts it visits

@@ -41,6 +41,7 @@ _PATHS = {"ldst": 0, "bulk": 1}
 _KERNEL_NAMES = {
     1: "signal", 2: "plan_publish", 3: "plan_tables", 4: "plan_tokens", 5: "dispatch_send", 6: "dispatch_expand",
     7: "combine_prologue", 8: "combine_pull", 9: "prefetch", 10: "grad_accum", 11: "grad_clear", 12: "wait",
+    13: "grouped_gemm", 14: "grouped_wgrad",
 }  # fmt: skip
 _FAMILY_NAMES = {0: "READY", 1: "TPE", 2: "PLAN", 3: "SENT", 4: "COMB", 5: "GRAD_READY", 6: "GRAD_DONE"}
 

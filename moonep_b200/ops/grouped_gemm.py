@@ -94,6 +94,61 @@ def grouped_gemm(x, w, cu_seqlens, *, w_up=None, row_scale=None, mode="plain", o
     return out
 
 
+WGRAD_STORE, WGRAD_ACCUMULATE, WGRAD_STORE_NONEMPTY = 0, 1, 2
+
+
+def grouped_wgrad_reference(left, right, cu_seqlens, targets, flags):
+    """Per-group matmuls: ``targets[g] (=, +=) left[rows of g].T @ right[rows of g]`` (the oracle and CPU path).
+    ``targets[g]`` is an fp32 ``[P, Q]`` tensor or None; ``flags`` as in ``grouped_wgrad``."""
+    ends = cu_seqlens.tolist()
+    start = 0
+    for g, tgt in enumerate(targets):
+        end = int(ends[g])
+        flag = int(flags[g])
+        if tgt is not None:
+            if end > start:
+                mm = left[start:end].float().t() @ right[start:end].float()
+                if flag == WGRAD_ACCUMULATE:
+                    tgt.add_(mm)
+                else:
+                    tgt.copy_(mm)
+            elif flag == WGRAD_STORE:
+                tgt.zero_()
+        start = max(start, end)
+
+
+def wgrad_kernel_supports(P: int, Q: int, ld: int, device) -> bool:
+    return torch.device(device).type == "cuda" and P % 128 == 0 and Q % 256 == 0 and ld % 64 == 0 and ld > 0
+
+
+def grouped_wgrad(left_t, right_t, cu_seqlens, out_ptrs, flags, *, status=None, num_sms=0):
+    """Weight gradients of every group in one launch of the tcgen05 kernel.
+
+    ``left_t``: ``[P, ld]`` bf16 and ``right_t``: ``[Q, ld]`` bf16 are the TRANSPOSED operands (column index =
+    row of the dispatched shard), so that the contraction over a group's rows is K-major for both.  For group
+    ``g`` with rows ``[cu[g-1], cu[g])`` (multiples of 16): the fp32 ``[P, Q]`` matrix at address ``out_ptrs[g]``
+    (int64 device tensor, 0 = skip) is overwritten (``flags[g] == 0``; zeros if the group is empty), added to
+    (``1``) or overwritten unless the group is empty (``2``).  ``flags``: int32 device tensor ``[G]``.
+    """
+    P, ld = (int(v) for v in left_t.shape)
+    Q = int(right_t.shape[0])
+    G = int(cu_seqlens.numel())
+    assert right_t.shape[1] == ld and left_t.dtype == torch.bfloat16 and right_t.dtype == torch.bfloat16
+    assert left_t.is_contiguous() and right_t.is_contiguous()
+    assert wgrad_kernel_supports(P, Q, ld, left_t.device), f"grouped_wgrad: P={P}, Q={Q}, ld={ld} do not fit the tiling"
+    assert out_ptrs.dtype == torch.int64 and out_ptrs.numel() == G and out_ptrs.is_cuda and out_ptrs.is_contiguous()
+    assert flags.dtype == torch.int32 and flags.numel() == G and flags.is_cuda and flags.is_contiguous()
+    assert cu_seqlens.dtype == torch.int32 and cu_seqlens.is_contiguous() and cu_seqlens.is_cuda
+    lib = _lib.load()
+    with torch.cuda.device(left_t.device):
+        rc = lib.moonep_grouped_wgrad(
+            left_t.data_ptr(), right_t.data_ptr(), ld, P, Q, cu_seqlens.data_ptr(), G, out_ptrs.data_ptr(),
+            flags.data_ptr(), ld, None if status is None else status.data_ptr(), config.timeout_ms(), int(num_sms),
+            torch.cuda.current_stream().cuda_stream,
+        )  # fmt: skip
+    _lib.check(rc, "moonep_grouped_wgrad")
+
+
 def _fallback_allowed() -> bool:
     import os
 

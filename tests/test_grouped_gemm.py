@@ -56,3 +56,73 @@ def test_grouped_gemm_matches_fp32_reference(mode, G, rows, K, N):
     y2 = grouped_gemm(x, w, cu, mode=mode, status=status, **kw)
     torch.cuda.synchronize()
     assert torch.equal(y[:total], y2[:total])
+
+
+def _wgrad_case(rows, P, Q, seed=0, device="cpu"):
+    g = torch.Generator().manual_seed(seed)
+    ends, total = [], 0
+    for r in rows:
+        total += r
+        ends.append(total)
+    cap = (total + 64 + 63) // 64 * 64
+    left = (torch.randn(cap, P, generator=g) * 0.5).to(torch.bfloat16).to(device)
+    right = (torch.randn(cap, Q, generator=g) * 0.5).to(torch.bfloat16).to(device)
+    cu = torch.tensor(ends, dtype=torch.int32, device=device)
+    return left, right, cu, cap
+
+
+def test_wgrad_reference_semantics_on_cpu():
+    from moonep_b200.ops.grouped_gemm import grouped_wgrad_reference
+
+    left, right, cu, cap = _wgrad_case([32, 0, 16, 0], 8, 4)
+    tg = [torch.full((8, 4), 7.0) for _ in range(4)]
+    tg[2] = None
+    grouped_wgrad_reference(left, right, cu, tg, [1, 0, 0, 2])
+    assert torch.allclose(tg[0], 7.0 + left[:32].float().t() @ right[:32].float())
+    assert not bool(tg[1].abs().max() > 0), "an empty group with the store flag is zeroed"
+    assert bool((tg[3] == 7.0).all()), "an empty group with the keep flag is left alone"
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize(
+    "rows,P,Q",
+    [
+        ([128], 128, 256),
+        ([64, 0, 192, 16, 80], 256, 256),
+        ([256, 128, 0, 0, 1024, 48, 128, 0], 128, 512),
+        ([128 * ((i * 5) % 4) for i in range(20)], 384, 768),
+    ],
+)
+def test_grouped_wgrad_matches_fp32_reference(rows, P, Q):
+    from moonep_b200.ops.grouped_gemm import grouped_wgrad, grouped_wgrad_reference
+    from moonep_b200.ops.moe_ops import transpose_experts
+
+    G = len(rows)
+    left, right, cu, cap = _wgrad_case(rows, P, Q, seed=len(rows), device="cuda")
+    lt = transpose_experts(left.unsqueeze(0), torch.empty(1, P, cap, dtype=torch.bfloat16, device="cuda"))[0]
+    rt = transpose_experts(right.unsqueeze(0), torch.empty(1, Q, cap, dtype=torch.bfloat16, device="cuda"))[0]
+    flag_list = [(0, 1, 2)[g % 3] for g in range(G)]
+    skipped = G - 1 if rows[-1] == 0 else None  # a group without a target is allowed when it has no rows
+    init = torch.randn(G, P, Q, device="cuda")
+    out = init.clone()
+    ptrs = [out[g].data_ptr() for g in range(G)]
+    if skipped is not None:
+        ptrs[skipped] = 0
+    status = torch.zeros(8, dtype=torch.int32, device="cuda")
+    flags = torch.tensor(flag_list, dtype=torch.int32, device="cuda")
+    grouped_wgrad(lt, rt, cu, torch.tensor(ptrs, dtype=torch.int64, device="cuda"), flags, status=status)
+    torch.cuda.synchronize()
+    assert status.tolist()[0] == 0, f"kernel reported status {status.tolist()}"
+    want = init.clone().cpu()
+    targets = [None if g == skipped else want[g] for g in range(G)]
+    grouped_wgrad_reference(left.cpu(), right.cpu(), cu.cpu(), targets, flag_list)
+    err = (out.cpu() - want).abs().max().item()
+    tol = 2e-3 * max(1.0, want.abs().max().item())
+    assert err <= tol, f"max abs err {err} > {tol}"
+    # again on the same buffers: accumulating groups add a second time, the others give the same result
+    grouped_wgrad(lt, rt, cu, torch.tensor(ptrs, dtype=torch.int64, device="cuda"), flags, status=status)
+    torch.cuda.synchronize()
+    assert status.tolist()[0] == 0
+    grouped_wgrad_reference(left.cpu(), right.cpu(), cu.cpu(), targets, flag_list)
+    err = (out.cpu() - want).abs().max().item()
+    assert err <= 2 * tol, f"second launch: max abs err {err}"
