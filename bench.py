@@ -276,7 +276,7 @@ def run_steps(args, BufferCls, rank, n, reference=False):
 def run_moe_step(args, rank, n):
     """SwiGLU MoE layer training step: dispatch -> prefetch -> grouped GEMMs -> combine, backward with the
     plan replayed, reduce_grad, SGD on the owned experts.  Device-timed, max over ranks."""
-    from moonep_b200 import Buffer
+    from moonep_b200 import Buffer, config
     from moonep_b200.models.moe_layer import ExpertParallelMoE
     from moonep_b200.models.routing import make_routing
     from moonep_b200.utils.clocks import ClockSampler
@@ -326,7 +326,9 @@ def run_moe_step(args, rank, n):
         "data": "synthetic, random-init weights ~N(0,0.02)",
         "config": {"model": "SwiGLU MoE layer (dispatch->prefetch->grouped GEMM->combine, backward with reduce_grad)",
                    "S_per_rank": S, "H": H, "K": K, "E": E, "inter": inter, "parallelism": f"ep{n}",
-                   "routing": args.routing, "backward_gemms": "activation grads: tcgen05 grouped GEMM; weight grads: torch matmul per group (bf16)"},
+                   "routing": args.routing, "prefetch_slots": slots,
+                   "backward_gemms": "activation and weight gradients: tcgen05 grouped GEMMs" if config.wgrad_on_kernel()
+                   else "activation grads: tcgen05 grouped GEMM; weight grads: torch matmul per group (bf16)"},
         "forward_tflops_per_gpu": flops_fwd / (t_f / 1e3) / 1e12, "finite": bool(torch.isfinite(out.float()).all()),
         "clocks": clocks.summary(),
     }  # fmt: skip

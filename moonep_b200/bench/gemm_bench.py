@@ -109,7 +109,7 @@ def main():
         t3t = _time(transposes, a.iters, flush)
         assert status.tolist()[0] == 0, status.tolist()
         ys = y.view(a.groups, per, a.H)
-        t3_ref = _time(lambda: torch.baddbmm(dw, ys.transpose(1, 2), hs, out=dw), a.iters, flush)
+        t3_ref = _time(lambda: dw.add_(torch.bmm(ys.transpose(1, 2), hs)), a.iters, flush)  # bf16 bmm, fp32 add
         dw.zero_()
         flags.zero_()
         grouped_wgrad(yt[0], ht[0], ends, ptrs, flags, status=status)
@@ -118,7 +118,7 @@ def main():
         print(json.dumps({
             "gemm": "wgrad_down_accumulate", "rows": total, "groups": a.groups, "H": a.H, "I": a.I, "ms": round(t3, 4),
             "tflops": round(f2 / t3 / 1e9, 1), "frac_of_measured_cublas_peak": round(f2 / t3 / 1e9 / peak, 3),
-            "operand_transposes_ms": round(t3t, 4), "torch_baddbmm_ms": round(t3_ref, 4),
+            "operand_transposes_ms": round(t3t, 4), "torch_bmm_then_add_ms": round(t3_ref, 4),
             "speedup_vs_torch": round(t3_ref / t3, 2), "speedup_vs_torch_with_transposes": round(t3_ref / (t3 + t3t), 2),
             "rel_err_vs_torch": round(err3, 6), "measured_peak_tflops": peak,
         }))  # fmt: skip

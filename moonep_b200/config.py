@@ -62,6 +62,17 @@ def debug() -> bool:
     return os.environ.get("MOONEP_DEBUG", "0") not in _FALSE
 
 
+def wgrad_on_kernel() -> bool:
+    """MOONEP_WGRAD=torch: the MoE layer computes weight gradients with per-group torch matmuls instead of the
+    grouped tcgen05 kernel (for comparisons)."""
+    return os.environ.get("MOONEP_WGRAD", "kernel").lower() != "torch"
+
+
+def nvtx() -> bool:
+    """MOONEP_NVTX=1: wrap every native call in an NVTX range named after the kernel."""
+    return os.environ.get("MOONEP_NVTX", "0") not in _FALSE
+
+
 def pipeline_enabled() -> bool:
     return os.environ.get("MOONEP_TD_PIPELINE", "0") not in _FALSE
 

@@ -102,6 +102,12 @@ __device__ __forceinline__ bool block_wait_flags(const MoonepDevCtx& c, int fami
           }
           __nanosleep(64);
         }
+        // wait statistics: longest wait on this family and number of waits that had to spin
+        if (blockIdx.x == 0) {
+          atomicMax(reinterpret_cast<unsigned long long*>(c.stats) + MOONEP_STAT_WAIT_MAX_NS + family,
+                    globaltimer_ns() - t0);
+          atomicAdd(reinterpret_cast<unsigned long long*>(c.stats) + MOONEP_STAT_WAIT_COUNT + family, 1ull);
+        }
       }
     }
   }

@@ -60,6 +60,10 @@
 #define MOONEP_K_GRAD_CLEAR 11
 #define MOONEP_K_WAIT 12
 #define MOONEP_NUM_KERNEL_IDS 16
+// stats[MOONEP_STAT_WAIT_MAX_NS + family]: longest time CTA 0 of any kernel spun on a flag of that family (ns);
+// stats[MOONEP_STAT_WAIT_COUNT + family]: number of such waits that did not find the flag already set.
+#define MOONEP_STAT_WAIT_MAX_NS 0
+#define MOONEP_STAT_WAIT_COUNT 8
 // counters[MOONEP_BIAS_OFF + family]: epoch bias added to every epoch argument of that family.
 #define MOONEP_BIAS_OFF 32
 
@@ -100,7 +104,7 @@ struct MoonepDevCtx {
   int* primary_packed;  // [R*S]
   int* kmask;           // [R*S]
   int* kidx_to_loff;    // [R*S*K]
-  long long* stats;     // [16] counters (rows sent, duplicates, ...)
+  long long* stats;     // [16] flag-wait statistics, see MOONEP_STAT_*
 };
 
 #ifdef __cplusplus

@@ -28,6 +28,7 @@ from __future__ import annotations
 
 import torch
 
+from .. import config
 from ..api import Buffer
 from ..ops.grouped_gemm import (
     WGRAD_ACCUMULATE,
@@ -207,7 +208,7 @@ class ExpertParallelMoE:
         rows = int(x_nvs.shape[0]) // 64 * 64
         dev = x_nvs.device
         ok = (
-            x_nvs.is_cuda and rows >= 64 and self.buffer._require_ctx()["token_padding"] % 16 == 0
+            config.wgrad_on_kernel() and x_nvs.is_cuda and rows >= 64 and self.buffer._require_ctx()["token_padding"] % 16 == 0
             and wgrad_kernel_supports(I, H, rows, dev) and wgrad_kernel_supports(H, I, rows, dev)
         )  # fmt: skip
         if not ok:

@@ -72,6 +72,7 @@ class CudaBackend:
         self.pull_path = _PATHS[config.copy_path("pull")]
         self.grad_path = _PATHS[config.copy_path("grad")]
         self._profile = None
+        self._nvtx = config.nvtx()
         self._quiesced = False  # every peer is known to be past its last pull from this rank's shard
 
         def i32(n):
@@ -139,9 +140,15 @@ class CudaBackend:
         out = {"backend": "cuda", "epochs": list(self.epoch), "status": self.status.cpu().tolist(),
                "native_launches_in_process": int(self.lib.moonep_launch_count()),
                "send_path": "bulk" if self.send_path else "ldst", "pull_path": "bulk" if self.pull_path else "ldst"}  # fmt: skip
+        st = self.stats_buf.cpu().tolist()
+        out["flag_wait_max_us"] = {_FAMILY_NAMES[f]: st[f] / 1e3 for f in _FAMILY_NAMES if st[8 + f]}
+        out["flag_waits_that_spun"] = {_FAMILY_NAMES[f]: st[8 + f] for f in _FAMILY_NAMES if st[8 + f]}
         if self._profile:
             out["phase_times_us"] = self.phase_times()
         return out
+
+    def reset_wait_stats(self):
+        self.stats_buf.zero_()
 
     def _next(self, family: int) -> int:
         """Advance the family's epoch; return it as a launch argument (relative to the device-side bias)."""
@@ -203,6 +210,13 @@ class CudaBackend:
 
     def _call(self, name, *args, tag=None):
         with torch.cuda.device(self.ctx["device"]):
+            if self._nvtx:
+                torch.cuda.nvtx.range_push(tag or name)
+                try:
+                    _lib.check(getattr(self.lib, name)(self.handle, *args), name)
+                finally:
+                    torch.cuda.nvtx.range_pop()
+                return
             if self._profile is None:
                 _lib.check(getattr(self.lib, name)(self.handle, *args), name)
                 return

@@ -54,6 +54,8 @@ def test_captured_round_trip_replays_and_mixes_with_eager_calls():
     buf.check_status()
     assert torch.equal(out, _expected(x2, K)) and out_b.data_ptr() == out.data_ptr()
     assert graph_step.replays == 5
+    st = buf.stats()
+    assert "flag_wait_max_us" in st and "flag_waits_that_spun" in st
     buf.destroy()
 
 
