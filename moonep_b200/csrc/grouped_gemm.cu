@@ -348,6 +348,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 // group's dW.  Per group, flags[g] selects: 0 store (and store zeros if the group has no rows),
 // 1 add to what is there, 2 store, leave the target alone if the group has no rows.  A null
 // out_ptrs[g] skips the group; rows without a target are reported through the status block.
+constexpr int kWgradStageLd = 36;  // floats per row of an epilogue warp's 32 x 32 staging block (16-byte aligned, conflict free)
+constexpr size_t kWgradStageBytes = 4 * 32 * kWgradStageLd * sizeof(float);
+
 struct WgradArgs {
   float* const* out_ptrs;  // [G] device array
   const int* flags;        // [G]
@@ -488,6 +491,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   } else {
     // ---------------- epilogue (warps 2..5): one output row per thread ----------------
     const int q = warp & 3;
+    float* stage_w = reinterpret_cast<float*>(s_tiles + (size_t)kStages * kStageBytes) + (warp - 2) * 32 * kWgradStageLd;
     unsigned tphase[2] = {0, 0};
     int it = 0;
     for (long long t = blockIdx.x; t < num_tiles; t += gridDim.x) {
@@ -526,24 +530,32 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       tphase[buf] ^= 1u;
       tc_fence_after();
       const unsigned taddr = tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)(buf * BN);
+      // A thread reads one accumulator row (32 columns) from TMEM; the chunk is turned through shared memory
+      // so that eight lanes write one full 128-byte line and a warp instruction covers four rows.
+      float* tile_out = w.out + (long long)(w.pb * BM + q * 32) * a.Q + (long long)w.qb * BN;
+      const int sub_row = lane >> 3, col4 = (lane & 7) * 4;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         unsigned v[32];
         tmem_ld32(taddr + (unsigned)c0, v);
         tmem_ld_wait();
-        if (flag == 1) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int4 old = ld16(orow + c0 + 4 * j);
-            v[4 * j] = __float_as_uint(__uint_as_float(v[4 * j]) + __int_as_float(old.x));
-            v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) + __int_as_float(old.y));
-            v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) + __int_as_float(old.z));
-            v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + __int_as_float(old.w));
-          }
-        }
 #pragma unroll
         for (int j = 0; j < 8; ++j)
-          st16(orow + c0 + 4 * j, make_int4((int)v[4 * j], (int)v[4 * j + 1], (int)v[4 * j + 2], (int)v[4 * j + 3]));
+          *reinterpret_cast<uint4*>(stage_w + lane * kWgradStageLd + 4 * j) =
+              make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int r = 4 * i + sub_row;
+          const float4 x = *reinterpret_cast<const float4*>(stage_w + r * kWgradStageLd + col4);
+          float* dst = tile_out + (long long)r * a.Q + c0 + col4;
+          if (flag == 1)
+            asm volatile("red.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(dst), "f"(x.x), "f"(x.y), "f"(x.z), "f"(x.w)
+                         : "memory");
+          else
+            st16(dst, make_int4(__float_as_int(x.x), __float_as_int(x.y), __float_as_int(x.z), __float_as_int(x.w)));
+        }
+        __syncwarp();
       }
       tc_fence_before();
       __syncwarp();
@@ -703,7 +715,7 @@ extern "C" int moonep_grouped_wgrad(const void* lt, const void* rt, long long ld
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int grid = imax(1, num_sms > 0 ? imin(num_sms, sms) : sms);
-  const size_t smem = (size_t)kStages * kStageBytes + 1024;
+  const size_t smem = (size_t)kStages * kStageBytes + 1024 + kWgradStageBytes;
   static bool attr_set = false;
   if (!attr_set) {
     if (int rc = check_cuda(cudaFuncSetAttribute(grouped_wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -25,9 +25,10 @@ constexpr int kTile = 64;
 
 __global__ void __launch_bounds__(256)
     transpose_experts_kernel(const uint16_t* __restrict__ src, uint16_t* __restrict__ dst, int d0, int d1,
-                             long long dst_ld, long long dst_expert_stride, int col0) {
+                             long long dst_ld, long long dst_expert_stride, int col0, const int* __restrict__ active) {
   __shared__ uint16_t tile[kTile][kTile + 8];
   const int n = blockIdx.z;
+  if (active != nullptr && active[n] < 0) return;  // e.g. a prefetch slot that holds no expert in this step
   const int i0 = blockIdx.y * kTile, j0 = blockIdx.x * kTile;
   const uint16_t* s = src + (long long)n * d0 * d1;
   uint16_t* d = dst + (long long)n * dst_expert_stride;
@@ -135,8 +136,9 @@ extern "C" int moonep_sgd_update(void* w, const float* g, long long n, float lr,
 }
 
 // src: [n, d0, d1] bf16 -> dst[n][j][col0 + i] with row stride dst_ld and expert stride dst_expert_stride (elements).
+// active (optional, device, [n]): matrices with a negative entry are skipped.
 extern "C" int moonep_transpose_experts(const void* src, void* dst, int n, int d0, int d1, long long dst_ld,
-                                        long long dst_expert_stride, int col0, void* stream) {
+                                        long long dst_expert_stride, int col0, const int* active, void* stream) {
   if (n <= 0) return 0;
   if (d0 % kTile != 0 || d1 % kTile != 0 || dst_ld % 8 != 0 || col0 % 8 != 0) {
     set_error("moonep_transpose_experts: dimensions must be multiples of 64 and the destination 16-byte aligned");
@@ -144,7 +146,7 @@ extern "C" int moonep_transpose_experts(const void* src, void* dst, int n, int d
   }
   dim3 grid(d1 / kTile, d0 / kTile, n);
   transpose_experts_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const uint16_t*)src, (uint16_t*)dst, d0, d1, dst_ld,
-                                                                   dst_expert_stride, col0);
+                                                                   dst_expert_stride, col0, active);
   return check_launch("transpose_experts_kernel");
 }
 

@@ -181,7 +181,7 @@ int moonep_grouped_wgrad(const void* lt, const void* rt, long long ld, int P, in
                          int num_sms, void* stream);
 // Helpers of the MoE layer's backward pass and optimiser step, see moe_kernels.cu.
 int moonep_transpose_experts(const void* src, void* dst, int n, int d0, int d1, long long dst_ld,
-                             long long dst_expert_stride, int col0, void* stream);
+                             long long dst_expert_stride, int col0, const int* active, void* stream);
 int moonep_swiglu_bwd(const void* a, const void* u, const void* g, const float* w, const int* total_rows, int rows_cap,
                       int I, void* dadu, void* hsw, float* dgate, void* stream);
 int moonep_sgd_update(void* w, const float* g, long long n, float lr, void* stream);

@@ -111,9 +111,10 @@ class ExpertParallelMoE:
         return out, saved
 
     # -- backward ------------------------------------------------------------------------------
-    def _local_transposed(self, weights):
+    def _local_transposed(self, weights, plan):
         """K-major copies of the experts this rank owns and of its prefetch slots for the activation-gradient
-        GEMMs: ``[epn+B, d1, sum(d0)]`` with the transposes of ``weights`` side by side along the last axis."""
+        GEMMs: ``[epn+B, d1, sum(d0)]`` with the transposes of ``weights`` side by side along the last axis.
+        Slots that hold no expert in this step (``experts_to_copy[rank, b] < 0``) are skipped on the device."""
         E, epn, own0, B = self.E, self.epn, self.rank * self.epn, self.B
         d1 = int(weights[0].shape[2])
         width = sum(int(w.shape[1]) for w in weights)
@@ -122,7 +123,7 @@ class ExpertParallelMoE:
         for w in weights:
             transpose_experts(w[own0 : own0 + epn], out[:epn], col)
             if B:
-                transpose_experts(w[E:], out[epn:], col)
+                transpose_experts(w[E:], out[epn:], col, active=plan.experts_to_copy[self.rank])
             col += int(w.shape[1])
         return out
 
@@ -156,14 +157,14 @@ class ExpertParallelMoE:
         dev = x_nvs.device
         a = grouped_gemm(x_nvs, self.w_gate, cu)
         u = grouped_gemm(x_nvs, self.w_up, cu)
-        g = grouped_gemm(dy_nvs, self._local_transposed([self.w_down]), cu, group_map=gmap)  # dy @ W_down, unscaled
+        g = grouped_gemm(dy_nvs, self._local_transposed([self.w_down], plan), cu, group_map=gmap)  # dy @ W_down, unscaled
         dadu = torch.empty(rows, 2 * I, dtype=torch.bfloat16, device=dev)
         hsw = torch.empty(rows, I, dtype=torch.bfloat16, device=dev)
         dgate_nvs = ctx["weights_buf_local"].view(torch.float32)  # gate gradients ride the weights channel home
         swiglu_bwd(a, u, g, w_nvs, cu[-1:], dadu, hsw, dgate_nvs)
         del a, u, g
         if self._weight_grads_on_kernel(x_nvs, dy_nvs, dadu, hsw, cu):
-            grouped_gemm(dadu, self._local_transposed([self.w_gate, self.w_up]), cu, group_map=gmap, out=dy_nvs)
+            grouped_gemm(dadu, self._local_transposed([self.w_gate, self.w_up], plan), cu, group_map=gmap, out=dy_nvs)
             dx, dgates, _ = buf.combine(plan, dy_nvs, dgate_nvs, zero_copy=True)
             buf.reduce_grad(plan, False, self.g_gate, self.g_up, self.g_down, self.red[0], self.red[1], self.red[2],
                             owner_local=True)  # fmt: skip
@@ -193,7 +194,7 @@ class ExpertParallelMoE:
                     for gt in (self.g_gate, self.g_up, self.g_down):
                         gt[le].zero_()
             self._fresh = False
-        grouped_gemm(dadu, self._local_transposed([self.w_gate, self.w_up]), cu, group_map=gmap, out=dy_nvs)
+        grouped_gemm(dadu, self._local_transposed([self.w_gate, self.w_up], plan), cu, group_map=gmap, out=dy_nvs)
         dx, dgates, _ = buf.combine(plan, dy_nvs, dgate_nvs, zero_copy=True)
         buf.reduce_grad(plan, False, self.g_gate, self.g_up, self.g_down, self.red[0], self.red[1], self.red[2],
                         owner_local=True)  # fmt: skip

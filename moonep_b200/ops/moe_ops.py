@@ -10,18 +10,23 @@ import torch
 from . import _lib
 
 
-def transpose_experts(src: torch.Tensor, dst: torch.Tensor, col0: int = 0) -> torch.Tensor:
-    """``dst[n, j, col0 + i] = src[n, i, j]``; ``src`` is ``[n, d0, d1]`` bf16, ``dst`` ``[n, d1, >= col0 + d0]``."""
+def transpose_experts(src: torch.Tensor, dst: torch.Tensor, col0: int = 0, active=None) -> torch.Tensor:
+    """``dst[n, j, col0 + i] = src[n, i, j]``; ``src`` is ``[n, d0, d1]`` bf16, ``dst`` ``[n, d1, >= col0 + d0]``.
+    ``active`` (int32 ``[n]``, optional): matrices whose entry is negative are skipped."""
     n, d0, d1 = (int(v) for v in src.shape)
     assert dst.shape[0] == n and dst.shape[1] == d1 and dst.shape[2] >= col0 + d0 and dst.is_contiguous()
+    if active is not None:
+        assert active.dtype == torch.int32 and active.numel() == n and active.is_contiguous()
     if not src.is_cuda:
-        dst[:, :, col0 : col0 + d0] = src.transpose(1, 2)
+        for i in range(n):
+            if active is None or int(active[i]) >= 0:
+                dst[i, :, col0 : col0 + d0] = src[i].transpose(0, 1)
         return dst
     assert src.is_contiguous() and src.dtype == torch.bfloat16 and dst.dtype == torch.bfloat16
     with torch.cuda.device(src.device):
         rc = _lib.load().moonep_transpose_experts(
             src.data_ptr(), dst.data_ptr(), n, d0, d1, int(dst.shape[2]), int(dst.shape[1]) * int(dst.shape[2]), int(col0),
-            torch.cuda.current_stream().cuda_stream,
+            None if active is None else active.data_ptr(), torch.cuda.current_stream().cuda_stream,
         )  # fmt: skip
     _lib.check(rc, "moonep_transpose_experts")
     return dst

@@ -78,6 +78,11 @@ def test_moe_helper_ops_match_torch(device):
     transpose_experts(src, dst, 64)
     assert torch.equal(dst[:, :, 64:].cpu(), src.transpose(1, 2).cpu()) and not bool(dst[:, :, :64].abs().max() > 0)
 
+    dst2 = torch.full((3, 192, 128), 7.0, dtype=torch.bfloat16, device=device)
+    transpose_experts(src, dst2, 0, active=torch.tensor([4, -1, 0], dtype=torch.int32, device=device))
+    assert torch.equal(dst2[0].cpu(), src[0].t().cpu()) and torch.equal(dst2[2].cpu(), src[2].t().cpu())
+    assert bool((dst2[1] == 7.0).all()), "a skipped matrix was written"
+
     rows, I, n = 70, 256, 50
     a, u, gg = (torch.randn(rows, I, generator=g).to(torch.bfloat16).to(device) for _ in range(3))
     w = torch.rand(rows, generator=g).to(device)
