@@ -66,6 +66,8 @@ struct GemmArgs {
   int rows_cap;      // rows of X
   const int* group_map;  // [G] weight slot of every group, or null for the identity
   int w_slots;           // number of weight slots (rows of W = w_slots * n_per_group)
+  uint16_t* pre_gate;    // SwiGLU only, optional: the pre-activations x Wg^T and x Wu^T, [rows, ldo] bf16 each,
+  uint16_t* pre_up;      // kept for the backward pass so that it need not recompute them
 };
 
 __device__ __forceinline__ void gemm_fail(int* status, int kernel, int where, int x, int y) {
@@ -305,6 +307,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 #pragma unroll
           for (int j = 0; j < 4; ++j)
             st16(orow + c0 + j * 8, make_int4((int)o[4 * j], (int)o[4 * j + 1], (int)o[4 * j + 2], (int)o[4 * j + 3]));
+          if (a.pre_gate != nullptr) {
+            const long long off = (long long)row * a.ldo + (long long)nb * 128 + c0;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              g[j] = pack_bf16(__uint_as_float(g[2 * j]), __uint_as_float(g[2 * j + 1]));
+              u[j] = pack_bf16(__uint_as_float(u[2 * j]), __uint_as_float(u[2 * j + 1]));
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              st16(a.pre_gate + off + j * 8, make_int4((int)g[4 * j], (int)g[4 * j + 1], (int)g[4 * j + 2], (int)g[4 * j + 3]));
+              st16(a.pre_up + off + j * 8, make_int4((int)u[4 * j], (int)u[4 * j + 1], (int)u[4 * j + 2], (int)u[4 * j + 3]));
+            }
+          }
         }
       } else {
         const float scale = (a.mode == kScale && a.row_scale != nullptr) ? a.row_scale[row] : 1.f;
@@ -625,11 +640,16 @@ using namespace moonep;
 // n_out = n_per_group (plain, scale) or n_per_group (swiglu: gate and up each have n_per_group rows).
 // cu_seqlens: [G] int32 inclusive padded ends (multiples of 128).  mode: 0 plain, 1 swiglu, 2 scale by row_scale.
 // group_map (optional): [G] int32, weight slot of every group when w holds only w_slots < G experts.
+// pre_gate, pre_up (optional, SwiGLU): [rows_cap, n_per_group] bf16, receive x Wg^T and x Wu^T.
 extern "C" int moonep_grouped_gemm(const void* x, const void* w0, const void* w1, void* out, const float* row_scale,
                                    const int* cu_seqlens, int G, int rows_cap, int K, int n_per_group, int mode,
                                    int* status, long long timeout_ms, int num_sms, const int* group_map, int w_slots,
-                                   void* stream) {
+                                   void* pre_gate, void* pre_up, void* stream) {
   if (group_map == nullptr || w_slots <= 0) w_slots = G;
+  if ((pre_gate != nullptr) != (pre_up != nullptr) || (pre_gate != nullptr && mode != kSwiglu)) {
+    set_error("moonep_grouped_gemm: pre_gate and pre_up go together and only with SwiGLU");
+    return 1;
+  }
   if (K % BK != 0 || K <= 0) {
     set_error("moonep_grouped_gemm: K must be a positive multiple of 64");
     return 1;
@@ -664,6 +684,8 @@ extern "C" int moonep_grouped_gemm(const void* x, const void* w0, const void* w1
   a.rows_cap = rows_cap;
   a.group_map = group_map;
   a.w_slots = w_slots;
+  a.pre_gate = (uint16_t*)pre_gate;
+  a.pre_up = (uint16_t*)pre_up;
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

@@ -169,10 +169,12 @@ int moonep_grad_reduce(void* ctx, float* const* grads, float* const* reduce, int
 
 // Expert computation (tcgen05 tensor cores).  None of these has a counterpart in the reference, which has no GEMM.
 // y[rows of g] = x[rows of g] @ w[g]^T for the padded row groups of a dispatched shard; mode 0 plain, 1 SwiGLU
-// (w0 = gate, w1 = up), 2 scaled by row_scale.  See grouped_gemm.cu.
+// (w0 = gate, w1 = up; pre_gate / pre_up optionally receive the two pre-activations), 2 scaled by row_scale.
+// See grouped_gemm.cu.
 int moonep_grouped_gemm(const void* x, const void* w0, const void* w1, void* out, const float* row_scale,
                         const int* cu_seqlens, int G, int rows_cap, int K, int n_per_group, int mode, int* status,
-                        long long timeout_ms, int num_sms, const int* group_map, int w_slots, void* stream);
+                        long long timeout_ms, int num_sms, const int* group_map, int w_slots, void* pre_gate,
+                        void* pre_up, void* stream);
 // Weight gradients of all groups: out_ptrs[g][P, Q] fp32 (=, +=) L_g^T R_g with the contraction over the rows of
 // group g.  lt = L^T [P, ld], rt = R^T [Q, ld] bf16 (ld a multiple of 8, >= rows_cap).  flags[g]: 0 store (zeros for
 // an empty group), 1 accumulate, 2 store and leave empty groups alone.  out_ptrs, flags: device arrays [G].

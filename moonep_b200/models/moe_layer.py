@@ -104,10 +104,13 @@ class ExpertParallelMoE:
         x_saved = x_nvs.clone()  # the shard is reused for the expert output
         if hasattr(fetched, "wait") and x_nvs.is_cuda:
             torch.cuda.current_stream().wait_event(fetched)
-        h = grouped_gemm(x_saved, self.w_gate, cu, w_up=self.w_up, mode="swiglu")
+        # the pre-activations are kept for the backward pass (two bf16 [NvS, I] tensors instead of two more GEMMs)
+        a = torch.empty(x_saved.shape[0], self.I, dtype=torch.bfloat16, device=x_saved.device)
+        u = torch.empty_like(a)
+        h = grouped_gemm(x_saved, self.w_gate, cu, w_up=self.w_up, mode="swiglu", save_pre=(a, u))
         grouped_gemm(h, self.w_down, cu, row_scale=w_nvs, mode="scale", out=x_nvs)
         out, _, _ = buf.combine(plan, x_nvs, None, zero_copy=True)
-        saved = {"plan": plan, "cu": cu, "x_nvs": x_saved, "w_nvs": w_nvs.clone(), "h": h}
+        saved = {"plan": plan, "cu": cu, "x_nvs": x_saved, "w_nvs": w_nvs.clone(), "h": h, "a": a, "u": u}
         return out, saved
 
     # -- backward ------------------------------------------------------------------------------
@@ -155,8 +158,7 @@ class ExpertParallelMoE:
         gmap = self.group_map
         rows = int(x_nvs.shape[0])
         dev = x_nvs.device
-        a = grouped_gemm(x_nvs, self.w_gate, cu)
-        u = grouped_gemm(x_nvs, self.w_up, cu)
+        a, u = saved["a"], saved["u"]
         g = grouped_gemm(dy_nvs, self._local_transposed([self.w_down], plan), cu, group_map=gmap)  # dy @ W_down, unscaled
         dadu = torch.empty(rows, 2 * I, dtype=torch.bfloat16, device=dev)
         hsw = torch.empty(rows, I, dtype=torch.bfloat16, device=dev)

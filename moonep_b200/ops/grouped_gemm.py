@@ -49,12 +49,13 @@ def kernel_supports(x, w, mode: str) -> bool:
 
 
 def grouped_gemm(x, w, cu_seqlens, *, w_up=None, row_scale=None, mode="plain", out=None, status=None, num_sms=0,
-                 group_map=None):
+                 group_map=None, save_pre=None):
     """See module docstring.  ``x``: ``[rows, K]`` bf16, ``w``: ``[G, N, K]`` bf16, returns ``[rows, N]`` bf16.
 
     Rows beyond ``cu_seqlens[-1]`` are not written.  Group ends must be multiples of 128.  With
     ``group_map`` (int32 ``[G]``) group ``g`` uses ``w[group_map[g]]`` and ``w`` may hold fewer experts
-    than there are groups (e.g. only the experts a rank owns or has prefetched).
+    than there are groups (e.g. only the experts a rank owns or has prefetched).  ``save_pre=(a, u)`` (SwiGLU
+    only, two ``[rows, N]`` bf16 tensors) also stores the pre-activations ``x @ w.T`` and ``x @ w_up.T``.
     """
     assert mode in _MODES
     W, N, K = (int(v) for v in w.shape)
@@ -69,6 +70,9 @@ def grouped_gemm(x, w, cu_seqlens, *, w_up=None, row_scale=None, mode="plain", o
                 "(K % 64, N % 256 or 128 for swiglu, rows >= 128); set MOONEP_GEMM_FALLBACK=1 to use the reference"
             )
         res = grouped_gemm_reference(x, w, cu_seqlens, w_up=w_up, row_scale=row_scale, mode=mode, group_map=group_map)
+        if save_pre is not None:
+            save_pre[0].copy_(grouped_gemm_reference(x, w, cu_seqlens, group_map=group_map))
+            save_pre[1].copy_(grouped_gemm_reference(x, w_up, cu_seqlens, group_map=group_map))
         if out is not None:
             out.copy_(res)
             return out
@@ -82,13 +86,19 @@ def grouped_gemm(x, w, cu_seqlens, *, w_up=None, row_scale=None, mode="plain", o
     if out is None:
         out = torch.empty(x.shape[0], N, dtype=torch.bfloat16, device=x.device)
     assert out.is_contiguous() and out.shape == (x.shape[0], N) and out.dtype == torch.bfloat16
+    if save_pre is not None:
+        assert mode == "swiglu", "save_pre goes with mode='swiglu'"
+        for t in save_pre:
+            assert t.is_contiguous() and t.shape == out.shape and t.dtype == torch.bfloat16 and t.device == out.device
     lib = _lib.load()
     with torch.cuda.device(x.device):
         rc = lib.moonep_grouped_gemm(
             x.data_ptr(), w.data_ptr(), None if w_up is None else w_up.data_ptr(), out.data_ptr(),
             None if row_scale is None else row_scale.data_ptr(), cu_seqlens.data_ptr(), G, int(x.shape[0]), K, N,
             _MODES[mode], None if status is None else status.data_ptr(), config.timeout_ms(), int(num_sms),
-            None if group_map is None else group_map.data_ptr(), W, torch.cuda.current_stream().cuda_stream,
+            None if group_map is None else group_map.data_ptr(), W,
+            None if save_pre is None else save_pre[0].data_ptr(), None if save_pre is None else save_pre[1].data_ptr(),
+            torch.cuda.current_stream().cuda_stream,
         )  # fmt: skip
     _lib.check(rc, "moonep_grouped_gemm")
     return out

@@ -56,6 +56,15 @@ def test_grouped_gemm_matches_fp32_reference(mode, G, rows, K, N):
     y2 = grouped_gemm(x, w, cu, mode=mode, status=status, **kw)
     torch.cuda.synchronize()
     assert torch.equal(y[:total], y2[:total])
+    if mode == "swiglu":  # the same pass can keep both pre-activations
+        pre = (torch.zeros_like(y), torch.zeros_like(y))
+        y3 = grouped_gemm(x, w, cu, mode=mode, status=status, save_pre=pre, **kw)
+        torch.cuda.synchronize()
+        assert torch.equal(y3[:total], y[:total])
+        for got_pre, wt in zip(pre, (w, w2)):
+            want_pre = grouped_gemm_reference(x, wt, cu)[:total].float()
+            err = (got_pre[:total].float() - want_pre).abs().max().item()
+            assert err <= 2e-2 * max(1.0, want_pre.abs().max().item()), f"pre-activation err {err}"
 
 
 def _wgrad_case(rows, P, Q, seed=0, device="cpu"):
