@@ -292,10 +292,13 @@ def run_moe_step(args, rank, n):
     go = (torch.randn(S, H, generator=g) * 0.1).to(torch.bfloat16).to(dev)
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
 
+    last = {}
+
     def step():
         out, saved = layer.forward(x, gates, topk, tpe)
         mid.record()
         dx, dg = layer.backward(saved, go)
+        last.update(dx=dx, dgates=dg)
         layer.sgd_step(1e-5)
         layer.zero_grad()
         return out
@@ -318,6 +321,9 @@ def run_moe_step(args, rank, n):
     t_f = max_over_ranks(sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps, n)
     t_all = max_over_ranks(sum(e[0].elapsed_time(e[2]) for e in ev) / args.steps, n)
     buf.check_status()
+    # every rank's outputs, input gradients, gate gradients and owned weight gradients must be finite
+    finite = all(bool(torch.isfinite(t.float()).all()) for t in (out, last["dx"], last["dgates"], *layer.owner_grads()))
+    finite = max_over_ranks(0.0 if finite else 1.0, n) == 0.0
     flops_fwd = 2.0 * S * K * H * inter * 3  # per rank, real rows
     return {
         "metric": "moe_layer_train_tokens_per_s", "value": n * S / (t_all / 1e3), "unit": "tokens/s", "n_gpus": n,
@@ -329,7 +335,7 @@ def run_moe_step(args, rank, n):
                    "routing": args.routing, "prefetch_slots": slots,
                    "backward_gemms": "activation and weight gradients: tcgen05 grouped GEMMs" if config.wgrad_on_kernel()
                    else "activation grads: tcgen05 grouped GEMM; weight grads: torch matmul per group (bf16)"},
-        "forward_tflops_per_gpu": flops_fwd / (t_f / 1e3) / 1e12, "finite": bool(torch.isfinite(out.float()).all()),
+        "forward_tflops_per_gpu": flops_fwd / (t_f / 1e3) / 1e12, "finite": finite,
         "clocks": clocks.summary(),
     }  # fmt: skip
 
