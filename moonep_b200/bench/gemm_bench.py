@@ -15,6 +15,7 @@ import os
 
 import torch
 
+from moonep_b200 import config
 from moonep_b200.ops.grouped_gemm import grouped_gemm, grouped_wgrad
 from moonep_b200.ops.moe_ops import transpose_experts
 
@@ -86,7 +87,8 @@ def main():
     f2 = 2.0 * total * a.H * a.I
     for name, t, tr, f in (("swiglu_gate_up", t1, t1_ref, f1), ("down_scale", t2, t2_ref, f2)):
         print(json.dumps({
-            "gemm": name, "rows": total, "groups": a.groups, "H": a.H, "I": a.I, "ms": round(t, 4),
+            "gemm": name, "kernel": "cta_pair (cta_group::2)" if config.gemm_on_cta_pairs() else "one CTA per tile",
+            "rows": total, "groups": a.groups, "H": a.H, "I": a.I, "ms": round(t, 4),
             "tflops": round(f / t / 1e9, 1), "frac_of_measured_cublas_peak": round(f / t / 1e9 / peak, 3),
             "torch_bmm_plus_elementwise_ms": round(tr, 4), "speedup_vs_torch": round(tr / t, 2),
             "rel_err_vs_torch": round(err, 5), "measured_peak_tflops": peak,

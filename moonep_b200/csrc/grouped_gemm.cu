@@ -29,129 +29,18 @@
 // The reference has no GEMM; this kernel serves the MoE-layer benchmark configuration (dispatch ->
 // prefetch_weight -> grouped GEMM -> combine) named beside the reference's Buffer API
 // (reference README.md:46-48).
-#include <cuda.h>
-
-#include "common.cuh"
-#include "host.h"
+#include "umma.cuh"
 
 namespace moonep {
 
 namespace {
 
-constexpr int BM = 128;
-constexpr int BN = 256;
-constexpr int BK = 64;
-constexpr int UMMA_K = 16;
 constexpr int kStages = 4;
 constexpr int kGemmThreads = 192;
 constexpr int kTmemCols = 512;
 constexpr unsigned kATileBytes = BM * BK * 2;        // 16 KB
 constexpr unsigned kBHalfBytes = 128 * BK * 2;       // 16 KB
 constexpr unsigned kStageBytes = kATileBytes + 2 * kBHalfBytes;  // 48 KB
-
-enum GemmMode { kPlain = 0, kSwiglu = 1, kScale = 2 };
-
-struct GemmArgs {
-  uint16_t* out;           // [rows, ldo] bf16
-  const float* row_scale;  // [rows] or null
-  const int* cu_seqlens;   // [G] inclusive padded ends
-  int* status;             // [MOONEP_ST_WORDS] or null
-  unsigned long long timeout_ns;
-  int G;
-  int n_per_group;   // rows of W per group (N)
-  int n_tiles;       // output column tiles per row block
-  int k_blocks;      // K / 64
-  int ldo;           // row stride of out in elements
-  int mode;
-  int rows_cap;      // rows of X
-  const int* group_map;  // [G] weight slot of every group, or null for the identity
-  int w_slots;           // number of weight slots (rows of W = w_slots * n_per_group)
-  uint16_t* pre_gate;    // SwiGLU only, optional: the pre-activations x Wg^T and x Wu^T, [rows, ldo] bf16 each,
-  uint16_t* pre_up;      // kept for the backward pass so that it need not recompute them
-};
-
-__device__ __forceinline__ void gemm_fail(int* status, int kernel, int where, int x, int y) {
-  if (status != nullptr && atomicCAS(status + MOONEP_ST_CODE, 0, MOONEP_STATUS_TIMEOUT) == 0) {
-    status[MOONEP_ST_KERNEL] = kernel;
-    status[MOONEP_ST_FAMILY] = where;
-    status[MOONEP_ST_PEER] = x;
-    status[MOONEP_ST_EXPECT] = y;
-    __threadfence();
-  }
-}
-
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* tmap, int c0, int c1,
-                                            unsigned long long* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
-          smem_u32(smem_dst)),
-      "l"(reinterpret_cast<unsigned long long>(tmap)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
-      : "memory");
-}
-
-__device__ __forceinline__ void tmem_alloc(unsigned* smem_dst, unsigned ncols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(ncols)
-               : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(unsigned taddr, unsigned ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void umma_bf16(unsigned d_tmem, unsigned long long adesc, unsigned long long bdesc,
-                                          unsigned idesc, unsigned accumulate) {
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
-      "}\n" ::"r"(d_tmem),
-      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
-__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,"
-      "%30,%31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor of a K-major tile stored with the 128-byte swizzle: rows are
-// 128 bytes apart, groups of eight rows 1024 bytes apart.
-__device__ __forceinline__ unsigned long long make_smem_desc(const void* tile) {
-  const unsigned addr = smem_u32(tile);
-  unsigned long long d = 0;
-  d |= (unsigned long long)((addr & 0x3FFFFu) >> 4);  // start address, 16-byte units
-  d |= (unsigned long long)1 << 16;                   // leading byte offset (unused for this layout)
-  d |= (unsigned long long)(1024 >> 4) << 32;         // stride byte offset: 8 rows * 128 bytes
-  d |= (unsigned long long)1 << 46;                   // descriptor version of sm_100
-  d |= (unsigned long long)2 << 61;                   // 128-byte swizzle
-  return d;
-}
-
-// kind::f16 instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, M x N.
-__host__ __device__ constexpr unsigned make_idesc(int m, int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
-}
-
-__device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
 
 __global__ void __launch_bounds__(kGemmThreads, 1)
     grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b0,
@@ -589,48 +478,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 }  // namespace
 
 // ---- host side --------------------------------------------------------------------------------------
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled() {
-  static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)p;
-    else
-      cudaGetLastError();
-  }
-  return fn;
-}
-
-// 2-D bf16 row-major [rows, cols] tensor, box = 64 columns x box_rows rows, 128-byte swizzle.
-static int make_tmap(CUtensorMap* m, const void* base, unsigned long long rows, unsigned long long cols,
-                     unsigned box_rows) {
-  EncodeTiledFn fn = encode_tiled();
-  if (fn == nullptr) {
-    set_error("cuTensorMapEncodeTiled is not available (no CUDA driver?)");
-    return 1;
-  }
-  cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {cols * 2};
-  cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) {
-    set_error("cuTensorMapEncodeTiled failed with CUresult " + std::to_string((int)r));
-    return (int)r;
-  }
-  return 0;
-}
 
 }  // namespace moonep
 

@@ -175,6 +175,12 @@ int moonep_grouped_gemm(const void* x, const void* w0, const void* w1, void* out
                         const int* cu_seqlens, int G, int rows_cap, int K, int n_per_group, int mode, int* status,
                         long long timeout_ms, int num_sms, const int* group_map, int w_slots, void* pre_gate,
                         void* pre_up, void* stream);
+// The same operation on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles per cluster of two CTAs), see
+// grouped_gemm_pair.cu.  Same arguments.
+int moonep_grouped_gemm_pair(const void* x, const void* w0, const void* w1, void* out, const float* row_scale,
+                             const int* cu_seqlens, int G, int rows_cap, int K, int n_per_group, int mode, int* status,
+                             long long timeout_ms, int num_sms, const int* group_map, int w_slots, void* pre_gate,
+                             void* pre_up, void* stream);
 // Weight gradients of all groups: out_ptrs[g][P, Q] fp32 (=, +=) L_g^T R_g with the contraction over the rows of
 // group g.  lt = L^T [P, ld], rt = R^T [Q, ld] bf16 (ld a multiple of 8, >= rows_cap).  flags[g]: 0 store (zeros for
 // an empty group), 1 accumulate, 2 store and leave empty groups alone.  out_ptrs, flags: device arrays [G].

@@ -49,13 +49,14 @@ def kernel_supports(x, w, mode: str) -> bool:
 
 
 def grouped_gemm(x, w, cu_seqlens, *, w_up=None, row_scale=None, mode="plain", out=None, status=None, num_sms=0,
-                 group_map=None, save_pre=None):
+                 group_map=None, save_pre=None, pair=None):
     """See module docstring.  ``x``: ``[rows, K]`` bf16, ``w``: ``[G, N, K]`` bf16, returns ``[rows, N]`` bf16.
 
     Rows beyond ``cu_seqlens[-1]`` are not written.  Group ends must be multiples of 128.  With
     ``group_map`` (int32 ``[G]``) group ``g`` uses ``w[group_map[g]]`` and ``w`` may hold fewer experts
     than there are groups (e.g. only the experts a rank owns or has prefetched).  ``save_pre=(a, u)`` (SwiGLU
     only, two ``[rows, N]`` bf16 tensors) also stores the pre-activations ``x @ w.T`` and ``x @ w_up.T``.
+    ``pair`` selects the kernel: True = CTA pairs (``cta_group::2``), False = one CTA per tile, None = ``MOONEP_GEMM_PAIR``.
     """
     assert mode in _MODES
     W, N, K = (int(v) for v in w.shape)
@@ -92,7 +93,8 @@ def grouped_gemm(x, w, cu_seqlens, *, w_up=None, row_scale=None, mode="plain", o
             assert t.is_contiguous() and t.shape == out.shape and t.dtype == torch.bfloat16 and t.device == out.device
     lib = _lib.load()
     with torch.cuda.device(x.device):
-        rc = lib.moonep_grouped_gemm(
+        fn = lib.moonep_grouped_gemm_pair if (config.gemm_on_cta_pairs() if pair is None else pair) else lib.moonep_grouped_gemm
+        rc = fn(
             x.data_ptr(), w.data_ptr(), None if w_up is None else w_up.data_ptr(), out.data_ptr(),
             None if row_scale is None else row_scale.data_ptr(), cu_seqlens.data_ptr(), G, int(x.shape[0]), K, N,
             _MODES[mode], None if status is None else status.data_ptr(), config.timeout_ms(), int(num_sms),

@@ -29,6 +29,7 @@ def test_reference_on_cpu_matches_dense():
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("pair", [False, True], ids=["cta", "cta_pair"])
 @pytest.mark.parametrize("mode", ["plain", "swiglu", "scale"])
 @pytest.mark.parametrize(
     "G,rows,K,N",
@@ -40,14 +41,17 @@ def test_reference_on_cpu_matches_dense():
         (36, [128 * ((i * 7) % 5) for i in range(36)], 2048, 512),
     ],
 )
-def test_grouped_gemm_matches_fp32_reference(mode, G, rows, K, N):
+def test_grouped_gemm_matches_fp32_reference(mode, G, rows, K, N, pair):
     x, w, w2, cu, scale, total = _case(G, rows, K, N)
     status = torch.zeros(8, dtype=torch.int32, device="cuda")
     kw = {"w_up": w2} if mode == "swiglu" else ({"row_scale": scale} if mode == "scale" else {})
+    kw["pair"] = pair
     y = grouped_gemm(x, w, cu, mode=mode, status=status, **kw)
     torch.cuda.synchronize()
     assert status.tolist()[0] == 0, f"kernel reported status {status.tolist()}"
+    kw.pop("pair")
     ref = grouped_gemm_reference(x, w, cu, mode=mode, **kw)
+    kw["pair"] = pair
     got, want = y[:total].float(), ref[:total].float()
     err = (got - want).abs().max().item()
     tol = 2e-2 * max(1.0, want.abs().max().item())
