@@ -74,6 +74,14 @@ def gemm_on_cta_pairs() -> bool:
     return os.environ.get("MOONEP_GEMM_PAIR", "1") not in _FALSE
 
 
+def wgrad_layout() -> str:
+    """MOONEP_WGRAD_LAYOUT: ``rows`` (default) feeds the weight-gradient kernel the activations as they are
+    (MN-major tiles), ``transposed`` makes K-major copies first."""
+    v = os.environ.get("MOONEP_WGRAD_LAYOUT", "rows").lower()
+    assert v in ("rows", "transposed"), f"MOONEP_WGRAD_LAYOUT={v!r}: expected rows or transposed"
+    return v
+
+
 def nvtx() -> bool:
     """MOONEP_NVTX=1: wrap every native call in an NVTX range named after the kernel."""
     return os.environ.get("MOONEP_NVTX", "0") not in _FALSE

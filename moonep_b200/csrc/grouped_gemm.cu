@@ -262,6 +262,7 @@ struct WgradArgs {
   int* status;
   unsigned long long timeout_ns;
   int G, P, Q, p_tiles, q_tiles, rows_cap;
+  int row_major;  // operands are L [rows, P] and R [rows, Q] as they are (MN-major tiles) instead of their transposes
 };
 
 struct WgradTile {
@@ -335,9 +336,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           }
           unsigned char* st = s_tiles + (size_t)stage * kStageBytes;
           mbar_expect_tx(s_full + stage, kStageBytes);
-          tma_load_2d(st, &tmap_l, w.k0 + kb * BK, w.pb * BM, s_full + stage);
-          tma_load_2d(st + kATileBytes, &tmap_r, w.k0 + kb * BK, w.qb * BN, s_full + stage);
-          tma_load_2d(st + kATileBytes + kBHalfBytes, &tmap_r, w.k0 + kb * BK, w.qb * BN + 128, s_full + stage);
+          if (a.row_major) {
+            // boxes of 64 columns (P or Q) x 64 rows (K): two for the L tile, four for the R tile
+            const int k = w.k0 + kb * BK;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) tma_load_2d(st + c * kMnBoxBytes, &tmap_l, w.pb * BM + 64 * c, k, s_full + stage);
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+              tma_load_2d(st + kATileBytes + c * kMnBoxBytes, &tmap_r, w.qb * BN + 64 * c, k, s_full + stage);
+          } else {
+            tma_load_2d(st, &tmap_l, w.k0 + kb * BK, w.pb * BM, s_full + stage);
+            tma_load_2d(st + kATileBytes, &tmap_r, w.k0 + kb * BK, w.qb * BN, s_full + stage);
+            tma_load_2d(st + kATileBytes + kBHalfBytes, &tmap_r, w.k0 + kb * BK, w.qb * BN + 128, s_full + stage);
+          }
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
@@ -350,6 +361,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       constexpr unsigned idesc = make_idesc(BM, BN);
+      constexpr unsigned idesc_mn = make_idesc(BM, BN, true, true);
+      const unsigned kstep = a.row_major ? kDescStepMn : kDescStepK;
       int stage = 0;
       unsigned phase = 0;
       unsigned tphase[2] = {0, 0};
@@ -376,12 +389,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           }
           tc_fence_after();
           const unsigned char* st = s_tiles + (size_t)stage * kStageBytes;
-          const unsigned long long adesc = make_smem_desc(st);
-          const unsigned long long bdesc = make_smem_desc(st + kATileBytes);
+          const unsigned long long adesc = a.row_major ? make_smem_desc_mn(st) : make_smem_desc(st);
+          const unsigned long long bdesc = a.row_major ? make_smem_desc_mn(st + kATileBytes) : make_smem_desc(st + kATileBytes);
           const int nkk = min(BK / UMMA_K, (w.krows - kb * BK) / UMMA_K);  // MMAs inside the group
           for (int kk = 0; kk < nkk; ++kk)
-            umma_bf16(d_tmem, adesc + (unsigned long long)(kk * 2), bdesc + (unsigned long long)(kk * 2), idesc,
-                      (kb | kk) != 0 ? 1u : 0u);
+            umma_bf16(d_tmem, adesc + (unsigned long long)(kk * kstep), bdesc + (unsigned long long)(kk * kstep),
+                      a.row_major ? idesc_mn : idesc, (kb | kk) != 0 ? 1u : 0u);
           umma_commit(s_empty + stage);
           if (++stage == kStages) {
             stage = 0;
@@ -533,6 +546,8 @@ extern "C" int moonep_grouped_gemm(const void* x, const void* w0, const void* w1
   a.w_slots = w_slots;
   a.pre_gate = (uint16_t*)pre_gate;
   a.pre_up = (uint16_t*)pre_up;
+  a.b_kn = 0;
+  a.k_split = a.k_blocks;
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -549,6 +564,8 @@ extern "C" int moonep_grouped_gemm(const void* x, const void* w0, const void* w1
   grouped_gemm_kernel<<<grid, kGemmThreads, smem, (cudaStream_t)stream>>>(ta, tb0, tb1, a);
   return check_launch("grouped_gemm_kernel");
 }
+
+static int launch_wgrad(const CUtensorMap& tl, const CUtensorMap& tr, const WgradArgs& a, int num_sms, void* stream);
 
 // lt: [P, ld] bf16 = L^T, rt: [Q, ld] bf16 = R^T (ld elements per row, a multiple of 8; the column index is the
 // row of the dispatched shard).  For every group g with rows [cu[g-1], cu[g]) (a multiple of 16 long):
@@ -580,6 +597,44 @@ extern "C" int moonep_grouped_wgrad(const void* lt, const void* rt, long long ld
   a.p_tiles = P / BM;
   a.q_tiles = Q / BN;
   a.rows_cap = rows_cap;
+  a.row_major = 0;
+  return launch_wgrad(tl, tr, a, num_sms, stream);
+}
+
+// The same with the operands as they are: l = L [rows, P] and r = R [rows, Q] bf16, rows ldl / ldr elements apart
+// (multiples of 8), so that column slices of wider tensors can be passed.  No transposed copies are needed: the
+// tiles are staged MN-major (see make_smem_desc_mn).
+extern "C" int moonep_grouped_wgrad_rows(const void* l, long long ldl, const void* r, long long ldr, int rows, int P,
+                                         int Q, const int* cu_seqlens, int G, void* const* out_ptrs, const int* flags,
+                                         int* status, long long timeout_ms, int num_sms, void* stream) {
+  if (P <= 0 || Q <= 0 || P % BM != 0 || Q % BN != 0) {
+    set_error("moonep_grouped_wgrad_rows: P must be a multiple of 128 and Q a multiple of 256");
+    return 1;
+  }
+  if (ldl < P || ldr < Q || ldl % 8 != 0 || ldr % 8 != 0 || rows <= 0) {
+    set_error("moonep_grouped_wgrad_rows: row strides must be multiples of 8 and at least the matrix width");
+    return 1;
+  }
+  CUtensorMap tl, tr;
+  if (int rc = make_tmap(&tl, l, (unsigned long long)rows, (unsigned long long)P, 64, (unsigned long long)ldl)) return rc;
+  if (int rc = make_tmap(&tr, r, (unsigned long long)rows, (unsigned long long)Q, 64, (unsigned long long)ldr)) return rc;
+  WgradArgs a;
+  a.out_ptrs = (float* const*)out_ptrs;
+  a.flags = flags;
+  a.cu_seqlens = cu_seqlens;
+  a.status = status;
+  a.timeout_ns = (unsigned long long)(timeout_ms > 0 ? timeout_ms : 10000) * 1000000ull;
+  a.G = G;
+  a.P = P;
+  a.Q = Q;
+  a.p_tiles = P / BM;
+  a.q_tiles = Q / BN;
+  a.rows_cap = rows;
+  a.row_major = 1;
+  return launch_wgrad(tl, tr, a, num_sms, stream);
+}
+
+static int launch_wgrad(const CUtensorMap& tl, const CUtensorMap& tr, const WgradArgs& a, int num_sms, void* stream) {
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

@@ -142,7 +142,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
           if (rank == 0) mbar_expect_tx(s_full + stage, 2 * kPairStageBytes);
           const unsigned full_of_leader = mapa_u32(s_full + stage, 0);
           tma_load_2d_pair(st, &tmap_a, kb * BK, row0, full_of_leader);
-          tma_load_2d_pair(st + kPairATileBytes, tb, kb * BK, brow, full_of_leader);
+          if (a.b_kn) {
+            // W is [slots, K, N]: this CTA's 128 columns of the tile as two boxes of 64 columns x 64 k
+            const bool second = kb >= a.k_split;
+            const int kdim = (second ? a.k_blocks - a.k_split : a.k_split) * BK;  // K rows per expert in that tensor
+            const int y = wslot * kdim + (second ? kb - a.k_split : kb) * BK;
+            const int x0 = nb * BN + (int)rank * 128;
+            const CUtensorMap* tw = second ? &tmap_b1 : &tmap_b0;
+            tma_load_2d_pair(st + kPairATileBytes, tw, x0, y, full_of_leader);
+            tma_load_2d_pair(st + kPairATileBytes + kMnBoxBytes, tw, x0 + 64, y, full_of_leader);
+          } else {
+            tma_load_2d_pair(st + kPairATileBytes, tb, kb * BK, brow, full_of_leader);
+          }
           if (++stage == kPairStages) {
             stage = 0;
             phase ^= 1u;
@@ -155,6 +166,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
     // ---------------- MMA issuer (leader only) ----------------
     if (lane == 0 && rank == 0 && tmem_ok) {
       constexpr unsigned idesc = make_idesc(2 * BM, BN);
+      constexpr unsigned idesc_kn = make_idesc(2 * BM, BN, false, true);
+      const unsigned bstep = a.b_kn ? kDescStepMn : kDescStepK;
       PairSched sched(a);
       int stage = 0;
       unsigned phase = 0;
@@ -181,11 +194,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
           tc_fence_after();
           const unsigned char* st = s_tiles + (size_t)stage * kPairStageBytes;
           const unsigned long long adesc = make_smem_desc(st);
-          const unsigned long long bdesc = make_smem_desc(st + kPairATileBytes);
+          const unsigned long long bdesc = a.b_kn ? make_smem_desc_mn(st + kPairATileBytes) : make_smem_desc(st + kPairATileBytes);
 #pragma unroll
           for (int kk = 0; kk < BK / UMMA_K; ++kk)
-            umma_bf16_pair(d_tmem, adesc + (unsigned long long)(kk * 2), bdesc + (unsigned long long)(kk * 2), idesc,
-                           (kb | kk) != 0 ? 1u : 0u);
+            umma_bf16_pair(d_tmem, adesc + (unsigned long long)(kk * kDescStepK), bdesc + (unsigned long long)(kk * bstep),
+                           a.b_kn ? idesc_kn : idesc, (kb | kk) != 0 ? 1u : 0u);
           umma_commit_pair(s_empty + stage, 3);
           if (++stage == kPairStages) {
             stage = 0;
@@ -294,6 +307,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 
 using namespace moonep;
 
+static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb0, const CUtensorMap& tb1, const GemmArgs& a,
+                       int num_sms, void* stream);
+
 // Same contract as moonep_grouped_gemm (moonep.h).  Returns an error (and launches nothing) when the device
 // cannot co-schedule a pair of these CTAs.
 extern "C" int moonep_grouped_gemm_pair(const void* x, const void* w0, const void* w1, void* out, const float* row_scale,
@@ -341,6 +357,52 @@ extern "C" int moonep_grouped_gemm_pair(const void* x, const void* w0, const voi
   a.w_slots = w_slots;
   a.pre_gate = (uint16_t*)pre_gate;
   a.pre_up = (uint16_t*)pre_up;
+  a.b_kn = 0;
+  a.k_split = a.k_blocks;
+  return launch_pair(ta, tb0, tb1, a, num_sms, stream);
+}
+
+// y[rows of g] = x[rows of g] @ W[g] with W given as [slots, K, N] (N contiguous): the layout in which the
+// activation gradients need the forward weights, so no transposed copies are made.  x: [rows_cap, K0 + K1];
+// w0: [w_slots, K0, N]; w1 (optional): [w_slots, K1, N], continuing the contraction (x = [a | b], W = [w0; w1]).
+// out: [rows_cap, N] bf16.  K0, K1 multiples of 64, N a multiple of 256.
+extern "C" int moonep_grouped_gemm_pair_kn(const void* x, const void* w0, int K0, const void* w1, int K1, void* out,
+                                           const int* cu_seqlens, int G, int rows_cap, int N, int w_slots, int* status,
+                                           long long timeout_ms, int num_sms, void* stream) {
+  if (w1 == nullptr) K1 = 0;
+  if (K0 <= 0 || K0 % BK != 0 || K1 < 0 || K1 % BK != 0 || N <= 0 || N % BN != 0 || w_slots <= 0) {
+    set_error("moonep_grouped_gemm_pair_kn: K0, K1 must be multiples of 64 and N a multiple of 256");
+    return 1;
+  }
+  CUtensorMap ta, tb0, tb1;
+  if (int rc = make_tmap(&ta, x, (unsigned long long)rows_cap, (unsigned long long)(K0 + K1), BM)) return rc;
+  if (int rc = make_tmap(&tb0, w0, (unsigned long long)w_slots * K0, (unsigned long long)N, 64)) return rc;
+  if (int rc = make_tmap(&tb1, K1 ? w1 : w0, (unsigned long long)w_slots * (K1 ? K1 : K0), (unsigned long long)N, 64))
+    return rc;
+  GemmArgs a;
+  a.out = (uint16_t*)out;
+  a.row_scale = nullptr;
+  a.cu_seqlens = cu_seqlens;
+  a.status = status;
+  a.timeout_ns = (unsigned long long)(timeout_ms > 0 ? timeout_ms : 10000) * 1000000ull;
+  a.G = G;
+  a.n_per_group = N;
+  a.n_tiles = N / BN;
+  a.k_blocks = (K0 + K1) / BK;
+  a.ldo = N;
+  a.mode = kPlain;
+  a.rows_cap = rows_cap;
+  a.group_map = nullptr;
+  a.w_slots = w_slots;
+  a.pre_gate = nullptr;
+  a.pre_up = nullptr;
+  a.b_kn = 1;
+  a.k_split = K0 / BK;
+  return launch_pair(ta, tb0, tb1, a, num_sms, stream);
+}
+
+static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb0, const CUtensorMap& tb1, const GemmArgs& a,
+                       int num_sms, void* stream) {
   const size_t smem = (size_t)kPairStages * kPairStageBytes + 1024;
   static int max_pairs = -1;  // pairs of these CTAs the device runs at once
   if (max_pairs < 0) {

@@ -181,12 +181,23 @@ int moonep_grouped_gemm_pair(const void* x, const void* w0, const void* w1, void
                              const int* cu_seqlens, int G, int rows_cap, int K, int n_per_group, int mode, int* status,
                              long long timeout_ms, int num_sms, const int* group_map, int w_slots, void* pre_gate,
                              void* pre_up, void* stream);
+// y[rows of g] = x[rows of g] @ W[g] with W as [slots, K, N] (N contiguous) on CTA pairs; w1 (optional) continues
+// the contraction: x = [a | b], W = [w0; w1].  This is the layout in which activation gradients need the forward
+// weights, so no transposed copies are made.  K0, K1 multiples of 64, N a multiple of 256.
+int moonep_grouped_gemm_pair_kn(const void* x, const void* w0, int K0, const void* w1, int K1, void* out,
+                                const int* cu_seqlens, int G, int rows_cap, int N, int w_slots, int* status,
+                                long long timeout_ms, int num_sms, void* stream);
 // Weight gradients of all groups: out_ptrs[g][P, Q] fp32 (=, +=) L_g^T R_g with the contraction over the rows of
 // group g.  lt = L^T [P, ld], rt = R^T [Q, ld] bf16 (ld a multiple of 8, >= rows_cap).  flags[g]: 0 store (zeros for
 // an empty group), 1 accumulate, 2 store and leave empty groups alone.  out_ptrs, flags: device arrays [G].
 int moonep_grouped_wgrad(const void* lt, const void* rt, long long ld, int P, int Q, const int* cu_seqlens, int G,
                          void* const* out_ptrs, const int* flags, int rows_cap, int* status, long long timeout_ms,
                          int num_sms, void* stream);
+// The same from the operands as they are, l = L [rows, P], r = R [rows, Q] (rows ldl / ldr elements apart): no
+// transposed copies, the tiles are staged MN-major.
+int moonep_grouped_wgrad_rows(const void* l, long long ldl, const void* r, long long ldr, int rows, int P, int Q,
+                              const int* cu_seqlens, int G, void* const* out_ptrs, const int* flags, int* status,
+                              long long timeout_ms, int num_sms, void* stream);
 // Helpers of the MoE layer's backward pass and optimiser step, see moe_kernels.cu.
 int moonep_transpose_experts(const void* src, void* dst, int n, int d0, int d1, long long dst_ld,
                              long long dst_expert_stride, int col0, const int* active, void* stream);

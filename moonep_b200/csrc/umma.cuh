@@ -93,9 +93,29 @@ __device__ __forceinline__ unsigned long long make_smem_desc(const void* tile) {
   return d;
 }
 
-// kind::f16 instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, M x N.
-__host__ __device__ constexpr unsigned make_idesc(int m, int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
+// Descriptor of an MN-major tile (the M or N index is contiguous in memory, e.g. a [k, n] row-major slice)
+// stored with the 128-byte swizzle as TMA writes it from boxes of 64 columns x 64 rows: a 128-byte line holds
+// 64 consecutive M/N elements of one k, eight consecutive k form a 1024-byte swizzle atom, the next eight k
+// follow 1024 bytes later (stride byte offset) and the next 64 M/N elements start one box (8192 bytes) later
+// (leading byte offset).  One MMA (K = 16) consumes two atoms, so its successor starts 2048 bytes further.
+__device__ __forceinline__ unsigned long long make_smem_desc_mn(const void* tile) {
+  const unsigned addr = smem_u32(tile);
+  unsigned long long d = 0;
+  d |= (unsigned long long)((addr & 0x3FFFFu) >> 4);
+  d |= (unsigned long long)(8192 >> 4) << 16;  // leading byte offset: next 64 elements along M/N
+  d |= (unsigned long long)(1024 >> 4) << 32;  // stride byte offset: next 8 elements along K
+  d |= (unsigned long long)1 << 46;
+  d |= (unsigned long long)2 << 61;
+  return d;
+}
+constexpr unsigned kDescStepK = 2;       // K-major: 16 elements = 32 bytes along the swizzled row, in 16-byte units
+constexpr unsigned kDescStepMn = 128;    // MN-major: 16 k = two 1024-byte atoms, in 16-byte units
+constexpr unsigned kMnBoxBytes = 64 * 64 * 2;  // one 64 x 64 bf16 box
+
+// kind::f16 instruction descriptor: bf16 x bf16 -> fp32, M x N; a_mn / b_mn: that operand is MN-major.
+__host__ __device__ constexpr unsigned make_idesc(int m, int n, bool a_mn = false, bool b_mn = false) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
+         ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
 }
 
 __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
@@ -118,6 +138,8 @@ struct GemmArgs {
   int rows_cap;      // rows of X
   const int* group_map;  // [G] weight slot of every group, or null for the identity
   int w_slots;           // number of weight slots (rows of W = w_slots * n_per_group)
+  int b_kn;              // CTA-pair kernel only: W is [slots, K, N] (N contiguous), staged as MN-major tiles
+  int k_split;           // with b_kn: K blocks served by the first W tensor, the rest come from the second
   uint16_t* pre_gate;    // SwiGLU only, optional: the pre-activations x Wg^T and x Wu^T, [rows, ldo] bf16 each,
   uint16_t* pre_up;      // kept for the backward pass so that it need not recompute them
 };
@@ -225,16 +247,17 @@ inline EncodeTiledFn encode_tiled() {
   return fn;
 }
 
-// 2-D bf16 row-major [rows, cols] tensor, box = 64 columns x box_rows rows, 128-byte swizzle.
+// 2-D bf16 row-major [rows, cols] tensor (rows ld elements apart; 0 = cols), box = 64 columns x box_rows rows,
+// 128-byte swizzle.
 inline int make_tmap(CUtensorMap* m, const void* base, unsigned long long rows, unsigned long long cols,
-                     unsigned box_rows) {
+                     unsigned box_rows, unsigned long long ld = 0) {
   EncodeTiledFn fn = encode_tiled();
   if (fn == nullptr) {
     set_error("cuTensorMapEncodeTiled is not available (no CUDA driver?)");
     return 1;
   }
   cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {cols * 2};
+  cuuint64_t strides[1] = {(ld ? ld : cols) * 2};
   cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,

@@ -35,7 +35,10 @@ from ..ops.grouped_gemm import (
     WGRAD_STORE,
     WGRAD_STORE_NONEMPTY,
     grouped_gemm,
+    grouped_gemm_kn,
     grouped_wgrad,
+    kn_kernel_supports,
+    grouped_wgrad_rows,
     wgrad_kernel_supports,
 )
 from ..ops.moe_ops import sgd_update, swiglu_bwd, transpose_experts
@@ -159,14 +162,23 @@ class ExpertParallelMoE:
         rows = int(x_nvs.shape[0])
         dev = x_nvs.device
         a, u = saved["a"], saved["u"]
-        g = grouped_gemm(dy_nvs, self._local_transposed([self.w_down], plan), cu, group_map=gmap)  # dy @ W_down, unscaled
+        # activation gradients multiply by the forward weights as stored ([E+B, out, in] = [G, K, N] for this product):
+        # the CTA-pair kernel stages them as MN-major tiles; otherwise K-major copies of the local experts are made
+        direct = kn_kernel_supports(dy_nvs, [self.w_down]) and kn_kernel_supports(dy_nvs, [self.w_gate, self.w_up])
+        if direct:
+            g = grouped_gemm_kn(dy_nvs, [self.w_down], cu)  # dy @ W_down, unscaled
+        else:
+            g = grouped_gemm(dy_nvs, self._local_transposed([self.w_down], plan), cu, group_map=gmap)
         dadu = torch.empty(rows, 2 * I, dtype=torch.bfloat16, device=dev)
         hsw = torch.empty(rows, I, dtype=torch.bfloat16, device=dev)
         dgate_nvs = ctx["weights_buf_local"].view(torch.float32)  # gate gradients ride the weights channel home
         swiglu_bwd(a, u, g, w_nvs, cu[-1:], dadu, hsw, dgate_nvs)
         del a, u, g
         if self._weight_grads_on_kernel(x_nvs, dy_nvs, dadu, hsw, cu):
-            grouped_gemm(dadu, self._local_transposed([self.w_gate, self.w_up], plan), cu, group_map=gmap, out=dy_nvs)
+            if direct:
+                grouped_gemm_kn(dadu, [self.w_gate, self.w_up], cu, out=dy_nvs)  # dx = da Wg + du Wu
+            else:
+                grouped_gemm(dadu, self._local_transposed([self.w_gate, self.w_up], plan), cu, group_map=gmap, out=dy_nvs)
             dx, dgates, _ = buf.combine(plan, dy_nvs, dgate_nvs, zero_copy=True)
             buf.reduce_grad(plan, False, self.g_gate, self.g_up, self.g_down, self.red[0], self.red[1], self.red[2],
                             owner_local=True)  # fmt: skip
@@ -196,7 +208,10 @@ class ExpertParallelMoE:
                     for gt in (self.g_gate, self.g_up, self.g_down):
                         gt[le].zero_()
             self._fresh = False
-        grouped_gemm(dadu, self._local_transposed([self.w_gate, self.w_up], plan), cu, group_map=gmap, out=dy_nvs)
+        if direct:
+            grouped_gemm_kn(dadu, [self.w_gate, self.w_up], cu, out=dy_nvs)
+        else:
+            grouped_gemm(dadu, self._local_transposed([self.w_gate, self.w_up], plan), cu, group_map=gmap, out=dy_nvs)
         dx, dgates, _ = buf.combine(plan, dy_nvs, dgate_nvs, zero_copy=True)
         buf.reduce_grad(plan, False, self.g_gate, self.g_up, self.g_down, self.red[0], self.red[1], self.red[2],
                         owner_local=True)  # fmt: skip
@@ -217,13 +232,20 @@ class ExpertParallelMoE:
         if not ok:
             return False
 
+        flags = self._wgrad_flags[bool(self._fresh)]
+        status = self.buffer._require_ctx()["_backend"].status
+        if config.wgrad_layout() == "rows":  # the kernel stages MN-major tiles: no transposed copies
+            grouped_wgrad_rows(dadu[:, :I], x_nvs, cu, self._wgrad_ptrs[0], flags, status=status)
+            grouped_wgrad_rows(dadu[:, I:], x_nvs, cu, self._wgrad_ptrs[1], flags, status=status)
+            grouped_wgrad_rows(dy_nvs, hsw, cu, self._wgrad_ptrs[2], flags, status=status)
+            self._fresh = False
+            return True
+
         def transposed(t):
             out = torch.empty(1, int(t.shape[1]), rows, dtype=torch.bfloat16, device=dev)
             return transpose_experts(t[:rows].unsqueeze(0), out)[0]
 
         xt, dadut, dyt, hswt = transposed(x_nvs), transposed(dadu), transposed(dy_nvs), transposed(hsw)
-        flags = self._wgrad_flags[bool(self._fresh)]
-        status = self.buffer._require_ctx()["_backend"].status
         grouped_wgrad(dadut[:I], xt, cu, self._wgrad_ptrs[0], flags, status=status)  # dW_gate = da^T x
         grouped_wgrad(dadut[I:], xt, cu, self._wgrad_ptrs[1], flags, status=status)  # dW_up   = du^T x
         grouped_wgrad(dyt, hswt, cu, self._wgrad_ptrs[2], flags, status=status)  # dW_down = dy^T (h * gate weight)

@@ -116,7 +116,9 @@ _SIGNATURES = {
     "moonep_grad_reduce": (_i, [_vp, ctypes.POINTER(_vp), ctypes.POINTER(_vp), _i, _vp, _i, _ll, _i, _i, _i, _i, _vp]),
     "moonep_grouped_gemm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _ll, _i, _vp, _i, _vp, _vp, _vp]),
     "moonep_grouped_gemm_pair": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _ll, _i, _vp, _i, _vp, _vp, _vp]),
+    "moonep_grouped_gemm_pair_kn": (_i, [_vp, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _ll, _i, _vp]),
     "moonep_grouped_wgrad": (_i, [_vp, _vp, _ll, _i, _i, _vp, _i, _vp, _vp, _i, _vp, _ll, _i, _vp]),
+    "moonep_grouped_wgrad_rows": (_i, [_vp, _ll, _vp, _ll, _i, _i, _i, _vp, _i, _vp, _vp, _vp, _ll, _i, _vp]),
     "moonep_transpose_experts": (_i, [_vp, _vp, _i, _i, _i, _ll, _ll, _i, _vp, _vp]),
     "moonep_sgd_update": (_i, [_vp, _vp, _ll, ctypes.c_float, _vp]),
     "moonep_swiglu_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp]),

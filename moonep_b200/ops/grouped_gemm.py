@@ -106,6 +106,57 @@ def grouped_gemm(x, w, cu_seqlens, *, w_up=None, row_scale=None, mode="plain", o
     return out
 
 
+def grouped_gemm_kn_reference(x, ws, cu_seqlens):
+    """``y[rows of g] = x[rows of g] @ cat([w[g] for w in ws], dim=0)`` per group in fp32."""
+    N = int(ws[0].shape[2])
+    out = torch.zeros(x.shape[0], N, dtype=torch.bfloat16, device=x.device)
+    start = 0
+    for g, end in enumerate(cu_seqlens.tolist()):
+        if end > start:
+            wcat = torch.cat([w[g].float() for w in ws], dim=0)
+            out[start:end] = (x[start:end].float() @ wcat).to(torch.bfloat16)
+        start = max(start, int(end))
+    return out
+
+
+def kn_kernel_supports(x, ws) -> bool:
+    N = int(ws[0].shape[2])
+    return (x.is_cuda and x.dtype == torch.bfloat16 and N % 256 == 0 and all(int(w.shape[1]) % 64 == 0 for w in ws)
+            and x.shape[0] >= 128 and len(ws) in (1, 2) and config.gemm_on_cta_pairs())  # fmt: skip
+
+
+def grouped_gemm_kn(x, ws, cu_seqlens, *, out=None, status=None, num_sms=0):
+    """``y[rows of g] = x[rows of g] @ W[g]`` with the weights given as ``[G, K, N]`` (N contiguous): the product an
+    activation gradient needs from forward weights stored ``[G, out, in]``, without transposed copies.  ``ws`` is one
+    tensor or two that continue the contraction (``x = [a | b]``, ``W = [ws[0]; ws[1]]``).  Runs on the CTA-pair kernel
+    (MN-major W tiles); a per-group fp32 reference elsewhere."""
+    ws = list(ws)
+    G, _, N = (int(v) for v in ws[0].shape)
+    Ks = [int(w.shape[1]) for w in ws]
+    assert x.dim() == 2 and x.shape[1] == sum(Ks) and cu_seqlens.numel() == G
+    assert all(w.shape[0] == G and w.shape[2] == N for w in ws)
+    if not kn_kernel_supports(x, ws):
+        res = grouped_gemm_kn_reference(x, ws, cu_seqlens)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
+    assert x.is_contiguous() and all(w.is_contiguous() and w.dtype == torch.bfloat16 for w in ws)
+    assert cu_seqlens.dtype == torch.int32 and cu_seqlens.is_contiguous() and cu_seqlens.is_cuda
+    if out is None:
+        out = torch.empty(x.shape[0], N, dtype=torch.bfloat16, device=x.device)
+    assert out.is_contiguous() and out.shape == (x.shape[0], N) and out.dtype == torch.bfloat16
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        rc = lib.moonep_grouped_gemm_pair_kn(
+            x.data_ptr(), ws[0].data_ptr(), Ks[0], ws[1].data_ptr() if len(ws) == 2 else None, Ks[1] if len(ws) == 2 else 0,
+            out.data_ptr(), cu_seqlens.data_ptr(), G, int(x.shape[0]), N, G, None if status is None else status.data_ptr(),
+            config.timeout_ms(), int(num_sms), torch.cuda.current_stream().cuda_stream,
+        )  # fmt: skip
+    _lib.check(rc, "moonep_grouped_gemm_pair_kn")
+    return out
+
+
 WGRAD_STORE, WGRAD_ACCUMULATE, WGRAD_STORE_NONEMPTY = 0, 1, 2
 
 
@@ -159,6 +210,30 @@ def grouped_wgrad(left_t, right_t, cu_seqlens, out_ptrs, flags, *, status=None, 
             torch.cuda.current_stream().cuda_stream,
         )  # fmt: skip
     _lib.check(rc, "moonep_grouped_wgrad")
+
+
+def grouped_wgrad_rows(left, right, cu_seqlens, out_ptrs, flags, *, status=None, num_sms=0):
+    """``grouped_wgrad`` from the operands as they are: ``left`` ``[rows, P]`` and ``right`` ``[rows, Q]`` bf16 with unit
+    column stride (column slices of wider tensors are fine), no transposed copies.  Same targets and flags."""
+    rows, P = (int(v) for v in left.shape)
+    Q = int(right.shape[1])
+    G = int(cu_seqlens.numel())
+    assert right.shape[0] == rows and left.dtype == torch.bfloat16 and right.dtype == torch.bfloat16
+    assert left.stride(1) == 1 and right.stride(1) == 1 and left.is_cuda
+    ldl, ldr = int(left.stride(0)), int(right.stride(0))
+    assert P % 128 == 0 and Q % 256 == 0 and ldl % 8 == 0 and ldr % 8 == 0, f"P={P}, Q={Q}, strides {ldl}, {ldr}"
+    assert left.data_ptr() % 16 == 0 and right.data_ptr() % 16 == 0
+    assert out_ptrs.dtype == torch.int64 and out_ptrs.numel() == G and out_ptrs.is_cuda and out_ptrs.is_contiguous()
+    assert flags.dtype == torch.int32 and flags.numel() == G and flags.is_cuda and flags.is_contiguous()
+    assert cu_seqlens.dtype == torch.int32 and cu_seqlens.is_contiguous() and cu_seqlens.is_cuda
+    lib = _lib.load()
+    with torch.cuda.device(left.device):
+        rc = lib.moonep_grouped_wgrad_rows(
+            left.data_ptr(), ldl, right.data_ptr(), ldr, rows, P, Q, cu_seqlens.data_ptr(), G, out_ptrs.data_ptr(),
+            flags.data_ptr(), None if status is None else status.data_ptr(), config.timeout_ms(), int(num_sms),
+            torch.cuda.current_stream().cuda_stream,
+        )  # fmt: skip
+    _lib.check(rc, "moonep_grouped_wgrad_rows")
 
 
 def _fallback_allowed() -> bool:

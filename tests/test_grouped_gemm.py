@@ -97,6 +97,7 @@ def test_wgrad_reference_semantics_on_cpu():
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("layout", ["transposed", "rows"])
 @pytest.mark.parametrize(
     "rows,P,Q",
     [
@@ -106,14 +107,24 @@ def test_wgrad_reference_semantics_on_cpu():
         ([128 * ((i * 5) % 4) for i in range(20)], 384, 768),
     ],
 )
-def test_grouped_wgrad_matches_fp32_reference(rows, P, Q):
-    from moonep_b200.ops.grouped_gemm import grouped_wgrad, grouped_wgrad_reference
+def test_grouped_wgrad_matches_fp32_reference(rows, P, Q, layout):
+    from moonep_b200.ops.grouped_gemm import grouped_wgrad, grouped_wgrad_reference, grouped_wgrad_rows
     from moonep_b200.ops.moe_ops import transpose_experts
 
     G = len(rows)
     left, right, cu, cap = _wgrad_case(rows, P, Q, seed=len(rows), device="cuda")
-    lt = transpose_experts(left.unsqueeze(0), torch.empty(1, P, cap, dtype=torch.bfloat16, device="cuda"))[0]
-    rt = transpose_experts(right.unsqueeze(0), torch.empty(1, Q, cap, dtype=torch.bfloat16, device="cuda"))[0]
+    if layout == "transposed":
+        lt = transpose_experts(left.unsqueeze(0), torch.empty(1, P, cap, dtype=torch.bfloat16, device="cuda"))[0]
+        rt = transpose_experts(right.unsqueeze(0), torch.empty(1, Q, cap, dtype=torch.bfloat16, device="cuda"))[0]
+
+        def run(ptrs_t, flags_t):
+            grouped_wgrad(lt, rt, cu, ptrs_t, flags_t, status=status)
+    else:  # the operands as they are, the left one as a column slice of a wider tensor
+        wide = torch.cat([torch.full_like(left, 3.0), left], dim=1)
+        left_view = wide[:, P:]
+
+        def run(ptrs_t, flags_t):
+            grouped_wgrad_rows(left_view, right, cu, ptrs_t, flags_t, status=status)
     flag_list = [(0, 1, 2)[g % 3] for g in range(G)]
     skipped = G - 1 if rows[-1] == 0 else None  # a group without a target is allowed when it has no rows
     init = torch.randn(G, P, Q, device="cuda")
@@ -123,7 +134,7 @@ def test_grouped_wgrad_matches_fp32_reference(rows, P, Q):
         ptrs[skipped] = 0
     status = torch.zeros(8, dtype=torch.int32, device="cuda")
     flags = torch.tensor(flag_list, dtype=torch.int32, device="cuda")
-    grouped_wgrad(lt, rt, cu, torch.tensor(ptrs, dtype=torch.int64, device="cuda"), flags, status=status)
+    run(torch.tensor(ptrs, dtype=torch.int64, device="cuda"), flags)
     torch.cuda.synchronize()
     assert status.tolist()[0] == 0, f"kernel reported status {status.tolist()}"
     want = init.clone().cpu()
@@ -133,9 +144,50 @@ def test_grouped_wgrad_matches_fp32_reference(rows, P, Q):
     tol = 2e-3 * max(1.0, want.abs().max().item())
     assert err <= tol, f"max abs err {err} > {tol}"
     # again on the same buffers: accumulating groups add a second time, the others give the same result
-    grouped_wgrad(lt, rt, cu, torch.tensor(ptrs, dtype=torch.int64, device="cuda"), flags, status=status)
+    run(torch.tensor(ptrs, dtype=torch.int64, device="cuda"), flags)
     torch.cuda.synchronize()
     assert status.tolist()[0] == 0
     grouped_wgrad_reference(left.cpu(), right.cpu(), cu.cpu(), targets, flag_list)
     err = (out.cpu() - want).abs().max().item()
     assert err <= 2 * tol, f"second launch: max abs err {err}"
+
+
+def test_kn_reference_on_cpu():
+    from moonep_b200.ops.grouped_gemm import grouped_gemm_kn
+
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(48, 24, generator=g).to(torch.bfloat16)
+    w0 = torch.randn(2, 16, 8, generator=g).to(torch.bfloat16)
+    w1 = torch.randn(2, 8, 8, generator=g).to(torch.bfloat16)
+    cu = torch.tensor([16, 48], dtype=torch.int32)
+    y = grouped_gemm_kn(x, [w0, w1], cu)
+    want = x[16:48].float() @ torch.cat([w0[1], w1[1]]).float()
+    assert torch.allclose(y[16:48].float(), want, atol=0.1, rtol=2e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize(
+    "rows,Ks,N",
+    [
+        ([128], [64], 256),
+        ([256, 0, 128], [128, 64], 256),
+        ([384, 128, 0, 640], [512], 512),
+        ([128 * ((i * 3) % 4) for i in range(12)], [256, 256], 768),
+    ],
+)
+def test_grouped_gemm_kn_matches_fp32_reference(rows, Ks, N):
+    """Weights given as [G, K, N] (the activation-gradient product), staged as MN-major tiles by the CTA-pair kernel."""
+    from moonep_b200.ops.grouped_gemm import grouped_gemm_kn, grouped_gemm_kn_reference
+
+    g = torch.Generator().manual_seed(len(rows))
+    G, total = len(rows), sum(rows)
+    cu = torch.tensor([sum(rows[: i + 1]) for i in range(G)], dtype=torch.int32, device="cuda")
+    x = (torch.randn(total + 256, sum(Ks), generator=g) * 0.5).to(torch.bfloat16).cuda()
+    ws = [(torch.randn(G, k, N, generator=g) * 0.05).to(torch.bfloat16).cuda() for k in Ks]
+    status = torch.zeros(8, dtype=torch.int32, device="cuda")
+    y = grouped_gemm_kn(x, ws, cu, status=status)
+    torch.cuda.synchronize()
+    assert status.tolist()[0] == 0, f"kernel reported status {status.tolist()}"
+    want = grouped_gemm_kn_reference(x, ws, cu)[:total].float()
+    err = (y[:total].float() - want).abs().max().item()
+    assert err <= 2e-2 * max(1.0, want.abs().max().item()), f"max abs err {err}"
