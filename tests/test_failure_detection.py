@@ -37,10 +37,15 @@ except Exception as exc:
 def test_rank_leaving_between_steps_is_detected_on_the_host(tmp_path):
     script = tmp_path / "leave.py"
     script.write_text(WORKER.format(root=ROOT))
+    import socket
+
+    with socket.socket() as sk:  # a fixed port can still be in TIME_WAIT from the previous run
+        sk.bind(("127.0.0.1", 0))
+        port = sk.getsockname()[1]
     env = dict(os.environ, MASTER_ADDR="127.0.0.1")
     out = subprocess.run(
         [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-         "--master-port", "29651", str(script)],
+         "--master-port", str(port), str(script)],
         capture_output=True, text=True, timeout=180, env=env, cwd=ROOT,
     )  # fmt: skip
     assert out.stdout.count("STEP1 OK") == 2, out.stdout + out.stderr[-2000:]

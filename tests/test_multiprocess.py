@@ -10,7 +10,16 @@ import torch
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
+def _free_port() -> int:
+    import socket
+
+    with socket.socket() as sk:
+        sk.bind(("127.0.0.1", 0))
+        return sk.getsockname()[1]
+
+
 def _run_worker(nproc, backend, port, timeout, extra_env=None):
+    port = _free_port()  # a fixed port can still be in TIME_WAIT from the previous run
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", MOONEP_TIMEOUT_MS=os.environ.get("MOONEP_TIMEOUT_MS", "5000"))
     env.update(extra_env or {})
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr",
