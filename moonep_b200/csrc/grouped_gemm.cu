@@ -245,11 +245,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 //
 //   dW[g] (P x Q, fp32) = L[rows of g, :P]^T  @  R[rows of g, :Q]
 //
-// The operands arrive transposed (Lt: [P, ld], Rt: [Q, ld], the row index contiguous), which makes
-// both K-major for the same TMA boxes, swizzle and MMA descriptors as the forward kernel; the K loop
-// of a tile runs over the group's rows (k0 = first row of the group, any multiple of 16 rows long; the
-// last 64-row block issues only the MMAs that lie inside the group).  One tile is 128 x 256 of one
-// group's dW.  Per group, flags[g] selects: 0 store (and store zeros if the group has no rows),
+// The operands are taken as stored (L: [rows, P], R: [rows, Q]; tiles are staged MN-major, see
+// make_smem_desc_mn) or transposed (Lt: [P, ld], Rt: [Q, ld], the row index contiguous, K-major tiles as
+// in the forward kernel).  The K loop of a tile runs over the group's rows (k0 = first row of the group,
+// any multiple of 16 rows long; the last 64-row block issues only the MMAs that lie inside the group).
+// One tile is 128 x 256 of one group's dW.  The groups that have anything to do are listed once per CTA
+// in shared memory (in group order, the same list in every CTA), so empty groups cost nothing.  Per group, flags[g] selects: 0 store (and store zeros if the group has no rows),
 // 1 add to what is there, 2 store, leave the target alone if the group has no rows.  A null
 // out_ptrs[g] skips the group; rows without a target are reported through the status block.
 constexpr int kWgradStageLd = 36;  // floats per row of an epilogue warp's 32 x 32 staging block (16-byte aligned, conflict free)
@@ -265,26 +266,67 @@ struct WgradArgs {
   int row_major;  // operands are L [rows, P] and R [rows, Q] as they are (MN-major tiles) instead of their transposes
 };
 
+constexpr int kWgradMaxGroups = 512;  // groups per launch (their work list lives in shared memory)
+
+struct WgradGroups {  // per listed group: which group, its first row, its rows, target and mode
+  int n;
+  short g[kWgradMaxGroups];
+  int start[kWgradMaxGroups];
+  int krows[kWgradMaxGroups];
+  int flag[kWgradMaxGroups];
+  float* out[kWgradMaxGroups];
+};
+
+// Warp-collective: list the groups with rows, and the empty ones whose target must be zeroed, in group order.
+__device__ __forceinline__ void wgrad_list_groups(const WgradArgs& a, WgradGroups& sg, int lane) {
+  int n = 0;
+  for (int base = 0; base < a.G; base += 32) {
+    const int g = base + lane;
+    bool listed = false;
+    int start = 0, krows = 0, flag = 0;
+    float* out = nullptr;
+    if (g < a.G) {
+      start = g > 0 ? min(a.cu_seqlens[g - 1], a.rows_cap) : 0;
+      const int end = min(a.cu_seqlens[g], a.rows_cap);
+      krows = end > start ? end - start : 0;
+      out = a.out_ptrs[g];
+      flag = a.flags[g];
+      // the K coordinate of a TMA copy must be a multiple of 8 elements and the MMAs take 16 rows at a time:
+      // a group that does not start and end on a multiple of 16 is refused (reported as rows without a target)
+      if (((start | end) & 15) != 0) out = nullptr;
+      listed = krows > 0 || (out != nullptr && flag == 0);
+    }
+    const unsigned mask = __ballot_sync(0xffffffffu, listed);
+    const int pos = n + __popc(mask & ((1u << lane) - 1u));
+    if (listed && pos < kWgradMaxGroups) {
+      sg.g[pos] = (short)g;
+      sg.start[pos] = start;
+      sg.krows[pos] = krows;
+      sg.flag[pos] = flag;
+      sg.out[pos] = out;
+    }
+    n += __popc(mask);
+  }
+  if (lane == 0) sg.n = min(n, kWgradMaxGroups);
+}
+
 struct WgradTile {
-  int g, pb, qb, k0, krows;
+  int g, pb, qb, k0, krows, flag;
   float* out;
 };
 
-__device__ __forceinline__ WgradTile wgrad_tile(const WgradArgs& a, long long t) {
+__device__ __forceinline__ WgradTile wgrad_tile(const WgradArgs& a, const WgradGroups& sg, long long t) {
   WgradTile w;
   const int per_group = a.p_tiles * a.q_tiles;
-  w.g = (int)(t / per_group);
+  const int idx = (int)(t / per_group);
   const int rem = (int)(t % per_group);
   w.pb = rem / a.q_tiles;
   w.qb = rem % a.q_tiles;
-  const int start = w.g > 0 ? min(a.cu_seqlens[w.g - 1], a.rows_cap) : 0;
-  const int end = min(a.cu_seqlens[w.g], a.rows_cap);
-  w.k0 = start;
-  w.krows = end > start ? end - start : 0;
-  w.out = a.out_ptrs[w.g];
-  // the K coordinate of a TMA copy must be a multiple of 8 elements and the MMAs take 16 rows at a time:
-  // a group that does not start and end on a multiple of 16 is refused (reported as rows without a target)
-  if (((start | end) & 15) != 0) w.out = nullptr;
+  w.g = sg.g[idx];
+  w.k0 = sg.start[idx];
+  w.krows = sg.krows[idx];
+  w.flag = sg.flag[idx];
+  w.out = sg.out[idx];
   return w;
 }
 
@@ -294,8 +336,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   extern __shared__ unsigned char s_raw[];
   __shared__ __align__(8) unsigned long long s_full[kStages], s_empty[kStages], s_tfull[2], s_tempty[2];
   __shared__ unsigned s_tmem_base;
+  __shared__ WgradGroups s_groups;
   unsigned char* s_tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(s_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (warp == 0) wgrad_list_groups(a, s_groups, lane);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -316,7 +360,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   __syncthreads();
   tc_fence_after();
   const unsigned tmem_base = s_tmem_base;
-  const long long num_tiles = (long long)a.G * a.p_tiles * a.q_tiles;
+  const long long num_tiles = (long long)s_groups.n * a.p_tiles * a.q_tiles;
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -325,7 +369,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       unsigned phase = 0;
       bool failed = false;
       for (long long t = blockIdx.x; t < num_tiles && !failed; t += gridDim.x) {
-        const WgradTile w = wgrad_tile(a, t);
+        const WgradTile w = wgrad_tile(a, s_groups, t);
         if (w.krows == 0 || w.out == nullptr) continue;
         const int kbs = (w.krows + BK - 1) / BK;
         for (int kb = 0; kb < kbs; ++kb) {
@@ -369,7 +413,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       int it = 0;
       bool failed = false;
       for (long long t = blockIdx.x; t < num_tiles && !failed; t += gridDim.x) {
-        const WgradTile w = wgrad_tile(a, t);
+        const WgradTile w = wgrad_tile(a, s_groups, t);
         if (w.krows == 0 || w.out == nullptr) continue;
         const int buf = it & 1;
         ++it;
@@ -412,8 +456,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     unsigned tphase[2] = {0, 0};
     int it = 0;
     for (long long t = blockIdx.x; t < num_tiles; t += gridDim.x) {
-      const WgradTile w = wgrad_tile(a, t);
-      const int flag = a.flags[w.g];
+      const WgradTile w = wgrad_tile(a, s_groups, t);
+      const int flag = w.flag;
       if (w.out == nullptr) {
         if (w.krows != 0 && q == 0 && lane == 0 && w.pb == 0 && w.qb == 0 && a.status != nullptr &&
             atomicCAS(a.status + MOONEP_ST_CODE, 0, MOONEP_STATUS_BAD_INDEX) == 0) {
@@ -578,6 +622,10 @@ extern "C" int moonep_grouped_wgrad(const void* lt, const void* rt, long long ld
     set_error("moonep_grouped_wgrad: P must be a multiple of 128 and Q a multiple of 256");
     return 1;
   }
+  if (G < 1 || G > kWgradMaxGroups) {
+    set_error("moonep_grouped_wgrad: at most " + std::to_string(kWgradMaxGroups) + " groups per launch");
+    return 1;
+  }
   if (ld <= 0 || ld % 8 != 0 || rows_cap > ld) {
     set_error("moonep_grouped_wgrad: ld must be a multiple of 8 and at least rows_cap");
     return 1;
@@ -609,6 +657,10 @@ extern "C" int moonep_grouped_wgrad_rows(const void* l, long long ldl, const voi
                                          int* status, long long timeout_ms, int num_sms, void* stream) {
   if (P <= 0 || Q <= 0 || P % BM != 0 || Q % BN != 0) {
     set_error("moonep_grouped_wgrad_rows: P must be a multiple of 128 and Q a multiple of 256");
+    return 1;
+  }
+  if (G < 1 || G > kWgradMaxGroups) {
+    set_error("moonep_grouped_wgrad_rows: at most " + std::to_string(kWgradMaxGroups) + " groups per launch");
     return 1;
   }
   if (ldl < P || ldr < Q || ldl % 8 != 0 || ldr % 8 != 0 || rows <= 0) {

@@ -41,21 +41,24 @@ constexpr unsigned kPairATileBytes = BM * BK * 2;                         // 16 
 constexpr unsigned kPairBHalfBytes = 128 * BK * 2;                        // 16 KB: this CTA's half of the W tile
 constexpr unsigned kPairStageBytes = kPairATileBytes + kPairBHalfBytes;   // 32 KB per CTA and stage
 constexpr int kPairKernelId = 15;
+constexpr int kPairGroupsInSmem = 2048;  // group ends are walked from shared memory up to this many groups
 
 // Walks the pair tiles in order: group-major, then pairs of row blocks, then column tiles (fastest).
 struct PairSched {
   const GemmArgs& a;
+  const int* cu;     // group ends: the shared-memory copy when it fits, else global memory
   int g;             // current group
   long long t_base;  // index of its first tile
   int blk0;          // its first 128-row block
   int nblk;          // its number of 128-row blocks
   long long tiles;   // its number of pair tiles
 
-  __device__ explicit PairSched(const GemmArgs& args) : a(args), g(-1), t_base(0), blk0(0), nblk(0), tiles(0) {}
+  __device__ PairSched(const GemmArgs& args, const int* ends)
+      : a(args), cu(ends), g(-1), t_base(0), blk0(0), nblk(0), tiles(0) {}
 
   __device__ void load_group() {
-    const int start = g > 0 ? min(a.cu_seqlens[g - 1], a.rows_cap) : 0;
-    const int end = min(a.cu_seqlens[g], a.rows_cap);
+    const int start = g > 0 ? min(cu[g - 1], a.rows_cap) : 0;
+    const int end = min(cu[g], a.rows_cap);
     blk0 = start / BM;
     nblk = end > start ? (end - start) / BM : 0;
     tiles = (long long)((nblk + 1) / 2) * a.n_tiles;
@@ -85,9 +88,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
   extern __shared__ unsigned char s_raw[];
   __shared__ __align__(8) unsigned long long s_full[kPairStages], s_empty[kPairStages], s_tfull[2], s_tempty[2], s_done;
   __shared__ unsigned s_tmem_base;
+  __shared__ int s_cu[kPairGroupsInSmem];
   unsigned char* s_tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(s_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const unsigned rank = cluster_ctarank();  // 0: leader (issues the MMAs), 1: its peer
+  // every role walks the groups once; from shared memory a group costs a few cycles instead of an L2 round trip
+  const int* cu = a.G <= kPairGroupsInSmem ? s_cu : a.cu_seqlens;
+  if (a.G <= kPairGroupsInSmem)
+    for (int g = threadIdx.x; g < a.G; g += blockDim.x) s_cu[g] = a.cu_seqlens[g];
   const long long pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
 
   if (threadIdx.x == 0) {
@@ -120,7 +128,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
   if (warp == 0) {
     // ---------------- TMA producer (both CTAs) ----------------
     if (lane == 0 && tmem_ok) {
-      PairSched sched(a);
+      PairSched sched(a, cu);
       int stage = 0;
       unsigned phase = 0;
       bool failed = false;
@@ -168,7 +176,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
       constexpr unsigned idesc = make_idesc(2 * BM, BN);
       constexpr unsigned idesc_kn = make_idesc(2 * BM, BN, false, true);
       const unsigned bstep = a.b_kn ? kDescStepMn : kDescStepK;
-      PairSched sched(a);
+      PairSched sched(a, cu);
       int stage = 0;
       unsigned phase = 0;
       unsigned tphase[2] = {0, 0};
@@ -216,7 +224,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
     // ---------------- epilogue (warps 2..5, both CTAs) ----------------
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     const unsigned tempty_of_leader[2] = {mapa_u32(s_tempty + 0, 0), mapa_u32(s_tempty + 1, 0)};
-    PairSched sched(a);
+    PairSched sched(a, cu);
     unsigned tphase[2] = {0, 0};
     int it = 0;
     int pig, nb;

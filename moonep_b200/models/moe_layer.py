@@ -38,6 +38,7 @@ from ..ops.grouped_gemm import (
     grouped_gemm_kn,
     grouped_wgrad,
     kn_kernel_supports,
+    WGRAD_MAX_GROUPS,
     grouped_wgrad_rows,
     wgrad_kernel_supports,
 )
@@ -226,7 +227,7 @@ class ExpertParallelMoE:
         rows = int(x_nvs.shape[0]) // 64 * 64
         dev = x_nvs.device
         ok = (
-            config.wgrad_on_kernel() and x_nvs.is_cuda and rows >= 64 and self.buffer._require_ctx()["token_padding"] % 16 == 0
+            config.wgrad_on_kernel() and x_nvs.is_cuda and rows >= 64 and self.E + self.B <= WGRAD_MAX_GROUPS and self.buffer._require_ctx()["token_padding"] % 16 == 0
             and wgrad_kernel_supports(I, H, rows, dev) and wgrad_kernel_supports(H, I, rows, dev)
         )  # fmt: skip
         if not ok:

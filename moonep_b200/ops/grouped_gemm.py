@@ -158,6 +158,7 @@ def grouped_gemm_kn(x, ws, cu_seqlens, *, out=None, status=None, num_sms=0):
 
 
 WGRAD_STORE, WGRAD_ACCUMULATE, WGRAD_STORE_NONEMPTY = 0, 1, 2
+WGRAD_MAX_GROUPS = 512  # groups per launch of the weight-gradient kernel (its work list lives in shared memory)
 
 
 def grouped_wgrad_reference(left, right, cu_seqlens, targets, flags):
@@ -199,6 +200,7 @@ def grouped_wgrad(left_t, right_t, cu_seqlens, out_ptrs, flags, *, status=None, 
     assert right_t.shape[1] == ld and left_t.dtype == torch.bfloat16 and right_t.dtype == torch.bfloat16
     assert left_t.is_contiguous() and right_t.is_contiguous()
     assert wgrad_kernel_supports(P, Q, ld, left_t.device), f"grouped_wgrad: P={P}, Q={Q}, ld={ld} do not fit the tiling"
+    assert G <= WGRAD_MAX_GROUPS, f"grouped_wgrad: at most {WGRAD_MAX_GROUPS} groups per launch"
     assert out_ptrs.dtype == torch.int64 and out_ptrs.numel() == G and out_ptrs.is_cuda and out_ptrs.is_contiguous()
     assert flags.dtype == torch.int32 and flags.numel() == G and flags.is_cuda and flags.is_contiguous()
     assert cu_seqlens.dtype == torch.int32 and cu_seqlens.is_contiguous() and cu_seqlens.is_cuda
@@ -222,6 +224,7 @@ def grouped_wgrad_rows(left, right, cu_seqlens, out_ptrs, flags, *, status=None,
     assert left.stride(1) == 1 and right.stride(1) == 1 and left.is_cuda
     ldl, ldr = int(left.stride(0)), int(right.stride(0))
     assert P % 128 == 0 and Q % 256 == 0 and ldl % 8 == 0 and ldr % 8 == 0, f"P={P}, Q={Q}, strides {ldl}, {ldr}"
+    assert G <= WGRAD_MAX_GROUPS, f"grouped_wgrad_rows: at most {WGRAD_MAX_GROUPS} groups per launch"
     assert left.data_ptr() % 16 == 0 and right.data_ptr() % 16 == 0
     assert out_ptrs.dtype == torch.int64 and out_ptrs.numel() == G and out_ptrs.is_cuda and out_ptrs.is_contiguous()
     assert flags.dtype == torch.int32 and flags.numel() == G and flags.is_cuda and flags.is_contiguous()
