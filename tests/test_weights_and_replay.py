@@ -37,25 +37,48 @@ TABLES = {
     "holes_and_duplicates": lambda R, B, E, epn: [[(-1 if b == 1 else ((r + 1) % R) * epn) for b in range(B)] for r in range(R)],
     "empty": lambda R, B, E, epn: [[-1] * B for _ in range(R)],
     "fan_in": lambda R, B, E, epn: [[(0 if r != 0 else epn) for _ in range(B)] for r in range(R)],
+    # one rank only sends (to the last rank's experts), the others only receive or idle
+    "send_only_rank0": lambda R, B, E, epn: [[(E - 1 - b % epn if r == 0 else -1) for b in range(B)] for r in range(R)],
+    # a rank's slot may hold one of its own experts, and the same expert twice
+    "self_send": lambda R, B, E, epn: [[r * epn + (b // 2) % epn for b in range(B)] for r in range(R)],
     "random": None,
+    "random_seed2": None,
+    "random_seed3": None,
 }
+_SEEDS = {"random": 17, "random_seed2": 202, "random_seed3": 3003}
 
 
 def _table(name, R, B, E, epn):
     if TABLES[name] is not None:
         return torch.tensor(TABLES[name](R, B, E, epn), dtype=torch.int32)
-    g = torch.Generator().manual_seed(17)
+    g = torch.Generator().manual_seed(_SEEDS[name])
     t = torch.randint(-1, E, (R, B), generator=g).to(torch.int32)
     return t
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize(
+    "Hw,Hp,epn,B,num_sms",
+    [(128, 128, 1, 1, 1), (256, 128, 2, 2, 7), (128, 384, 3, 4, 2), (384, 256, 2, 1, 64)],
+    ids=["one_tile_epn1_one_sm", "tall", "wide_more_slots", "more_sms_than_pieces"],
+)
+def test_prefetch_and_reduce_grad_shapes(device, Hw, Hp, epn, B, num_sms):
+    """Expert shapes, slot counts and SM budgets around the kernels' piece sizes (parity: reference
+    tests/test_prefetch.py:45-156 single tile / rectangular / more SMs than tiles, tests/test_grad_reduce.py epn=1)."""
+    _prefetch_and_reduce_grad(device, "random_seed2", 2, Hw=Hw, Hp=Hp, epn=epn, B=B, num_sms=num_sms)
 
 
 @pytest.mark.parametrize("device", DEVICES)
 @pytest.mark.parametrize("table", list(TABLES))
 @pytest.mark.parametrize("R", [2, 4])
 def test_prefetch_and_reduce_grad(device, table, R):
-    S, H, K, epn, B = 32, 64, 2, 4, 3
-    E, Hw, Hp = R * epn, 128, 256
-    lw, bufs = _world(R, device, S, H, K, epn, B)
+    _prefetch_and_reduce_grad(device, table, R)
+
+
+def _prefetch_and_reduce_grad(device, table, R, Hw=128, Hp=256, epn=4, B=3, num_sms=5):
+    S, H, K = 32, 64, 2
+    E = R * epn
+    lw, bufs = _world(R, device, S, H, K, epn, B, num_sms=num_sms)
     plans = _plans(lw, bufs, R, S, H, K, E, device)
     etc = _table(table, R, B, E, epn)
 
