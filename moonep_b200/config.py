@@ -9,6 +9,10 @@ MOONEP_LOCAL_SMS      CTAs of the kernels that only touch local memory (default:
                       the Buffer bounds the kernels that move data between ranks.
 MOONEP_NUM_SMS_DEDUP  number of SMs the dedup builder may use (validated, 1..SM count).
 MOONEP_DEBUG          ``1`` enables device-side index checks that record a status instead of faulting.
+MOONEP_NVTX           ``1`` wraps every native call in an NVTX range.
+MOONEP_GEMM_PAIR      ``1`` (default): grouped GEMMs on CTA pairs (tcgen05 cta_group::2); ``0``: one CTA per tile.
+MOONEP_WGRAD          ``kernel`` (default) or ``torch``: weight gradients of the MoE layer.
+MOONEP_WGRAD_LAYOUT   ``rows`` (default: activations as stored, MN-major tiles) or ``transposed``.
 
 Parity: reference ``moonep_td/_pipeline.py:1-14``, ``moonep_td/api.py:40-47``,
 ``moonep_td/_planning_gpu.py:14-16`` (``MOONEP_TD_PLANNING_TRITON`` is accepted as an alias).

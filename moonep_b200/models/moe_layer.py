@@ -19,9 +19,10 @@ prefetch slot ``b``.  On multi-GPU worlds ``[:E]`` is peer mapped (``create_full
 remote expert that did not get a prefetch slot is read in place over NVLink.
 
 Usage pattern of the reference's Buffer API: reference ``README.md:46-48`` and ``tests/test_e2e.py:201-431``.
-In the backward pass the activation gradients run on the same grouped GEMM (with per-call K-major copies of
-the local experts); the weight gradients run on its sibling kernel whose contraction is over the rows of a
-group (per-group matmuls where the shapes do not fit its tiling, and on CPU).
+Every GEMM of the layer is a tcgen05 kernel of this package: forward and activation gradients on CTA pairs
+(``grouped_gemm``, ``grouped_gemm_kn``), weight gradients on ``grouped_wgrad_rows``; the backward takes the weights
+and activations as they are stored (MN-major tiles), the forward keeps both SwiGLU pre-activations for it.
+Per-group torch matmuls remain for CPU tensors and for shapes outside the kernels' tiling.
 """
 
 from __future__ import annotations
@@ -150,46 +151,78 @@ class ExpertParallelMoE:
     def backward(self, saved, grad_out):
         """Returns ``(grad_x[S,H], grad_gates[S,K])`` and accumulates the weight gradients.
 
-        Activation gradients and the recomputed pre-activations run on the grouped GEMM (K-major copies of
-        the local experts are rebuilt per call because the weights change every step); the weight gradients,
-        whose contraction runs over the rows of a group, are written straight into the gradient of an owned
-        expert or into the reduce-buffer slot of a prefetched copy.
+        The plan is replayed to bring ``grad_out`` to the expert rows.  Activation gradients multiply by the
+        forward weights exactly as they are stored; weight gradients contract over the rows of a group and go
+        straight into the gradient of an owned expert or into the reduce-buffer slot of a prefetched copy.  The
+        pre-activations come from the forward pass.  On the kernel paths nothing synchronises with the host.
         """
-        buf, E, B, epn, I = self.buffer, self.E, self.B, self.epn, self.I
+        buf, I = self.buffer, self.I
         ctx = buf._require_ctx()
         plan, cu, x_nvs, w_nvs = saved["plan"], saved["cu"], saved["x_nvs"], saved["w_nvs"]
         dy_nvs, _, _, _ = buf.dispatch(grad_out.contiguous(), None, plan=plan, zero_copy=True)
-        gmap = self.group_map
-        rows = int(x_nvs.shape[0])
-        dev = x_nvs.device
-        a, u = saved["a"], saved["u"]
-        # activation gradients multiply by the forward weights as stored ([E+B, out, in] = [G, K, N] for this product):
-        # the CTA-pair kernel stages them as MN-major tiles; otherwise K-major copies of the local experts are made
-        direct = kn_kernel_supports(dy_nvs, [self.w_down]) and kn_kernel_supports(dy_nvs, [self.w_gate, self.w_up])
-        if direct:
-            g = grouped_gemm_kn(dy_nvs, [self.w_down], cu)  # dy @ W_down, unscaled
-        else:
-            g = grouped_gemm(dy_nvs, self._local_transposed([self.w_down], plan), cu, group_map=gmap)
+        rows, dev = int(x_nvs.shape[0]), x_nvs.device
+        g = self._times_weights(dy_nvs, [self.w_down], cu, plan)  # dL/dh before the gate weight: dy @ W_down
         dadu = torch.empty(rows, 2 * I, dtype=torch.bfloat16, device=dev)
         hsw = torch.empty(rows, I, dtype=torch.bfloat16, device=dev)
         dgate_nvs = ctx["weights_buf_local"].view(torch.float32)  # gate gradients ride the weights channel home
-        swiglu_bwd(a, u, g, w_nvs, cu[-1:], dadu, hsw, dgate_nvs)
-        del a, u, g
-        if self._weight_grads_on_kernel(x_nvs, dy_nvs, dadu, hsw, cu):
-            if direct:
-                grouped_gemm_kn(dadu, [self.w_gate, self.w_up], cu, out=dy_nvs)  # dx = da Wg + du Wu
-            else:
-                grouped_gemm(dadu, self._local_transposed([self.w_gate, self.w_up], plan), cu, group_map=gmap, out=dy_nvs)
-            dx, dgates, _ = buf.combine(plan, dy_nvs, dgate_nvs, zero_copy=True)
-            buf.reduce_grad(plan, False, self.g_gate, self.g_up, self.g_down, self.red[0], self.red[1], self.red[2],
-                            owner_local=True)  # fmt: skip
-            return dx, dgates
-        ends = cu.tolist()
+        swiglu_bwd(saved["a"], saved["u"], g, w_nvs, cu[-1:], dadu, hsw, dgate_nvs)
+        del g
+        if not self._weight_grads_on_kernel(x_nvs, dy_nvs, dadu, hsw, cu):
+            self._weight_grads_per_group(x_nvs, dy_nvs, dadu, hsw, cu)
+        self._times_weights(dadu, [self.w_gate, self.w_up], cu, plan, out=dy_nvs)  # dx rows = da Wg + du Wu
+        dx, dgates, _ = buf.combine(plan, dy_nvs, dgate_nvs, zero_copy=True)
+        buf.reduce_grad(plan, False, self.g_gate, self.g_up, self.g_down, self.red[0], self.red[1], self.red[2],
+                        owner_local=True)  # fmt: skip
+        return dx, dgates
+
+    def _times_weights(self, x, ws, cu, plan, out=None):
+        """``x[rows of g] @ cat(ws, dim=1)[g]`` per group: what an activation gradient needs from forward weights
+        stored ``[E+B, out, in]`` (which is ``[G, K, N]`` for this product).  The CTA-pair kernel stages them as
+        MN-major tiles; elsewhere K-major copies of the local experts feed the ordinary grouped GEMM."""
+        if kn_kernel_supports(x, ws):
+            return grouped_gemm_kn(x, ws, cu, out=out)
+        return grouped_gemm(x, self._local_transposed(ws, plan), cu, group_map=self.group_map, out=out)
+
+    def _weight_grads_on_kernel(self, x_nvs, dy_nvs, dadu, hsw, cu) -> bool:
+        """All weight gradients with three launches of the grouped tcgen05 kernel (no host synchronisation); every
+        group's result goes straight to the owner's gradient or to the reduce-buffer slot of a prefetched copy.
+        Returns False (nothing done) when the shapes do not fit the kernel."""
+        I, H = self.I, self.H
+        rows = int(x_nvs.shape[0]) // 64 * 64
+        dev = x_nvs.device
+        ok = (
+            config.wgrad_on_kernel() and x_nvs.is_cuda and rows >= 64 and self.E + self.B <= WGRAD_MAX_GROUPS
+            and self.buffer._require_ctx()["token_padding"] % 16 == 0
+            and wgrad_kernel_supports(I, H, rows, dev) and wgrad_kernel_supports(H, I, rows, dev)
+        )  # fmt: skip
+        if not ok:
+            return False
+        flags = self._wgrad_flags[bool(self._fresh)]
+        status = self.buffer._require_ctx()["_backend"].status
+        ptrs = self._wgrad_ptrs
+        if config.wgrad_layout() == "rows":  # the kernel stages MN-major tiles: the activations as they are
+            grouped_wgrad_rows(dadu[:, :I], x_nvs, cu, ptrs[0], flags, status=status)  # dW_gate = da^T x
+            grouped_wgrad_rows(dadu[:, I:], x_nvs, cu, ptrs[1], flags, status=status)  # dW_up   = du^T x
+            grouped_wgrad_rows(dy_nvs, hsw, cu, ptrs[2], flags, status=status)  # dW_down = dy^T (h * gate weight)
+        else:  # K-major tiles from transposed copies
+
+            def transposed(t):
+                out = torch.empty(1, int(t.shape[1]), rows, dtype=torch.bfloat16, device=dev)
+                return transpose_experts(t[:rows].unsqueeze(0), out)[0]
+
+            xt, dadut, dyt, hswt = transposed(x_nvs), transposed(dadu), transposed(dy_nvs), transposed(hsw)
+            grouped_wgrad(dadut[:I], xt, cu, ptrs[0], flags, status=status)
+            grouped_wgrad(dadut[I:], xt, cu, ptrs[1], flags, status=status)
+            grouped_wgrad(dyt, hswt, cu, ptrs[2], flags, status=status)
+        self._fresh = False
+        return True
+
+    def _weight_grads_per_group(self, x_nvs, dy_nvs, dadu, hsw, cu):
+        """Per-group matmuls (the CPU path, and shapes outside the kernel's tiling); reads ``cu`` on the host."""
+        E, B, epn, I, md = self.E, self.B, self.epn, self.I, self.matmul_dtype
         start = 0
-        md = self.matmul_dtype
         visited = set()
-        for grp in range(E + B):
-            end = int(ends[grp])
+        for grp, end in enumerate(int(v) for v in cu.tolist()):
             if end > start:
                 sl = slice(start, end)
                 xs, dys = x_nvs[sl].to(md), dy_nvs[sl].to(md)
@@ -203,55 +236,13 @@ class ExpertParallelMoE:
                 if grp < E:
                     visited.add(grp - self.rank * epn)
             start = max(start, end)
+        assert grp == E + B - 1
         if self._fresh:  # zero_grad() only set a flag: clear the owned experts that got no rows
             for le in range(epn):
                 if le not in visited:
                     for gt in (self.g_gate, self.g_up, self.g_down):
                         gt[le].zero_()
             self._fresh = False
-        if direct:
-            grouped_gemm_kn(dadu, [self.w_gate, self.w_up], cu, out=dy_nvs)
-        else:
-            grouped_gemm(dadu, self._local_transposed([self.w_gate, self.w_up], plan), cu, group_map=gmap, out=dy_nvs)
-        dx, dgates, _ = buf.combine(plan, dy_nvs, dgate_nvs, zero_copy=True)
-        buf.reduce_grad(plan, False, self.g_gate, self.g_up, self.g_down, self.red[0], self.red[1], self.red[2],
-                        owner_local=True)  # fmt: skip
-        return dx, dgates
-
-    def _weight_grads_on_kernel(self, x_nvs, dy_nvs, dadu, hsw, cu) -> bool:
-        """All weight gradients with three launches of the grouped tcgen05 kernel (no host synchronisation):
-        the operands are transposed once so that the contraction over a group's rows is K-major, and every
-        group's result goes straight to the owner's gradient or to the reduce-buffer slot of a prefetched copy.
-        Returns False (nothing done) when the shapes do not fit the kernel."""
-        I, H = self.I, self.H
-        rows = int(x_nvs.shape[0]) // 64 * 64
-        dev = x_nvs.device
-        ok = (
-            config.wgrad_on_kernel() and x_nvs.is_cuda and rows >= 64 and self.E + self.B <= WGRAD_MAX_GROUPS and self.buffer._require_ctx()["token_padding"] % 16 == 0
-            and wgrad_kernel_supports(I, H, rows, dev) and wgrad_kernel_supports(H, I, rows, dev)
-        )  # fmt: skip
-        if not ok:
-            return False
-
-        flags = self._wgrad_flags[bool(self._fresh)]
-        status = self.buffer._require_ctx()["_backend"].status
-        if config.wgrad_layout() == "rows":  # the kernel stages MN-major tiles: no transposed copies
-            grouped_wgrad_rows(dadu[:, :I], x_nvs, cu, self._wgrad_ptrs[0], flags, status=status)
-            grouped_wgrad_rows(dadu[:, I:], x_nvs, cu, self._wgrad_ptrs[1], flags, status=status)
-            grouped_wgrad_rows(dy_nvs, hsw, cu, self._wgrad_ptrs[2], flags, status=status)
-            self._fresh = False
-            return True
-
-        def transposed(t):
-            out = torch.empty(1, int(t.shape[1]), rows, dtype=torch.bfloat16, device=dev)
-            return transpose_experts(t[:rows].unsqueeze(0), out)[0]
-
-        xt, dadut, dyt, hswt = transposed(x_nvs), transposed(dadu), transposed(dy_nvs), transposed(hsw)
-        grouped_wgrad(dadut[:I], xt, cu, self._wgrad_ptrs[0], flags, status=status)  # dW_gate = da^T x
-        grouped_wgrad(dadut[I:], xt, cu, self._wgrad_ptrs[1], flags, status=status)  # dW_up   = du^T x
-        grouped_wgrad(dyt, hswt, cu, self._wgrad_ptrs[2], flags, status=status)  # dW_down = dy^T (h * gate weight)
-        self._fresh = False
-        return True
 
     def zero_grad(self):
         """Lazy: the next backward overwrites (instead of adding to) the gradients of the experts it visits
