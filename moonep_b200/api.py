@@ -200,7 +200,8 @@ class Buffer:
         runs the whole sequence with one launch.  Collective: every rank captures the same sequence and
         replays it the same number of times.  ``fn`` runs ``warmup`` times for real before the capture
         (lazy initialisation, allocator warm-up); its return value of the captured run is ``step.outputs``
-        (tensors that every replay overwrites).  Ordinary calls and replays can be mixed freely.
+        (tensors that every replay overwrites).  Ordinary calls and replays can be mixed, in stream order: wait for an
+        ``async_finish`` operation of this Buffer before replaying.
         No counterpart in the reference, whose barriers are host-driven."""
         ctx = self._require_ctx()
         assert ctx["world"].is_cuda, "graph capture needs the CUDA backend"
