@@ -53,19 +53,19 @@ struct PairSched {
   int nblk;          // its number of 128-row blocks
   long long tiles;   // its number of pair tiles
 
-  __device__ PairSched(const GemmArgs& args, const int* ends)
+  __host__ __device__ PairSched(const GemmArgs& args, const int* ends)
       : a(args), cu(ends), g(-1), t_base(0), blk0(0), nblk(0), tiles(0) {}
 
-  __device__ void load_group() {
-    const int start = g > 0 ? min(cu[g - 1], a.rows_cap) : 0;
-    const int end = min(cu[g], a.rows_cap);
+  __host__ __device__ void load_group() {
+    const int start = g > 0 ? (cu[g - 1] < a.rows_cap ? cu[g - 1] : a.rows_cap) : 0;
+    const int end = cu[g] < a.rows_cap ? cu[g] : a.rows_cap;
     blk0 = start / BM;
     nblk = end > start ? (end - start) / BM : 0;
     tiles = (long long)((nblk + 1) / 2) * a.n_tiles;
   }
 
   // tile t (t never decreases between calls) -> pair index inside the group and column tile; false past the end
-  __device__ bool locate(long long t, int& pair_in_group, int& nb) {
+  __host__ __device__ bool locate(long long t, int& pair_in_group, int& nb) {
     if (g < 0) {
       g = 0;
       load_group();
@@ -446,4 +446,27 @@ static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb0, const CUte
   if (num_sms > 0) pairs = imax(1, imin(pairs, num_sms / 2));
   grouped_gemm_pair_kernel<<<2 * pairs, kPairThreads, smem, (cudaStream_t)stream>>>(ta, tb0, tb1, a);
   return check_launch("grouped_gemm_pair_kernel");
+}
+
+// Host-side walk of the tile schedule of one CTA pair (for tests): writes, for every tile that pair `pair` of
+// `npairs` visits, {group, first row of the leader's block, first row of the peer's block or -1 when the group has no
+// such block, column tile} into out[4 * i]; returns the number of tiles (at most max_tiles are written).
+extern "C" int moonep_pair_schedule(const int* cu_seqlens, int G, int rows_cap, int n_tiles, int pair, int npairs,
+                                    int* out, int max_tiles) {
+  GemmArgs a = {};
+  a.G = G;
+  a.rows_cap = rows_cap;
+  a.n_tiles = n_tiles;
+  PairSched sched(a, cu_seqlens);
+  int n = 0, pig = 0, nb = 0;
+  for (long long t = pair; sched.locate(t, pig, nb); t += npairs) {
+    if (n < max_tiles) {
+      out[4 * n + 0] = sched.g;
+      out[4 * n + 1] = (sched.blk0 + 2 * pig) * BM;
+      out[4 * n + 2] = 2 * pig + 1 < sched.nblk ? (sched.blk0 + 2 * pig + 1) * BM : -1;
+      out[4 * n + 3] = nb;
+    }
+    ++n;
+  }
+  return n;
 }

@@ -187,6 +187,9 @@ int moonep_grouped_gemm_pair(const void* x, const void* w0, const void* w1, void
 int moonep_grouped_gemm_pair_kn(const void* x, const void* w0, int K0, const void* w1, int K1, void* out,
                                 const int* cu_seqlens, int G, int rows_cap, int N, int w_slots, int* status,
                                 long long timeout_ms, int num_sms, void* stream);
+// Host-side walk of the CTA-pair kernel's tile schedule, for tests (grouped_gemm_pair.cu).
+int moonep_pair_schedule(const int* cu_seqlens, int G, int rows_cap, int n_tiles, int pair, int npairs, int* out,
+                         int max_tiles);
 // Weight gradients of all groups: out_ptrs[g][P, Q] fp32 (=, +=) L_g^T R_g with the contraction over the rows of
 // group g.  lt = L^T [P, ld], rt = R^T [Q, ld] bf16 (ld a multiple of 8, >= rows_cap).  flags[g]: 0 store (zeros for
 // an empty group), 1 accumulate, 2 store and leave empty groups alone.  out_ptrs, flags: device arrays [G].

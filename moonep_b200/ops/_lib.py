@@ -117,6 +117,7 @@ _SIGNATURES = {
     "moonep_grouped_gemm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _ll, _i, _vp, _i, _vp, _vp, _vp]),
     "moonep_grouped_gemm_pair": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _ll, _i, _vp, _i, _vp, _vp, _vp]),
     "moonep_grouped_gemm_pair_kn": (_i, [_vp, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _ll, _i, _vp]),
+    "moonep_pair_schedule": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _i]),
     "moonep_grouped_wgrad": (_i, [_vp, _vp, _ll, _i, _i, _vp, _i, _vp, _vp, _i, _vp, _ll, _i, _vp]),
     "moonep_grouped_wgrad_rows": (_i, [_vp, _ll, _vp, _ll, _i, _i, _i, _vp, _i, _vp, _vp, _vp, _ll, _i, _vp]),
     "moonep_transpose_experts": (_i, [_vp, _vp, _i, _i, _i, _ll, _ll, _i, _vp, _vp]),

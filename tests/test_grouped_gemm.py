@@ -191,3 +191,45 @@ def test_grouped_gemm_kn_matches_fp32_reference(rows, Ks, N):
     want = grouped_gemm_kn_reference(x, ws, cu)[:total].float()
     err = (y[:total].float() - want).abs().max().item()
     assert err <= 2e-2 * max(1.0, want.abs().max().item()), f"max abs err {err}"
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_pair_tile_schedule_covers_every_block_once(seed):
+    """The CTA-pair kernel's tile walk (compiled host-side from the same code): over all pairs, every 128-row
+    block of every group appears exactly once per column tile, in its own group, and a pair never straddles groups."""
+    import ctypes
+
+    import numpy as np
+
+    from moonep_b200.ops import _lib
+
+    lib = _lib.load()
+    rng = np.random.default_rng(seed)
+    G = int(rng.integers(1, 40))
+    blocks = rng.integers(0, 6, size=G) * (rng.random(G) < 0.7)
+    ends = np.cumsum(blocks * 128).astype(np.int32)
+    rows_cap = int(ends[-1]) + 256 if seed % 2 else max(128, int(ends[-1]) - 128)  # also a capacity that cuts the tail
+    n_tiles, npairs = int(rng.integers(1, 5)), int(rng.integers(1, 9))
+    seen = {}
+    for pair in range(npairs):
+        out = np.zeros(4 * 4096, dtype=np.int32)
+        n = lib.moonep_pair_schedule(ends.ctypes.data_as(ctypes.c_void_p), G, rows_cap, n_tiles, pair, npairs,
+                                     out.ctypes.data_as(ctypes.c_void_p), 4096)  # fmt: skip
+        assert 0 <= n <= 4096
+        for g, r0, r1, nb in out[: 4 * n].reshape(n, 4):
+            start = min(int(ends[g - 1]), rows_cap) if g > 0 else 0
+            end = min(int(ends[g]), rows_cap)
+            for r in (r0, r1):
+                if r >= 0:
+                    assert start <= r and r + 128 <= end, f"block at row {r} is not inside group {g}"
+                    assert (int(r), int(nb)) not in seen, "a block was scheduled twice"
+                    seen[(int(r), int(nb))] = g
+            assert r0 >= 0 and (r1 == -1 or r1 == r0 + 128)
+    want = set()
+    for g in range(G):
+        start = min(int(ends[g - 1]), rows_cap) if g > 0 else 0
+        end = min(int(ends[g]), rows_cap)
+        for r in range(start, end - 127, 128):
+            for nb in range(n_tiles):
+                want.add((r, nb))
+    assert set(seen) == want
