@@ -193,7 +193,7 @@ __device__ __forceinline__ bool dst_in_range(const MoonepDevCtx& c, int dest, in
 
 __global__ void __launch_bounds__(kSendThreadsLdst) dispatch_send_ldst_kernel(const MoonepDevCtx c, const SendArgs a) {
   const bool ok = block_wait_flags(c, a.wait_family, a.wait_epoch, MOONEP_K_DISPATCH_SEND);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
   int* work = c.counters + MOONEP_NUM_KERNEL_IDS;  // token counter of this kernel
   if (ok) {
     if (a.build_dedup) build_dedup_rows(c, a, blockIdx.x * blockDim.x + threadIdx.x, gridDim.x * blockDim.x);

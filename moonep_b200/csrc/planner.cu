@@ -310,7 +310,7 @@ __global__ void __launch_bounds__(kTokensThreads)
   __shared__ short s_dest[MOONEP_PLAN_BLOCK];
   const bool live = !poisoned(c);
   const int R = c.R, E = c.E, K = c.K, NvS = c.NvS;
-  const int tid = threadIdx.x, lane = tid & 31;
+  const int tid = threadIdx.x;
   const int t0 = blockIdx.x * tokens_per_block;
   const int t1 = min(c.S, t0 + tokens_per_block);
   const int start = t0 * K;
