@@ -53,11 +53,19 @@ def parse_args():
     return p.parse_args()
 
 
+HOST_AFFINITY: dict = {}
+
+
 def init_dist(n):
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", str(rank)))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     torch.cuda.set_device(local)
+    # host threads and the pinned staging buffers of the end-to-end loop stay on the GPU's CPU socket
+    from moonep_b200.utils.affinity import bind_to_gpu_socket
+
+    global HOST_AFFINITY
+    HOST_AFFINITY = bind_to_gpu_socket(local)
     if n > 1:
         import torch.distributed as dist
 
@@ -267,6 +275,7 @@ def run_steps(args, BufferCls, rank, n, reference=False):
             "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
         },
         "gpu_launches": int(launches),
+        "host_cpu_affinity": HOST_AFFINITY,
     }  # fmt: skip
     if phases is not None:
         res["phases_us"] = phases
