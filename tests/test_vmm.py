@@ -61,16 +61,20 @@ def test_fd_exchange_over_unix_sockets_gloo(tmp_path):
         "fd = os.memfd_create(f'rank{r}')\n"
         "os.write(fd, f'hello from {r}'.encode())\n"
         "fds = exchange_fds(None, r, n, fd)\n"
-        "for p in range(n):\n"
-        "    os.lseek(fds[p], 0, 0)\n"
-        "    assert os.read(fds[p], 64) == f'hello from {p}'.encode(), (r, p)\n"
+        "for p in range(n):\n"  # pread: the received descriptors share one file offset with every other rank's copy
+        "    assert os.pread(fds[p], 64, 0) == f'hello from {p}'.encode(), (r, p)\n"
         "dist.barrier()\n"
         "print('ok', r)\n"
     )
+    import socket
+
+    with socket.socket() as sk:  # a fixed port can still be in TIME_WAIT from the previous run
+        sk.bind(("127.0.0.1", 0))
+        port = sk.getsockname()[1]
     env = dict(os.environ, MASTER_ADDR="127.0.0.1")
     out = subprocess.run(
         [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=3", "--master-addr", "127.0.0.1",
-         "--master-port", "29611", str(script)],
+         "--master-port", str(port), str(script)],
         capture_output=True, text=True, timeout=120, env=env,
     )  # fmt: skip
     assert out.returncode == 0, out.stdout + out.stderr
