@@ -204,7 +204,8 @@ class Buffer:
         ``async_finish`` operation of this Buffer before replaying.
         No counterpart in the reference, whose barriers are host-driven."""
         ctx = self._require_ctx()
-        assert ctx["world"].is_cuda, "graph capture needs the CUDA backend"
+        if not ctx["world"].is_cuda:
+            return _EagerStep(fn)  # host backend: same interface, every replay simply runs ``fn``
         return CapturedStep(self, fn, warmup)
 
     # -- stream helpers ------------------------------------------------------------
@@ -448,6 +449,20 @@ class CapturedStep:
         be.replay_prepare()
         self.graph.replay()
         be.replay_done(self._end)
+        self.replays += 1
+        return self.outputs
+
+
+class _EagerStep:
+    """``CapturedStep`` interface on the CPU backend, where there is nothing to capture."""
+
+    def __init__(self, fn):
+        self._fn = fn
+        self.outputs = None
+        self.replays = 0
+
+    def replay(self):
+        self.outputs = self._fn()
         self.replays += 1
         return self.outputs
 

@@ -60,3 +60,26 @@ def test_capture_abort_restores_the_state():
     assert be.epoch == [2] * NUM_FLAG_FAMILIES and be.bias == [0] * NUM_FLAG_FAMILIES and be._capture is None
     be.capture_begin()  # a new capture can start
     be.capture_abort()
+
+
+def test_capture_on_the_cpu_backend_runs_eagerly():
+    import torch
+
+    from moonep_b200 import Buffer
+    from moonep_b200.models.routing import make_routing
+
+    S, H, K, E = 16, 32, 2, 4
+    buf = Buffer(S, H, K, E, 1, token_padding=8)
+    topk, tpe, gates = make_routing("balanced", S, K, E, 1, 0)
+    x = torch.randn(S, H).to(torch.bfloat16)
+
+    def step():
+        xn, wn, _, plan = buf.dispatch(x, gates, topk, tpe)
+        return buf.combine(plan, xn, wn)[0]
+
+    st = buf.capture(step)
+    for _ in range(2):
+        x.copy_(torch.randn(S, H).to(torch.bfloat16))
+        assert torch.equal(st.replay(), (x.float() * K).to(torch.bfloat16))
+    assert st.replays == 2
+    buf.destroy()
