@@ -87,3 +87,20 @@ def test_hidden_only_dispatch_without_weights(device):
     check_dispatch_records(case, 2, recs)
     for r in range(2):
         assert recs[r]["weights_nvs"] is None and recs[r]["weights_back"] is None
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("paths", [{"MOONEP_SEND_PATH": "ldst", "MOONEP_PULL_PATH": "bulk"},
+                                   {"MOONEP_COPY_PATH": "bulk", "MOONEP_PULL_PATH": "bulk", "MOONEP_GRAD_PATH": "bulk"},
+                                   {"MOONEP_COPY_PATH": "ldst"}], ids=["send_ldst_pull_bulk", "all_bulk", "all_ldst"])  # fmt: skip
+@pytest.mark.parametrize("case", ROUNDTRIP_CASES[:3] + ROUNDTRIP_CASES[7:10], ids=lambda c: c.name)
+def test_round_trip_on_the_alternative_copy_paths(case, paths, monkeypatch):
+    """Every kernel keeps a bulk-copy (TMA) and a register implementation; the non-default ones stay correct."""
+    for k, v in paths.items():
+        monkeypatch.setenv(k, v)
+    R = 4 if case.supports(4) else 2
+    recs, tabs, dst_pos = _check(case, R, "cuda")
+    want = expected_combine(case, R, recs, dst_pos)
+    for r in range(R):
+        assert_within_ulp(recs[r]["out"], want[r], max_ulps=1, what=f"rank {r} combine")
+        assert torch.equal(recs[r]["weights_back"], recs[r]["w"]), f"rank {r}: weights did not round-trip"

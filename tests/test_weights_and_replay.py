@@ -75,6 +75,14 @@ def test_prefetch_and_reduce_grad(device, table, R):
     _prefetch_and_reduce_grad(device, table, R)
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("table", ["fan_in", "random"])
+def test_reduce_grad_on_the_bulk_copy_path(table, monkeypatch):
+    """The TMA-ring variant of the gradient accumulation (``MOONEP_GRAD_PATH=bulk``) keeps the bitwise order."""
+    monkeypatch.setenv("MOONEP_GRAD_PATH", "bulk")
+    _prefetch_and_reduce_grad("cuda", table, 4)
+
+
 def _prefetch_and_reduce_grad(device, table, R, Hw=128, Hp=256, epn=4, B=3, num_sms=5):
     S, H, K = 32, 64, 2
     E = R * epn
