@@ -105,3 +105,43 @@ def test_moe_helper_ops_match_torch(device):
     want = (wt.float() - 0.5 * gr).to(torch.bfloat16)
     sgd_update(wt, gr, 0.5)
     assert torch.allclose(wt.float().cpu(), want.float().cpu(), rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("device", ["cpu"])
+def test_moe_block_autograd_matches_dense_reference(device):
+    """Router + experts through autograd on one rank: output, input gradient and router gradient against a dense
+    fp32 model with the same weights (emulated multi-rank worlds use the layer's explicit backward, see moe_block.py)."""
+    from moonep_b200.models.moe_block import MoEBlock
+
+    S, H, I, K, E = 96, 256, 256, 2, 4
+    buf = Buffer(S, H, K, E, 1, num_sms=8, token_padding=128, B=1)
+    block = MoEBlock(buf, I, init_std=0.05, seed=5)
+    g = torch.Generator().manual_seed(9)
+    x = (torch.randn(S, H, generator=g) * 0.5).to(torch.bfloat16).to(device).requires_grad_(True)
+    go = (torch.randn(S, H, generator=g) * 0.5).to(torch.bfloat16).to(device)
+    out = block(x)
+    out.backward(go)
+    if device == "cuda":
+        torch.cuda.synchronize()
+        buf.check_status()
+    # dense reference with the same router and expert weights
+    wr = block.router.weight.detach().float().cpu().requires_grad_(True)
+    ex = block.experts
+    wg, wu, wd = (w[:E].float().cpu() for w in (ex.w_gate, ex.w_up, ex.w_down))
+    xr = x.detach().float().cpu().requires_grad_(True)
+    probs = torch.softmax(xr @ wr.t(), dim=-1)
+    top_p, top_i = torch.topk(probs, K, dim=-1)
+    gates = top_p / top_p.sum(dim=-1, keepdim=True)
+    ref = dense_reference(xr, gates, top_i, wg, wu, wd)
+    ref.backward(go.float().cpu())
+
+    def close(a, b, what, tol=4e-2):
+        err = (a.float().cpu() - b.float()).abs().max().item()
+        scale = max(1e-3, b.float().abs().max().item())
+        assert err <= tol * scale, f"{what}: max abs err {err} vs scale {scale}"
+
+    close(out.detach(), ref.detach(), "output")
+    close(block.router.weight.grad, wr.grad, "router gradient", tol=6e-2)
+    # the input gradient has two parts: through the experts (from the layer) and through the router (from autograd)
+    close(x.grad, xr.grad, "input gradient", tol=6e-2)
+    buf.destroy()
