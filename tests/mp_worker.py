@@ -299,10 +299,46 @@ def scenario_graph(rank, R, dev):
         print("  graph capture ok", flush=True)
 
 
+def scenario_moe_block(rank, R, dev):
+    """Router + experts with autograd, one process per rank (host backend): output and router gradient against a
+    dense model that holds all experts."""
+    if dev.type != "cpu":
+        return
+    from moonep_b200.models.moe_block import MoEBlock
+    from moonep_b200.models.moe_layer import dense_reference
+
+    S, H, I, K, epn = 64, 128, 128, 2, 2
+    E = R * epn
+    buf = Buffer(S, H, K, E, R, token_padding=16, B=2)
+    block = MoEBlock(buf, I, init_std=0.05, seed=21)
+    g = torch.Generator().manual_seed(300 + rank)
+    x = (torch.randn(S, H, generator=g) * 0.5).to(torch.bfloat16).requires_grad_(True)
+    go = (torch.randn(S, H, generator=g) * 0.5).to(torch.bfloat16)
+    out = block(x)
+    out.backward(go)
+    barrier(dev)
+    ex = block.experts
+    wr = block.router.weight.detach().float().clone().requires_grad_(True)
+    xr = x.detach().float().requires_grad_(True)
+    probs = torch.softmax(xr @ wr.t(), dim=-1)
+    top_p, top_i = torch.topk(probs, K, dim=-1)
+    ref = dense_reference(xr, top_p / top_p.sum(dim=-1, keepdim=True), top_i, ex.w_gate[:E].float(), ex.w_up[:E].float(),
+                          ex.w_down[:E].float())  # fmt: skip
+    ref.backward(go.float())
+    for got, want, what in ((out.detach(), ref.detach(), "output"), (x.grad, xr.grad, "input gradient"),
+                            (block.router.weight.grad, wr.grad, "router gradient")):  # fmt: skip
+        err = (got.float() - want.float()).abs().max().item()
+        assert err <= 6e-2 * max(1e-3, want.abs().max().item()), f"moe block rank {rank}: {what} err {err}"
+    barrier(dev)
+    buf.destroy()
+    if rank == 0:
+        print("  moe block ok", flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--backend", default="gloo", choices=["gloo", "nccl"])
-    ap.add_argument("--scenarios", default="round_trips,plan_reuse,weights,moe_layer,graph")
+    ap.add_argument("--scenarios", default="round_trips,plan_reuse,weights,moe_layer,graph,moe_block")
     args = ap.parse_args()
     rank = int(os.environ["RANK"])
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -326,6 +362,8 @@ def main():
         scenario_moe_layer(rank, R, dev)
     if "graph" in todo:
         scenario_graph(rank, R, dev)
+    if "moe_block" in todo:
+        scenario_moe_block(rank, R, dev)
     barrier(dev)
     print(f"WORKER OK rank {rank}", flush=True)
     dist.destroy_process_group()
