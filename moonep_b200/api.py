@@ -128,7 +128,7 @@ class Buffer:
         assert not self._destroyed, "Buffer has been destroyed"
         return self._ctx
 
-    def destroy(self) -> None:
+    def destroy(self, _collective: bool = True) -> None:
         """Collective: wait for outstanding work on every rank, then free the symmetric memory."""
         if self._destroyed:
             return
@@ -141,7 +141,8 @@ class Buffer:
             if self._comm_stream is not None:
                 self._comm_stream.synchronize()
             torch.cuda.synchronize(w.device)
-        w.host_barrier()
+        if _collective:
+            w.host_barrier()
         ctx["_backend"].destroy()
         for key in ("hidden_buf", "meta_buf", "hidden_buf_local", "weights_buf_local"):
             ctx.pop(key, None)
@@ -158,7 +159,10 @@ class Buffer:
             warnings.warn("Buffer was not destroyed explicitly.", ResourceWarning)
             return
         try:
-            self.destroy()
+            # emulated ranks are threads of this process: the garbage collector runs on one of them and a thread
+            # barrier would wait for the others forever (e.g. after a failed test), so only local cleanup here
+            w = (self._ctx or {}).get("world")
+            self.destroy(_collective=not getattr(w, "emulated", False))
         except Exception as exc:  # noqa: BLE001 - never raise from a destructor
             warnings.warn(f"Buffer destructor failed: {exc!r}", ResourceWarning)
 

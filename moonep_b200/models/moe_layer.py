@@ -82,6 +82,13 @@ class ExpertParallelMoE:
         self._red_full = [create_nvl_dist_tensor([B, d0, d1], torch.float32, w, pad_dim0=False)
                           for d0, d1 in ((I, H), (I, H), (H, I))]  # fmt: skip
         self.red = [view_nvl_dist_rows(t, self.R, B) for t in self._red_full]
+        # Worlds without peer mapping (host backend, emulated ranks) keep a private copy of every expert per rank.
+        # Changes of the owned experts (optimizer step, checkpoint load) are published to the other ranks' copies
+        # through a symmetric staging tensor, which plays the part the peer mapping plays on real GPUs.
+        self._pub = None
+        if not self.mapped and self.R > 1:
+            self._pub = [w.alloc_symmetric(self.epn * d0 * d1, torch.bfloat16, w.granularity())
+                         for d0, d1 in ((I, H), (I, H), (H, I))]  # fmt: skip
         # per group: where its weight gradient goes (0 = nowhere: a remote expert without a prefetch slot) and how
         own0 = self.rank * self.epn
         self._wgrad_ptrs, fresh, later = [], [], []
@@ -258,6 +265,52 @@ class ExpertParallelMoE:
         s = slice(self.rank * self.epn, (self.rank + 1) * self.epn)
         for w, g in ((self.w_gate, self.g_gate), (self.w_up, self.g_up), (self.w_down, self.g_down)):
             sgd_update(w[s], g, lr)
+        self.publish_owned()
+
+    def publish_owned(self):
+        """Collective on worlds without peer mapping: make every rank's copy of ``w[:E]`` current after the owned
+        experts changed.  On peer-mapped worlds (real GPUs) and single-rank worlds there is nothing to do."""
+        if self._pub is None:
+            return
+        E, epn = self.E, self.epn
+        own = slice(self.rank * epn, (self.rank + 1) * epn)
+        weights = (self.w_gate, self.w_up, self.w_down)
+        for wt, st in zip(weights, self._pub):
+            st.full.view(self.R, epn, *wt.shape[1:])[self.rank].copy_(wt[own])
+        self.world.host_barrier()
+        for wt, st in zip(weights, self._pub):
+            wt[:E].copy_(st.full.view(E, *wt.shape[1:]))
+        self.world.host_barrier()
+
+
+    # -- owned experts: views, checkpoints --------------------------------------------------------
+    def owner_weights(self):
+        """bf16 views of the experts this rank owns: three tensors ``[E/R, ...]`` inside the symmetric weights."""
+        s = slice(self.rank * self.epn, (self.rank + 1) * self.epn)
+        return self.w_gate[s], self.w_up[s], self.w_down[s]
+
+    def state_dict(self) -> dict:
+        """This rank's shard of the layer: the experts it owns (host copies), keyed so that a checkpoint written by
+        one expert-parallel layout can be checked against another.  Every rank saves its own shard."""
+        g, u, d = (t.detach().to("cpu", copy=True) for t in self.owner_weights())
+        return {"format": "moonep_b200.expert_shard.v1", "rank": self.rank, "ranks": self.R, "experts": self.E,
+                "first_expert": self.rank * self.epn, "hidden": self.H, "inter": self.I,
+                "w_gate": g, "w_up": u, "w_down": d}  # fmt: skip
+
+    def load_state_dict(self, state: dict) -> None:
+        """Collective: every rank loads the shard it owns; peers see the new weights after the closing barrier
+        (their prefetch slots are refilled by the next ``prefetch_weight``)."""
+        assert state.get("format") == "moonep_b200.expert_shard.v1", "not an expert shard of this package"
+        for key, mine in (("first_expert", self.rank * self.epn), ("experts", self.E), ("hidden", self.H), ("inter", self.I)):
+            assert int(state[key]) == int(mine), f"checkpoint {key}={state[key]} does not match this layer ({mine})"
+        for dst, key in zip(self.owner_weights(), ("w_gate", "w_up", "w_down")):
+            src = state[key]
+            assert tuple(src.shape) == tuple(dst.shape) and src.dtype == dst.dtype, f"{key}: shape or dtype mismatch"
+            dst.copy_(src.to(dst.device))
+        if self.w_gate.is_cuda:
+            torch.cuda.synchronize(self.w_gate.device)
+        self.world.host_barrier()
+        self.publish_owned()
 
 
 def dense_reference(x, gates, topk, w_gate, w_up, w_down):

@@ -145,3 +145,58 @@ def test_moe_block_autograd_matches_dense_reference(device):
     # the input gradient has two parts: through the experts (from the layer) and through the router (from autograd)
     close(x.grad, xr.grad, "input gradient", tol=6e-2)
     buf.destroy()
+
+
+@pytest.mark.parametrize("device", ["cpu"])
+def test_expert_shards_save_and_load(device, tmp_path):
+    """Every rank checkpoints the experts it owns; a fresh layer that loads the shards computes the same output."""
+    R, S, H, I, K, epn = 2, 32, 128, 128, 2, 2
+    E = R * epn
+    lw = LocalWorld(R, device)
+    bufs = lw.run(lambda r: Buffer(S, H, K, E, R, token_padding=16, B=1, world=lw.view(r)))
+    layers = lw.run(lambda r: ExpertParallelMoE(bufs[r], I, init_std=0.05, seed=3))
+    others = lw.run(lambda r: ExpertParallelMoE(bufs[r], I, init_std=0.05, seed=99))  # different weights
+
+    def body(r):
+        path = tmp_path / f"shard{r}.pt"
+        torch.save(layers[r].state_dict(), path)
+        others[r].load_state_dict(torch.load(path))
+        topk, tpe, gates = make_routing("biased", S, K, E, R, r, bias=1.0, seed=4)
+        x = (torch.randn(S, H, generator=torch.Generator().manual_seed(r)) * 0.5).to(torch.bfloat16)
+        a, _ = layers[r].forward(x, gates, topk, tpe)
+        b, _ = others[r].forward(x, gates, topk, tpe)
+        return torch.equal(a, b)
+
+    assert all(lw.run(body))
+    with pytest.raises(AssertionError):
+        bad = layers[0].state_dict()
+        bad["first_expert"] = 1
+        layers[0].load_state_dict(bad)
+    lw.run(lambda r: bufs[r].destroy())
+
+
+@pytest.mark.parametrize("device", ["cpu"])
+def test_owned_expert_updates_reach_the_other_ranks_copies(device):
+    """Without peer mapping every rank keeps a copy of all experts: an optimizer step on the owners must show up in
+    every copy (what the peer mapping gives for free on real GPUs), so that later prefetches read current weights."""
+    R, S, H, I, K, epn = 2, 32, 128, 128, 2, 2
+    E = R * epn
+    lw = LocalWorld(R, device)
+    bufs = lw.run(lambda r: Buffer(S, H, K, E, R, token_padding=16, B=1, world=lw.view(r)))
+    layers = lw.run(lambda r: ExpertParallelMoE(bufs[r], I, init_std=0.05, seed=3))
+
+    def body(r):
+        topk, tpe, gates = make_routing("biased", S, K, E, R, r, bias=1.0, seed=4)
+        g = torch.Generator().manual_seed(r)
+        x = (torch.randn(S, H, generator=g) * 0.5).to(torch.bfloat16)
+        go = (torch.randn(S, H, generator=g) * 0.5).to(torch.bfloat16)
+        before = layers[r].w_gate[:E].clone()
+        out, saved = layers[r].forward(x, gates, topk, tpe)
+        layers[r].backward(saved, go)
+        layers[r].sgd_step(0.5)
+        return before, layers[r].w_gate[:E].clone(), layers[r].w_down[:E].clone()
+
+    res = lw.run(body)
+    assert torch.equal(res[0][1], res[1][1]) and torch.equal(res[0][2], res[1][2]), "the ranks' copies diverged"
+    assert not torch.equal(res[0][0], res[0][1]), "the step changed nothing"
+    lw.run(lambda r: bufs[r].destroy())
