@@ -200,3 +200,30 @@ def test_owned_expert_updates_reach_the_other_ranks_copies(device):
     assert torch.equal(res[0][1], res[1][1]) and torch.equal(res[0][2], res[1][2]), "the ranks' copies diverged"
     assert not torch.equal(res[0][0], res[0][1]), "the step changed nothing"
     lw.run(lambda r: bufs[r].destroy())
+
+
+def test_expert_adamw_matches_torch_adamw():
+    """fp32 master weights and moments for the owned experts; the same numbers as torch.optim.AdamW on fp32 copies."""
+    from moonep_b200.models.optim import ExpertAdamW
+
+    S, H, I, K, E = 32, 128, 128, 2, 2
+    buf = Buffer(S, H, K, E, 1, token_padding=16, B=1)
+    layer = ExpertParallelMoE(buf, I, init_std=0.05, seed=3)
+    opt = ExpertAdamW(layer, lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    ref_params = [torch.nn.Parameter(w.float().clone()) for w in layer.owner_weights()]
+    ref = torch.optim.AdamW(ref_params, lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    g = torch.Generator().manual_seed(0)
+    for _ in range(3):
+        for p, gr in zip(ref_params, layer.owner_grads()):
+            gr.copy_(torch.randn(gr.shape, generator=g) * 0.1)
+            p.grad = gr.clone()
+        opt.step()
+        ref.step()
+    for p, m, w in zip(ref_params, opt.master, layer.owner_weights()):
+        assert torch.allclose(m, p.detach(), rtol=1e-5, atol=1e-6)
+        assert torch.equal(w, m.to(torch.bfloat16)), "the symmetric bf16 weights are the rounded master weights"
+    state = opt.state_dict()
+    opt2 = ExpertAdamW(layer)
+    opt2.load_state_dict(state)
+    assert opt2.steps == 3 and torch.equal(opt2.exp_avg[0], opt.exp_avg[0])
+    buf.destroy()
