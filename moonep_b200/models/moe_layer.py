@@ -107,15 +107,22 @@ class ExpertParallelMoE:
         w.host_barrier()
 
     # -- forward -------------------------------------------------------------------------------
-    def forward(self, x, gates, topk, tokens_per_expert):
+    def forward(self, x, gates, topk, tokens_per_expert, save_for_backward: bool = True):
+        """Returns ``(out[S, H], saved)``.  ``save_for_backward=False`` (inference): nothing is kept, the expert
+        GEMMs read the dispatched rows in place, ``saved`` is None."""
         buf = self.buffer
         x_nvs, w_nvs, cu, plan = buf.dispatch(x, gates, topk, tokens_per_expert, zero_copy=True)
         # the weight copies run on the communication stream while this stream saves the dispatched rows
         fetched = buf.prefetch_weight(plan, async_finish=True, full_gate_weight=self.w_gate,
                                       full_up_weight=self.w_up, full_down_weight=self.w_down)  # fmt: skip
-        x_saved = x_nvs.clone()  # the shard is reused for the expert output
+        x_saved = x_nvs.clone() if save_for_backward else x_nvs  # training: the shard is reused for the expert output
         if hasattr(fetched, "wait") and x_nvs.is_cuda:
             torch.cuda.current_stream().wait_event(fetched)
+        if not save_for_backward:
+            h = grouped_gemm(x_nvs, self.w_gate, cu, w_up=self.w_up, mode="swiglu")
+            grouped_gemm(h, self.w_down, cu, row_scale=w_nvs, mode="scale", out=x_nvs)
+            out, _, _ = buf.combine(plan, x_nvs, None, zero_copy=True)
+            return out, None
         # the pre-activations are kept for the backward pass (two bf16 [NvS, I] tensors instead of two more GEMMs)
         a = torch.empty(x_saved.shape[0], self.I, dtype=torch.bfloat16, device=x_saved.device)
         u = torch.empty_like(a)

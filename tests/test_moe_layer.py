@@ -227,3 +227,24 @@ def test_expert_adamw_matches_torch_adamw():
     opt2.load_state_dict(state)
     assert opt2.steps == 3 and torch.equal(opt2.exp_avg[0], opt.exp_avg[0])
     buf.destroy()
+
+
+@pytest.mark.parametrize("device", ["cpu"])
+@pytest.mark.parametrize("R", [1, 2])
+def test_inference_forward_equals_training_forward(device, R):
+    """``save_for_backward=False`` keeps nothing and reads the dispatched rows in place; same output."""
+    S, H, I, K, epn = 48, 128, 128, 2, 2
+    E = R * epn
+    lw = LocalWorld(R, device)
+    bufs = lw.run(lambda r: Buffer(S, H, K, E, R, token_padding=16, B=1, world=lw.view(r)))
+    layers = lw.run(lambda r: ExpertParallelMoE(bufs[r], I, init_std=0.05, seed=3))
+
+    def body(r):
+        topk, tpe, gates = make_routing("biased", S, K, E, R, r, bias=1.5, seed=4, device=device)
+        x = (torch.randn(S, H, generator=torch.Generator().manual_seed(r)) * 0.5).to(torch.bfloat16).to(device)
+        a, saved = layers[r].forward(x, gates, topk, tpe)
+        b, none = layers[r].forward(x, gates, topk, tpe, save_for_backward=False)
+        return saved is not None and none is None and torch.equal(a, b)
+
+    assert all(lw.run(body))
+    lw.run(lambda r: bufs[r].destroy())
