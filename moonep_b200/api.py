@@ -173,7 +173,8 @@ class Buffer:
     def stats(self, plan: MoonEPCommPlan | None = None) -> dict:
         """Runtime figures.  With ``plan``: rows this rank sends (primary entries), how many of them leave
         the rank, duplicate entries saved by per-rank dedup, rows and duplicate groups received, remote experts
-        hosted here and ranks copying this rank's experts (``remote_stats``).  Reads the plan (synchronises).
+        hosted here and ranks copying this rank's experts (``remote_stats``), and the load balance of the most recent
+        fresh dispatch (rows per rank, max/mean with and without the planner's re-homing).  Reads the plan (synchronises).
         Always: the backend's counters (flag epochs, status block, per-call device times when profiling)."""
         ctx = self._require_ctx()
         out = dict(ctx["_backend"].stats())
@@ -195,6 +196,19 @@ class Buffer:
                 "ranks_copying_my_experts": int(rs[1]),
                 "bytes_sent_remote": int((primary & (dest != ctx["rank"])).sum()) * ctx["H"] * 2,
             })  # fmt: skip
+            # load balance of the most recent fresh dispatch, from the planner's global allocation table
+            R, E, epn = ctx["R"], ctx["E"], ctx["epn"]
+            alloc = ctx["_backend"].global_alloc()  # [R, E]: rows of expert e placed on rank d
+            per_rank = alloc.sum(dim=1)
+            per_home = alloc.sum(dim=0).view(R, epn).sum(dim=1)  # rows each rank would get without re-homing
+            if int(per_rank.sum()) > 0:
+                mean = float(per_rank.sum()) / R
+                out.update({
+                    "rows_per_rank": per_rank.tolist(),
+                    "imbalance": float(per_rank.max()) / mean,
+                    "imbalance_without_balancing": float(per_home.max()) / mean,
+                    "rows_rehomed": int((per_home - per_rank).clamp(min=0).sum()),
+                })  # fmt: skip
         return out
 
     # -- CUDA graphs ---------------------------------------------------------------

@@ -77,6 +77,11 @@ class CpuBackend:
     def stats(self) -> dict:
         return {"backend": "cpu"}
 
+    def global_alloc(self) -> torch.Tensor:
+        """``[R, E]`` int64 on the host: rows of expert e the last planning placed on rank d."""
+        c = self.ctx
+        return c["alloc"].cpu().to(torch.int64).view(c["R"], c["E"])
+
     # -- planning ------------------------------------------------------------
     def plan_publish(self, tokens_per_expert: torch.Tensor, topk_flat=None):
         c = self.ctx

@@ -88,7 +88,8 @@ class CudaBackend:
         tokens_per_block = max(1, PLAN_BLOCK // K)
         self.block_hist = i32(-(-S // tokens_per_block) * E)
         sm_count = torch.cuda.get_device_properties(dev).multi_processor_count
-        c["alloc"] = self.tables[2 * E : 2 * E + R * E]  # planner's alloc[d*E+e]
+        # the planner's alloc[d*E+e]; only current when its tables did not fit shared memory (use global_alloc())
+        c["alloc"] = self.tables[2 * E : 2 * E + R * E]
 
         hid_base = c["hidden_buf"].data_ptr()
         meta_base = c["meta_buf"].data_ptr()
@@ -146,6 +147,15 @@ class CudaBackend:
         if self._profile:
             out["phase_times_us"] = self.phase_times()
         return out
+
+    def global_alloc(self) -> torch.Tensor:
+        """``[R, E]`` int64 on the host: rows of expert e the last planning placed on rank d.  Derived from the
+        planner's inclusive prefix over destination ranks, the form it keeps in global memory (synchronises)."""
+        c = self.ctx
+        cum = self.alloc_cum.cpu().to(torch.int64).view(c["E"], c["R"])
+        alloc = cum.clone()
+        alloc[:, 1:] -= cum[:, :-1]
+        return alloc.t().contiguous()
 
     def reset_wait_stats(self):
         self.stats_buf.zero_()

@@ -301,4 +301,8 @@ def test_stats_report_rows_and_dedup(device):
         assert st[r]["entries"] == S * K and st[r]["rows_sent"] + st[r]["entries_deduplicated"] == S * K
         assert st[r]["rows_sent_remote"] <= st[r]["rows_sent"] and st[r]["bytes_sent_remote"] == st[r]["rows_sent_remote"] * H * 2
     assert sum(s["entries_deduplicated"] for s in st) == sum(s["dup_rows_received"] for s in st)
+    # load balance: all ranks see the same global table; no rank gets more than S*K rows; re-homing never hurts
+    assert st[0]["rows_per_rank"] == st[1]["rows_per_rank"] and sum(st[0]["rows_per_rank"]) == R * S * K
+    assert max(st[0]["rows_per_rank"]) <= S * K
+    assert 1.0 <= st[0]["imbalance"] <= st[0]["imbalance_without_balancing"] + 1e-9
     lw.run(lambda r: bufs[r].destroy())
