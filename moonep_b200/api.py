@@ -55,20 +55,26 @@ def _create_context(S, H, K, E, num_ep_ranks, num_sms=None, token_padding=128, B
     ctx["hidden_buf_local"] = hidden_buf[rank * nvsp : rank * nvsp + ctx["NvS"]]
     ctx["weights_buf_local"] = meta_buf[rank * ms + ctx["WEIGHTS_OFF"] : rank * ms + ctx["WEIGHTS_OFF"] + ctx["NvS"]]
 
-    def i32(n, zero=False):
-        return (torch.zeros if zero else torch.empty)(max(int(n), 1), dtype=torch.int32, device=dev)
+    # planner result kept for Buffer.stats: rows of expert e placed on rank d (the CUDA backend keeps its own tables)
+    ctx["alloc"] = torch.empty(max(E * R, 1), dtype=torch.int32, device=dev)
 
-    N = ctx["N"]
-    ctx["alloc"] = i32(E * R)
-    ctx["group_tokens"] = i32(R)
-    ctx["z"] = i32(R * R)
-    ctx["local_hist"] = i32(E * ctx["num_vblocks"])
-    ctx["grid_sync_bar"] = i32(1, zero=True)
-    ctx["primary_packed"] = i32(R * S)
-    ctx["kmask"] = i32(R * S)
-    ctx["kidx_to_loff"] = i32(R * S * K)
-    ctx["builder_bar"] = i32(1, zero=True)
-    del N
+    ctx["stage_buf"] = None
+    if w.is_cuda and config.combine_mode() == "push" and R > 1:
+        # Staging memory of the push combine: per token up to min(K, R) rows (one per destination rank), their arrival
+        # flags and the K gate weights on their way home.
+        from .ops import _lib
+
+        import ctypes
+
+        fo, wo = ctypes.c_longlong(0), ctypes.c_longlong(0)
+        nbytes = int(_lib.load().moonep_stage_layout(S, K, H, ctx["Kp"], ctypes.byref(fo), ctypes.byref(wo)))
+        gran = ctx["gran_bytes"]
+        nbytes = (nbytes + gran - 1) // gran * gran
+        stage = w.alloc_symmetric(nbytes, torch.uint8, gran)
+        ctx["_symm"].append(stage)
+        stage.full[rank * nbytes : (rank + 1) * nbytes].zero_()
+        ctx["stage_buf"] = stage.full
+        ctx["stage_chunk_bytes"], ctx["stage_flag_off"], ctx["stage_w_off"] = nbytes, int(fo.value), int(wo.value)
 
     if w.is_cuda:
         from .ops.cuda_backend import CudaBackend
@@ -115,7 +121,8 @@ class Buffer:
         w = self._ctx["world"]
         if w.is_cuda:
             max_sms = torch.cuda.get_device_properties(w.device).multi_processor_count
-            self._ctx["num_sms_dedup"] = config.num_sms_dedup(max_sms)
+            self._ctx["num_sms_dedup"] = config.num_sms_dedup(max_sms)  # CTAs of the destination-side dedup/expand role
+            self._ctx["_backend"].n_expand = self._ctx["num_sms_dedup"] if config.num_sms_dedup_is_set() else 0
             assert 1 <= self._ctx["num_sms"] <= max_sms, f"num_sms must be in [1, {max_sms}]"
         self._comm_stream = w.comm_stream(comm_stream_priority)
 
@@ -144,7 +151,7 @@ class Buffer:
         if _collective:
             w.host_barrier()
         ctx["_backend"].destroy()
-        for key in ("hidden_buf", "meta_buf", "hidden_buf_local", "weights_buf_local"):
+        for key in ("hidden_buf", "meta_buf", "hidden_buf_local", "weights_buf_local", "stage_buf"):
             ctx.pop(key, None)
         for st in ctx.pop("_symm", []):
             w.free_symmetric(st)
@@ -245,6 +252,11 @@ class Buffer:
     def _run_dispatch(self, ctx, hidden_sh, route_weights_sk, planning_args, plan, hidden_nvsh, route_weights_nvs,
                       *, inter_rank_sync, zero_copy):  # fmt: skip
         be = ctx["_backend"]
+        if hasattr(be, "dispatch_all"):  # CUDA: fused launches (one role per phase for emulated ranks)
+            be.dispatch_all(hidden_sh, route_weights_sk, plan, planning_args, inter_rank_sync)
+            if not zero_copy:
+                be.copy_out(hidden_nvsh, route_weights_nvs)
+            return
         wait = None
         if planning_args is not None:
             topk_flat, tpe, cu_seqlens = planning_args
@@ -345,6 +357,9 @@ class Buffer:
     def _run_combine(self, ctx, hidden_sh, plan, hidden_nvsh, route_weights_nvs, route_weights_sk,
                      *, inter_rank_sync, zero_copy):  # fmt: skip
         be = ctx["_backend"]
+        if hasattr(be, "combine_all"):
+            be.combine_all(plan, hidden_nvsh, route_weights_nvs, hidden_sh, route_weights_sk, inter_rank_sync, zero_copy)
+            return
         wait = None
         # The barrier protects the shard from being rewritten while a peer still pulls from it.  A
         # dispatch that waited for all peers since the last pull already gives that guarantee.

@@ -5,10 +5,12 @@ MOONEP_TIMEOUT_MS     budget of every device-side wait (default 10000).
 MOONEP_COPY_PATH      ``bulk`` (default: TMA bulk copies through shared memory) or ``ldst``
                       (plain 16-byte loads/stores) for dispatch/combine/prefetch;
                       ``MOONEP_SEND_PATH`` / ``MOONEP_PULL_PATH`` / ``MOONEP_GRAD_PATH`` set one kernel only.
+MOONEP_COMBINE        ``push`` (default: the expert side folds duplicates and pushes rows to the tokens' home ranks,
+                      which sum them as they arrive) or ``pull`` (fold pass, then the home ranks pull).
 MOONEP_LOCAL_SMS      CTAs of the kernels that only touch local memory (default: all SMs); ``num_sms`` of
                       the Buffer bounds the kernels that move data between ranks.
-MOONEP_NUM_SMS_DEDUP  number of SMs the dedup builder may use (validated, 1..SM count).
-MOONEP_DEBUG          ``1`` enables device-side index checks that record a status instead of faulting.
+MOONEP_NUM_SMS_DEDUP  CTAs of the dispatch kernel's destination-side role (zero fill, dedup builder, duplicate
+                      expansion); validated, 1..SM count; default: every SM the senders leave free.
 MOONEP_NVTX           ``1`` wraps every native call in an NVTX range.
 MOONEP_GEMM_PAIR      ``1`` (default): grouped GEMMs on CTA pairs (tcgen05 cta_group::2); ``0``: one CTA per tile.
 MOONEP_WGRAD          ``kernel`` (default) or ``torch``: weight gradients of the MoE layer.
@@ -62,8 +64,12 @@ def local_sms(sm_count: int) -> int:
     return max(1, min(int(raw), sm_count))
 
 
-def debug() -> bool:
-    return os.environ.get("MOONEP_DEBUG", "0") not in _FALSE
+def combine_mode() -> str:
+    """``push`` or ``pull`` (see the module docstring)."""
+    v = os.environ.get("MOONEP_COMBINE", "push").lower()
+    if v not in ("push", "pull"):
+        raise ValueError(f"MOONEP_COMBINE must be 'push' or 'pull', got {v!r}")
+    return v
 
 
 def wgrad_on_kernel() -> bool:
@@ -91,8 +97,8 @@ def nvtx() -> bool:
     return os.environ.get("MOONEP_NVTX", "0") not in _FALSE
 
 
-def pipeline_enabled() -> bool:
-    return os.environ.get("MOONEP_TD_PIPELINE", "0") not in _FALSE
+def num_sms_dedup_is_set() -> bool:
+    return bool(os.environ.get("MOONEP_NUM_SMS_DEDUP"))
 
 
 def num_sms_dedup(max_sms: int) -> int:

@@ -134,6 +134,11 @@ class CpuBackend:
         plan.dup_groups.copy_(torch.from_numpy(g).to(torch.int32))
         plan.dup_loffs.copy_(torch.from_numpy(l).to(torch.int32))
         plan.dup_counts.copy_(torch.from_numpy(n).to(torch.int32))
+        if plan.src_info is not None:
+            plan.src_info.copy_(self._meta(c["rank"], c["SRC_INFO_OFF"], c["NvS"]))
+        if plan.link is not None:
+            link = self._meta(c["rank"], c["LINK_OFF"], c["NvS"])
+            plan.link.copy_(torch.where(plan.src_info >= 0, link, torch.zeros_like(link)) if plan.src_info is not None else link)
 
     # -- dispatch --------------------------------------------------------------
     def dispatch_send(self, hidden_sh, route_weights_sk, plan, build_dedup_map, wait=None):

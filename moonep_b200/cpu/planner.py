@@ -192,11 +192,13 @@ def mark_duplicates(dst_pos: np.ndarray, S: int, K: int, NvS: int) -> np.ndarray
 
 LINK_PRIMARY = 1 << 30
 LINK_HAS_NEXT = 1 << 29
+LINK_ORD_SHIFT = 24  # bits 24..28 of a primary's word: its position among the primaries of its token
 
 
 def link_words(dst_pos: np.ndarray, S: int, K: int, NvS: int) -> np.ndarray:
-    """Per local entry, the word its source pushes beside src_info: primary bit, and the row of the
-    next entry (higher k) of the same token on the same destination rank."""
+    """Per local entry, the word its source pushes beside src_info: primary bit, the position of a primary
+    among the primaries of its token (ascending k), and the row of the next entry (higher k) of the same
+    token on the same destination rank."""
     d = dst_pos.reshape(S, K)
     dest = d // NvS
     loff = d - dest * NvS
@@ -208,7 +210,8 @@ def link_words(dst_pos: np.ndarray, S: int, K: int, NvS: int) -> np.ndarray:
     has_next = cand.any(axis=2)
     nxt_k = cand.argmax(axis=2)  # first later k' on the same destination
     nxt = np.take_along_axis(loff, nxt_k, axis=1)
-    words = np.where(is_dup, 0, LINK_PRIMARY) | np.where(has_next, LINK_HAS_NEXT | nxt, 0)
+    ord_ = np.cumsum(~is_dup, axis=1) - 1  # primaries before k, for primaries
+    words = np.where(is_dup, 0, LINK_PRIMARY | (ord_ << LINK_ORD_SHIFT)) | np.where(has_next, LINK_HAS_NEXT | nxt, 0)
     return words.reshape(-1)
 
 

@@ -46,6 +46,16 @@ __device__ __forceinline__ void st_release_sys(int* p, int v) {
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ void st_release_gpu(int* p, int v) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
 __device__ __forceinline__ int ld_volatile(const int* p) {
   int v;
   asm volatile("ld.volatile.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -110,6 +120,36 @@ __device__ __forceinline__ bool block_wait_flags(const MoonepDevCtx& c, int fami
         }
       }
     }
+  }
+  __syncthreads();
+  const bool ok = s_ok != 0;
+  __syncthreads();
+  return ok;
+}
+
+// Block-wide: wait until counters[word] >= epoch, a value another CTA of this GPU publishes with
+// st_release_gpu (e.g. "the planner tables of this dispatch are ready").  Returns false (to every thread) on
+// timeout or if the context is poisoned.  Must be called by all threads.
+__device__ __forceinline__ bool wait_local_epoch(const MoonepDevCtx& c, int word, int epoch, int kernel_id) {
+  __shared__ int s_ok;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int ok = poisoned(c) ? 0 : 1;
+    const int* p = c.counters + word;
+    int v;
+    if (ok && (v = ld_acquire_gpu(p)) - epoch < 0) {
+      const unsigned long long t0 = globaltimer_ns();
+      unsigned spins = 0;
+      while ((v = ld_acquire_gpu(p)) - epoch < 0) {
+        if ((++spins & 63u) == 0 && (globaltimer_ns() - t0 > c.timeout_ns || poisoned(c))) {
+          record_status(c, MOONEP_STATUS_TIMEOUT, kernel_id, 64 + word, c.rank, epoch, v);
+          ok = 0;
+          break;
+        }
+        __nanosleep(64);
+      }
+    }
+    s_ok = ok;
   }
   __syncthreads();
   const bool ok = s_ok != 0;

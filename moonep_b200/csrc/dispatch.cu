@@ -1,56 +1,82 @@
-// Dispatch for sm_100a: push token rows and gate weights into the destination ranks'
-// shards over NVLink peer memory, build the duplicate map on the destination, and expand
-// duplicates locally.
+// Dispatch for sm_100a: one kernel whose CTAs take roles; launched with all roles it is the fused
+// dispatch (planner tables -> token planning -> row push over NVLink, overlapped with zero fill,
+// duplicate-map construction and duplicate expansion on the destination), launched role by role it
+// gives the stand-alone stages of the launch-level API and of emulated ranks that share one GPU.
 //
-//   dispatch_send    persistent, num_sms CTAs.  Waits (bounded) until every peer is ready
-//                    (FLAG_PLAN after a fresh plan, FLAG_READY for a replayed plan).  Tokens are
-//                    handed out in small batches from an atomic counter.  Each token row is
-//                    read from HBM once and written to every destination rank that owns one of
-//                    its experts (only the first entry per rank: per-rank dedup); the K gate
-//                    weights go to the rows' weight slots.  Two copy paths:
-//                      bulk: one lane per warp drives a 3-stage shared-memory ring with
-//                            cp.async.bulk (global->shared on an mbarrier, shared->peer global in
-//                            bulk groups); no register traffic, one instruction per 14 KB row.
-//                      ldst: 16-byte loads into registers, 16-byte stores to every destination.
-//                    Meanwhile, for a fresh
-//                    plan, dup_groups/dup_loffs/dup_counts are built from the link words the
-//                    peers pushed during planning (all CTAs share the rows).  The last CTA to finish signals FLAG_SENT.
-//   dispatch_expand  all SMs: zero-fills the pad rows of the local shard, waits for every peer's
-//                    FLAG_SENT, then copies each primary row to its duplicate rows inside the shard.
+//   TABLES   (CTA 0) waits for every peer's tokens-per-expert row (FLAG_TPE), derives the global tables
+//            (planner.cuh) and publishes "tables ready" to the other CTAs of this GPU.
+//   TOKENS   sender CTAs plan their blocks of tokens (destination rows, duplicate marking, src_info and
+//            link words pushed to the destinations); the last one signals FLAG_PLAN to every peer.
+//   SEND     persistent sender CTAs; tokens are handed out in small batches from an atomic counter.  Each
+//            row is read from HBM once and written to every destination rank that owns one of its experts
+//            (only the first entry per rank crosses NVLink: per-rank dedup).  Two copy paths:
+//              bulk: one lane per warp drives a 3-stage shared-memory ring with cp.async.bulk
+//                    (global->shared on an mbarrier, shared->peer global in bulk groups);
+//              ldst: 16-byte loads into registers, 16-byte stores to every destination.
+//            When the copies of a row are complete (bulk group retired, or stores issued) the row's
+//            flag in the destination's meta chunk is released with the dispatch's SENT epoch, so a
+//            consumer there (the EXPAND role, a grouped GEMM's producer warp) can start on that row
+//            without waiting for the whole all-to-all.  The last sender CTA signals FLAG_SENT.
+//   EXPAND   every other CTA: zero-fills the pad rows of the local shard (flagging them as well), waits for
+//            every peer's FLAG_PLAN, builds dup_groups/dup_loffs/dup_counts from the link words (and keeps
+//            a copy of src_info and link words in the plan), then copies each primary row to its
+//            duplicate rows as soon as the primary's row flag shows it has landed.  Ends with a wait for
+//            every peer's FLAG_SENT, so all rows of the shard are present when the kernel is.
+//
+// CTA order: TABLES is CTA 0, senders follow, expanders come last, so a CTA only ever waits for CTAs with a
+// lower index (which the hardware dispatches first) or for other GPUs.  Every wait is bounded.
 //
 // Parity: reference moonep_td/dispatch.py:42-117 (dispatch_kernel, zero_fill_kernel),
-// moonep_td/_dedup_builder.py:23-108 (three dedup kernels), moonep_td/dispatch_epilogue.py:21-40.
-// The reference moves 2 bytes per thread per iteration, launches one CTA per (token, k) entry
-// and re-reads the source row for every destination.
+// moonep_td/_dedup_builder.py:23-108 (three dedup kernels), moonep_td/dispatch_epilogue.py:21-40, driven
+// by moonep_td/api.py:275-305 with six cross-rank barriers and a host read of dup_counts.  The reference
+// moves 2 bytes per thread per iteration, launches one CTA per (token, k) entry and re-reads the source
+// row for every destination.
 #include <climits>
 
 #include "common.cuh"
 #include "host.h"
+#include "planner.cuh"
 
 namespace moonep {
 
 namespace {
 
-constexpr int kSendThreadsLdst = 512;
-constexpr int kSendThreadsBulk = 256;
-constexpr int kBulkWarps = 4;    // warps of a CTA that drive bulk copies
+constexpr int kDispatchThreads = 512;
+constexpr int kBulkWarps = 4;    // warps of a sender CTA that drive bulk copies
 constexpr int kBulkStages = 3;   // ring depth per warp
 constexpr int kTokenBatch = 4;   // tokens handed out per grab
 constexpr int kVecPerLane = 8;   // int4 per lane per register chunk (4 KB per warp)
 constexpr int kMaxChunkBytes = 16 * 1024;
+constexpr int kExpandSlice = 2048;  // rows whose duplicate groups an expander CTA lists in shared memory at a time
 
-struct SendArgs {
+struct DispatchArgs {
+  // planner (fresh plans)
+  const int* topk;   // [N]
+  const int* tpe2d;  // [R, E] or null (rows pushed by plan_publish are used)
+  int* dst;          // [N] written by TOKENS, read by SEND
+  int* cu_seqlens;
+  int* experts_to_copy;
+  int* zero_fill;    // [E+B, 2] written by TABLES, read by EXPAND
+  int* remote_stats;
+  int tokens_per_block, n_blocks, tables_in_smem;
+  // send
   const uint16_t* hidden;  // [S, H] bf16
   const float* weights;    // [S, K] or null
-  const int* dst;          // [N]
-  const int* zero_fill;    // [E+B, 2]
-  int* dup_groups;         // [NvS, 3]
-  int* dup_loffs;          // [NvS]
-  int* dup_counts;         // [2]
-  int build_dedup;
-  int wait_family, wait_epoch, signal_epoch;
-  int vec_ok;              // rows are 16-byte aligned and a multiple of 16 bytes
+  // destination side
+  int* dup_groups;     // [NvS, 3]
+  int* dup_loffs;      // [NvS]
+  int* dup_counts;     // [2]
+  int* plan_src_info;  // [NvS] or null: the plan's copy of src_info
+  int* plan_link;      // [NvS] or null: the plan's copy of the link words
+  int fresh;           // planning and the duplicate map belong to this dispatch
+  int roles, n_send;
+  int with_weights;    // the zero fill also clears the pad rows' weight slots
+  int wait_family, wait_epoch;  // replayed plans: what SEND waits for (FLAG_READY or nothing)
+  int epoch_tpe, epoch_plan, epoch_sent;
+  int vec_ok;                // rows are 16-byte aligned and a multiple of 16 bytes
   int chunk_bytes, nchunks;  // bulk path: a row is sent in nchunks pieces
+  int bulk;
+  int build_only;  // EXPAND: only build the duplicate map (no zero fill, no copies)
 };
 
 __device__ __forceinline__ void decode_dst(int d, int NvS, int& dest, int& loff) {
@@ -59,81 +85,43 @@ __device__ __forceinline__ void decode_dst(int d, int NvS, int& dest, int& loff)
   loff = raw - dest * NvS;
 }
 
-// ---- destination-side dedup builder (all CTAs share the rows) ----------------------------------
-//
-// During planning every source pushed, next to src_info, a link word per landed row: whether the
-// row is the first of its (source, token) on this rank and which row holds the next entry of the
-// same token.  A primary row that has a successor opens a group; walking the chain lists its
-// duplicates in ascending k.  Rows are independent, so any number of threads can share them; groups
-// and duplicate rows are numbered with one pair of atomics per warp.  dup_counts is zeroed by the
-// host wrapper before the launch.
-__device__ void build_dedup_rows(const MoonepDevCtx& c, const SendArgs& a, int gthread, int gthreads) {
-  const int lane = threadIdx.x & 31;
-  const int NvS = c.NvS;
-  const int* src_info = c.meta_peer[c.rank] + c.src_info_off;
-  const int* link = c.meta_peer[c.rank] + c.link_off;
-  const int rounds = (NvS + gthreads - 1) / gthreads;
-  for (int it = 0; it < rounds; ++it) {
-    const int loff = it * gthreads + gthread;
-    int dup_n = 0, first = -1;
-    if (loff < NvS && src_info[loff] >= 0) {
-      const int l = link[loff];
-      if ((l & MOONEP_LINK_PRIMARY) && (l & MOONEP_LINK_HAS_NEXT)) {
-        first = l & MOONEP_NVS_MASK;
-        int cur = first;
-        while (dup_n < MOONEP_MAX_TOPK) {
-          if (cur < 0 || cur >= NvS) {
-            record_status(c, MOONEP_STATUS_BAD_INDEX, MOONEP_K_DISPATCH_SEND, 5, cur, loff, 0);
-            dup_n = 0;
-            break;
-          }
-          ++dup_n;
-          const int l2 = link[cur];
-          if (!(l2 & MOONEP_LINK_HAS_NEXT)) break;
-          cur = l2 & MOONEP_NVS_MASK;
-        }
-      }
-    }
-    const unsigned has = __ballot_sync(0xffffffffu, dup_n > 0);
-    if (has == 0) continue;
-    int incl = dup_n;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int v = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += v;
-    }
-    const int total = __shfl_sync(0xffffffffu, incl, 31);
-    int gbase = 0, dbase = 0;
-    if (lane == 0) {
-      gbase = atomicAdd(a.dup_counts, __popc(has));
-      dbase = atomicAdd(a.dup_counts + 1, total);
-    }
-    gbase = __shfl_sync(0xffffffffu, gbase, 0);
-    dbase = __shfl_sync(0xffffffffu, dbase, 0);
-    if (dup_n > 0) {
-      const int g = gbase + __popc(has & ((1u << lane) - 1u));
-      int ds = dbase + incl - dup_n;
-      if (g < NvS && ds + dup_n <= NvS) {
-        a.dup_groups[3 * g] = loff;
-        a.dup_groups[3 * g + 1] = ds;
-        a.dup_groups[3 * g + 2] = dup_n;
-        int cur = first;
-        for (int q = 0; q < dup_n; ++q) {
-          a.dup_loffs[ds + q] = cur;
-          cur = link[cur] & MOONEP_NVS_MASK;
-        }
-      }
+__device__ __forceinline__ bool dst_in_range(const MoonepDevCtx& c, int dest, int loff) {
+  return dest >= 0 && dest < c.R && loff >= 0 && loff < c.NvS;
+}
+
+__device__ __forceinline__ int* rowflag_ptr(const MoonepDevCtx& c, int on_rank, int loff) {
+  return c.meta_peer[on_rank] + c.rowflag_off + loff;
+}
+
+// CTAs of one role finish: true (to every thread) in the last of `count` CTAs, after a system-scope fence
+// that orders every CTA's earlier writes before whatever the last CTA publishes next.
+__device__ __forceinline__ bool role_tail(const MoonepDevCtx& c, int counter, int count) {
+  __shared__ int s_last;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    fence_sys();
+    const int arrived = atomicAdd(c.counters + counter, 1);
+    s_last = (arrived == count - 1);
+    if (s_last) {
+      c.counters[counter] = 0;
+      fence_sys();
     }
   }
+  __syncthreads();
+  const bool last = s_last != 0;
+  __syncthreads();
+  return last;
 }
 
 // ---- zero fill of pad rows ---------------------------------------------------------------------
 
 // Reads the (start, count) pairs of 32 groups at a time, then spreads the pad rows of every
-// non-empty range over all participating warps.
-__device__ void zero_fill_rows(const MoonepDevCtx& c, const SendArgs& a, int warp_global, int warps_total, int lane) {
+// non-empty range over all participating warps.  Every cleared row gets its row flag.
+__device__ void zero_fill_rows(const MoonepDevCtx& c, const int* __restrict__ zero_fill, int with_weights, int vec_ok,
+                               int epoch, int warp_global, int warps_total, int lane) {
   uint16_t* shard = c.hidden_peer[c.rank];
   float* wbuf = reinterpret_cast<float*>(c.meta_peer[c.rank] + c.weights_off);
+  int* rowflag = c.meta_peer[c.rank] + c.rowflag_off;
   const int ngroups = c.E + c.B;
   const int H = c.H;
   int seen = 0;  // pad rows of the ranges before this one: rows are dealt round-robin across ranges
@@ -141,8 +129,8 @@ __device__ void zero_fill_rows(const MoonepDevCtx& c, const SendArgs& a, int war
     const int g = base + lane;
     int n_pad = 0, start = 0;
     if (g < ngroups) {
-      n_pad = a.zero_fill[2 * g + 1];
-      start = a.zero_fill[2 * g];
+      n_pad = zero_fill[2 * g + 1];
+      start = zero_fill[2 * g];
     }
     unsigned m = __ballot_sync(0xffffffffu, n_pad > 0);
     while (m) {
@@ -156,14 +144,16 @@ __device__ void zero_fill_rows(const MoonepDevCtx& c, const SendArgs& a, int war
         const int row = s0 + r;
         if (row < 0 || row >= c.NvS) continue;
         uint16_t* p = shard + (long long)row * H;
-        if (a.vec_ok) {
+        if (vec_ok) {
           const int nvec = H / 8;
           const int4 z = make_int4(0, 0, 0, 0);
           for (int i = lane; i < nvec; i += 32) st16(reinterpret_cast<int4*>(p) + i, z);
         } else {
           for (int i = lane; i < H; i += 32) p[i] = 0;
         }
-        if (a.weights != nullptr && lane == 0) wbuf[row] = 0.f;
+        if (with_weights && lane == 0) wbuf[row] = 0.f;
+        __syncwarp();
+        if (lane == 0) st_release_gpu(rowflag + row, epoch);
       }
     }
   }
@@ -177,7 +167,7 @@ __device__ __forceinline__ int grab_tokens(int* counter, int lane) {
 }
 
 // Store the K gate weights of a token next to the rows they belong to.
-__device__ __forceinline__ void push_weights(const MoonepDevCtx& c, const SendArgs& a, int token, int lane, int dest,
+__device__ __forceinline__ void push_weights(const MoonepDevCtx& c, const DispatchArgs& a, int token, int lane, int dest,
                                              int loff) {
   if (a.weights != nullptr && lane < c.K) {
     float* w = reinterpret_cast<float*>(c.meta_peer[dest] + c.weights_off);
@@ -185,294 +175,499 @@ __device__ __forceinline__ void push_weights(const MoonepDevCtx& c, const SendAr
   }
 }
 
-__device__ __forceinline__ bool dst_in_range(const MoonepDevCtx& c, int dest, int loff) {
-  return dest >= 0 && dest < c.R && loff >= 0 && loff < c.NvS;
+// Lane `lane` < K holds routing entry d of a token whose copies are complete: release the flags of the rows
+// this rank wrote (the token's primary row on every destination rank).
+__device__ __forceinline__ void release_row_flags(const MoonepDevCtx& c, int d, int lane, int epoch) {
+  __syncwarp();
+  if (lane < c.K && d >= 0) {
+    int dest, loff;
+    decode_dst(d, c.NvS, dest, loff);
+    if (dst_in_range(c, dest, loff)) st_release_sys(rowflag_ptr(c, dest, loff), epoch);
+  }
 }
 
-// ---- send kernel, register path ------------------------------------------------------------------
+// ---- send role, register path ------------------------------------------------------------------
 
-__global__ void __launch_bounds__(kSendThreadsLdst) dispatch_send_ldst_kernel(const MoonepDevCtx c, const SendArgs a) {
-  const bool ok = block_wait_flags(c, a.wait_family, a.wait_epoch, MOONEP_K_DISPATCH_SEND);
+__device__ void send_ldst(const MoonepDevCtx& c, const DispatchArgs& a, int epoch) {
   const int lane = threadIdx.x & 31;
-  int* work = c.counters + MOONEP_NUM_KERNEL_IDS;  // token counter of this kernel
-  if (ok) {
-    if (a.build_dedup) build_dedup_rows(c, a, blockIdx.x * blockDim.x + threadIdx.x, gridDim.x * blockDim.x);
-    const int H = c.H, K = c.K, S = c.S;
-    for (;;) {
-      const int b0 = grab_tokens(work, lane);
-      if (b0 >= S) break;
-      const int b1 = min(S, b0 + kTokenBatch);
-      for (int token = b0; token < b1; ++token) {
-        int d = 0, dest = 0, loff = 0;
-        bool valid = false;
-        if (lane < K) {
-          d = a.dst[token * K + lane];
-          decode_dst(d, c.NvS, dest, loff);
-          valid = dst_in_range(c, dest, loff);
-          if (!valid) record_status(c, MOONEP_STATUS_BAD_INDEX, MOONEP_K_DISPATCH_SEND, 6, d, token, lane);
-        }
-        if (valid) push_weights(c, a, token, lane, dest, loff);
-        const unsigned prim = __ballot_sync(0xffffffffu, valid && d >= 0);
-        const uint16_t* src = a.hidden + (long long)token * H;
-        if (a.vec_ok) {
-          const int nvec = H / 8;
-          const int4* s4 = reinterpret_cast<const int4*>(src);
-          for (int c0 = 0; c0 < nvec; c0 += 32 * kVecPerLane) {
-            int4 v[kVecPerLane];
+  int* work = c.counters + MOONEP_CTR_SEND_WORK;
+  const int H = c.H, K = c.K, S = c.S;
+  for (;;) {
+    const int b0 = grab_tokens(work, lane);
+    if (b0 >= S) break;
+    const int b1 = min(S, b0 + kTokenBatch);
+    for (int token = b0; token < b1; ++token) {
+      int d = 0, dest = 0, loff = 0;
+      bool valid = false;
+      if (lane < K) {
+        d = a.dst[token * K + lane];
+        decode_dst(d, c.NvS, dest, loff);
+        valid = dst_in_range(c, dest, loff);
+        if (!valid) record_status(c, MOONEP_STATUS_BAD_INDEX, MOONEP_K_DISPATCH_SEND, 6, d, token, lane);
+      }
+      if (valid) push_weights(c, a, token, lane, dest, loff);
+      const unsigned prim = __ballot_sync(0xffffffffu, valid && d >= 0);
+      const uint16_t* src = a.hidden + (long long)token * H;
+      if (a.vec_ok) {
+        const int nvec = H / 8;
+        const int4* s4 = reinterpret_cast<const int4*>(src);
+        for (int c0 = 0; c0 < nvec; c0 += 32 * kVecPerLane) {
+          int4 v[kVecPerLane];
 #pragma unroll
-            for (int j = 0; j < kVecPerLane; ++j) {
-              const int i = c0 + j * 32 + lane;
-              if (i < nvec) v[j] = ld16(s4 + i);
-            }
-            unsigned m = prim;
-            while (m) {
-              const int kk = __ffs(m) - 1;
-              m &= m - 1;
-              const int dd = __shfl_sync(0xffffffffu, dest, kk);
-              const int ll = __shfl_sync(0xffffffffu, loff, kk);
-              int4* o4 = reinterpret_cast<int4*>(c.hidden_peer[dd] + (long long)ll * H);
-#pragma unroll
-              for (int j = 0; j < kVecPerLane; ++j) {
-                const int i = c0 + j * 32 + lane;
-                if (i < nvec) st16(o4 + i, v[j]);
-              }
-            }
+          for (int j = 0; j < kVecPerLane; ++j) {
+            const int i = c0 + j * 32 + lane;
+            if (i < nvec) v[j] = ld16(s4 + i);
           }
-        } else {
           unsigned m = prim;
           while (m) {
             const int kk = __ffs(m) - 1;
             m &= m - 1;
             const int dd = __shfl_sync(0xffffffffu, dest, kk);
             const int ll = __shfl_sync(0xffffffffu, loff, kk);
-            uint16_t* o = c.hidden_peer[dd] + (long long)ll * H;
-            for (int i = lane; i < H; i += 32) o[i] = src[i];
-          }
-        }
-      }
-    }
-  }
-  // tail: last CTA resets the token counter and signals
-  __shared__ int s_last;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    fence_sys();
-    const int arrived = atomicAdd(c.counters + MOONEP_K_DISPATCH_SEND, 1);
-    s_last = arrived == (int)gridDim.x - 1;
-    if (s_last) {
-      c.counters[MOONEP_K_DISPATCH_SEND] = 0;
-      *work = 0;
-      fence_sys();
-    }
-  }
-  __syncthreads();
-  if (s_last && ok) {
-    for (int r = threadIdx.x; r < c.R; r += blockDim.x)
-      st_release_sys(flag_ptr(c, r, MOONEP_FLAG_SENT, c.rank), abs_epoch(c, MOONEP_FLAG_SENT, a.signal_epoch));
-  }
-}
-
-// ---- send kernel, bulk-copy path -----------------------------------------------------------------
-
-__global__ void __launch_bounds__(kSendThreadsBulk) dispatch_send_bulk_kernel(const MoonepDevCtx c, const SendArgs a) {
-  extern __shared__ __align__(128) unsigned char s_ring[];  // [kBulkWarps][kBulkStages][chunk_bytes]
-  __shared__ __align__(8) unsigned long long s_bar[kBulkWarps][kBulkStages];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  if (threadIdx.x < kBulkWarps * kBulkStages) mbar_init(&s_bar[0][0] + threadIdx.x, 1);
-  fence_barrier_init();
-  const bool ok = block_wait_flags(c, a.wait_family, a.wait_epoch, MOONEP_K_DISPATCH_SEND);
-  int* work = c.counters + MOONEP_NUM_KERNEL_IDS;
-  if (ok) {
-    if (warp >= kBulkWarps) {
-      // helper warps: duplicate map
-      const int hw = nwarps - kBulkWarps;
-      const int hthreads = hw * 32;
-      if (a.build_dedup)
-        build_dedup_rows(c, a, blockIdx.x * hthreads + (threadIdx.x - kBulkWarps * 32), gridDim.x * hthreads);
-    } else {
-      const int H = c.H, K = c.K, S = c.S;
-      const long long row_bytes = (long long)H * 2;
-      unsigned char* ring = s_ring + (size_t)warp * kBulkStages * a.chunk_bytes;
-      unsigned long long* bar = s_bar[warp];
-      int ring_tok[kBulkStages], ring_chunk[kBulkStages];
-      int batch_next = 0, batch_end = 0, cur_chunk = 0;
-      bool more = true;
-      int loaded = 0, done = 0;
-      bool failed = false;
-
-      auto next_item = [&](int& tok, int& ch) -> bool {
-        if (batch_next == batch_end) {
-          const int b = grab_tokens(work, lane);
-          if (b >= S) return false;
-          batch_next = b;
-          batch_end = min(S, b + kTokenBatch);
-          cur_chunk = 0;
-        }
-        tok = batch_next;
-        ch = cur_chunk;
-        if (++cur_chunk == a.nchunks) {
-          cur_chunk = 0;
-          ++batch_next;
-        }
-        return true;
-      };
-      auto chunk_len = [&](int ch) -> unsigned {
-        const long long off = (long long)ch * a.chunk_bytes;
-        const long long rest = row_bytes - off;
-        return (unsigned)(rest < a.chunk_bytes ? rest : a.chunk_bytes);
-      };
-      auto issue_load = [&](int tok, int ch) {
-        const int s = loaded % kBulkStages;
+            int4* o4 = reinterpret_cast<int4*>(c.hidden_peer[dd] + (long long)ll * H);
 #pragma unroll
-        for (int q = 0; q < kBulkStages; ++q)
-          if (q == s) {
-            ring_tok[q] = tok;
-            ring_chunk[q] = ch;
-          }
-        if (lane == 0) {
-          const unsigned len = chunk_len(ch);
-          mbar_expect_tx(bar + s, len);
-          bulk_g2s(ring + (size_t)s * a.chunk_bytes,
-                   reinterpret_cast<const unsigned char*>(a.hidden) + tok * row_bytes + (long long)ch * a.chunk_bytes, len,
-                   bar + s);
-        }
-        ++loaded;
-      };
-
-      int tok, ch;
-      more = next_item(tok, ch);
-      if (more) issue_load(tok, ch);
-      while (done < loaded && !failed) {
-        if (more) {
-          more = next_item(tok, ch);
-          if (more) {
-            // the stage about to be refilled was read by the bulk group committed two items ago
-            if (lane == 0) bulk_wait_read<1>();
-            issue_load(tok, ch);
+            for (int j = 0; j < kVecPerLane; ++j) {
+              const int i = c0 + j * 32 + lane;
+              if (i < nvec) st16(o4 + i, v[j]);
+            }
           }
         }
-        const int s = done % kBulkStages;
-        int ctok = 0, cch = 0;
-#pragma unroll
-        for (int q = 0; q < kBulkStages; ++q)
-          if (q == s) {
-            ctok = ring_tok[q];
-            cch = ring_chunk[q];
-          }
-        int d = 0, dest = 0, loff = 0;
-        bool valid = false;
-        if (lane < K) {
-          d = a.dst[ctok * K + lane];
-          decode_dst(d, c.NvS, dest, loff);
-          valid = dst_in_range(c, dest, loff);
-          if (!valid) record_status(c, MOONEP_STATUS_BAD_INDEX, MOONEP_K_DISPATCH_SEND, 6, d, ctok, lane);
-        }
-        if (valid && cch == 0) push_weights(c, a, ctok, lane, dest, loff);
-        unsigned m = __ballot_sync(0xffffffffu, valid && d >= 0);
-        int got = 1;
-        if (lane == 0) got = mbar_wait(bar + s, (unsigned)((done / kBulkStages) & 1), c.timeout_ns) ? 1 : 0;
-        got = __shfl_sync(0xffffffffu, got, 0);
-        if (!got) {
-          if (lane == 0) record_status(c, MOONEP_STATUS_TIMEOUT, MOONEP_K_DISPATCH_SEND, 100, s, done, ctok);
-          failed = true;
-          break;
-        }
-        const unsigned len = chunk_len(cch);
+      } else {
+        unsigned m = prim;
         while (m) {
           const int kk = __ffs(m) - 1;
           m &= m - 1;
           const int dd = __shfl_sync(0xffffffffu, dest, kk);
           const int ll = __shfl_sync(0xffffffffu, loff, kk);
-          if (lane == 0) {
-            unsigned char* o = reinterpret_cast<unsigned char*>(c.hidden_peer[dd]) + (long long)ll * row_bytes +
-                               (long long)cch * a.chunk_bytes;
-            bulk_s2g(o, ring + (size_t)s * a.chunk_bytes, len);
-          }
+          uint16_t* o = c.hidden_peer[dd] + (long long)ll * H;
+          for (int i = lane; i < H; i += 32) o[i] = src[i];
         }
-        if (lane == 0) bulk_commit();
-        ++done;
       }
-      if (lane == 0) bulk_wait<0>();
-      __syncwarp();
+      release_row_flags(c, valid ? d : -1, lane, epoch);
     }
-  }
-  __shared__ int s_last;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    fence_sys();
-    const int arrived = atomicAdd(c.counters + MOONEP_K_DISPATCH_SEND, 1);
-    s_last = arrived == (int)gridDim.x - 1;
-    if (s_last) {
-      c.counters[MOONEP_K_DISPATCH_SEND] = 0;
-      *work = 0;
-      fence_sys();
-    }
-  }
-  __syncthreads();
-  if (s_last && ok) {
-    for (int r = threadIdx.x; r < c.R; r += blockDim.x)
-      st_release_sys(flag_ptr(c, r, MOONEP_FLAG_SENT, c.rank), abs_epoch(c, MOONEP_FLAG_SENT, a.signal_epoch));
   }
 }
 
-// ---- duplicate expansion --------------------------------------------------------------------------
+// ---- send role, bulk-copy path -----------------------------------------------------------------
 
-__global__ void __launch_bounds__(512)
-    dispatch_expand_kernel(const MoonepDevCtx c, const int* __restrict__ zero_fill, int with_weights,
-                           const int* __restrict__ dup_groups, const int* __restrict__ dup_loffs,
-                           const int* __restrict__ dup_counts, int wait_epoch, int vec_ok) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  if (!poisoned(c) && zero_fill != nullptr) {
-    // pad rows belong to this rank alone, so they are cleared while the peers' rows are still arriving
-    SendArgs z;
-    z.zero_fill = zero_fill;
-    z.vec_ok = vec_ok;
-    z.weights = with_weights ? reinterpret_cast<const float*>(zero_fill) : nullptr;  // only tested for null
-    zero_fill_rows(c, z, blockIdx.x * nwarps + warp, gridDim.x * nwarps, lane);
+// Runs in warps 0..kBulkWarps-1 of a sender CTA.  s_ring: [kBulkWarps][kBulkStages][chunk_bytes],
+// s_bar: [kBulkWarps][kBulkStages] initialised mbarriers (count 1).  Returns false after a timeout.
+__device__ bool send_bulk(const MoonepDevCtx& c, const DispatchArgs& a, int epoch, unsigned char* s_ring,
+                          unsigned long long* s_bar) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int* work = c.counters + MOONEP_CTR_SEND_WORK;
+  const int H = c.H, K = c.K, S = c.S;
+  const long long row_bytes = (long long)H * 2;
+  unsigned char* ring = s_ring + (size_t)warp * kBulkStages * a.chunk_bytes;
+  unsigned long long* bar = s_bar + warp * kBulkStages;
+  int ring_tok[kBulkStages], ring_chunk[kBulkStages], ring_d[kBulkStages];
+  // what the row flags of an item need; one entry more than the ring has stages, because an item is flagged
+  // (three items late) after the load of the item that reuses its stage has been issued
+  int flag_chunk[kBulkStages + 1], flag_d[kBulkStages + 1];
+  int batch_next = 0, batch_end = 0, cur_chunk = 0;
+  bool more = true;
+  int loaded = 0, done = 0;
+  bool failed = false;
+
+  auto next_item = [&](int& tok, int& ch) -> bool {
+    if (batch_next == batch_end) {
+      const int b = grab_tokens(work, lane);
+      if (b >= S) return false;
+      batch_next = b;
+      batch_end = min(S, b + kTokenBatch);
+      cur_chunk = 0;
+    }
+    tok = batch_next;
+    ch = cur_chunk;
+    if (++cur_chunk == a.nchunks) {
+      cur_chunk = 0;
+      ++batch_next;
+    }
+    return true;
+  };
+  auto chunk_len = [&](int ch) -> unsigned {
+    const long long off = (long long)ch * a.chunk_bytes;
+    const long long rest = row_bytes - off;
+    return (unsigned)(rest < a.chunk_bytes ? rest : a.chunk_bytes);
+  };
+  auto issue_load = [&](int tok, int ch) {
+    const int s = loaded % kBulkStages;
+    const int d = lane < K ? a.dst[tok * K + lane] : 0;
+#pragma unroll
+    for (int q = 0; q < kBulkStages; ++q)
+      if (q == s) {
+        ring_tok[q] = tok;
+        ring_chunk[q] = ch;
+        ring_d[q] = d;
+      }
+    const int fs = loaded % (kBulkStages + 1);
+#pragma unroll
+    for (int q = 0; q < kBulkStages + 1; ++q)
+      if (q == fs) {
+        flag_chunk[q] = ch;
+        flag_d[q] = d;
+      }
+    if (lane == 0) {
+      const unsigned len = chunk_len(ch);
+      mbar_expect_tx(bar + s, len);
+      bulk_g2s(ring + (size_t)s * a.chunk_bytes,
+               reinterpret_cast<const unsigned char*>(a.hidden) + tok * row_bytes + (long long)ch * a.chunk_bytes, len,
+               bar + s);
+    }
+    ++loaded;
+  };
+  // the stores of item j are complete: flag its rows if it was the last piece of its token
+  auto flag_item = [&](int j) {
+    const int fs = j % (kBulkStages + 1);
+    int ch = 0, d = 0;
+#pragma unroll
+    for (int q = 0; q < kBulkStages + 1; ++q)
+      if (q == fs) {
+        ch = flag_chunk[q];
+        d = flag_d[q];
+      }
+    if (ch == a.nchunks - 1) release_row_flags(c, d, lane, epoch);
+  };
+
+  int tok, ch;
+  more = next_item(tok, ch);
+  if (more) issue_load(tok, ch);
+  while (done < loaded && !failed) {
+    if (more) {
+      more = next_item(tok, ch);
+      if (more) {
+        // the stage about to be refilled belongs to item loaded-3, whose stores are complete (and flagged) by now:
+        // item done-2 at the latest was retired by the wait below in the previous iteration
+        if (lane == 0) bulk_wait_read<1>();
+        __syncwarp();
+        issue_load(tok, ch);
+      }
+    }
+    const int s = done % kBulkStages;
+    int ctok = 0, cch = 0, d = 0;
+#pragma unroll
+    for (int q = 0; q < kBulkStages; ++q)
+      if (q == s) {
+        ctok = ring_tok[q];
+        cch = ring_chunk[q];
+        d = ring_d[q];
+      }
+    int dest = 0, loff = 0;
+    bool valid = false;
+    if (lane < K) {
+      decode_dst(d, c.NvS, dest, loff);
+      valid = dst_in_range(c, dest, loff);
+      if (!valid) record_status(c, MOONEP_STATUS_BAD_INDEX, MOONEP_K_DISPATCH_SEND, 6, d, ctok, lane);
+    }
+    if (valid && cch == 0) push_weights(c, a, ctok, lane, dest, loff);
+    unsigned m = __ballot_sync(0xffffffffu, valid && d >= 0);
+    int got = 1;
+    if (lane == 0) got = mbar_wait(bar + s, (unsigned)((done / kBulkStages) & 1), c.timeout_ns) ? 1 : 0;
+    got = __shfl_sync(0xffffffffu, got, 0);
+    if (!got) {
+      if (lane == 0) record_status(c, MOONEP_STATUS_TIMEOUT, MOONEP_K_DISPATCH_SEND, 100, s, done, ctok);
+      failed = true;
+      break;
+    }
+    const unsigned len = chunk_len(cch);
+    while (m) {
+      const int kk = __ffs(m) - 1;
+      m &= m - 1;
+      const int dd = __shfl_sync(0xffffffffu, dest, kk);
+      const int ll = __shfl_sync(0xffffffffu, loff, kk);
+      if (lane == 0) {
+        unsigned char* o = reinterpret_cast<unsigned char*>(c.hidden_peer[dd]) + (long long)ll * row_bytes +
+                           (long long)cch * a.chunk_bytes;
+        bulk_s2g(o, ring + (size_t)s * a.chunk_bytes, len);
+      }
+    }
+    if (lane == 0) bulk_commit();
+    ++done;
+    if (done >= kBulkStages) {
+      // all but the two most recent groups have completed: item done-3 is in its destinations' memory
+      if (lane == 0) bulk_wait<kBulkStages - 1>();
+      flag_item(done - kBulkStages);
+    }
   }
-  if (!block_wait_flags(c, MOONEP_FLAG_SENT, wait_epoch, MOONEP_K_DISPATCH_EXPAND)) return;
+  if (lane == 0) bulk_wait<0>();
+  __syncwarp();
+  if (!failed)
+    for (int j = done >= kBulkStages ? done - kBulkStages + 1 : 0; j < done; ++j) flag_item(j);
+  return !failed;
+}
+
+// ---- expand role ---------------------------------------------------------------------------------
+
+// Copy row `primary` of the local shard to the rows lane q holds in my_dup (q < dn), then flag them.
+__device__ void expand_group(const MoonepDevCtx& c, int primary, int my_dup, int dn, int vec_ok, int epoch, int lane) {
   const int H = c.H;
-  int ngroups = dup_counts[0];
-  if (ngroups < 0 || ngroups > c.NvS) ngroups = 0;
   uint16_t* shard = c.hidden_peer[c.rank];
-  for (int g = blockIdx.x * nwarps + warp; g < ngroups; g += gridDim.x * nwarps) {
-    const int primary = dup_groups[3 * g];
-    const int ds = dup_groups[3 * g + 1];
-    const int dn = dup_groups[3 * g + 2];
-    if (primary < 0 || primary >= c.NvS || ds < 0 || dn < 0 || ds + dn > c.NvS) continue;
-    const uint16_t* src = shard + (long long)primary * H;
-    // lane q holds the q-th duplicate row (a group has fewer than 32 duplicates)
-    const int my_dup = (lane < dn && lane < 32) ? dup_loffs[ds + lane] : -1;
-    if (vec_ok) {
-      const int nvec = H / 8;
-      const int4* s4 = reinterpret_cast<const int4*>(src);
-      for (int c0 = 0; c0 < nvec; c0 += 32 * kVecPerLane) {
-        int4 v[kVecPerLane];
+  const uint16_t* src = shard + (long long)primary * H;
+  if (vec_ok) {
+    const int nvec = H / 8;
+    const int4* s4 = reinterpret_cast<const int4*>(src);
+    for (int c0 = 0; c0 < nvec; c0 += 32 * kVecPerLane) {
+      int4 v[kVecPerLane];
+#pragma unroll
+      for (int j = 0; j < kVecPerLane; ++j) {
+        const int i = c0 + j * 32 + lane;
+        if (i < nvec) v[j] = ld16(s4 + i);
+      }
+      for (int q = 0; q < dn && q < 32; ++q) {
+        const int row = __shfl_sync(0xffffffffu, my_dup, q);
+        if (row < 0 || row >= c.NvS) continue;
+        int4* o4 = reinterpret_cast<int4*>(shard + (long long)row * H);
 #pragma unroll
         for (int j = 0; j < kVecPerLane; ++j) {
           const int i = c0 + j * 32 + lane;
-          if (i < nvec) v[j] = ld16(s4 + i);
-        }
-        for (int q = 0; q < dn && q < 32; ++q) {
-          const int row = __shfl_sync(0xffffffffu, my_dup, q);
-          if (row < 0 || row >= c.NvS) continue;
-          int4* o4 = reinterpret_cast<int4*>(shard + (long long)row * H);
-#pragma unroll
-          for (int j = 0; j < kVecPerLane; ++j) {
-            const int i = c0 + j * 32 + lane;
-            if (i < nvec) st16(o4 + i, v[j]);
-          }
+          if (i < nvec) st16(o4 + i, v[j]);
         }
       }
-    } else {
-      for (int q = 0; q < dn; ++q) {
-        const int row = dup_loffs[ds + q];
-        if (row < 0 || row >= c.NvS) continue;
-        uint16_t* o = shard + (long long)row * H;
-        for (int i = lane; i < H; i += 32) o[i] = src[i];
+    }
+  } else {
+    for (int q = 0; q < dn && q < 32; ++q) {
+      const int row = __shfl_sync(0xffffffffu, my_dup, q);
+      if (row < 0 || row >= c.NvS) continue;
+      uint16_t* o = shard + (long long)row * H;
+      for (int i = lane; i < H; i += 32) o[i] = src[i];
+    }
+  }
+  __syncwarp();
+  if (lane < dn && my_dup >= 0 && my_dup < c.NvS) st_release_gpu(c.meta_peer[c.rank] + c.rowflag_off + my_dup, epoch);
+}
+
+// Warp-wide bounded wait until row `loff` of the local shard carries `epoch`.
+__device__ bool wait_row(const MoonepDevCtx& c, int loff, int epoch, int lane) {
+  int ok = 1;
+  if (lane == 0) {
+    const int* f = c.meta_peer[c.rank] + c.rowflag_off + loff;
+    if (ld_acquire_sys(f) - epoch < 0) {
+      const unsigned long long t0 = globaltimer_ns();
+      unsigned spins = 0;
+      int v;
+      while ((v = ld_acquire_sys(f)) - epoch < 0) {
+        if ((++spins & 63u) == 0 && (globaltimer_ns() - t0 > c.timeout_ns || poisoned(c))) {
+          record_status(c, MOONEP_STATUS_TIMEOUT, MOONEP_K_DISPATCH_EXPAND, 200, loff, epoch, v);
+          ok = 0;
+          break;
+        }
+        __nanosleep(128);
       }
     }
   }
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
+// xidx of xcnt expander CTAs.  Returns false after a failed wait.
+__device__ bool expand_role(const MoonepDevCtx& c, const DispatchArgs& a, int xidx, int xcnt, bool ok) {
+  __shared__ int s_groups[kExpandSlice];  // group numbers found by this CTA in the current slice
+  __shared__ int s_ngroups;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int NvS = c.NvS;
+  const int epoch = abs_epoch(c, MOONEP_FLAG_SENT, a.epoch_sent);
+  // zero_fill comes from the table stage of this dispatch when the planner ran on the device
+  if (a.fresh && a.wait_family < 0)
+    ok = wait_local_epoch(c, MOONEP_CTR_TABLES_READY, abs_epoch(c, MOONEP_FLAG_PLAN, a.epoch_plan),
+                          MOONEP_K_DISPATCH_EXPAND) && ok;
+  if (ok && a.zero_fill != nullptr && !a.build_only)
+    zero_fill_rows(c, a.zero_fill, a.with_weights, a.vec_ok, epoch, xidx * nwarps + warp, xcnt * nwarps, lane);
+  if (a.fresh) ok = block_wait_flags(c, MOONEP_FLAG_PLAN, a.epoch_plan, MOONEP_K_DISPATCH_EXPAND) && ok;
+  if (ok && a.fresh) {
+    // Every source pushed, next to src_info, a link word per landed row: whether the row is the first of its
+    // (source, token) on this rank and which row holds the next entry of the same token.  A primary row that
+    // has a successor opens a group; walking the chain lists its duplicates in ascending k.
+    const int* src_info = c.meta_peer[c.rank] + c.src_info_off;
+    const int* link = c.meta_peer[c.rank] + c.link_off;
+    const int per_cta = (NvS + xcnt - 1) / xcnt;
+    const int lo = xidx * per_cta, hi = min(NvS, lo + per_cta);
+    for (int s0 = lo; s0 < hi && ok; s0 += kExpandSlice) {
+      const int s1 = min(hi, s0 + kExpandSlice);
+      if (threadIdx.x == 0) s_ngroups = 0;
+      __syncthreads();
+      for (int base = s0; base < s1; base += blockDim.x) {  // uniform trip count: the ballots need whole warps
+        const int loff = base + threadIdx.x;
+        int dup_n = 0, first = -1;
+        if (loff < s1) {
+          const int si = src_info[loff];
+          const int l = si >= 0 ? link[loff] : 0;
+          if (a.plan_src_info != nullptr) a.plan_src_info[loff] = si;
+          if (a.plan_link != nullptr) a.plan_link[loff] = l;
+          if (si >= 0 && (l & MOONEP_LINK_PRIMARY) && (l & MOONEP_LINK_HAS_NEXT)) {
+            first = l & MOONEP_NVS_MASK;
+            int cur = first;
+            while (dup_n < MOONEP_MAX_TOPK) {
+              if (cur < 0 || cur >= NvS) {
+                record_status(c, MOONEP_STATUS_BAD_INDEX, MOONEP_K_DISPATCH_EXPAND, 5, cur, loff, 0);
+                dup_n = 0;
+                break;
+              }
+              ++dup_n;
+              const int l2 = link[cur];
+              if (!(l2 & MOONEP_LINK_HAS_NEXT)) break;
+              cur = l2 & MOONEP_NVS_MASK;
+            }
+          }
+        }
+        const unsigned has = __ballot_sync(0xffffffffu, dup_n > 0);
+        if (has == 0) continue;
+        int incl = dup_n;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int v = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane >= o) incl += v;
+        }
+        const int total = __shfl_sync(0xffffffffu, incl, 31);
+        int gbase = 0, dbase = 0, lbase = 0;
+        if (lane == 0) {
+          gbase = atomicAdd(a.dup_counts, __popc(has));
+          dbase = atomicAdd(a.dup_counts + 1, total);
+          lbase = atomicAdd(&s_ngroups, __popc(has));
+        }
+        gbase = __shfl_sync(0xffffffffu, gbase, 0);
+        dbase = __shfl_sync(0xffffffffu, dbase, 0);
+        lbase = __shfl_sync(0xffffffffu, lbase, 0);
+        if (dup_n > 0) {
+          const int before = __popc(has & ((1u << lane) - 1u));
+          const int g = gbase + before;
+          const int ds = dbase + incl - dup_n;
+          if (g < NvS && ds + dup_n <= NvS) {
+            a.dup_groups[3 * g] = loff;
+            a.dup_groups[3 * g + 1] = ds;
+            a.dup_groups[3 * g + 2] = dup_n;
+            int cur = first;
+            for (int q = 0; q < dup_n; ++q) {
+              a.dup_loffs[ds + q] = cur;
+              cur = link[cur] & MOONEP_NVS_MASK;
+            }
+            s_groups[lbase + before] = g;
+          } else {
+            s_groups[lbase + before] = -1;
+          }
+        }
+      }
+      __syncthreads();
+      const int ng = a.build_only ? 0 : s_ngroups;
+      for (int i = warp; i < ng && ok; i += nwarps) {
+        const int g = s_groups[i];
+        if (g < 0) continue;
+        const int primary = a.dup_groups[3 * g], ds = a.dup_groups[3 * g + 1], dn = a.dup_groups[3 * g + 2];
+        const int my_dup = lane < dn ? a.dup_loffs[ds + lane] : -1;
+        if (!wait_row(c, primary, epoch, lane)) {
+          ok = false;
+          break;
+        }
+        expand_group(c, primary, my_dup, dn, a.vec_ok, epoch, lane);
+      }
+      ok = __syncthreads_and(ok ? 1 : 0) != 0;
+    }
+  } else if (ok) {
+    // replayed plan: the groups are in the plan
+    int ngroups = a.dup_counts[0];
+    if (ngroups < 0 || ngroups > NvS) ngroups = 0;
+    for (int g = xidx * nwarps + warp; g < ngroups && ok; g += xcnt * nwarps) {
+      const int primary = a.dup_groups[3 * g], ds = a.dup_groups[3 * g + 1], dn = a.dup_groups[3 * g + 2];
+      if (primary < 0 || primary >= NvS || ds < 0 || dn < 0 || ds + dn > NvS) continue;
+      const int my_dup = lane < dn ? a.dup_loffs[ds + lane] : -1;
+      if (!wait_row(c, primary, epoch, lane)) {
+        ok = false;
+        break;
+      }
+      expand_group(c, primary, my_dup, dn, a.vec_ok, epoch, lane);
+    }
+    ok = __syncthreads_and(ok ? 1 : 0) != 0;
+  }
+  // the kernel ends when every row of the shard is present
+  return block_wait_flags(c, MOONEP_FLAG_SENT, a.epoch_sent, MOONEP_K_DISPATCH_EXPAND) && ok;
+}
+
+// ---- the kernel ------------------------------------------------------------------------------------
+
+__global__ void __launch_bounds__(kDispatchThreads, 1) dispatch_kernel(const MoonepDevCtx c, const DispatchArgs a) {
+  extern __shared__ __align__(128) unsigned char s_dyn[];  // sender ring / planner tables / expert histogram
+  __shared__ __align__(8) unsigned long long s_bar[kBulkWarps * kBulkStages];
+  __shared__ TokenScratch s_tok;
+  const int roles = a.roles;
+  const int warp = threadIdx.x >> 5;
+  if (threadIdx.x < kBulkWarps * kBulkStages) mbar_init(s_bar + threadIdx.x, 1);
+  fence_barrier_init();
+  __syncthreads();
+  bool ok = !poisoned(c);
+
+  // which roles this CTA plays
+  const bool mixed = (roles & MOONEP_ROLE_EXPAND) && (roles & (MOONEP_ROLE_TOKENS | MOONEP_ROLE_SEND));
+  const int s0 = (mixed && (roles & MOONEP_ROLE_TABLES)) ? 1 : 0;
+  bool is_sender = (roles & (MOONEP_ROLE_TOKENS | MOONEP_ROLE_SEND)) != 0;
+  bool is_expander = (roles & MOONEP_ROLE_EXPAND) != 0;
+  int sidx = blockIdx.x, scnt = gridDim.x, xidx = blockIdx.x, xcnt = gridDim.x;
+  if (mixed) {
+    is_sender = (int)blockIdx.x >= s0 && (int)blockIdx.x < s0 + a.n_send;
+    is_expander = !is_sender;
+    sidx = blockIdx.x - s0;
+    scnt = a.n_send;
+    xidx = (int)blockIdx.x < s0 ? blockIdx.x : blockIdx.x - a.n_send;
+    xcnt = gridDim.x - a.n_send;
+  }
+  const int plan_epoch = abs_epoch(c, MOONEP_FLAG_PLAN, a.epoch_plan);
+
+  if ((roles & MOONEP_ROLE_TABLES) && blockIdx.x == 0) {
+    ok = block_wait_flags(c, MOONEP_FLAG_TPE, a.epoch_tpe, MOONEP_K_PLAN_TABLES) && ok;
+    if (ok) {
+      TablesIO io;
+      io.tpe = a.tpe2d != nullptr ? a.tpe2d : (c.meta_peer[c.rank] + c.tpe_off);
+      io.R = c.R, io.E = c.E, io.B = c.B, io.epn = c.epn, io.cap = c.N, io.P = c.token_padding, io.rank = c.rank;
+      io.NvS = c.NvS;
+      io.cu_out = a.cu_seqlens, io.etc_out = a.experts_to_copy, io.zf_out = a.zero_fill, io.rs_out = a.remote_stats;
+      io.tpe_prev = c.tpe_prev, io.alloc_cum = c.alloc_cum, io.expert_off = c.expert_off;
+      const int bad = plan_tables_body(io, carve(a.tables_in_smem ? reinterpret_cast<int*>(s_dyn) : c.tables, c.R, c.E));
+      if (threadIdx.x == 0) {
+        if (a.dup_counts != nullptr) {
+          a.dup_counts[0] = 0;
+          a.dup_counts[1] = 0;
+        }
+        if (bad) record_status(c, MOONEP_STATUS_BAD_INDEX, MOONEP_K_PLAN_TABLES, 1, bad, c.NvS, 0);
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        __threadfence();
+        st_release_gpu(c.counters + MOONEP_CTR_TABLES_READY, plan_epoch);
+      }
+    }
+  }
+
+  if (is_sender && (roles & MOONEP_ROLE_TOKENS)) {
+    ok = wait_local_epoch(c, MOONEP_CTR_TABLES_READY, plan_epoch, MOONEP_K_PLAN_TOKENS) && ok;
+    if (ok)
+      for (int b = sidx; b < a.n_blocks; b += scnt)
+        plan_tokens_block(c, a.topk, a.dst, a.tokens_per_block, b, reinterpret_cast<int*>(s_dyn), s_tok);
+    if (role_tail(c, MOONEP_CTR_PLAN_ARRIVE, scnt) && !poisoned(c)) {
+      if (threadIdx.x == 0) st_release_gpu(c.counters + MOONEP_CTR_PLAN_DONE, plan_epoch);
+      for (int r = threadIdx.x; r < c.R; r += blockDim.x) st_release_sys(flag_ptr(c, r, MOONEP_FLAG_PLAN, c.rank), plan_epoch);
+    }
+  }
+
+  if (is_sender && (roles & MOONEP_ROLE_SEND)) {
+    // a plan made on the device by this dispatch: every sender CTA must have planned its tokens; otherwise
+    // (replayed plan, plan made on the host) whatever cross-rank flag the caller named
+    if (a.fresh && a.wait_family < 0)
+      ok = wait_local_epoch(c, MOONEP_CTR_PLAN_DONE, plan_epoch, MOONEP_K_DISPATCH_SEND) && ok;
+    else
+      ok = block_wait_flags(c, a.wait_family, a.wait_epoch, MOONEP_K_DISPATCH_SEND) && ok;
+    const int epoch = abs_epoch(c, MOONEP_FLAG_SENT, a.epoch_sent);
+    if (ok) {
+      if (a.bulk) {
+        if (warp < kBulkWarps) send_bulk(c, a, epoch, s_dyn, s_bar);
+      } else {
+        send_ldst(c, a, epoch);
+      }
+    }
+    if (role_tail(c, MOONEP_CTR_SEND_ARRIVE, scnt)) {
+      if (threadIdx.x == 0) c.counters[MOONEP_CTR_SEND_WORK] = 0;
+      if (ok && !poisoned(c))
+        for (int r = threadIdx.x; r < c.R; r += blockDim.x) st_release_sys(flag_ptr(c, r, MOONEP_FLAG_SENT, c.rank), epoch);
+    }
+  }
+
+  if (is_expander) expand_role(c, a, xidx, xcnt, ok);
 }
 
 }  // namespace
@@ -483,56 +678,90 @@ using namespace moonep;
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-extern "C" int moonep_dispatch_send(void* ctx, const void* hidden, const float* weights, const int* dst,
-                                    const int* zero_fill, int* dup_groups, int* dup_loffs, int* dup_counts,
-                                    int build_dedup, int wait_family, int wait_epoch, int signal_epoch_sent, int path,
-                                    void* stream) {
+// One launch of the dispatch kernel with the given roles (see the head of this file).
+//   fresh != 0: topk/tpe2d/dst/cu_seqlens/experts_to_copy/zero_fill/remote_stats are the planner's inputs and
+//   outputs and the duplicate map is (re)built; fresh == 0: dst, zero_fill and the duplicate map come from a plan.
+//   n_send: sender CTAs (num_sms of the Buffer when <= 0); n_expand: expander CTAs (as many as fit when <= 0).
+extern "C" int moonep_dispatch(void* ctx, int roles, int fresh, const int* topk, const int* tpe2d, int* dst,
+                               int* cu_seqlens, int* experts_to_copy, int* zero_fill, int* remote_stats,
+                               const void* hidden, const float* weights, int with_weights, int* dup_groups,
+                               int* dup_loffs, int* dup_counts, int* plan_src_info, int* plan_link, int wait_family,
+                               int wait_epoch, int epoch_tpe, int epoch_plan, int epoch_sent, int path, int n_send,
+                               int n_expand, int build_only, void* stream) {
   auto* h = (HostCtx*)ctx;
   const MoonepDevCtx& c = h->dev;
-  SendArgs a;
+  DispatchArgs a;
+  a.topk = topk;
+  a.tpe2d = tpe2d;
+  a.dst = dst;
+  a.cu_seqlens = cu_seqlens;
+  a.experts_to_copy = experts_to_copy;
+  a.zero_fill = zero_fill;
+  a.remote_stats = remote_stats;
+  a.tokens_per_block = imax(1, MOONEP_PLAN_BLOCK / c.K);
+  a.n_blocks = (c.S + a.tokens_per_block - 1) / a.tokens_per_block;
   a.hidden = (const uint16_t*)hidden;
   a.weights = weights;
-  a.dst = dst;
-  a.zero_fill = zero_fill;
   a.dup_groups = dup_groups;
   a.dup_loffs = dup_loffs;
   a.dup_counts = dup_counts;
-  a.build_dedup = build_dedup;
+  a.plan_src_info = plan_src_info;
+  a.plan_link = plan_link;
+  a.fresh = fresh;
+  a.roles = roles;
+  a.build_only = build_only;
+  a.with_weights = with_weights;
   a.wait_family = wait_family;
   a.wait_epoch = wait_epoch;
-  a.signal_epoch = signal_epoch_sent;
-  a.vec_ok = (c.H % 8 == 0) && aligned16(hidden);
+  a.epoch_tpe = epoch_tpe;
+  a.epoch_plan = epoch_plan;
+  a.epoch_sent = epoch_sent;
+  a.vec_ok = (c.H % 8 == 0) && (hidden == nullptr || aligned16(hidden));
   const long long row_bytes = (long long)c.H * 2;
   a.nchunks = (int)((row_bytes + kMaxChunkBytes - 1) / kMaxChunkBytes);
-  long long cb = (row_bytes + a.nchunks - 1) / a.nchunks;
+  const long long cb = (row_bytes + a.nchunks - 1) / a.nchunks;
   a.chunk_bytes = (int)((cb + 15) / 16 * 16);
-  const int grid = imax(1, imin(c.num_sms, h->sm_count));
-  cudaStream_t st = (cudaStream_t)stream;
-  if (build_dedup) {
-    if (int rc = check_cuda(cudaMemsetAsync(dup_counts, 0, 2 * sizeof(int), st), "cudaMemsetAsync(dup_counts)"))
-      return rc;
-  }
-  if (path == MOONEP_PATH_BULK && a.vec_ok) {
-    const size_t smem = (size_t)kBulkWarps * kBulkStages * a.chunk_bytes;
-    if ((int)smem + 4096 <= h->max_smem_optin) {
-      if (int rc = check_cuda(cudaFuncSetAttribute(dispatch_send_bulk_kernel,
-                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
-                              "cudaFuncSetAttribute(dispatch_send_bulk_kernel)"))
-        return rc;
-      dispatch_send_bulk_kernel<<<grid, kSendThreadsBulk, smem, st>>>(c, a);
-      return check_launch("dispatch_send_bulk_kernel");
+
+  // dynamic shared memory: the senders' ring, the table stage's work area, the token stage's histogram
+  size_t smem = 0;
+  const size_t ring_bytes = (size_t)kBulkWarps * kBulkStages * a.chunk_bytes;
+  const size_t limit = (size_t)imax(0, h->max_smem_optin - 20 * 1024);  // static arrays take about 17 KB
+  a.bulk = (path == MOONEP_PATH_BULK && a.vec_ok && ring_bytes <= limit) ? 1 : 0;
+  if ((roles & MOONEP_ROLE_SEND) && a.bulk) smem = ring_bytes;
+  a.tables_in_smem = 0;
+  if (roles & MOONEP_ROLE_TABLES) {
+    const size_t tb = (size_t)table_words(c.R, c.E) * sizeof(int);
+    if (tb <= limit) {
+      a.tables_in_smem = 1;
+      if (tb > smem) smem = tb;
     }
   }
-  dispatch_send_ldst_kernel<<<grid, kSendThreadsLdst, 0, st>>>(c, a);
-  return check_launch("dispatch_send_ldst_kernel");
-}
+  if (roles & MOONEP_ROLE_TOKENS) {
+    const size_t hb = (size_t)c.E * sizeof(int);
+    if (hb > limit) {
+      set_error("moonep_dispatch: E too large for the shared-memory histogram of the token stage");
+      return 1;
+    }
+    if (hb > smem) smem = hb;
+  }
+  if (int rc = check_cuda(cudaFuncSetAttribute(dispatch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               (int)imax((int)smem, 1024)),
+                          "cudaFuncSetAttribute(dispatch_kernel)"))
+    return rc;
 
-extern "C" int moonep_dispatch_expand(void* ctx, const int* zero_fill, int with_weights, const int* dup_groups,
-                                      const int* dup_loffs, const int* dup_counts, int wait_epoch_sent, void* stream) {
-  auto* h = (HostCtx*)ctx;
-  const MoonepDevCtx& c = h->dev;
-  const int grid = imax(1, imin(c.local_sms, h->sm_count));
-  dispatch_expand_kernel<<<grid, 512, 0, (cudaStream_t)stream>>>(c, zero_fill, with_weights, dup_groups, dup_loffs,
-                                                                dup_counts, wait_epoch_sent, (c.H % 8 == 0) ? 1 : 0);
-  return check_launch("dispatch_expand_kernel");
+  const bool senders = (roles & (MOONEP_ROLE_TOKENS | MOONEP_ROLE_SEND)) != 0;
+  const bool expanders = (roles & MOONEP_ROLE_EXPAND) != 0;
+  int grid = 1;
+  a.n_send = 0;
+  if (senders) {
+    a.n_send = imax(1, imin(n_send > 0 ? n_send : c.num_sms, h->sm_count - (expanders ? 2 : 0)));
+    grid = a.n_send;
+  }
+  if (expanders) {
+    const int room = imax(1, imin(c.local_sms, h->sm_count) - a.n_send);
+    const int nx = n_expand > 0 ? imin(n_expand, room) : room;
+    grid = a.n_send + imax(1, nx);
+  }
+  dispatch_kernel<<<grid, kDispatchThreads, smem, (cudaStream_t)stream>>>(c, a);
+  return check_launch("dispatch_kernel");
 }

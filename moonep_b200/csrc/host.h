@@ -3,6 +3,7 @@
 
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <string>
 
 #include "moonep.h"
@@ -20,7 +21,7 @@ void set_error(const std::string& s);
 int check_cuda(cudaError_t e, const char* what);
 
 // Every kernel launch of the library goes through check_launch, which also counts it.
-extern long long g_launch_count;
+extern std::atomic<long long> g_launch_count;
 inline int check_launch(const char* what) {
   ++g_launch_count;
   return check_cuda(cudaGetLastError(), what);

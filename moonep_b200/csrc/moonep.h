@@ -60,6 +60,22 @@
 #define MOONEP_K_GRAD_CLEAR 11
 #define MOONEP_K_WAIT 12
 #define MOONEP_NUM_KERNEL_IDS 16
+// ids 13-15 are the GEMM kernels' (grouped_gemm, grouped_wgrad, grouped_gemm_pair); the ones below exceed
+// MOONEP_NUM_KERNEL_IDS because they own no arrival counter named after them
+#define MOONEP_K_COMBINE_PUSH 16
+#define MOONEP_K_COMBINE_SUM 17
+// counters[]: words 0..15 are arrival counters of kernel tails (indexed by kernel id), then:
+#define MOONEP_CTR_SEND_WORK 16      // token hand-out of the send role
+#define MOONEP_CTR_PULL_WORK 17      // token hand-out of combine_pull
+#define MOONEP_CTR_TABLES_READY 18   // PLAN epoch of the last finished table stage (local release/acquire)
+#define MOONEP_CTR_PLAN_DONE 19      // PLAN epoch of the last finished token stage
+#define MOONEP_CTR_PLAN_ARRIVE 20    // CTAs that finished the token stage
+#define MOONEP_CTR_SEND_ARRIVE 21    // CTAs that finished the send role
+#define MOONEP_CTR_DISPATCH_ARRIVE 22  // CTAs of the dispatch kernel that reached its end
+#define MOONEP_CTR_PUSH_WORK 23      // row hand-out of the combine push role
+#define MOONEP_CTR_SUM_WORK 24       // token hand-out of the combine sum role
+#define MOONEP_CTR_COMBINE_ARRIVE 25 // CTAs of the push-combine kernel that reached its end
+#define MOONEP_CTR_PREFETCH_ARRIVE 26  // CTAs of the prefetch kernel that reached its end
 // stats[MOONEP_STAT_WAIT_MAX_NS + family]: longest time CTA 0 of any kernel spun on a flag of that family (ns);
 // stats[MOONEP_STAT_WAIT_COUNT + family]: number of such waits that did not find the flag already set.
 #define MOONEP_STAT_WAIT_MAX_NS 0
@@ -70,6 +86,18 @@
 // link word of a landed row (pushed by the source rank during planning).
 #define MOONEP_LINK_PRIMARY (1 << 30)
 #define MOONEP_LINK_HAS_NEXT (1 << 29)
+// bits 24..28 of a primary row's link word: its position among the primaries of its token (ascending k)
+#define MOONEP_LINK_ORD_SHIFT 24
+#define MOONEP_LINK_ORD_MASK 31
+
+// Roles of the dispatch kernel (bit mask); all of them in one launch is the fused dispatch.
+#define MOONEP_ROLE_TABLES 1   // table stage of the planner (one CTA)
+#define MOONEP_ROLE_TOKENS 2   // token stage of the planner
+#define MOONEP_ROLE_SEND 4     // push rows, gate weights and row flags
+#define MOONEP_ROLE_EXPAND 8   // zero fill, duplicate map, duplicate expansion as rows arrive
+// Roles of the push-combine kernel.
+#define MOONEP_ROLE_PUSH 1     // expert side: fold duplicates, push rows to the tokens' home ranks
+#define MOONEP_ROLE_SUM 2      // home side: sum the rows of a token as they arrive
 
 // Routing entries per planner block (whole tokens, at most this many entries).
 #define MOONEP_PLAN_BLOCK 512
@@ -87,9 +115,13 @@ struct MoonepDevCtx {
   int weights_off, tpe_off, plan_off, src_info_off, sync_off, r32;
   int link_off;   // [NvS] per landed row: LINK_PRIMARY | LINK_HAS_NEXT | next row of the same (source, token)
   int local_sms;  // CTAs used by kernels that only touch local memory
-  int debug;
-  int pad0;
+  int rowflag_off;  // [NvS] per row: SENT epoch of the dispatch that last put data into it
+  int kp;           // staging rows per token in the combine staging chunk: min(K, R)
   unsigned long long timeout_ns;
+  // Combine staging (push path): chunk of rank r holds [S*kp, H] bf16 rows, then arrival flags, then gate weights.
+  unsigned char* const* stage_peer;  // [R] or null when the Buffer has no staging memory
+  long long stage_flag_off;          // byte offset of the [S*kp] int32 COMB epochs of the staged rows
+  long long stage_w_off;             // byte offset of the [S*K] fp32 gate weights on their way home
   // Peer tables: base address of every rank's chunk as seen from this GPU.
   uint16_t* const* hidden_peer;  // [R] -> bf16 [nvs_padded, H]
   int* const* meta_peer;         // [R] -> int32 [meta_stride]
@@ -101,9 +133,6 @@ struct MoonepDevCtx {
   int* tpe_prev;      // [E]      tokens of expert e on source ranks < rank
   int* tables;        // planner work area, see planner.cu
   int* block_hist;    // [planner blocks, E] per-block expert histograms of the local routing
-  int* primary_packed;  // [R*S]
-  int* kmask;           // [R*S]
-  int* kidx_to_loff;    // [R*S*K]
   long long* stats;     // [16] flag-wait statistics, see MOONEP_STAT_*
 };
 
@@ -122,7 +151,7 @@ long long moonep_planner_table_words(int R, int E, int B);
 // ctx: params is an int64 array in the order of MoonepDevCtx's integer fields (see runtime.cu),
 // followed by the scratch pointers.  Returns an opaque handle or null.
 void* moonep_ctx_create(const long long* params, int nparams, const unsigned long long* hidden_peers,
-                        const unsigned long long* meta_peers);
+                        const unsigned long long* meta_peers, const unsigned long long* stage_peers);
 void moonep_ctx_destroy(void* ctx);
 int moonep_ctx_set_timeout_ms(void* ctx, long long ms);
 
@@ -141,16 +170,19 @@ int moonep_epoch_bias(void* ctx, const int* values, int mode, void* stream);
 // Planner.  tpe is [E] (pushed to all peers) or [R, E] (tpe_is_2d, used as is).
 int moonep_plan_publish(void* ctx, const int* topk, const int* tpe, int tpe_is_2d, int epoch_tpe, void* stream);
 int moonep_plan_compute(void* ctx, const int* topk, const int* tpe2d, int* dst, int* cu_seqlens,
-                        int* experts_to_copy, int* zero_fill, int* remote_stats, int wait_epoch_tpe,
+                        int* experts_to_copy, int* zero_fill, int* remote_stats, int* dup_counts, int wait_epoch_tpe,
                         int signal_epoch_plan, void* stream);
 
-// Dispatch.
-int moonep_dispatch_send(void* ctx, const void* hidden, const float* weights, const int* dst,
-                         const int* zero_fill, int* dup_groups, int* dup_loffs, int* dup_counts,
-                         int build_dedup, int wait_family, int wait_epoch, int signal_epoch_sent, int path,
-                         void* stream);
-int moonep_dispatch_expand(void* ctx, const int* zero_fill, int with_weights, const int* dup_groups,
-                           const int* dup_loffs, const int* dup_counts, int wait_epoch_sent, void* stream);
+// Dispatch: one launch of the dispatch kernel with the roles in `roles` (MOONEP_ROLE_*; see dispatch.cu).  With all four
+// roles it is the fused fresh dispatch, with SEND | EXPAND the replay of a plan; single roles give the stages of the
+// launch-level API.  fresh != 0: the planner arguments (topk .. remote_stats) are used and the duplicate map is built;
+// plan_src_info / plan_link ([NvS] each, optional) receive the plan's copy of src_info and the link words.
+// build_only: the EXPAND role only rebuilds the duplicate map.
+int moonep_dispatch(void* ctx, int roles, int fresh, const int* topk, const int* tpe2d, int* dst, int* cu_seqlens,
+                    int* experts_to_copy, int* zero_fill, int* remote_stats, const void* hidden, const float* weights,
+                    int with_weights, int* dup_groups, int* dup_loffs, int* dup_counts, int* plan_src_info,
+                    int* plan_link, int wait_family, int wait_epoch, int epoch_tpe, int epoch_plan, int epoch_sent,
+                    int path, int n_send, int n_expand, int build_only, void* stream);
 
 // Combine.
 int moonep_combine_prologue(void* ctx, const int* dup_groups, const int* dup_loffs, const int* dup_counts,
@@ -158,6 +190,13 @@ int moonep_combine_prologue(void* ctx, const int* dup_groups, const int* dup_lof
                             int signal_epoch_comb, void* stream);
 int moonep_combine_pull(void* ctx, const int* dst, void* out_hidden, float* out_weights, int wait_epoch_comb,
                         int path, void* stream);
+// Push combine (combine_push.cu): roles MOONEP_ROLE_PUSH | MOONEP_ROLE_SUM.  Needs the Buffer's staging memory
+// (stage_peers of moonep_ctx_create, laid out by moonep_stage_layout) and the plan's copies of src_info and link words.
+long long moonep_stage_layout(int S, int K, int H, int kp, long long* flag_off, long long* w_off);
+int moonep_combine_push(void* ctx, int roles, const int* src_info, const int* link, const int* dst, const void* in_rows,
+                        const float* in_w, void* out_hidden, float* out_weights, int wait_family, int wait_epoch,
+                        int epoch_comb, const int* ready, int ready_expect, const int* dup_groups, const int* dup_loffs,
+                        const int* dup_counts, int n_push, int n_sum, void* stream);
 
 // Expert weights: src[i] is [nexperts, H, Hp] bf16 (peer mapped), dst[i] is [nslots, H, Hp] bf16 (local).
 int moonep_prefetch(void* ctx, void* const* src3, void* const* dst3, int n_tensors, const int* experts_to_copy_row,

@@ -39,6 +39,9 @@ extern "C" {
 // zero_fill:        [E+B,2] out, (first pad row, pad rows) per group on `rank`.
 // remote_stats:     [2]     out, (#remote experts received by `rank`, #ranks copying its experts).
 // S, K, token_padding, NvS as in the Buffer that will use the tables (capacity per rank = S*K).
+// NvS is the number of rows the rank's shard can hold: when the padded groups of `rank` need more than that,
+// the kernel stores -1 in remote_stats[0] and the other outputs must not be used (the Buffer's own planner
+// records an index error in that case).
 // Returns 0 on success; on failure moonep_last_error() explains.
 int moonep_plan_tables_noalloc(const int* tpe, int R, int E, int B, int S, int K, int token_padding, int rank, int NvS,
                                int* cu_seqlens, int* experts_to_copy, int* zero_fill, int* remote_stats, void* stream);

@@ -16,6 +16,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <atomic>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -26,7 +27,7 @@
 namespace moonep {
 
 static thread_local std::string g_last_error;
-long long g_launch_count = 0;
+std::atomic<long long> g_launch_count{0};
 
 void set_error(const std::string& s) { g_last_error = s; }
 
@@ -43,20 +44,20 @@ using namespace moonep;
 extern "C" int moonep_version(void) { return MOONEP_VERSION; }
 extern "C" const char* moonep_last_error(void) { return g_last_error.c_str(); }
 extern "C" int moonep_sizeof_devctx(void) { return (int)sizeof(MoonepDevCtx); }
-extern "C" long long moonep_launch_count(void) { return g_launch_count; }
+extern "C" long long moonep_launch_count(void) { return g_launch_count.load(); }
 
 // ---- context ----------------------------------------------------------------------------------
 
 enum ParamIndex {
   P_RANK = 0, P_R, P_E, P_S, P_K, P_H, P_B, P_N, P_NVS, P_EPN, P_TOKEN_PADDING, P_NUM_SMS, P_NVS_PADDED,
   P_META_STRIDE, P_WEIGHTS_OFF, P_TPE_OFF, P_PLAN_OFF, P_SRC_INFO_OFF, P_SYNC_OFF, P_R32, P_LINK_OFF, P_LOCAL_SMS,
-  P_DEBUG, P_TIMEOUT_MS,
+  P_ROWFLAG_OFF, P_KP, P_TIMEOUT_MS, P_STAGE_FLAG_OFF, P_STAGE_W_OFF,
   P_PTR_STATUS, P_PTR_COUNTERS, P_PTR_ALLOC_CUM, P_PTR_EXPERT_OFF, P_PTR_TPE_PREV, P_PTR_TABLES,
-  P_PTR_PRIMARY_PACKED, P_PTR_KMASK, P_PTR_KIDX_TO_LOFF, P_PTR_STATS, P_PTR_BLOCK_HIST, P_COUNT
+  P_PTR_STATS, P_PTR_BLOCK_HIST, P_COUNT
 };
 
 extern "C" void* moonep_ctx_create(const long long* p, int nparams, const unsigned long long* hidden_peers,
-                                   const unsigned long long* meta_peers) {
+                                   const unsigned long long* meta_peers, const unsigned long long* stage_peers) {
   if (nparams != P_COUNT) {
     set_error("moonep_ctx_create: expected " + std::to_string((int)P_COUNT) + " params, got " + std::to_string(nparams));
     return nullptr;
@@ -71,13 +72,13 @@ extern "C" void* moonep_ctx_create(const long long* p, int nparams, const unsign
   d.weights_off = (int)p[P_WEIGHTS_OFF]; d.tpe_off = (int)p[P_TPE_OFF]; d.plan_off = (int)p[P_PLAN_OFF];
   d.src_info_off = (int)p[P_SRC_INFO_OFF]; d.sync_off = (int)p[P_SYNC_OFF]; d.r32 = (int)p[P_R32];
   d.link_off = (int)p[P_LINK_OFF]; d.local_sms = (int)p[P_LOCAL_SMS];
-  d.debug = (int)p[P_DEBUG];
+  d.rowflag_off = (int)p[P_ROWFLAG_OFF]; d.kp = (int)p[P_KP];
+  d.stage_flag_off = p[P_STAGE_FLAG_OFF]; d.stage_w_off = p[P_STAGE_W_OFF];
   d.timeout_ns = (unsigned long long)p[P_TIMEOUT_MS] * 1000000ull;
   d.status = (int*)p[P_PTR_STATUS]; d.counters = (int*)p[P_PTR_COUNTERS];
   d.alloc_cum = (int*)p[P_PTR_ALLOC_CUM]; d.expert_off = (int*)p[P_PTR_EXPERT_OFF];
   d.tpe_prev = (int*)p[P_PTR_TPE_PREV]; d.tables = (int*)p[P_PTR_TABLES];
-  d.primary_packed = (int*)p[P_PTR_PRIMARY_PACKED]; d.kmask = (int*)p[P_PTR_KMASK];
-  d.kidx_to_loff = (int*)p[P_PTR_KIDX_TO_LOFF]; d.stats = (long long*)p[P_PTR_STATS];
+  d.stats = (long long*)p[P_PTR_STATS];
   d.block_hist = (int*)p[P_PTR_BLOCK_HIST];
   if (d.R < 1 || d.R > MOONEP_MAX_RANKS || d.K < 1 || d.K > MOONEP_MAX_TOPK) {
     set_error("moonep_ctx_create: R or K out of range");
@@ -86,7 +87,7 @@ extern "C" void* moonep_ctx_create(const long long* p, int nparams, const unsign
   }
   const size_t tbytes = sizeof(void*) * (size_t)d.R;
   void* tab = nullptr;
-  if (check_cuda(cudaMalloc(&tab, 2 * tbytes), "cudaMalloc(peer tables)")) {
+  if (check_cuda(cudaMalloc(&tab, 3 * tbytes), "cudaMalloc(peer tables)")) {
     delete h;
     return nullptr;
   }
@@ -99,6 +100,15 @@ extern "C" void* moonep_ctx_create(const long long* p, int nparams, const unsign
   }
   d.hidden_peer = (uint16_t* const*)tab;
   d.meta_peer = (int* const*)((char*)tab + tbytes);
+  d.stage_peer = nullptr;
+  if (stage_peers != nullptr) {
+    if (check_cuda(cudaMemcpy((char*)tab + 2 * tbytes, stage_peers, tbytes, cudaMemcpyHostToDevice), "copy stage peers")) {
+      cudaFree(tab);
+      delete h;
+      return nullptr;
+    }
+    d.stage_peer = (unsigned char* const*)((char*)tab + 2 * tbytes);
+  }
   cudaDeviceGetAttribute(&h->sm_count, cudaDevAttrMultiProcessorCount, 0);
   int devid = 0;
   cudaGetDevice(&devid);

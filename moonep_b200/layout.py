@@ -13,7 +13,10 @@ Every rank owns one chunk of each buffer; chunk ``r`` of the *hidden* buffer is
     BARRIER_OFF   [3]        legacy barrier words
     SRC_INFO_OFF  [NvS]      src_rank*NvS + slot of the row that lands here, or -1
     SYNC_OFF      [F*R32]    epoch flags, one per (family, source rank)
-    LINK_OFF      [NvS]      per landed row: primary bit, and the next row of the same (source, token)
+    LINK_OFF      [NvS]      per landed row: primary bit, position among the token's primaries, and the next
+                             row of the same (source, token)
+    ROWFLAG_OFF   [NvS]      per row: epoch of the dispatch that last put data into it (rows are flagged one by
+                             one as they land, so consumers need not wait for the whole all-to-all)
 
 All chunks of a buffer are mapped back to back in one virtual address range, so
 chunk ``r`` starts ``r * chunk_bytes`` after the base on every rank.  The chunk
@@ -22,7 +25,7 @@ VMM allocation granularity (2 MiB) for real peer-mapped memory.
 
 Parity: reference ``moonep_td/api.py:50-149`` (``_create_context``) and
 ``moonep_td/buffer.py:22-37`` (padding helpers).  Offsets up to ``SRC_INFO_OFF``
-are the reference's; ``SYNC_OFF`` and ``LINK_OFF`` are additions placed past the reference's logical end.
+are the reference's; ``SYNC_OFF``, ``LINK_OFF`` and ``ROWFLAG_OFF`` are additions placed past the reference's logical end.
 """
 
 from __future__ import annotations
@@ -92,7 +95,8 @@ def compute_layout(S, H, K, E, R, *, B=None, num_sms=None, token_padding=128, gr
     R32 = align_up(R, 32)
     SYNC_OFF = align_up(SRC_INFO_OFF + NvS, 32)
     LINK_OFF = SYNC_OFF + NUM_FLAG_FAMILIES * R32
-    meta_chunk_logical = LINK_OFF + NvS
+    ROWFLAG_OFF = LINK_OFF + NvS
+    meta_chunk_logical = ROWFLAG_OFF + NvS
     meta_chunk_padded = align_up(meta_chunk_logical * 4, gran_bytes) // 4
 
     return {
@@ -124,6 +128,8 @@ def compute_layout(S, H, K, E, R, *, B=None, num_sms=None, token_padding=128, gr
         "SRC_INFO_OFF": SRC_INFO_OFF,
         "SYNC_OFF": SYNC_OFF,
         "LINK_OFF": LINK_OFF,
+        "ROWFLAG_OFF": ROWFLAG_OFF,
+        "Kp": min(K, R),
         "R32": R32,
     }
 

@@ -101,15 +101,16 @@ _SIGNATURES = {
     "moonep_sizeof_devctx": (_i, []),
     "moonep_launch_count": (_ll, []),
     "moonep_planner_table_words": (_ll, [_i, _i, _i]),
-    "moonep_ctx_create": (_vp, [ctypes.POINTER(_ll), _i, ctypes.POINTER(_ull), ctypes.POINTER(_ull)]),
+    "moonep_ctx_create": (_vp, [ctypes.POINTER(_ll), _i, ctypes.POINTER(_ull), ctypes.POINTER(_ull), ctypes.POINTER(_ull)]),
     "moonep_ctx_destroy": (None, [_vp]),
     "moonep_ctx_set_timeout_ms": (_i, [_vp, _ll]),
     "moonep_signal_wait": (_i, [_vp, _i, _i, _i, _i, _vp]),
     "moonep_epoch_bias": (_i, [_vp, _vp, _i, _vp]),
     "moonep_plan_publish": (_i, [_vp, _vp, _vp, _i, _i, _vp]),
-    "moonep_plan_compute": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp]),
-    "moonep_dispatch_send": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
-    "moonep_dispatch_expand": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _i, _vp]),
+    "moonep_plan_compute": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp]),
+    "moonep_dispatch": (_i, [_vp, _i, _i] + [_vp] * 9 + [_i] + [_vp] * 5 + [_i] * 9 + [_vp]),
+    "moonep_stage_layout": (_ll, [_i, _i, _i, _i, ctypes.POINTER(_ll), ctypes.POINTER(_ll)]),
+    "moonep_combine_push": (_i, [_vp, _i] + [_vp] * 7 + [_i, _i, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _vp]),
     "moonep_combine_prologue": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "moonep_combine_pull": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp]),
     "moonep_prefetch": (_i, [_vp, ctypes.POINTER(_vp), ctypes.POINTER(_vp), _i, _vp, _ll, _i, _i, _i, _vp]),

@@ -41,8 +41,10 @@ _PATHS = {"ldst": 0, "bulk": 1}
 _KERNEL_NAMES = {
     1: "signal", 2: "plan_publish", 3: "plan_tables", 4: "plan_tokens", 5: "dispatch_send", 6: "dispatch_expand",
     7: "combine_prologue", 8: "combine_pull", 9: "prefetch", 10: "grad_accum", 11: "grad_clear", 12: "wait",
-    13: "grouped_gemm", 14: "grouped_wgrad",
+    13: "grouped_gemm", 14: "grouped_wgrad", 15: "grouped_gemm_pair", 16: "combine_push", 17: "combine_sum",
 }  # fmt: skip
+ROLE_TABLES, ROLE_TOKENS, ROLE_SEND, ROLE_EXPAND = 1, 2, 4, 8
+ROLE_PUSH, ROLE_SUM = 1, 2
 _FAMILY_NAMES = {0: "READY", 1: "TPE", 2: "PLAN", 3: "SENT", 4: "COMB", 5: "GRAD_READY", 6: "GRAD_DONE"}
 
 
@@ -68,7 +70,8 @@ class CudaBackend:
         self.bias = [0] * NUM_FLAG_FAMILIES  # host mirror of the device-side epoch bias (in stream order)
         self._capture = None
         self.path = _PATHS[config.copy_path()]
-        self.send_path = _PATHS[config.copy_path("send")]
+        # with a single rank the send is a local copy, which all warps of a CTA share on the register path
+        self.send_path = _PATHS[config.copy_path("send")] if R > 1 else _PATHS["ldst"]
         self.pull_path = _PATHS[config.copy_path("pull")]
         self.grad_path = _PATHS[config.copy_path("grad")]
         self._profile = None
@@ -88,24 +91,35 @@ class CudaBackend:
         tokens_per_block = max(1, PLAN_BLOCK // K)
         self.block_hist = i32(-(-S // tokens_per_block) * E)
         sm_count = torch.cuda.get_device_properties(dev).multi_processor_count
+        self.sm_count = sm_count
         # the planner's alloc[d*E+e]; only current when its tables did not fit shared memory (use global_alloc())
         c["alloc"] = self.tables[2 * E : 2 * E + R * E]
+        # Emulated ranks share one GPU and one stream: a kernel of one rank must never wait for a kernel of another
+        # rank that is launched later, so they run the dispatch and combine kernels one role per phase.
+        self.phased = bool(getattr(world, "emulated", False)) and world.size > 1
+        self.combine_mode = config.combine_mode()
+        self.n_expand = 0  # CTAs of the dispatch kernel's destination-side role; 0 = every SM the senders leave free
 
         hid_base = c["hidden_buf"].data_ptr()
         meta_base = c["meta_buf"].data_ptr()
         hp = (ctypes.c_ulonglong * R)(*[hid_base + r * c["NvS_padded"] * c["H"] * 2 for r in range(R)])
         mp = (ctypes.c_ulonglong * R)(*[meta_base + r * c["meta_chunk_padded"] * 4 for r in range(R)])
+        sp, flag_off, w_off = None, 0, 0
+        if c.get("stage_buf") is not None:
+            stage_base = c["stage_buf"].data_ptr()
+            sp = (ctypes.c_ulonglong * R)(*[stage_base + r * c["stage_chunk_bytes"] for r in range(R)])
+            flag_off, w_off = c["stage_flag_off"], c["stage_w_off"]
         params = [
             c["rank"], R, E, S, K, c["H"], B, c["N"], c["NvS"], c["epn"], c["token_padding"], c["num_sms"],
             c["NvS_padded"], c["meta_chunk_padded"], c["WEIGHTS_OFF"], c["TPE_OFF"], c["PLAN_OFF"], c["SRC_INFO_OFF"],
-            c["SYNC_OFF"], c["R32"], c["LINK_OFF"], config.local_sms(sm_count), int(config.debug()), config.timeout_ms(),
+            c["SYNC_OFF"], c["R32"], c["LINK_OFF"], config.local_sms(sm_count), c["ROWFLAG_OFF"], c["Kp"],
+            config.timeout_ms(), flag_off, w_off,
             self.status.data_ptr(), self.counters.data_ptr(), self.alloc_cum.data_ptr(), self.expert_off.data_ptr(),
-            self.tpe_prev.data_ptr(), self.tables.data_ptr(), c["primary_packed"].data_ptr(), c["kmask"].data_ptr(),
-            c["kidx_to_loff"].data_ptr(), self.stats_buf.data_ptr(), self.block_hist.data_ptr(),
+            self.tpe_prev.data_ptr(), self.tables.data_ptr(), self.stats_buf.data_ptr(), self.block_hist.data_ptr(),
         ]  # fmt: skip
         arr = (ctypes.c_longlong * len(params))(*params)
         with torch.cuda.device(dev):
-            self.handle = self.lib.moonep_ctx_create(arr, len(params), hp, mp)
+            self.handle = self.lib.moonep_ctx_create(arr, len(params), hp, mp, sp)
         if not self.handle:
             raise _lib.NativeError("moonep_ctx_create failed: " + self.lib.moonep_last_error().decode())
 
@@ -276,7 +290,7 @@ class CudaBackend:
         tpe2d = _ptr(tpe) if tpe.dim() == 2 else None
         self._call(
             "moonep_plan_compute", _ptr(topk_flat), tpe2d, _ptr(plan.dst), _ptr(cu_seqlens),
-            _ptr(plan.experts_to_copy), _ptr(plan.zero_fill_ranges), _ptr(plan.remote_stats),
+            _ptr(plan.experts_to_copy), _ptr(plan.zero_fill_ranges), _ptr(plan.remote_stats), _ptr(plan.dup_counts),
             self._cur(FLAG_TPE), self._next(FLAG_PLAN), _stream(),
         )  # fmt: skip
         self.world.step()
@@ -306,6 +320,7 @@ class CudaBackend:
         put(plan.experts_to_copy, tabs["experts_to_copy"])
         put(plan.remote_stats, tabs["remote_stats"][rank])
         put(plan.zero_fill_ranges, tabs["zero_fill"][rank])
+        plan.dup_counts.zero_()
         dest = dst_pos // NvS
         loff = dst_pos - dest * NvS
         idx = torch.from_numpy(dest * ms + c["SRC_INFO_OFF"] + loff).to(dev)
@@ -316,30 +331,133 @@ class CudaBackend:
         self.world.step()
 
     # -- dispatch ------------------------------------------------------------------------
+    def _dispatch_launch(self, roles, fresh, plan, *, topk=None, tpe=None, cu_seqlens=None, hidden=None, weights=None,
+                         with_weights=False, wait_family=-1, wait_epoch=0, epoch_sent=0, n_send=0, build_only=False,
+                         tag=None):  # fmt: skip
+        """One launch of the dispatch kernel with the given roles (``csrc/dispatch.cu``)."""
+        tpe2d = _ptr(tpe) if (tpe is not None and tpe.dim() == 2) else None
+        self._call(
+            "moonep_dispatch", int(roles), int(bool(fresh)), _ptr(topk), tpe2d, _ptr(plan.dst), _ptr(cu_seqlens),
+            _ptr(plan.experts_to_copy), _ptr(plan.zero_fill_ranges), _ptr(plan.remote_stats), _ptr(hidden),
+            _ptr(weights), int(bool(with_weights)), _ptr(plan.dup_groups), _ptr(plan.dup_loffs), _ptr(plan.dup_counts),
+            _ptr(plan.src_info), _ptr(plan.link), int(wait_family), int(wait_epoch), self._cur(FLAG_TPE),
+            self._cur(FLAG_PLAN), int(epoch_sent), self.send_path, int(n_send), int(self.n_expand), int(bool(build_only)),
+            _stream(),
+            tag=tag,
+        )  # fmt: skip
+
+    def dispatch_all(self, hidden_sh, route_weights_sk, plan, planning_args, inter_rank_sync):
+        """The whole dispatch.  Fresh plan: ``plan_publish`` plus one fused launch (planner tables, token planning, row
+        push, and on the destination side zero fill, duplicate map and duplicate expansion as rows arrive).  Replayed
+        plan: an optional READY round plus one launch (push and expansion).  Emulated ranks run one role per phase."""
+        with_w = route_weights_sk is not None
+        self._sent_weights = with_w
+        if planning_args is not None:
+            topk_flat, tpe, cu_seqlens = planning_args
+            self.plan_publish(tpe, topk_flat)
+            on_dev = config.planner_on_gpu()
+            if not on_dev:
+                self._plan_compute_host(topk_flat, tpe, cu_seqlens, plan)
+                wf, we = FLAG_PLAN, self._cur(FLAG_PLAN)
+            else:
+                self._next(FLAG_PLAN)
+                wf, we = -1, 0
+            sent = self._next(FLAG_SENT)
+            kw = dict(topk=topk_flat, tpe=tpe, cu_seqlens=cu_seqlens, hidden=hidden_sh, weights=route_weights_sk,
+                      with_weights=with_w, wait_family=wf, wait_epoch=we, epoch_sent=sent)  # fmt: skip
+            plan_roles = (ROLE_TABLES | ROLE_TOKENS) if on_dev else 0
+            if not self.phased:
+                self._dispatch_launch(plan_roles | ROLE_SEND | ROLE_EXPAND, True, plan, tag="dispatch_fused", **kw)
+            else:
+                self._dispatch_launch(plan_roles | ROLE_SEND, True, plan, tag="dispatch_plan_send", **kw)
+                self.world.step()
+                self._dispatch_launch(ROLE_EXPAND, True, plan, tag="dispatch_expand", **kw)
+            self._quiesced = True
+        else:
+            wf, we = -1, 0
+            if inter_rank_sync:
+                self.signal(FLAG_READY)
+                wf, we = FLAG_READY, self._cur(FLAG_READY)
+                self._quiesced = True
+            sent = self._next(FLAG_SENT)
+            kw = dict(hidden=hidden_sh, weights=route_weights_sk, with_weights=with_w, wait_family=wf, wait_epoch=we,
+                      epoch_sent=sent)  # fmt: skip
+            if not self.phased:
+                self._dispatch_launch(ROLE_SEND | ROLE_EXPAND, False, plan, tag="dispatch_replay", **kw)
+            else:
+                self._dispatch_launch(ROLE_SEND, False, plan, tag="dispatch_send", **kw)
+                self.world.step()
+                self._dispatch_launch(ROLE_EXPAND, False, plan, tag="dispatch_expand", **kw)
+        self.world.step()
+
+    def copy_out(self, out_hidden, out_weights):
+        out_hidden.copy_(self.ctx["hidden_buf_local"])
+        if out_weights is not None:
+            out_weights.copy_(self.ctx["weights_buf_local"].view(torch.float32))
+
+    # launch-level stages (``ops/launch.py``)
     def dispatch_send(self, hidden_sh, route_weights_sk, plan, build_dedup_map, wait=None):
         wf = -1 if wait is None else int(wait)
         we = 0 if wait is None else self._cur(wf)
-        self._call(
-            "moonep_dispatch_send", _ptr(hidden_sh), _ptr(route_weights_sk), _ptr(plan.dst),
-            _ptr(plan.zero_fill_ranges), _ptr(plan.dup_groups), _ptr(plan.dup_loffs), _ptr(plan.dup_counts),
-            int(bool(build_dedup_map)), wf, we, self._next(FLAG_SENT), self.send_path, _stream(),
-        )  # fmt: skip
+        self._dispatch_launch(ROLE_SEND, bool(build_dedup_map), plan, hidden=hidden_sh, weights=route_weights_sk,
+                              with_weights=route_weights_sk is not None, wait_family=wf, wait_epoch=we,
+                              epoch_sent=self._next(FLAG_SENT), tag="dispatch_send")  # fmt: skip
         if wait is not None:
             self._quiesced = True
         self._sent_weights = route_weights_sk is not None
         self.world.step()
+        if build_dedup_map:
+            self.build_dedup(plan)
+
+    def build_dedup(self, plan):
+        """Rebuild the plan's duplicate map (and its copies of src_info and link words) from what the last planning
+        published into this rank's meta chunk."""
+        self.wait(FLAG_PLAN)
+        plan.dup_counts.zero_()
+        self._dispatch_launch(ROLE_EXPAND, True, plan, wait_family=FLAG_PLAN, wait_epoch=self._cur(FLAG_PLAN),
+                              epoch_sent=self._cur(FLAG_SENT), build_only=True, tag="dedup_builder")  # fmt: skip
 
     def dispatch_expand(self, plan, out_hidden, out_weights, zero_copy):
-        self._call(
-            "moonep_dispatch_expand", _ptr(plan.zero_fill_ranges), int(self._sent_weights), _ptr(plan.dup_groups),
-            _ptr(plan.dup_loffs), _ptr(plan.dup_counts), self._cur(FLAG_SENT), _stream(),
-        )  # fmt: skip
+        self._dispatch_launch(ROLE_EXPAND, False, plan, with_weights=getattr(self, "_sent_weights", False),
+                              epoch_sent=self._cur(FLAG_SENT), tag="dispatch_expand")  # fmt: skip
         if not zero_copy:
-            out_hidden.copy_(self.ctx["hidden_buf_local"])
-            if out_weights is not None:
-                out_weights.copy_(self.ctx["weights_buf_local"].view(torch.float32))
+            self.copy_out(out_hidden, out_weights)
 
     # -- combine -------------------------------------------------------------------------
+    def can_push(self, plan) -> bool:
+        return (self.combine_mode == "push" and (self.ctx.get("stage_buf") is not None or self.ctx["R"] == 1)
+                and plan.src_info is not None and plan.link is not None)  # fmt: skip
+
+    def combine_all(self, plan, hidden_nvsh, route_weights_nvs, out_hidden, out_weights_sk, inter_rank_sync,
+                    zero_copy, ready=None, ready_expect=0):  # fmt: skip
+        """The whole combine.  Push path (default): the expert side folds duplicates while it pushes each token's row
+        to the token's home rank, which sums rows as they land; one launch, no copy of the caller's rows into the
+        shard.  Pull path (``MOONEP_COMBINE=pull`` or a plan without src_info/link): fold pass, then pull."""
+        wf, we = -1, 0
+        # A round of READY flags keeps a rank from overwriting staging rows (or shard rows) a peer still reads from
+        # the previous combine; a dispatch that waited for all peers since then already gives that guarantee.
+        if inter_rank_sync and not self._quiesced:
+            self.signal(FLAG_READY)
+            wf, we = FLAG_READY, self._cur(FLAG_READY)
+        if not self.can_push(plan):
+            self.combine_prologue(plan, hidden_nvsh, route_weights_nvs, zero_copy, wait=None if wf < 0 else wf)
+            self.combine_pull(plan.dst, out_hidden, out_weights_sk)
+            return
+        self._quiesced = False
+        comb = self._next(FLAG_COMB)
+        args = (_ptr(plan.src_info), _ptr(plan.link), _ptr(plan.dst), _ptr(hidden_nvsh), _ptr(route_weights_nvs),
+                _ptr(out_hidden), _ptr(out_weights_sk), wf, we, comb, _ptr(ready), int(ready_expect),
+                _ptr(plan.dup_groups), _ptr(plan.dup_loffs), _ptr(plan.dup_counts), 0, 0, _stream())  # fmt: skip
+        if self.ctx["R"] == 1:  # nothing to stage: the push role writes the results itself
+            self._call("moonep_combine_push", ROLE_PUSH, *args, tag="combine_fold")
+        elif not self.phased:
+            self._call("moonep_combine_push", ROLE_PUSH | ROLE_SUM, *args, tag="combine_push_sum")
+        else:
+            self._call("moonep_combine_push", ROLE_PUSH, *args, tag="combine_push")
+            self.world.step()
+            self._call("moonep_combine_push", ROLE_SUM, *args, tag="combine_sum")
+        self.world.step()
+
     def combine_prologue(self, plan, hidden_nvsh, route_weights_nvs, zero_copy, wait=None):
         wf = -1 if wait is None else int(wait)
         if not zero_copy:

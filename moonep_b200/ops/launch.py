@@ -80,21 +80,9 @@ def launch_dispatch(ctx, hidden_sh, route_weights_sk, plan, *, build_dedup_map=F
 
 
 def launch_dedup_builder(ctx, plan) -> None:
-    """Rebuild ``dup_groups / dup_loffs / dup_counts`` of ``plan`` from what the last planning published."""
-    be = _be(ctx)
-    if hasattr(be, "build_dedup"):
-        be.build_dedup(plan)
-    else:
-        from ..cpu import planner as P
-
-        c = ctx
-        r, ms = c["rank"], c["meta_chunk_padded"]
-        src = c["meta_buf"][r * ms + c["SRC_INFO_OFF"] : r * ms + c["SRC_INFO_OFF"] + c["NvS"]].cpu().numpy()
-        g, l, n = P.build_dedup(src, S=c["S"], K=c["K"], NvS=c["NvS"])
-        dev = plan.dup_groups.device
-        plan.dup_groups.copy_(torch.from_numpy(g).to(torch.int32).to(dev))
-        plan.dup_loffs.copy_(torch.from_numpy(l).to(torch.int32).to(dev))
-        plan.dup_counts.copy_(torch.from_numpy(n).to(torch.int32).to(dev))
+    """Rebuild ``dup_groups / dup_loffs / dup_counts`` of ``plan`` (and its copies of src_info and the link words)
+    from what the last planning published into this rank's meta chunk."""
+    _be(ctx).build_dedup(plan)
 
 
 def launch_dispatch_epilogue(ctx, plan, *, pdl_launch=False) -> None:

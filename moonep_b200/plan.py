@@ -18,6 +18,11 @@ remote_stats[2]         ``(#remote experts received here, #ranks copying my expe
 dup_groups[NvS,3]       destination side: ``(primary loff, dup_start, dup_n)``.
 dup_loffs[NvS]          duplicate row offsets, indexed by ``dup_start``.
 dup_counts[2]           ``(#groups, #duplicate rows)``.
+src_info[NvS]           (optional) destination side: ``src_rank*NvS + token*K + k`` of the entry that landed in
+                        each row, ``-1`` for unused rows.
+link[NvS]               (optional) destination side: the link word of each row (primary bit, position among the
+                        token's primaries, next row of the same token).  With ``src_info`` it lets ``combine``
+                        push rows to the tokens' home ranks; plans without them are combined by pulling.
 
 Parity: reference ``moonep_td/planning.py:12-115``.
 """
@@ -46,6 +51,8 @@ class MoonEPCommPlan:
     dup_groups: torch.Tensor
     dup_loffs: torch.Tensor
     dup_counts: torch.Tensor
+    src_info: torch.Tensor | None = None
+    link: torch.Tensor | None = None
 
     def __post_init__(self) -> None:
         N, R, E, B, NvS = int(self.N), int(self.R), int(self.E), int(self.B), int(self.NvS)
@@ -61,10 +68,13 @@ class MoonEPCommPlan:
         ):
             got = tuple(getattr(self, name).shape)
             assert got == shape, f"{name} has shape {got}, expected {shape}"
+        for name in ("src_info", "link"):
+            t = getattr(self, name)
+            assert t is None or tuple(t.shape) == (NvS,), f"{name} must have shape ({NvS},)"
 
     def tensors(self):
         """The tensors a stream must keep alive while it uses this plan."""
-        return (
+        base = (
             self.dst,
             self.experts_to_copy,
             self.zero_fill_ranges,
@@ -73,6 +83,7 @@ class MoonEPCommPlan:
             self.dup_loffs,
             self.dup_counts,
         )
+        return base + tuple(t for t in (self.src_info, self.link) if t is not None)
 
     def clone(self) -> "MoonEPCommPlan":
         """Deep copy, e.g. to keep a plan for the backward pass."""
@@ -84,6 +95,8 @@ class MoonEPCommPlan:
             dup_groups=self.dup_groups.clone(),
             dup_loffs=self.dup_loffs.clone(),
             dup_counts=self.dup_counts.clone(),
+            src_info=None if self.src_info is None else self.src_info.clone(),
+            link=None if self.link is None else self.link.clone(),
             N=self.N,
             R=self.R,
             E=self.E,
@@ -114,6 +127,8 @@ def allocate_planning_outputs(ctx: dict) -> tuple[MoonEPCommPlan, torch.Tensor]:
         dup_groups=_i32(NvS * 3, dev).view(NvS, 3),
         dup_loffs=_i32(NvS, dev),
         dup_counts=_i32(2, dev),
+        src_info=_i32(NvS, dev),
+        link=_i32(NvS, dev),
         N=N,
         R=R,
         E=E,
