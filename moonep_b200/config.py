@@ -7,6 +7,8 @@ MOONEP_COPY_PATH      ``bulk`` (default: TMA bulk copies through shared memory) 
                       ``MOONEP_SEND_PATH`` / ``MOONEP_PULL_PATH`` / ``MOONEP_GRAD_PATH`` set one kernel only.
 MOONEP_COMBINE        ``push`` (default: the expert side folds duplicates and pushes rows to the tokens' home ranks,
                       which sum them as they arrive) or ``pull`` (fold pass, then the home ranks pull).
+MOONEP_PHASED         ``1``: launch the dispatch and combine kernels one role at a time even on real multi-GPU worlds
+                      (what emulated ranks always do); for per-role timing and debugging.
 MOONEP_LOCAL_SMS      CTAs of the kernels that only touch local memory (default: all SMs); ``num_sms`` of
                       the Buffer bounds the kernels that move data between ranks.
 MOONEP_NUM_SMS_DEDUP  CTAs of the dispatch kernel's destination-side role (zero fill, dedup builder, duplicate
@@ -62,6 +64,10 @@ def local_sms(sm_count: int) -> int:
     if raw is None or raw == "":
         return sm_count
     return max(1, min(int(raw), sm_count))
+
+
+def force_phased() -> bool:
+    return os.environ.get("MOONEP_PHASED", "0") not in _FALSE
 
 
 def combine_mode() -> str:

@@ -1,28 +1,29 @@
 // Push combine for sm_100a: the rank that ran the experts folds each token's duplicate rows and
 // pushes the result to the token's home rank over NVLink; the home rank sums the rows of a token as
-// they arrive.  One kernel, two roles:
+// they arrive.  One kernel, three roles:
 //
-//   PUSH  (expert side, num_sms CTAs) rows of the local expert output are handed out in small batches.
-//         For every primary row (first row of its (source, token) on this rank, known from the plan's
-//         copy of src_info and link words) a warp reads the row and its duplicates from local HBM, adds
-//         them in fp32 in ascending k, rounds to bf16 into shared memory and sends the row with one
-//         cp.async.bulk store into the staging chunk of the home rank, slot (token, position of this
-//         rank among the token's destinations).  Gate weights of all of the token's entries on this rank
-//         go to the home rank's weight staging.  When the bulk group has completed, the slot's flag is
-//         released with the combine's COMB epoch.
-//   SUM   (home side, the remaining CTAs) tokens are handed out from an atomic counter; a warp waits
-//         (bounded) for the flags of the token's primaries, adds the staged rows in fp32 in ascending k,
-//         stores the bf16 result and copies the K gate weights into the [S, K] output.
+//   FOLD  (expert side, the CTAs that do not drive NVLink) duplicate groups of the plan are handed out from an
+//         atomic counter; a warp adds the rows of a group (primary, then duplicates in ascending k) in fp32,
+//         rounds to bf16 into a local buffer and releases the group's flag.  These CTAs then take the SUM role.
+//   PUSH  (expert side, num_sms CTAs, pure copy engines) every primary row of the local expert output - as it
+//         is when it has no duplicates, from the FOLD role's buffer otherwise - goes through a shared-memory
+//         ring (cp.async.bulk global -> shared -> the home rank's staging chunk, slot (token, position of this
+//         rank among the token's destinations)).  The gate weights of all of the token's entries on this rank
+//         go to the home rank's weight staging.  Helper warps release the slot's flag with the combine's COMB
+//         epoch once the row's bulk group has completed.
+//   SUM   (home side) tokens are handed out from an atomic counter; a warp waits (bounded) for the flags of the
+//         token's primaries, adds the staged rows in fp32 in ascending k, stores the bf16 result and copies the
+//         K gate weights into the [S, K] output.
 //
-// Compared with pulling (combine.cu) the expert side needs no separate fold pass over its shard, every
-// NVLink transfer is a bulk store (which measured faster than loads from peer memory), and the
-// home-side sum overlaps the transfers.  Numerics are those of the pull path and of the reference: duplicates
-// are added in fp32 and rounded to bf16, the per-token sum is fp32 rounded to bf16.  The expert output rows are
-// not modified.
+// Compared with pulling (combine.cu) the fold overlaps the transfers instead of preceding them, every NVLink
+// transfer is a bulk store (which measured faster than loads from peer memory), and the home-side sum overlaps
+// the transfers too.  Numerics are those of the pull path and of the reference: duplicates are added in fp32 and
+// rounded to bf16, the per-token sum is fp32 rounded to bf16.  The expert output rows are not modified.
 //
-// Launched with both roles it is one fused kernel (CTAs 0..n_push-1 push, the rest sum; a SUM CTA only
-// waits for other GPUs' PUSH CTAs or for lower-numbered CTAs of its own GPU); emulated ranks that share one GPU
-// launch the roles one after the other.
+// CTA order in a launch with all roles: FOLD/SUM CTAs first, PUSH CTAs last, so that the PUSH role only waits
+// for lower-numbered CTAs (which the hardware dispatches first) and the SUM role only for PUSH CTAs of this or
+// other GPUs; the grid never exceeds the number of SMs.  Emulated ranks that share one GPU launch the roles one
+// after the other.  With a single rank the FOLD role alone writes the results.
 //
 // Parity: reference moonep_td/combine_prologue.py:19-40 and moonep_td/combine.py:22-68.
 #include "common.cuh"
@@ -32,9 +33,8 @@ namespace moonep {
 
 namespace {
 
-constexpr int kPushThreads = 384;       // 12 warps, each with one staged row piece in shared memory
-constexpr int kPushWarps = kPushThreads / 32;
-constexpr int kPushMaxChunk = 14336;    // bytes of a row piece (one stage per warp)
+constexpr int kPushThreads = 512;
+constexpr int kPushMaxChunk = 16384;    // bytes of a row piece (one ring stage)
 constexpr int kPushRowBatch = 8;        // rows handed out per grab
 constexpr int kFoldVec = 4;             // int4 per lane per inner step (2 KB per warp)
 constexpr int kFoldRows = 4;            // rows of a duplicate group whose loads are in flight together
@@ -58,7 +58,10 @@ struct PushArgs {
   const int* dup_groups;    // [NvS, 3] the plan's duplicate groups
   const int* dup_loffs;     // [NvS]
   const int* dup_counts;    // [2]
-  int direct;               // single rank: PUSH writes the folded rows and the weights straight into out / out_w
+  uint16_t* fold_buf;       // [fold_rows, H] local: folded row of every duplicate group
+  int* fold_flag;           // [fold_rows] local: COMB epoch of the combine that last folded the group
+  int fold_rows;
+  int direct;               // single rank: FOLD writes the results straight into out / out_w
 };
 
 __device__ __forceinline__ void acc_add(float* acc, const int4& v) {
@@ -117,187 +120,52 @@ __device__ bool wait_block_ready(const MoonepDevCtx& c, const PushArgs& a, int r
 
 // ---- PUSH role -------------------------------------------------------------------------------------
 
-// One group: the row `prow` (primary of its (source, token) on this rank) and its duplicates.  Lane q holds the q-th
-// row of the group in my_row (q = 0 the primary, then the duplicates in ascending k), n_rows of them.
-struct PushState {
-  int* pending_flag;  // lane 0: flag of the row whose last bulk group may still be in flight
-  unsigned bar_phase;
-  bool failed;
-};
-
-__device__ void push_group(const MoonepDevCtx& c, const PushArgs& a, unsigned char* s_stage, unsigned long long* s_bar,
-                           PushState& st, int epoch, int prow, int p_si, int p_l, int my_row, int n_rows) {
-  const int lane = threadIdx.x & 31;
-  const int NvS = c.NvS, K = c.K, H = c.H, S = c.S, kp = c.kp;
-  const long long row_bytes = (long long)H * 2;
-  const int home = p_si / NvS;
-  const int slot = p_si - home * NvS;
-  const int token = slot / K;
-  const int ord = (p_l >> MOONEP_LINK_ORD_SHIFT) & MOONEP_LINK_ORD_MASK;
-  if (p_si < 0 || home >= c.R || token >= S || ord >= kp || !(p_l & MOONEP_LINK_PRIMARY)) {
-    record_status(c, MOONEP_STATUS_BAD_INDEX, MOONEP_K_COMBINE_PUSH, 8, p_si, prow, ord);
-    return;
+// Rows of one duplicate group, one per lane: lane 0 the primary, lanes 1..dn the duplicates in ascending k.
+// Returns -1 in every lane (after recording a status) when the plan's lists are inconsistent.
+__device__ __forceinline__ int group_rows(const MoonepDevCtx& c, const PushArgs& a, int g, int lane, int& prow, int& dn,
+                                          int kernel_id) {
+  prow = a.dup_groups[3 * g];
+  const int ds = a.dup_groups[3 * g + 1];
+  dn = a.dup_groups[3 * g + 2];
+  bool bad = prow < 0 || prow >= c.NvS || ds < 0 || dn < 1 || dn >= MOONEP_MAX_TOPK || ds + dn > c.NvS;
+  int my_row = -1;
+  if (!bad) {
+    if (lane == 0) my_row = prow;
+    else if (lane <= dn) my_row = a.dup_loffs[ds + lane - 1];
+    bad = __any_sync(0xffffffffu, lane <= dn && (my_row < 0 || my_row >= c.NvS)) != 0;
   }
-  // the producer of the rows (a grouped GEMM running beside this kernel) must be done with every block involved
-  if (a.ready != nullptr) {
-    for (int q = 0; q < n_rows; ++q) {
-      const int row = __shfl_sync(0xffffffffu, my_row, q);
-      if (row >= 0 && row < NvS && !wait_block_ready(c, a, row, lane)) {
-        st.failed = true;
-        return;
-      }
-    }
+  if (bad) {
+    record_status(c, MOONEP_STATUS_BAD_INDEX, kernel_id, 9, prow, ds, dn);
+    return -1;
   }
-  // a single rank needs no staging: the folded row is the token's result
-  unsigned char* stage_home = a.direct ? nullptr : c.stage_peer[home];
-  // gate weights of all entries of this group travel to the home rank's weight staging
-  if (a.in_w != nullptr && lane < n_rows && my_row >= 0 && my_row < NvS) {
-    const int s_q = a.src_info[my_row];
-    const int slot_q = s_q - home * NvS;
-    if (s_q >= 0 && slot_q >= 0 && slot_q < S * K) {
-      float* wdst = a.direct ? a.out_w : reinterpret_cast<float*>(stage_home + c.stage_w_off);
-      if (wdst != nullptr) wdst[slot_q] = a.in_w[my_row];
-    }
-  }
-  const long long stage_row = (long long)token * kp + ord;
-  unsigned char* o_row = a.direct ? reinterpret_cast<unsigned char*>(a.out) + (long long)token * row_bytes
-                                  : stage_home + stage_row * row_bytes;
-  int* flag = a.direct ? nullptr : reinterpret_cast<int*>(stage_home + c.stage_flag_off) + stage_row;
-  if (a.vec_ok) {
-    for (int ch = 0; ch < a.nchunks; ++ch) {
-      const long long off = (long long)ch * a.chunk_bytes;
-      const int len = (int)((row_bytes - off) < a.chunk_bytes ? (row_bytes - off) : a.chunk_bytes);
-      const int nvec = len / 16;
-      // the stage is free once the previous bulk store has read it
-      if (lane == 0) bulk_wait_read<0>();
-      __syncwarp();
-      const unsigned char* src0 = reinterpret_cast<const unsigned char*>(a.in_rows) + (long long)prow * row_bytes + off;
-      if (n_rows == 1) {
-        // nothing to fold: the piece goes global -> shared -> home rank without touching registers
-        int got = 1;
-        if (lane == 0) {
-          mbar_expect_tx(s_bar, (unsigned)len);
-          bulk_g2s(s_stage, src0, (unsigned)len, s_bar);
-          got = mbar_wait(s_bar, st.bar_phase, c.timeout_ns) ? 1 : 0;
-          if (!got) record_status(c, MOONEP_STATUS_TIMEOUT, MOONEP_K_COMBINE_PUSH, 100, prow, ch, 0);
-        }
-        st.bar_phase ^= 1u;
-        if (!__shfl_sync(0xffffffffu, got, 0)) {
-          st.failed = true;
-          return;
-        }
-      } else {
-        for (int v0 = 0; v0 < nvec; v0 += 32 * kFoldVec) {
-          float acc[kFoldVec][8];
-#pragma unroll
-          for (int jv = 0; jv < kFoldVec; ++jv)
-#pragma unroll
-            for (int e = 0; e < 8; ++e) acc[jv][e] = 0.f;
-          // loads of up to kFoldRows rows are issued before the first add; adds keep the order primary, duplicates by k
-          for (int q0 = 0; q0 < n_rows; q0 += kFoldRows) {
-            int4 dv[kFoldRows][kFoldVec];
-#pragma unroll
-            for (int r = 0; r < kFoldRows; ++r) {
-              int row = __shfl_sync(0xffffffffu, my_row, (q0 + r) & 31);
-              if (row < 0 || row >= NvS) row = prow;  // never dereference a bad index (status recorded by the caller)
-              if (q0 + r < n_rows) {
-                const int4* r4 = reinterpret_cast<const int4*>(reinterpret_cast<const unsigned char*>(a.in_rows) +
-                                                                (long long)row * row_bytes + off);
-#pragma unroll
-                for (int jv = 0; jv < kFoldVec; ++jv) {
-                  const int i = v0 + jv * 32 + lane;
-                  if (i < nvec) dv[r][jv] = ld16(r4 + i);
-                }
-              }
-            }
-#pragma unroll
-            for (int r = 0; r < kFoldRows; ++r) {
-              if (q0 + r < n_rows) {
-#pragma unroll
-                for (int jv = 0; jv < kFoldVec; ++jv)
-                  if (v0 + jv * 32 + lane < nvec) acc_add(acc[jv], dv[r][jv]);
-              }
-            }
-          }
-#pragma unroll
-          for (int jv = 0; jv < kFoldVec; ++jv) {
-            const int i = v0 + jv * 32 + lane;
-            if (i < nvec) sts16(s_stage + (size_t)i * 16, acc_pack(acc[jv]));
-          }
-        }
-      }
-      fence_proxy_async();
-      __syncwarp();
-      if (lane == 0) {
-        bulk_s2g(o_row + off, s_stage, (unsigned)len);
-        bulk_commit();
-        if (st.pending_flag != nullptr) {
-          // every group but the one just committed has completed: the previous row is in its home's memory
-          bulk_wait<1>();
-          st_release_sys(st.pending_flag, epoch);
-          st.pending_flag = nullptr;
-        }
-      }
-    }
-    if (lane == 0) st.pending_flag = flag;
-  } else {
-    // rows that are not multiples of 16 bytes: element-wise, straight into the home rank's staging chunk
-    uint16_t* o = reinterpret_cast<uint16_t*>(o_row);
-    // every lane runs the same number of iterations: the shuffles need the whole warp
-    for (int i0 = 0; i0 < H; i0 += 32) {
-      const int i = i0 + lane;
-      uint16_t v = i < H ? a.in_rows[(long long)prow * H + i] : (uint16_t)0;
-      if (n_rows > 1) {
-        float acc = bf16_to_f32(v);
-        for (int q = 1; q < n_rows; ++q) {
-          int row = __shfl_sync(0xffffffffu, my_row, q);
-          if (row < 0 || row >= NvS) row = prow;
-          if (i < H) acc += bf16_to_f32(a.in_rows[(long long)row * H + i]);
-        }
-        v = f32_to_bf16(acc);
-      }
-      if (i < H) o[i] = v;
-    }
-    __syncwarp();
-    if (lane == 0 && flag != nullptr) st_release_sys(flag, epoch);
-  }
+  return my_row;
 }
 
-// s_stage: this warp's row piece in shared memory (chunk_bytes, 128-byte aligned).  Work items, handed out from an
-// atomic counter: first the duplicate groups of the plan (primary row plus duplicates, folded), then batches of rows
-// of which the primaries without duplicates are sent as they are.
-__device__ void push_role(const MoonepDevCtx& c, const PushArgs& a, unsigned char* s_stage, unsigned long long* s_bar) {
+// ---- FOLD role ---------------------------------------------------------------------------------------
+
+// Duplicate groups are handed out from an atomic counter; a warp adds the rows of a group in fp32 (primary first,
+// then the duplicates in ascending k), rounds to bf16 and stores the row into fold_buf[g] (or, with a single rank,
+// straight into the token's output row), then releases fold_flag[g] for the PUSH role.
+__device__ void fold_role(const MoonepDevCtx& c, const PushArgs& a) {
   const int lane = threadIdx.x & 31;
-  const int NvS = c.NvS;
+  const int NvS = c.NvS, K = c.K, H = c.H, S = c.S;
+  const long long row_bytes = (long long)H * 2;
   const int epoch = abs_epoch(c, MOONEP_FLAG_COMB, a.epoch_comb);
-  int* work = c.counters + MOONEP_CTR_PUSH_WORK;
-  PushState st;
-  st.pending_flag = nullptr;
-  st.bar_phase = 0;
-  st.failed = false;
+  int* work = c.counters + MOONEP_CTR_FOLD_WORK;
   int ngroups = a.dup_counts[0];
-  if (ngroups < 0 || ngroups > NvS) ngroups = 0;
-  const int nbatches = (NvS + kPushRowBatch - 1) / kPushRowBatch;
+  if (ngroups < 0 || ngroups > a.fold_rows) {
+    if (ngroups > a.fold_rows) record_status(c, MOONEP_STATUS_BAD_INDEX, MOONEP_K_COMBINE_PUSH, 10, ngroups, a.fold_rows, 0);
+    ngroups = 0;
+  }
+  // with a single rank this role also copies the rows that have no duplicates
+  const int nbatches = a.direct ? (NvS + kPushRowBatch - 1) / kPushRowBatch : 0;
   for (;;) {
     int item = 0;
     if (lane == 0) item = atomicAdd(work, 1);
     item = __shfl_sync(0xffffffffu, item, 0);
-    if (item >= ngroups + nbatches || st.failed) break;
-    if (item < ngroups) {
-      const int prow = a.dup_groups[3 * item], ds = a.dup_groups[3 * item + 1], dn = a.dup_groups[3 * item + 2];
-      if (prow < 0 || prow >= NvS || ds < 0 || dn < 1 || dn >= MOONEP_MAX_TOPK || ds + dn > NvS) {
-        record_status(c, MOONEP_STATUS_BAD_INDEX, MOONEP_K_COMBINE_PUSH, 9, prow, ds, dn);
-        continue;
-      }
-      int my_row = -1;
-      if (lane == 0) my_row = prow;
-      else if (lane <= dn) my_row = a.dup_loffs[ds + lane - 1];
-      if (__any_sync(0xffffffffu, lane <= dn && (my_row < 0 || my_row >= NvS))) {
-        record_status(c, MOONEP_STATUS_BAD_INDEX, MOONEP_K_COMBINE_PUSH, 5, my_row, prow, 0);
-        continue;
-      }
-      push_group(c, a, s_stage, s_bar, st, epoch, prow, a.src_info[prow], a.link[prow], my_row, 1 + dn);
-    } else {
+    if (item >= ngroups + nbatches) break;
+    if (item >= ngroups) {
+      // single rank: rows without duplicates go to the output as they are
       const int base = (item - ngroups) * kPushRowBatch;
       int si = -1, l = 0;
       if (lane < kPushRowBatch && base + lane < NvS) {
@@ -305,19 +173,417 @@ __device__ void push_role(const MoonepDevCtx& c, const PushArgs& a, unsigned cha
         l = si >= 0 ? a.link[base + lane] : 0;
       }
       unsigned prim = __ballot_sync(0xffffffffu, si >= 0 && (l & MOONEP_LINK_PRIMARY) && !(l & MOONEP_LINK_HAS_NEXT));
-      while (prim && !st.failed) {
+      while (prim) {
         const int j = __ffs(prim) - 1;
         prim &= prim - 1;
         const int p_si = __shfl_sync(0xffffffffu, si, j);
-        const int p_l = __shfl_sync(0xffffffffu, l, j);
-        push_group(c, a, s_stage, s_bar, st, epoch, base + j, p_si, p_l, lane == 0 ? base + j : -1, 1);
+        const int slot = p_si % NvS;
+        if (slot >= S * K) continue;
+        const int prow = base + j;
+        if (!wait_block_ready(c, a, prow, lane)) return;
+        if (a.in_w != nullptr && a.out_w != nullptr && lane == 0) a.out_w[slot] = a.in_w[prow];
+        const uint16_t* src = a.in_rows + (long long)prow * H;
+        uint16_t* o = a.out + (long long)(slot / K) * H;
+        if (a.vec_ok) {
+          for (int i = lane; i < H / 8; i += 32) st16(reinterpret_cast<int4*>(o) + i, ld16(reinterpret_cast<const int4*>(src) + i));
+        } else {
+          for (int i = lane; i < H; i += 32) o[i] = src[i];
+        }
+      }
+      continue;
+    }
+    int prow, dn;
+    const int my_row = group_rows(c, a, item, lane, prow, dn, MOONEP_K_COMBINE_PUSH);
+    if (__shfl_sync(0xffffffffu, my_row, 0) < 0) continue;
+    const int n_rows = 1 + dn;
+    // the producer of the rows (a grouped GEMM running beside this kernel) must be done with every block involved
+    if (a.ready != nullptr) {
+      bool ok = true;
+      for (int q = 0; q < n_rows && ok; ++q) ok = wait_block_ready(c, a, __shfl_sync(0xffffffffu, my_row, q), lane);
+      if (!ok) return;
+    }
+    uint16_t* o = a.fold_buf + (long long)item * H;
+    if (a.direct) {
+      const int p_si = a.src_info[prow];
+      const int slot = p_si % NvS;
+      if (p_si < 0 || slot >= S * K) {
+        record_status(c, MOONEP_STATUS_BAD_INDEX, MOONEP_K_COMBINE_PUSH, 8, p_si, prow, 0);
+        continue;
+      }
+      o = a.out + (long long)(slot / K) * H;
+      if (a.in_w != nullptr && a.out_w != nullptr && lane < n_rows) {
+        const int s_q = a.src_info[my_row];
+        if (s_q >= 0 && s_q % NvS < S * K) a.out_w[s_q % NvS] = a.in_w[my_row];
       }
     }
+    if (a.vec_ok) {
+      const int nvec = H / 8;
+      for (int v0 = 0; v0 < nvec; v0 += 32 * kFoldVec) {
+        float acc[kFoldVec][8];
+#pragma unroll
+        for (int jv = 0; jv < kFoldVec; ++jv)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[jv][e] = 0.f;
+        // loads of up to kFoldRows rows are issued before the first add
+        for (int q0 = 0; q0 < n_rows; q0 += kFoldRows) {
+          int4 dv[kFoldRows][kFoldVec];
+#pragma unroll
+          for (int r = 0; r < kFoldRows; ++r) {
+            const int row = __shfl_sync(0xffffffffu, my_row, (q0 + r) & 31);
+            if (q0 + r < n_rows) {
+              const int4* r4 = reinterpret_cast<const int4*>(reinterpret_cast<const unsigned char*>(a.in_rows) +
+                                                              (long long)row * row_bytes);
+#pragma unroll
+              for (int jv = 0; jv < kFoldVec; ++jv) {
+                const int i = v0 + jv * 32 + lane;
+                if (i < nvec) dv[r][jv] = ld16(r4 + i);
+              }
+            }
+          }
+#pragma unroll
+          for (int r = 0; r < kFoldRows; ++r) {
+            if (q0 + r < n_rows) {
+#pragma unroll
+              for (int jv = 0; jv < kFoldVec; ++jv)
+                if (v0 + jv * 32 + lane < nvec) acc_add(acc[jv], dv[r][jv]);
+            }
+          }
+        }
+#pragma unroll
+        for (int jv = 0; jv < kFoldVec; ++jv) {
+          const int i = v0 + jv * 32 + lane;
+          if (i < nvec) st16(reinterpret_cast<int4*>(o) + i, acc_pack(acc[jv]));
+        }
+      }
+    } else {
+      // every lane runs the same number of iterations: the shuffles need the whole warp
+      for (int i0 = 0; i0 < H; i0 += 32) {
+        const int i = i0 + lane;
+        float acc = 0.f;
+        for (int q = 0; q < n_rows; ++q) {
+          const int row = __shfl_sync(0xffffffffu, my_row, q);
+          if (i < H) acc += bf16_to_f32(a.in_rows[(long long)row * H + i]);
+        }
+        if (i < H) o[i] = f32_to_bf16(acc);
+      }
+    }
+    __syncwarp();
+    if (lane == 0 && !a.direct) st_release_gpu(a.fold_flag + item, epoch);
   }
-  if (lane == 0) {
-    bulk_wait<0>();
-    if (st.pending_flag != nullptr && !st.failed) st_release_sys(st.pending_flag, epoch);
+}
+
+// ---- PUSH role ---------------------------------------------------------------------------------------
+//
+// Pure copy engines: warps 0..kMoveWarps-1 each drive a three-stage shared-memory ring with cp.async.bulk (local
+// global -> shared on an mbarrier, shared -> the home rank's staging chunk in bulk groups); warps
+// kMoveWarps..2*kMoveWarps-1 release the staging flags of rows whose copies have completed, so that the
+// system-scope fence of a release never stalls a lane that issues copies.  Work items, handed out from an atomic
+// counter: first batches of rows, of which the primaries without duplicates are sent as they are (they depend on
+// nothing), then the duplicate groups in the order the FOLD role finishes them.
+
+constexpr int kMoveWarps = 4;
+constexpr int kMoveStages = 3;
+constexpr int kMoveQ = 16;
+
+struct MoveQueue {
+  int* flag[kMoveWarps][kMoveQ];
+  int head[kMoveWarps], tail[kMoveWarps], done[kMoveWarps];
+};
+
+__device__ __forceinline__ int lds_acquire(const int* p) {
+  int v;
+  asm volatile("ld.acquire.cta.shared::cta.s32 %0, [%1];" : "=r"(v) : "r"(smem_u32(p)) : "memory");
+  return v;
+}
+__device__ __forceinline__ void sts_release(int* p, int v) {
+  asm volatile("st.release.cta.shared::cta.s32 [%0], %1;" ::"r"(smem_u32(p)), "r"(v) : "memory");
+}
+
+__device__ void move_helper(const MoonepDevCtx& c, int epoch, MoveQueue& q, int w) {
+  const int lane = threadIdx.x & 31;
+  int consumed = 0;
+  for (;;) {
+    int avail = 0;
+    if (lane == 0) {
+      const unsigned long long t0 = globaltimer_ns();
+      unsigned spins = 0;
+      for (;;) {
+        const int fin = lds_acquire(&q.done[w]);  // read before head: a row pushed before `done` is never missed
+        avail = lds_acquire(&q.head[w]) - consumed;
+        if (avail > 0) break;
+        if (fin) {
+          avail = -1;
+          break;
+        }
+        if ((++spins & 255u) == 0 && (globaltimer_ns() - t0 > c.timeout_ns || poisoned(c))) {
+          avail = -1;
+          break;
+        }
+        __nanosleep(64);
+      }
+    }
+    avail = __shfl_sync(0xffffffffu, avail, 0);
+    if (avail <= 0) break;
+    if (lane < avail) st_release_sys(q.flag[w][(consumed + lane) % kMoveQ], epoch);
+    consumed += avail;
+    __syncwarp();
+    if (lane == 0) sts_release(&q.tail[w], consumed);
   }
+}
+
+// Job generator of the PUSH role: one job = one row to stage on its home rank.  All lanes of a warp call next()
+// together; the results are warp-uniform.
+struct PushJobs {
+  const MoonepDevCtx& c;
+  const PushArgs& a;
+  int lane, epoch, ngroups, nbatches;
+  unsigned pend;   // singles of the current batch still to send
+  int b_base, b_si;
+  bool failed, drained;
+
+  __device__ PushJobs(const MoonepDevCtx& c_, const PushArgs& a_, int epoch_)
+      : c(c_), a(a_), lane(threadIdx.x & 31), epoch(epoch_), pend(0), b_base(0), b_si(-1), failed(false), drained(false) {
+    ngroups = a.dup_counts[0];
+    if (ngroups < 0 || ngroups > a.fold_rows) ngroups = 0;
+    nbatches = (c.NvS + kPushRowBatch - 1) / kPushRowBatch;
+  }
+
+  // (prow, p_si, p_l) describe a primary row; lanes < n_rows hold its group's rows in my_row
+  __device__ bool describe(int prow, int p_si, int p_l, int my_row, int n_rows, unsigned char*& dst, int*& flag) {
+    const int NvS = c.NvS, K = c.K, S = c.S;
+    const int home = p_si / NvS;
+    const int slot = p_si - home * NvS;
+    const int token = slot / K;
+    const int ord = (p_l >> MOONEP_LINK_ORD_SHIFT) & MOONEP_LINK_ORD_MASK;
+    if (p_si < 0 || home >= c.R || token >= S || ord >= c.kp || !(p_l & MOONEP_LINK_PRIMARY)) {
+      record_status(c, MOONEP_STATUS_BAD_INDEX, MOONEP_K_COMBINE_PUSH, 8, p_si, prow, ord);
+      return false;
+    }
+    unsigned char* stage_home = c.stage_peer[home];
+    // gate weights of all entries of this group travel to the home rank's weight staging
+    if (a.in_w != nullptr && lane < n_rows && my_row >= 0 && my_row < NvS) {
+      const int s_q = a.src_info[my_row];
+      const int slot_q = s_q - home * NvS;
+      if (s_q >= 0 && slot_q >= 0 && slot_q < S * K)
+        reinterpret_cast<float*>(stage_home + c.stage_w_off)[slot_q] = a.in_w[my_row];
+    }
+    const long long stage_row = (long long)token * c.kp + ord;
+    dst = stage_home + stage_row * ((long long)c.H * 2);
+    flag = reinterpret_cast<int*>(stage_home + c.stage_flag_off) + stage_row;
+    return true;
+  }
+
+  __device__ bool next(const unsigned char*& src, unsigned char*& dst, int*& flag) {
+    const long long row_bytes = (long long)c.H * 2;
+    for (;;) {
+      if (failed || drained) return false;
+      if (pend) {
+        const int j = __ffs(pend) - 1;
+        pend &= pend - 1;
+        const int p_si = __shfl_sync(0xffffffffu, b_si, j);
+        const int prow = b_base + j;
+        if (!wait_block_ready(c, a, prow, lane)) {
+          failed = true;
+          return false;
+        }
+        if (!describe(prow, p_si, a.link[prow], lane == 0 ? prow : -1, 1, dst, flag)) continue;
+        src = reinterpret_cast<const unsigned char*>(a.in_rows) + (long long)prow * row_bytes;
+        if (a.ready != nullptr) fence_proxy_async_all();  // rows written by other SMs are about to be read by bulk copies
+        return true;
+      }
+      int item = 0;
+      if (lane == 0) item = atomicAdd(c.counters + MOONEP_CTR_PUSH_WORK, 1);
+      item = __shfl_sync(0xffffffffu, item, 0);
+      if (item >= nbatches + ngroups) {
+        drained = true;
+        return false;
+      }
+      if (item < nbatches) {
+        b_base = item * kPushRowBatch;
+        b_si = -1;
+        int l = 0;
+        if (lane < kPushRowBatch && b_base + lane < c.NvS) {
+          b_si = a.src_info[b_base + lane];
+          l = b_si >= 0 ? a.link[b_base + lane] : 0;
+        }
+        pend = __ballot_sync(0xffffffffu, b_si >= 0 && (l & MOONEP_LINK_PRIMARY) && !(l & MOONEP_LINK_HAS_NEXT));
+        continue;
+      }
+      const int g = item - nbatches;
+      int prow, dn;
+      const int my_row = group_rows(c, a, g, lane, prow, dn, MOONEP_K_COMBINE_PUSH);
+      if (__shfl_sync(0xffffffffu, my_row, 0) < 0) continue;
+      // wait (bounded) for the FOLD role
+      int ok = 1;
+      if (lane == 0) {
+        const int* f = a.fold_flag + g;
+        if (ld_acquire_gpu(f) - epoch < 0) {
+          const unsigned long long t0 = globaltimer_ns();
+          unsigned spins = 0;
+          int v;
+          while ((v = ld_acquire_gpu(f)) - epoch < 0) {
+            if ((++spins & 63u) == 0 && (globaltimer_ns() - t0 > c.timeout_ns || poisoned(c))) {
+              record_status(c, MOONEP_STATUS_TIMEOUT, MOONEP_K_COMBINE_PUSH, 203, g, epoch, v);
+              ok = 0;
+              break;
+            }
+            __nanosleep(128);
+          }
+        }
+      }
+      if (!__shfl_sync(0xffffffffu, ok, 0)) {
+        failed = true;
+        return false;
+      }
+      if (!describe(prow, a.src_info[prow], a.link[prow], my_row, 1 + dn, dst, flag)) continue;
+      src = reinterpret_cast<const unsigned char*>(a.fold_buf) + (long long)g * row_bytes;
+      fence_proxy_async_all();  // the FOLD role's stores are about to be read by bulk copies
+      return true;
+    }
+  }
+};
+
+// Rows that are not multiples of 16 bytes cannot use bulk copies: every warp copies rows element by element.
+__device__ void push_role_plain(const MoonepDevCtx& c, const PushArgs& a) {
+  const int lane = threadIdx.x & 31;
+  const int epoch = abs_epoch(c, MOONEP_FLAG_COMB, a.epoch_comb);
+  PushJobs jobs(c, a, epoch);
+  const unsigned char* src;
+  unsigned char* dst;
+  int* flag;
+  while (jobs.next(src, dst, flag)) {
+    const uint16_t* s16 = reinterpret_cast<const uint16_t*>(src);
+    uint16_t* d16 = reinterpret_cast<uint16_t*>(dst);
+    for (int i = lane; i < c.H; i += 32) d16[i] = s16[i];
+    __syncwarp();
+    if (lane == 0) st_release_sys(flag, epoch);
+  }
+}
+
+// s_ring: this warp's kMoveStages pieces of chunk_bytes; s_bar: its kMoveStages mbarriers (count 1).
+__device__ void push_role(const MoonepDevCtx& c, const PushArgs& a, unsigned char* s_ring, unsigned long long* s_bar,
+                          MoveQueue& mq, int w) {
+  const int lane = threadIdx.x & 31;
+  const long long row_bytes = (long long)c.H * 2;
+  const int epoch = abs_epoch(c, MOONEP_FLAG_COMB, a.epoch_comb);
+  PushJobs jobs(c, a, epoch);
+  const unsigned char* j_src = nullptr;
+  unsigned char* j_dst = nullptr;
+  int* j_flag = nullptr;
+  int j_chunk = a.nchunks;  // next piece of the current job; == nchunks: no current job
+  bool failed = false;
+
+  // Advance to the next piece to copy: (src, dst, len, flag or null when more pieces of the row follow).
+  auto next_item = [&](const unsigned char*& src, unsigned char*& dst, unsigned& len, int*& flag) -> bool {
+    if (j_chunk >= a.nchunks) {
+      if (!jobs.next(j_src, j_dst, j_flag)) return false;
+      j_chunk = 0;
+    }
+    const long long off = (long long)j_chunk * a.chunk_bytes;
+    const long long rest = row_bytes - off;
+    len = (unsigned)(rest < a.chunk_bytes ? rest : a.chunk_bytes);
+    src = j_src + off;
+    dst = j_dst + off;
+    ++j_chunk;
+    flag = j_chunk >= a.nchunks ? j_flag : nullptr;
+    return true;
+  };
+
+  // three-stage ring, as in the dispatch send role: the load of item i+1 is in flight while item i is stored
+  unsigned char* r_dst[kMoveStages];
+  unsigned r_len[kMoveStages];
+  int* r_flag[kMoveStages + 1];  // one entry more than stages: an item is flagged three items late
+  int loaded = 0, done = 0, pushed = 0;
+  auto issue_load = [&](const unsigned char* src, unsigned char* dst, unsigned len, int* flag) {
+    const int s = loaded % kMoveStages;
+#pragma unroll
+    for (int q = 0; q < kMoveStages; ++q)
+      if (q == s) {
+        r_dst[q] = dst;
+        r_len[q] = len;
+      }
+    const int fs = loaded % (kMoveStages + 1);
+#pragma unroll
+    for (int q = 0; q < kMoveStages + 1; ++q)
+      if (q == fs) r_flag[q] = flag;
+    if (lane == 0) {
+      mbar_expect_tx(s_bar + s, len);
+      bulk_g2s(s_ring + (size_t)s * a.chunk_bytes, src, len, s_bar + s);
+    }
+    ++loaded;
+  };
+  auto flag_item = [&](int j) {
+    const int fs = j % (kMoveStages + 1);
+    int* flag = nullptr;
+#pragma unroll
+    for (int q = 0; q < kMoveStages + 1; ++q)
+      if (q == fs) flag = r_flag[q];
+    if (flag != nullptr && lane == 0) {
+      if (pushed - lds_acquire(&mq.tail[w]) >= kMoveQ) {
+        const unsigned long long t0 = globaltimer_ns();
+        unsigned spins = 0;
+        while (pushed - lds_acquire(&mq.tail[w]) >= kMoveQ) {
+          if ((++spins & 255u) == 0 && (globaltimer_ns() - t0 > c.timeout_ns || poisoned(c))) {
+            record_status(c, MOONEP_STATUS_TIMEOUT, MOONEP_K_COMBINE_PUSH, 101, w, pushed, 0);
+            failed = true;
+            return;
+          }
+        }
+      }
+      mq.flag[w][pushed % kMoveQ] = flag;
+      ++pushed;
+      sts_release(&mq.head[w], pushed);
+    }
+  };
+
+  const unsigned char* src;
+  unsigned char* dst;
+  unsigned len;
+  int* flag;
+  bool more = next_item(src, dst, len, flag);
+  if (more) issue_load(src, dst, len, flag);
+  while (done < loaded && !failed) {
+    if (more) {
+      more = next_item(src, dst, len, flag);
+      if (more) {
+        if (lane == 0) bulk_wait_read<1>();  // the stage to refill was read by the group committed two items ago
+        __syncwarp();
+        issue_load(src, dst, len, flag);
+      }
+    }
+    const int s = done % kMoveStages;
+    unsigned char* o = nullptr;
+    unsigned olen = 0;
+#pragma unroll
+    for (int q = 0; q < kMoveStages; ++q)
+      if (q == s) {
+        o = r_dst[q];
+        olen = r_len[q];
+      }
+    int got = 1;
+    if (lane == 0) got = mbar_wait(s_bar + s, (unsigned)((done / kMoveStages) & 1), c.timeout_ns) ? 1 : 0;
+    got = __shfl_sync(0xffffffffu, got, 0);
+    if (!got) {
+      if (lane == 0) record_status(c, MOONEP_STATUS_TIMEOUT, MOONEP_K_COMBINE_PUSH, 100, s, done, 0);
+      failed = true;
+      break;
+    }
+    if (lane == 0) {
+      bulk_s2g(o, s_ring + (size_t)s * a.chunk_bytes, olen);
+      bulk_commit();
+    }
+    ++done;
+    if (done >= kMoveStages) {
+      if (lane == 0) bulk_wait<kMoveStages - 1>();  // item done-3 has reached its home rank
+      flag_item(done - kMoveStages);
+      failed = __shfl_sync(0xffffffffu, failed ? 1 : 0, 0) != 0;
+    }
+  }
+  if (lane == 0) bulk_wait<0>();
+  __syncwarp();
+  if (!failed)
+    for (int j = done >= kMoveStages ? done - kMoveStages + 1 : 0; j < done; ++j) flag_item(j);
+  if (lane == 0) sts_release(&mq.done[w], 1);
   __syncwarp();
 }
 
@@ -424,19 +690,36 @@ __device__ void sum_role(const MoonepDevCtx& c, const PushArgs& a) {
 }
 
 __global__ void __launch_bounds__(kPushThreads, 1) combine_push_kernel(const MoonepDevCtx c, const PushArgs a) {
-  extern __shared__ __align__(128) unsigned char s_dyn[];  // [kPushWarps][chunk_bytes rounded up to 128]
-  __shared__ __align__(8) unsigned long long s_bar[kPushWarps];
+  extern __shared__ __align__(128) unsigned char s_dyn[];  // PUSH: [kMoveWarps][kMoveStages][chunk_bytes]
+  __shared__ __align__(8) unsigned long long s_bar[kMoveWarps * kMoveStages];
+  __shared__ MoveQueue s_mq;
   const int warp = threadIdx.x >> 5;
-  if (threadIdx.x < kPushWarps) mbar_init(s_bar + threadIdx.x, 1);
+  if (threadIdx.x < kMoveWarps * kMoveStages) mbar_init(s_bar + threadIdx.x, 1);
+  if (threadIdx.x < kMoveWarps) {
+    s_mq.head[threadIdx.x] = 0;
+    s_mq.tail[threadIdx.x] = 0;
+    s_mq.done[threadIdx.x] = 0;
+  }
   fence_barrier_init();
   __syncthreads();
-  const bool mixed = (a.roles & MOONEP_ROLE_PUSH) && (a.roles & MOONEP_ROLE_SUM);
-  const bool pusher = (a.roles & MOONEP_ROLE_PUSH) && (!mixed || (int)blockIdx.x < a.n_push);
+  const bool has_push = (a.roles & MOONEP_ROLE_PUSH) != 0;
+  const bool has_local = (a.roles & (MOONEP_ROLE_FOLD | MOONEP_ROLE_SUM)) != 0;
+  // PUSH CTAs are the last n_push of the grid
+  const bool pusher = has_push && (!has_local || (int)blockIdx.x >= (int)gridDim.x - a.n_push);
   if (pusher) {
-    if (block_wait_flags(c, a.wait_family, a.wait_epoch, MOONEP_K_COMBINE_PUSH))
-      push_role(c, a, s_dyn + (size_t)warp * ((a.chunk_bytes + 127) / 128 * 128), s_bar + warp);
-  } else if (a.roles & MOONEP_ROLE_SUM) {
-    if (!poisoned(c)) sum_role(c, a);
+    if (block_wait_flags(c, a.wait_family, a.wait_epoch, MOONEP_K_COMBINE_PUSH)) {
+      if (!a.vec_ok) {
+        push_role_plain(c, a);
+      } else if (warp < kMoveWarps) {
+        const size_t stage = (size_t)(a.chunk_bytes + 127) / 128 * 128;
+        push_role(c, a, s_dyn + (size_t)warp * kMoveStages * stage, s_bar + warp * kMoveStages, s_mq, warp);
+      } else if (warp < 2 * kMoveWarps) {
+        move_helper(c, abs_epoch(c, MOONEP_FLAG_COMB, a.epoch_comb), s_mq, warp - kMoveWarps);
+      }
+    }
+  } else if (has_local && !poisoned(c)) {
+    if (a.roles & MOONEP_ROLE_FOLD) fold_role(c, a);
+    if (a.roles & MOONEP_ROLE_SUM) sum_role(c, a);
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -445,6 +728,7 @@ __global__ void __launch_bounds__(kPushThreads, 1) combine_push_kernel(const Moo
       c.counters[MOONEP_CTR_COMBINE_ARRIVE] = 0;
       if (a.roles & MOONEP_ROLE_PUSH) c.counters[MOONEP_CTR_PUSH_WORK] = 0;
       if (a.roles & MOONEP_ROLE_SUM) c.counters[MOONEP_CTR_SUM_WORK] = 0;
+      if (a.roles & MOONEP_ROLE_FOLD) c.counters[MOONEP_CTR_FOLD_WORK] = 0;
       __threadfence();
     }
   }
@@ -466,18 +750,20 @@ extern "C" long long moonep_stage_layout(int S, int K, int H, int kp, long long*
   return rows + flags + w;
 }
 
-// roles: MOONEP_ROLE_PUSH | MOONEP_ROLE_SUM (a single rank launches PUSH alone, which then writes the results itself).
-// src_info / link: the plan's copies ([NvS] each); dup_groups / dup_loffs / dup_counts: the plan's duplicate map.  in_rows: the local expert
-// output rows [NvS, H] (the shard or any other local tensor), in_w: their gate weights [NvS] or null.  ready /
-// ready_expect: optional per-128-row-block counters bumped by the producer of in_rows (see moonep_grouped_gemm_pair).
+// roles: MOONEP_ROLE_FOLD | MOONEP_ROLE_PUSH | MOONEP_ROLE_SUM (a single rank launches FOLD alone, which then writes the
+// results itself).  src_info / link: the plan's copies ([NvS] each); dup_groups / dup_loffs / dup_counts: the plan's
+// duplicate map.  in_rows: the local expert output rows [NvS, H] (the shard or any other local tensor), in_w: their gate
+// weights [NvS] or null.  fold_buf [fold_rows, H] bf16 and fold_flag [fold_rows] int32 (zero-initialised once) are
+// local scratch of the Buffer; fold_rows bounds the number of duplicate groups.  ready / ready_expect: optional
+// per-128-row-block counters bumped by the producer of in_rows (see moonep_grouped_gemm_pair).
 extern "C" int moonep_combine_push(void* ctx, int roles, const int* src_info, const int* link, const int* dst,
                                    const void* in_rows, const float* in_w, void* out_hidden, float* out_weights,
                                    int wait_family, int wait_epoch, int epoch_comb, const int* ready, int ready_expect,
-                                   const int* dup_groups, const int* dup_loffs, const int* dup_counts, int n_push,
-                                   int n_sum, void* stream) {
+                                   const int* dup_groups, const int* dup_loffs, const int* dup_counts, void* fold_buf,
+                                   int* fold_flag, int fold_rows, int n_push, int n_local, void* stream) {
   auto* h = (HostCtx*)ctx;
   const MoonepDevCtx& c = h->dev;
-  const int direct = (c.R == 1 && roles == MOONEP_ROLE_PUSH) ? 1 : 0;
+  const int direct = (c.R == 1 && roles == MOONEP_ROLE_FOLD) ? 1 : 0;
   if (c.stage_peer == nullptr && !direct) {
     set_error("moonep_combine_push: this Buffer has no combine staging memory");
     return 1;
@@ -499,15 +785,20 @@ extern "C" int moonep_combine_push(void* ctx, int roles, const int* src_info, co
   a.dup_groups = dup_groups;
   a.dup_loffs = dup_loffs;
   a.dup_counts = dup_counts;
+  a.fold_buf = (uint16_t*)fold_buf;
+  a.fold_flag = fold_flag;
+  a.fold_rows = fold_rows;
   a.direct = direct;
-  const bool al = ((reinterpret_cast<uintptr_t>(in_rows) | reinterpret_cast<uintptr_t>(out_hidden)) & 15u) == 0;
+  const bool al = ((reinterpret_cast<uintptr_t>(in_rows) | reinterpret_cast<uintptr_t>(out_hidden) |
+                    reinterpret_cast<uintptr_t>(fold_buf)) & 15u) == 0;
   a.vec_ok = (c.H % 8 == 0) && al;
   const long long row_bytes = (long long)c.H * 2;
   a.nchunks = (int)((row_bytes + kPushMaxChunk - 1) / kPushMaxChunk);
   const long long cb = (row_bytes + a.nchunks - 1) / a.nchunks;
   a.chunk_bytes = (int)((cb + 15) / 16 * 16);
   size_t smem = 0;
-  if (roles & MOONEP_ROLE_PUSH) smem = (size_t)kPushWarps * ((a.chunk_bytes + 127) / 128 * 128);
+  if ((roles & MOONEP_ROLE_PUSH) && a.vec_ok)
+    smem = (size_t)kMoveWarps * kMoveStages * ((size_t)(a.chunk_bytes + 127) / 128 * 128);
   if ((int)smem + 4096 > h->max_smem_optin) {
     set_error("moonep_combine_push: staging ring does not fit shared memory");
     return 1;
@@ -516,17 +807,17 @@ extern "C" int moonep_combine_push(void* ctx, int roles, const int* src_info, co
                                                (int)imax((int)smem, 1024)),
                           "cudaFuncSetAttribute(combine_push_kernel)"))
     return rc;
+  const bool local = (roles & (MOONEP_ROLE_FOLD | MOONEP_ROLE_SUM)) != 0;
   int grid = 0;
   a.n_push = 0;
   if (roles & MOONEP_ROLE_PUSH) {
-    // num_sms bounds the CTAs that move data between ranks; with a single rank nothing leaves the GPU
-    const int want = n_push > 0 ? n_push : (direct ? imin(c.local_sms, h->sm_count) : c.num_sms);
-    a.n_push = imax(1, imin(want, h->sm_count - ((roles & MOONEP_ROLE_SUM) ? 1 : 0)));
+    // num_sms bounds the CTAs that move data between ranks
+    a.n_push = imax(1, imin(n_push > 0 ? n_push : c.num_sms, h->sm_count - (local ? 1 : 0)));
     grid = a.n_push;
   }
-  if (roles & MOONEP_ROLE_SUM) {
+  if (local) {
     const int room = imax(1, imin(c.local_sms, h->sm_count) - a.n_push);
-    grid += n_sum > 0 ? imin(n_sum, room) : room;
+    grid += n_local > 0 ? imin(n_local, room) : room;
   }
   combine_push_kernel<<<grid, kPushThreads, smem, (cudaStream_t)stream>>>(c, a);
   return check_launch("combine_push_kernel");

@@ -245,6 +245,8 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned pari
 
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// All state spaces: orders this thread's view of global memory written with ordinary stores before bulk copies it issues next.
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
 // global -> shared of this CTA, completion on an mbarrier.
 __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, unsigned bytes, unsigned long long* bar) {

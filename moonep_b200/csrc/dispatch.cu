@@ -182,7 +182,87 @@ __device__ __forceinline__ void release_row_flags(const MoonepDevCtx& c, int d, 
   if (lane < c.K && d >= 0) {
     int dest, loff;
     decode_dst(d, c.NvS, dest, loff);
-    if (dst_in_range(c, dest, loff)) st_release_sys(rowflag_ptr(c, dest, loff), epoch);
+    if (dst_in_range(c, dest, loff)) {
+      if (dest == c.rank)
+        st_release_gpu(rowflag_ptr(c, dest, loff), epoch);  // only kernels of this GPU read it
+      else
+        st_release_sys(rowflag_ptr(c, dest, loff), epoch);
+    }
+  }
+}
+
+// ---- row flags off the copy path ----------------------------------------------------------------
+//
+// Releasing a row flag costs a system-scope fence, which would stall the lane that drives the bulk copies.
+// Each bulk warp therefore hands the tokens whose copies have completed to a helper warp through a small
+// queue in shared memory; the helper re-reads the token's routing entries and releases the flags.
+
+constexpr int kFlagQ = 16;  // tokens a bulk warp may be ahead of its helper
+
+struct FlagQueue {
+  int tok[kBulkWarps][kFlagQ];
+  int head[kBulkWarps];  // tokens pushed so far (written by the bulk warp)
+  int tail[kBulkWarps];  // tokens consumed so far (written by the helper)
+  int done[kBulkWarps];  // 1 once the bulk warp has pushed its last token
+};
+
+__device__ __forceinline__ int lds_acquire(const int* p) {
+  int v;
+  asm volatile("ld.acquire.cta.shared::cta.s32 %0, [%1];" : "=r"(v) : "r"(smem_u32(p)) : "memory");
+  return v;
+}
+__device__ __forceinline__ void sts_release(int* p, int v) {
+  asm volatile("st.release.cta.shared::cta.s32 [%0], %1;" ::"r"(smem_u32(p)), "r"(v) : "memory");
+}
+
+// Bulk warp w, lane 0 only: the copies of `tok` are complete.
+__device__ __forceinline__ bool flagq_push(const MoonepDevCtx& c, FlagQueue& q, int w, int& pushed, int tok) {
+  if (pushed - lds_acquire(&q.tail[w]) >= kFlagQ) {
+    const unsigned long long t0 = globaltimer_ns();
+    unsigned spins = 0;
+    while (pushed - lds_acquire(&q.tail[w]) >= kFlagQ) {
+      if ((++spins & 255u) == 0 && (globaltimer_ns() - t0 > c.timeout_ns || poisoned(c))) return false;
+    }
+  }
+  q.tok[w][pushed % kFlagQ] = tok;
+  ++pushed;
+  sts_release(&q.head[w], pushed);
+  return true;
+}
+
+// Helper warp of bulk warp w: release the row flags of every token the bulk warp hands over.
+__device__ void flag_helper(const MoonepDevCtx& c, const DispatchArgs& a, int epoch, FlagQueue& q, int w) {
+  const int lane = threadIdx.x & 31;
+  int consumed = 0;
+  for (;;) {
+    int avail = 0;
+    if (lane == 0) {
+      const unsigned long long t0 = globaltimer_ns();
+      unsigned spins = 0;
+      for (;;) {
+        const int fin = lds_acquire(&q.done[w]);  // read before head: a token pushed before `done` is never missed
+        avail = lds_acquire(&q.head[w]) - consumed;
+        if (avail > 0) break;
+        if (fin) {
+          avail = -1;
+          break;
+        }
+        if ((++spins & 255u) == 0 && (globaltimer_ns() - t0 > c.timeout_ns || poisoned(c))) {
+          avail = -1;
+          break;
+        }
+        __nanosleep(64);
+      }
+    }
+    avail = __shfl_sync(0xffffffffu, avail, 0);
+    if (avail <= 0) break;
+    for (int i = 0; i < avail; ++i, ++consumed) {
+      const int tok = q.tok[w][consumed % kFlagQ];
+      const int d = lane < c.K ? a.dst[tok * c.K + lane] : -1;
+      release_row_flags(c, d, lane, epoch);
+    }
+    __syncwarp();
+    if (lane == 0) sts_release(&q.tail[w], consumed);
   }
 }
 
@@ -253,7 +333,7 @@ __device__ void send_ldst(const MoonepDevCtx& c, const DispatchArgs& a, int epoc
 // Runs in warps 0..kBulkWarps-1 of a sender CTA.  s_ring: [kBulkWarps][kBulkStages][chunk_bytes],
 // s_bar: [kBulkWarps][kBulkStages] initialised mbarriers (count 1).  Returns false after a timeout.
 __device__ bool send_bulk(const MoonepDevCtx& c, const DispatchArgs& a, int epoch, unsigned char* s_ring,
-                          unsigned long long* s_bar) {
+                          unsigned long long* s_bar, FlagQueue& fq) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   int* work = c.counters + MOONEP_CTR_SEND_WORK;
   const int H = c.H, K = c.K, S = c.S;
@@ -263,7 +343,8 @@ __device__ bool send_bulk(const MoonepDevCtx& c, const DispatchArgs& a, int epoc
   int ring_tok[kBulkStages], ring_chunk[kBulkStages], ring_d[kBulkStages];
   // what the row flags of an item need; one entry more than the ring has stages, because an item is flagged
   // (three items late) after the load of the item that reuses its stage has been issued
-  int flag_chunk[kBulkStages + 1], flag_d[kBulkStages + 1];
+  int flag_chunk[kBulkStages + 1], flag_tok[kBulkStages + 1];
+  int pushed = 0;  // lane 0: tokens handed to the helper warp
   int batch_next = 0, batch_end = 0, cur_chunk = 0;
   bool more = true;
   int loaded = 0, done = 0;
@@ -305,7 +386,7 @@ __device__ bool send_bulk(const MoonepDevCtx& c, const DispatchArgs& a, int epoc
     for (int q = 0; q < kBulkStages + 1; ++q)
       if (q == fs) {
         flag_chunk[q] = ch;
-        flag_d[q] = d;
+        flag_tok[q] = tok;
       }
     if (lane == 0) {
       const unsigned len = chunk_len(ch);
@@ -316,17 +397,20 @@ __device__ bool send_bulk(const MoonepDevCtx& c, const DispatchArgs& a, int epoc
     }
     ++loaded;
   };
-  // the stores of item j are complete: flag its rows if it was the last piece of its token
+  // the stores of item j are complete: if it was the last piece of its token, the helper warp flags the token's rows
   auto flag_item = [&](int j) {
     const int fs = j % (kBulkStages + 1);
-    int ch = 0, d = 0;
+    int ch = 0, ftok = 0;
 #pragma unroll
     for (int q = 0; q < kBulkStages + 1; ++q)
       if (q == fs) {
         ch = flag_chunk[q];
-        d = flag_d[q];
+        ftok = flag_tok[q];
       }
-    if (ch == a.nchunks - 1) release_row_flags(c, d, lane, epoch);
+    if (ch == a.nchunks - 1 && lane == 0 && !flagq_push(c, fq, warp, pushed, ftok)) {
+      record_status(c, MOONEP_STATUS_TIMEOUT, MOONEP_K_DISPATCH_SEND, 101, warp, pushed, ftok);
+      failed = true;  // lane 0 only; the loop condition below is evaluated after a warp-wide exchange
+    }
   };
 
   int tok, ch;
@@ -387,12 +471,15 @@ __device__ bool send_bulk(const MoonepDevCtx& c, const DispatchArgs& a, int epoc
       // all but the two most recent groups have completed: item done-3 is in its destinations' memory
       if (lane == 0) bulk_wait<kBulkStages - 1>();
       flag_item(done - kBulkStages);
+      failed = __shfl_sync(0xffffffffu, failed ? 1 : 0, 0) != 0;
     }
   }
   if (lane == 0) bulk_wait<0>();
   __syncwarp();
   if (!failed)
     for (int j = done >= kBulkStages ? done - kBulkStages + 1 : 0; j < done; ++j) flag_item(j);
+  if (lane == 0) sts_release(&fq.done[warp], 1);
+  __syncwarp();
   return !failed;
 }
 
@@ -478,8 +565,16 @@ __device__ bool expand_role(const MoonepDevCtx& c, const DispatchArgs& a, int xi
     // has a successor opens a group; walking the chain lists its duplicates in ascending k.
     const int* src_info = c.meta_peer[c.rank] + c.src_info_off;
     const int* link = c.meta_peer[c.rank] + c.link_off;
-    const int per_cta = (NvS + xcnt - 1) / xcnt;
-    const int lo = xidx * per_cta, hi = min(NvS, lo + per_cta);
+    // rows past the last group are unused: the CTAs share the used part of the shard (and mark the rest as empty
+    // in the plan's copies)
+    int used = a.cu_seqlens != nullptr ? a.cu_seqlens[c.E + c.B - 1] : NvS;
+    if (used < 0 || used > NvS) used = NvS;
+    for (int loff = used + xidx * blockDim.x + threadIdx.x; loff < NvS; loff += xcnt * blockDim.x) {
+      if (a.plan_src_info != nullptr) a.plan_src_info[loff] = -1;
+      if (a.plan_link != nullptr) a.plan_link[loff] = 0;
+    }
+    const int per_cta = (used + xcnt - 1) / xcnt;
+    const int lo = xidx * per_cta, hi = min(used, lo + per_cta);
     for (int s0 = lo; s0 < hi && ok; s0 += kExpandSlice) {
       const int s1 = min(hi, s0 + kExpandSlice);
       if (threadIdx.x == 0) s_ngroups = 0;
@@ -586,9 +681,15 @@ __global__ void __launch_bounds__(kDispatchThreads, 1) dispatch_kernel(const Moo
   extern __shared__ __align__(128) unsigned char s_dyn[];  // sender ring / planner tables / expert histogram
   __shared__ __align__(8) unsigned long long s_bar[kBulkWarps * kBulkStages];
   __shared__ TokenScratch s_tok;
+  __shared__ FlagQueue s_fq;
   const int roles = a.roles;
   const int warp = threadIdx.x >> 5;
   if (threadIdx.x < kBulkWarps * kBulkStages) mbar_init(s_bar + threadIdx.x, 1);
+  if (threadIdx.x < kBulkWarps) {
+    s_fq.head[threadIdx.x] = 0;
+    s_fq.tail[threadIdx.x] = 0;
+    s_fq.done[threadIdx.x] = 0;
+  }
   fence_barrier_init();
   __syncthreads();
   bool ok = !poisoned(c);
@@ -655,7 +756,10 @@ __global__ void __launch_bounds__(kDispatchThreads, 1) dispatch_kernel(const Moo
     const int epoch = abs_epoch(c, MOONEP_FLAG_SENT, a.epoch_sent);
     if (ok) {
       if (a.bulk) {
-        if (warp < kBulkWarps) send_bulk(c, a, epoch, s_dyn, s_bar);
+        if (warp < kBulkWarps)
+          send_bulk(c, a, epoch, s_dyn, s_bar, s_fq);
+        else if (warp < 2 * kBulkWarps)
+          flag_helper(c, a, epoch, s_fq, warp - kBulkWarps);
       } else {
         send_ldst(c, a, epoch);
       }

@@ -76,6 +76,7 @@
 #define MOONEP_CTR_SUM_WORK 24       // token hand-out of the combine sum role
 #define MOONEP_CTR_COMBINE_ARRIVE 25 // CTAs of the push-combine kernel that reached its end
 #define MOONEP_CTR_PREFETCH_ARRIVE 26  // CTAs of the prefetch kernel that reached its end
+#define MOONEP_CTR_FOLD_WORK 27      // group hand-out of the combine fold role
 // stats[MOONEP_STAT_WAIT_MAX_NS + family]: longest time CTA 0 of any kernel spun on a flag of that family (ns);
 // stats[MOONEP_STAT_WAIT_COUNT + family]: number of such waits that did not find the flag already set.
 #define MOONEP_STAT_WAIT_MAX_NS 0
@@ -96,8 +97,9 @@
 #define MOONEP_ROLE_SEND 4     // push rows, gate weights and row flags
 #define MOONEP_ROLE_EXPAND 8   // zero fill, duplicate map, duplicate expansion as rows arrive
 // Roles of the push-combine kernel.
-#define MOONEP_ROLE_PUSH 1     // expert side: fold duplicates, push rows to the tokens' home ranks
+#define MOONEP_ROLE_PUSH 1     // expert side: copy primary rows (folded where they have duplicates) to the tokens' home ranks
 #define MOONEP_ROLE_SUM 2      // home side: sum the rows of a token as they arrive
+#define MOONEP_ROLE_FOLD 4     // expert side: fold the duplicate groups into a local buffer
 
 // Routing entries per planner block (whole tokens, at most this many entries).
 #define MOONEP_PLAN_BLOCK 512
@@ -190,13 +192,15 @@ int moonep_combine_prologue(void* ctx, const int* dup_groups, const int* dup_lof
                             int signal_epoch_comb, void* stream);
 int moonep_combine_pull(void* ctx, const int* dst, void* out_hidden, float* out_weights, int wait_epoch_comb,
                         int path, void* stream);
-// Push combine (combine_push.cu): roles MOONEP_ROLE_PUSH | MOONEP_ROLE_SUM.  Needs the Buffer's staging memory
-// (stage_peers of moonep_ctx_create, laid out by moonep_stage_layout) and the plan's copies of src_info and link words.
+// Push combine (combine_push.cu): roles MOONEP_ROLE_FOLD | MOONEP_ROLE_PUSH | MOONEP_ROLE_SUM.  Needs the Buffer's staging
+// memory (stage_peers of moonep_ctx_create, laid out by moonep_stage_layout), the plan's copies of src_info and link
+// words, and local scratch for the folded rows.
 long long moonep_stage_layout(int S, int K, int H, int kp, long long* flag_off, long long* w_off);
 int moonep_combine_push(void* ctx, int roles, const int* src_info, const int* link, const int* dst, const void* in_rows,
                         const float* in_w, void* out_hidden, float* out_weights, int wait_family, int wait_epoch,
                         int epoch_comb, const int* ready, int ready_expect, const int* dup_groups, const int* dup_loffs,
-                        const int* dup_counts, int n_push, int n_sum, void* stream);
+                        const int* dup_counts, void* fold_buf, int* fold_flag, int fold_rows, int n_push, int n_local,
+                        void* stream);
 
 // Expert weights: src[i] is [nexperts, H, Hp] bf16 (peer mapped), dst[i] is [nslots, H, Hp] bf16 (local).
 int moonep_prefetch(void* ctx, void* const* src3, void* const* dst3, int n_tensors, const int* experts_to_copy_row,

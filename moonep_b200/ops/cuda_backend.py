@@ -44,7 +44,7 @@ _KERNEL_NAMES = {
     13: "grouped_gemm", 14: "grouped_wgrad", 15: "grouped_gemm_pair", 16: "combine_push", 17: "combine_sum",
 }  # fmt: skip
 ROLE_TABLES, ROLE_TOKENS, ROLE_SEND, ROLE_EXPAND = 1, 2, 4, 8
-ROLE_PUSH, ROLE_SUM = 1, 2
+ROLE_PUSH, ROLE_SUM, ROLE_FOLD = 1, 2, 4
 _FAMILY_NAMES = {0: "READY", 1: "TPE", 2: "PLAN", 3: "SENT", 4: "COMB", 5: "GRAD_READY", 6: "GRAD_DONE"}
 
 
@@ -96,7 +96,7 @@ class CudaBackend:
         c["alloc"] = self.tables[2 * E : 2 * E + R * E]
         # Emulated ranks share one GPU and one stream: a kernel of one rank must never wait for a kernel of another
         # rank that is launched later, so they run the dispatch and combine kernels one role per phase.
-        self.phased = bool(getattr(world, "emulated", False)) and world.size > 1
+        self.phased = (bool(getattr(world, "emulated", False)) and world.size > 1) or config.force_phased()
         self.combine_mode = config.combine_mode()
         self.n_expand = 0  # CTAs of the dispatch kernel's destination-side role; 0 = every SM the senders leave free
 
@@ -369,7 +369,11 @@ class CudaBackend:
             if not self.phased:
                 self._dispatch_launch(plan_roles | ROLE_SEND | ROLE_EXPAND, True, plan, tag="dispatch_fused", **kw)
             else:
-                self._dispatch_launch(plan_roles | ROLE_SEND, True, plan, tag="dispatch_plan_send", **kw)
+                if config.force_phased() and plan_roles:  # per-role timing: planner and send as separate launches
+                    self._dispatch_launch(plan_roles, True, plan, tag="dispatch_plan", **kw)
+                    self._dispatch_launch(ROLE_SEND, True, plan, tag="dispatch_send", **kw)
+                else:
+                    self._dispatch_launch(plan_roles | ROLE_SEND, True, plan, tag="dispatch_plan_send", **kw)
                 self.world.step()
                 self._dispatch_launch(ROLE_EXPAND, True, plan, tag="dispatch_expand", **kw)
             self._quiesced = True
@@ -445,18 +449,32 @@ class CudaBackend:
             return
         self._quiesced = False
         comb = self._next(FLAG_COMB)
+        fold_buf, fold_flag = self._fold_scratch()
         args = (_ptr(plan.src_info), _ptr(plan.link), _ptr(plan.dst), _ptr(hidden_nvsh), _ptr(route_weights_nvs),
                 _ptr(out_hidden), _ptr(out_weights_sk), wf, we, comb, _ptr(ready), int(ready_expect),
-                _ptr(plan.dup_groups), _ptr(plan.dup_loffs), _ptr(plan.dup_counts), 0, 0, _stream())  # fmt: skip
-        if self.ctx["R"] == 1:  # nothing to stage: the push role writes the results itself
-            self._call("moonep_combine_push", ROLE_PUSH, *args, tag="combine_fold")
+                _ptr(plan.dup_groups), _ptr(plan.dup_loffs), _ptr(plan.dup_counts), _ptr(fold_buf), _ptr(fold_flag),
+                int(fold_flag.numel()), 0, 0, _stream())  # fmt: skip
+        if self.ctx["R"] == 1:  # nothing to stage: the fold role writes the results itself
+            self._call("moonep_combine_push", ROLE_FOLD, *args, tag="combine_fold")
         elif not self.phased:
-            self._call("moonep_combine_push", ROLE_PUSH | ROLE_SUM, *args, tag="combine_push_sum")
+            self._call("moonep_combine_push", ROLE_FOLD | ROLE_PUSH | ROLE_SUM, *args, tag="combine_fused")
         else:
+            self._call("moonep_combine_push", ROLE_FOLD, *args, tag="combine_fold")
             self._call("moonep_combine_push", ROLE_PUSH, *args, tag="combine_push")
             self.world.step()
             self._call("moonep_combine_push", ROLE_SUM, *args, tag="combine_sum")
         self.world.step()
+
+    def _fold_scratch(self):
+        """Local scratch of the push combine: one folded row and one flag per duplicate group (a group has at least two
+        rows of the shard, so there are at most NvS/2 of them).  A single rank folds straight into the output."""
+        if getattr(self, "_fold", None) is None:
+            c = self.ctx
+            rows = 1 if c["R"] == 1 else c["NvS"] // 2 + 1
+            dev = c["device"]
+            self._fold = (torch.empty(rows, c["H"], dtype=torch.bfloat16, device=dev),
+                          torch.zeros(c["NvS"] // 2 + 1, dtype=torch.int32, device=dev))  # fmt: skip
+        return self._fold
 
     def combine_prologue(self, plan, hidden_nvsh, route_weights_nvs, zero_copy, wait=None):
         wf = -1 if wait is None else int(wait)
