@@ -35,7 +35,8 @@ namespace {
 
 constexpr int kPushThreads = 512;
 constexpr int kPushMaxChunk = 16384;    // bytes of a row piece (one ring stage)
-constexpr int kPushRowBatch = 8;        // rows handed out per grab
+constexpr int kPushRowBatch = 32;       // rows handed out per grab (the primaries without duplicates among them are sent)
+constexpr int kPushGroupBatch = 8;      // duplicate groups handed out per grab
 constexpr int kFoldVec = 4;             // int4 per lane per inner step (2 KB per warp)
 constexpr int kFoldRows = 4;            // rows of a duplicate group whose loads are in flight together
 constexpr int kSumVec = 4;
@@ -203,6 +204,14 @@ __device__ void fold_role(const MoonepDevCtx& c, const PushArgs& a) {
       if (!ok) return;
     }
     uint16_t* o = a.fold_buf + (long long)item * H;
+    if (!a.direct && a.in_w != nullptr && lane < n_rows) {
+      // gate weights of all entries of this group travel to the home rank's weight staging
+      const int s_q = a.src_info[my_row];
+      const int home = a.src_info[prow] / NvS;
+      const int slot_q = s_q - home * NvS;
+      if (s_q >= 0 && home >= 0 && home < c.R && slot_q >= 0 && slot_q < S * K)
+        reinterpret_cast<float*>(c.stage_peer[home] + c.stage_w_off)[slot_q] = a.in_w[my_row];
+    }
     if (a.direct) {
       const int p_si = a.src_info[prow];
       const int slot = p_si % NvS;
@@ -268,7 +277,11 @@ __device__ void fold_role(const MoonepDevCtx& c, const PushArgs& a) {
       }
     }
     __syncwarp();
-    if (lane == 0 && !a.direct) st_release_gpu(a.fold_flag + item, epoch);
+    if (lane == 0 && !a.direct) {
+      // the weights went to another GPU: they must have arrived before the PUSH role's flag for this row can
+      if (a.in_w != nullptr) fence_sys(); else fence_gpu();
+      st_relaxed_gpu(a.fold_flag + item, epoch);
+    }
   }
 }
 
@@ -283,9 +296,13 @@ __device__ void fold_role(const MoonepDevCtx& c, const PushArgs& a) {
 
 constexpr int kMoveWarps = 4;
 constexpr int kMoveStages = 3;
-constexpr int kMoveQ = 16;
+constexpr int kMoveQ = 32;
+// A row is flagged once its bulk group has completed on the home rank, which takes several microseconds over NVLink;
+// the copy loop looks kMoveLag items back so that the completion wait never stalls the issue of new copies.
+constexpr int kMoveLag = 12;
 
 struct MoveQueue {
+  int* lagged[kMoveWarps][kMoveLag + 2];  // flag of every item in flight that is the last piece of its row, else null
   int* flag[kMoveWarps][kMoveQ];
   int head[kMoveWarps], tail[kMoveWarps], done[kMoveWarps];
 };
@@ -324,32 +341,61 @@ __device__ void move_helper(const MoonepDevCtx& c, int epoch, MoveQueue& q, int 
     }
     avail = __shfl_sync(0xffffffffu, avail, 0);
     if (avail <= 0) break;
-    if (lane < avail) st_release_sys(q.flag[w][(consumed + lane) % kMoveQ], epoch);
+    // a system-scope fence waits for everything this SM has in flight, so it is paid once per batch
+    if (lane == 0) {
+      fence_sys();
+      for (int i = 0; i < avail; ++i) st_relaxed_sys(q.flag[w][(consumed + i) % kMoveQ], epoch);
+    }
     consumed += avail;
     __syncwarp();
     if (lane == 0) sts_release(&q.tail[w], consumed);
   }
 }
 
-// Job generator of the PUSH role: one job = one row to stage on its home rank.  All lanes of a warp call next()
-// together; the results are warp-uniform.
+// Job generator of the PUSH role: one job = one row to stage on its home rank.  Work is handed out in batches of
+// kPushRowBatch rows (or groups): the lanes of the warp read the metadata of a whole batch in parallel (row ->
+// src_info / link -> home rank, staging slot; the row's gate weight goes to the home rank on the way), then the
+// jobs of the batch are taken one by one without further memory traffic.  All lanes call next() together; its
+// results are warp-uniform.
 struct PushJobs {
   const MoonepDevCtx& c;
   const PushArgs& a;
-  int lane, epoch, ngroups, nbatches;
-  unsigned pend;   // singles of the current batch still to send
-  int b_base, b_si;
+  int lane, epoch, ngroups, nbatches, ngbatches;
+  unsigned pend;  // jobs of the current batch still to hand out
+  // this lane's job of the current batch
+  const unsigned char* j_src;
+  unsigned char* j_dst;
+  int* j_flag;
+  int j_g, j_row;
   bool failed, drained;
 
   __device__ PushJobs(const MoonepDevCtx& c_, const PushArgs& a_, int epoch_)
-      : c(c_), a(a_), lane(threadIdx.x & 31), epoch(epoch_), pend(0), b_base(0), b_si(-1), failed(false), drained(false) {
+      : c(c_), a(a_), lane(threadIdx.x & 31), epoch(epoch_), pend(0), j_src(nullptr), j_dst(nullptr), j_flag(nullptr),
+        j_g(-1), j_row(-1), failed(false), drained(false) {
     ngroups = a.dup_counts[0];
     if (ngroups < 0 || ngroups > a.fold_rows) ngroups = 0;
     nbatches = (c.NvS + kPushRowBatch - 1) / kPushRowBatch;
+    ngbatches = (ngroups + kPushGroupBatch - 1) / kPushGroupBatch;
   }
 
-  // (prow, p_si, p_l) describe a primary row; lanes < n_rows hold its group's rows in my_row
-  __device__ bool describe(int prow, int p_si, int p_l, int my_row, int n_rows, unsigned char*& dst, int*& flag) {
+  // Bounded wait of this lane until *f >= want; false on timeout (status recorded).
+  __device__ bool lane_wait(const int* f, int want, int what, int id) {
+    int v;
+    if ((v = ld_acquire_gpu(f)) - want >= 0) return true;
+    const unsigned long long t0 = globaltimer_ns();
+    unsigned spins = 0;
+    while ((v = ld_acquire_gpu(f)) - want < 0) {
+      if ((++spins & 63u) == 0 && (globaltimer_ns() - t0 > c.timeout_ns || poisoned(c))) {
+        record_status(c, MOONEP_STATUS_TIMEOUT, MOONEP_K_COMBINE_PUSH, what, id, want, v);
+        return false;
+      }
+      __nanosleep(128);
+    }
+    return true;
+  }
+
+  // this lane's primary row `prow` (p_si, p_l its src_info and link word): where it goes; false if the words are bad
+  __device__ bool describe(int prow, int p_si, int p_l) {
     const int NvS = c.NvS, K = c.K, S = c.S;
     const int home = p_si / NvS;
     const int slot = p_si - home * NvS;
@@ -360,16 +406,10 @@ struct PushJobs {
       return false;
     }
     unsigned char* stage_home = c.stage_peer[home];
-    // gate weights of all entries of this group travel to the home rank's weight staging
-    if (a.in_w != nullptr && lane < n_rows && my_row >= 0 && my_row < NvS) {
-      const int s_q = a.src_info[my_row];
-      const int slot_q = s_q - home * NvS;
-      if (s_q >= 0 && slot_q >= 0 && slot_q < S * K)
-        reinterpret_cast<float*>(stage_home + c.stage_w_off)[slot_q] = a.in_w[my_row];
-    }
     const long long stage_row = (long long)token * c.kp + ord;
-    dst = stage_home + stage_row * ((long long)c.H * 2);
-    flag = reinterpret_cast<int*>(stage_home + c.stage_flag_off) + stage_row;
+    j_dst = stage_home + stage_row * ((long long)c.H * 2);
+    j_flag = reinterpret_cast<int*>(stage_home + c.stage_flag_off) + stage_row;
+    j_row = prow;
     return true;
   }
 
@@ -380,65 +420,62 @@ struct PushJobs {
       if (pend) {
         const int j = __ffs(pend) - 1;
         pend &= pend - 1;
-        const int p_si = __shfl_sync(0xffffffffu, b_si, j);
-        const int prow = b_base + j;
-        if (!wait_block_ready(c, a, prow, lane)) {
-          failed = true;
-          return false;
-        }
-        if (!describe(prow, p_si, a.link[prow], lane == 0 ? prow : -1, 1, dst, flag)) continue;
-        src = reinterpret_cast<const unsigned char*>(a.in_rows) + (long long)prow * row_bytes;
-        if (a.ready != nullptr) fence_proxy_async_all();  // rows written by other SMs are about to be read by bulk copies
+        src = reinterpret_cast<const unsigned char*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(j_src), j));
+        dst = reinterpret_cast<unsigned char*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(j_dst), j));
+        flag = reinterpret_cast<int*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(j_flag), j));
         return true;
       }
       int item = 0;
       if (lane == 0) item = atomicAdd(c.counters + MOONEP_CTR_PUSH_WORK, 1);
       item = __shfl_sync(0xffffffffu, item, 0);
-      if (item >= nbatches + ngroups) {
+      if (item >= nbatches + ngbatches) {
         drained = true;
         return false;
       }
+      bool mine = false;
+      j_g = -1;
       if (item < nbatches) {
-        b_base = item * kPushRowBatch;
-        b_si = -1;
-        int l = 0;
-        if (lane < kPushRowBatch && b_base + lane < c.NvS) {
-          b_si = a.src_info[b_base + lane];
-          l = b_si >= 0 ? a.link[b_base + lane] : 0;
-        }
-        pend = __ballot_sync(0xffffffffu, b_si >= 0 && (l & MOONEP_LINK_PRIMARY) && !(l & MOONEP_LINK_HAS_NEXT));
-        continue;
-      }
-      const int g = item - nbatches;
-      int prow, dn;
-      const int my_row = group_rows(c, a, g, lane, prow, dn, MOONEP_K_COMBINE_PUSH);
-      if (__shfl_sync(0xffffffffu, my_row, 0) < 0) continue;
-      // wait (bounded) for the FOLD role
-      int ok = 1;
-      if (lane == 0) {
-        const int* f = a.fold_flag + g;
-        if (ld_acquire_gpu(f) - epoch < 0) {
-          const unsigned long long t0 = globaltimer_ns();
-          unsigned spins = 0;
-          int v;
-          while ((v = ld_acquire_gpu(f)) - epoch < 0) {
-            if ((++spins & 63u) == 0 && (globaltimer_ns() - t0 > c.timeout_ns || poisoned(c))) {
-              record_status(c, MOONEP_STATUS_TIMEOUT, MOONEP_K_COMBINE_PUSH, 203, g, epoch, v);
-              ok = 0;
-              break;
+        // rows without duplicates are sent as they are; their gate weight goes along
+        const int row = item * kPushRowBatch + lane;
+        if (lane < kPushRowBatch && row < c.NvS) {
+          const int si = a.src_info[row];
+          const int l = si >= 0 ? a.link[row] : 0;
+          if (si >= 0 && (l & MOONEP_LINK_PRIMARY) && !(l & MOONEP_LINK_HAS_NEXT) && describe(row, si, l)) {
+            mine = true;
+            j_src = reinterpret_cast<const unsigned char*>(a.in_rows) + (long long)row * row_bytes;
+            if (a.in_w != nullptr) {
+              const int home = si / c.NvS;
+              reinterpret_cast<float*>(c.stage_peer[home] + c.stage_w_off)[si - home * c.NvS] = a.in_w[row];
             }
-            __nanosleep(128);
+          }
+        }
+      } else {
+        // duplicate groups: the folded row comes from the FOLD role's buffer (which also sent the weights)
+        const int g = (item - nbatches) * kPushGroupBatch + lane;
+        if (lane < kPushGroupBatch && g < ngroups) {
+          const int prow = a.dup_groups[3 * g];
+          if (prow >= 0 && prow < c.NvS) {
+            if (describe(prow, a.src_info[prow], a.link[prow])) {
+              mine = true;
+              j_g = g;
+              j_src = reinterpret_cast<const unsigned char*>(a.fold_buf) + (long long)g * row_bytes;
+            }
+          } else {
+            record_status(c, MOONEP_STATUS_BAD_INDEX, MOONEP_K_COMBINE_PUSH, 9, prow, g, 0);
           }
         }
       }
-      if (!__shfl_sync(0xffffffffu, ok, 0)) {
+      // The rows of the batch must be final before bulk copies read them: groups wait for the FOLD role, rows of a
+      // producer that runs beside this kernel for its block counters.  One proxy fence per batch, not per row.
+      bool ok = true;
+      if (mine && j_g >= 0) ok = lane_wait(a.fold_flag + j_g, epoch, 203, j_g);
+      if (mine && j_g < 0 && a.ready != nullptr) ok = lane_wait(a.ready + (j_row >> 7), a.ready_expect, 201, j_row >> 7);
+      if (!__all_sync(0xffffffffu, ok)) {
         failed = true;
         return false;
       }
-      if (!describe(prow, a.src_info[prow], a.link[prow], my_row, 1 + dn, dst, flag)) continue;
-      src = reinterpret_cast<const unsigned char*>(a.fold_buf) + (long long)g * row_bytes;
-      fence_proxy_async_all();  // the FOLD role's stores are about to be read by bulk copies
-      return true;
+      pend = __ballot_sync(0xffffffffu, mine);
+      if (pend && (item >= nbatches || a.ready != nullptr)) fence_proxy_async_all();
     }
   }
 };
@@ -492,7 +529,6 @@ __device__ void push_role(const MoonepDevCtx& c, const PushArgs& a, unsigned cha
   // three-stage ring, as in the dispatch send role: the load of item i+1 is in flight while item i is stored
   unsigned char* r_dst[kMoveStages];
   unsigned r_len[kMoveStages];
-  int* r_flag[kMoveStages + 1];  // one entry more than stages: an item is flagged three items late
   int loaded = 0, done = 0, pushed = 0;
   auto issue_load = [&](const unsigned char* src, unsigned char* dst, unsigned len, int* flag) {
     const int s = loaded % kMoveStages;
@@ -502,22 +538,15 @@ __device__ void push_role(const MoonepDevCtx& c, const PushArgs& a, unsigned cha
         r_dst[q] = dst;
         r_len[q] = len;
       }
-    const int fs = loaded % (kMoveStages + 1);
-#pragma unroll
-    for (int q = 0; q < kMoveStages + 1; ++q)
-      if (q == fs) r_flag[q] = flag;
     if (lane == 0) {
+      mq.lagged[w][loaded % (kMoveLag + 2)] = flag;
       mbar_expect_tx(s_bar + s, len);
       bulk_g2s(s_ring + (size_t)s * a.chunk_bytes, src, len, s_bar + s);
     }
     ++loaded;
   };
   auto flag_item = [&](int j) {
-    const int fs = j % (kMoveStages + 1);
-    int* flag = nullptr;
-#pragma unroll
-    for (int q = 0; q < kMoveStages + 1; ++q)
-      if (q == fs) flag = r_flag[q];
+    int* flag = lane == 0 ? mq.lagged[w][j % (kMoveLag + 2)] : nullptr;
     if (flag != nullptr && lane == 0) {
       if (pushed - lds_acquire(&mq.tail[w]) >= kMoveQ) {
         const unsigned long long t0 = globaltimer_ns();
@@ -573,16 +602,16 @@ __device__ void push_role(const MoonepDevCtx& c, const PushArgs& a, unsigned cha
       bulk_commit();
     }
     ++done;
-    if (done >= kMoveStages) {
-      if (lane == 0) bulk_wait<kMoveStages - 1>();  // item done-3 has reached its home rank
-      flag_item(done - kMoveStages);
+    if (done > kMoveLag) {
+      if (lane == 0) bulk_wait<kMoveLag>();  // item done-1-kMoveLag has reached its home rank
+      flag_item(done - 1 - kMoveLag);
       failed = __shfl_sync(0xffffffffu, failed ? 1 : 0, 0) != 0;
     }
   }
   if (lane == 0) bulk_wait<0>();
   __syncwarp();
   if (!failed)
-    for (int j = done >= kMoveStages ? done - kMoveStages + 1 : 0; j < done; ++j) flag_item(j);
+    for (int j = done > kMoveLag ? done - kMoveLag : 0; j < done; ++j) flag_item(j);
   if (lane == 0) sts_release(&mq.done[w], 1);
   __syncwarp();
 }

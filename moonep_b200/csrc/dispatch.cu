@@ -152,8 +152,17 @@ __device__ void zero_fill_rows(const MoonepDevCtx& c, const int* __restrict__ ze
           for (int i = lane; i < H; i += 32) p[i] = 0;
         }
         if (with_weights && lane == 0) wbuf[row] = 0.f;
+      }
+      // one fence for the rows this warp cleared in the range, then their flags
+      if (first < np) {
         __syncwarp();
-        if (lane == 0) st_release_gpu(rowflag + row, epoch);
+        if (lane == 0) {
+          fence_gpu();
+          for (int r = first; r < np; r += warps_total) {
+            const int row = s0 + r;
+            if (row >= 0 && row < c.NvS) st_relaxed_gpu(rowflag + row, epoch);
+          }
+        }
       }
     }
   }
@@ -197,9 +206,14 @@ __device__ __forceinline__ void release_row_flags(const MoonepDevCtx& c, int d, 
 // Each bulk warp therefore hands the tokens whose copies have completed to a helper warp through a small
 // queue in shared memory; the helper re-reads the token's routing entries and releases the flags.
 
-constexpr int kFlagQ = 16;  // tokens a bulk warp may be ahead of its helper
+constexpr int kFlagQ = 32;  // tokens a bulk warp may be ahead of its helper
+// A row is flagged once its bulk group has completed at the destination, which takes several microseconds over
+// NVLink; the copy loop therefore looks kFlagLag items back, so that the completion wait never stalls the issue of
+// new copies (the shared-memory stages are recycled as soon as they have been read, as before).
+constexpr int kFlagLag = 12;
 
 struct FlagQueue {
+  int lagged[kBulkWarps][kFlagLag + 2];  // token of every item in flight whose last piece it is, else -1
   int tok[kBulkWarps][kFlagQ];
   int head[kBulkWarps];  // tokens pushed so far (written by the bulk warp)
   int tail[kBulkWarps];  // tokens consumed so far (written by the helper)
@@ -256,10 +270,25 @@ __device__ void flag_helper(const MoonepDevCtx& c, const DispatchArgs& a, int ep
     }
     avail = __shfl_sync(0xffffffffu, avail, 0);
     if (avail <= 0) break;
+    // A system-scope fence waits for everything this SM has in flight, so it is paid once per batch: lane 0
+    // fences, then stores the flags of all tokens that have queued up meanwhile.
+    if (lane == 0) fence_sys();
     for (int i = 0; i < avail; ++i, ++consumed) {
       const int tok = q.tok[w][consumed % kFlagQ];
-      const int d = lane < c.K ? a.dst[tok * c.K + lane] : -1;
-      release_row_flags(c, d, lane, epoch);
+      int* f = nullptr;
+      if (lane < c.K) {
+        const int d = a.dst[tok * c.K + lane];
+        int dest, loff;
+        decode_dst(d, c.NvS, dest, loff);
+        if (d >= 0 && dst_in_range(c, dest, loff)) f = rowflag_ptr(c, dest, loff);
+      }
+      unsigned m = __ballot_sync(0xffffffffu, f != nullptr);
+      while (m) {
+        const int kk = __ffs(m) - 1;
+        m &= m - 1;
+        int* fk = reinterpret_cast<int*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(f), kk));
+        if (lane == 0) st_relaxed_sys(fk, epoch);
+      }
     }
     __syncwarp();
     if (lane == 0) sts_release(&q.tail[w], consumed);
@@ -341,9 +370,6 @@ __device__ bool send_bulk(const MoonepDevCtx& c, const DispatchArgs& a, int epoc
   unsigned char* ring = s_ring + (size_t)warp * kBulkStages * a.chunk_bytes;
   unsigned long long* bar = s_bar + warp * kBulkStages;
   int ring_tok[kBulkStages], ring_chunk[kBulkStages], ring_d[kBulkStages];
-  // what the row flags of an item need; one entry more than the ring has stages, because an item is flagged
-  // (three items late) after the load of the item that reuses its stage has been issued
-  int flag_chunk[kBulkStages + 1], flag_tok[kBulkStages + 1];
   int pushed = 0;  // lane 0: tokens handed to the helper warp
   int batch_next = 0, batch_end = 0, cur_chunk = 0;
   bool more = true;
@@ -381,14 +407,8 @@ __device__ bool send_bulk(const MoonepDevCtx& c, const DispatchArgs& a, int epoc
         ring_chunk[q] = ch;
         ring_d[q] = d;
       }
-    const int fs = loaded % (kBulkStages + 1);
-#pragma unroll
-    for (int q = 0; q < kBulkStages + 1; ++q)
-      if (q == fs) {
-        flag_chunk[q] = ch;
-        flag_tok[q] = tok;
-      }
     if (lane == 0) {
+      fq.lagged[warp][loaded % (kFlagLag + 2)] = (ch == a.nchunks - 1) ? tok : -1;
       const unsigned len = chunk_len(ch);
       mbar_expect_tx(bar + s, len);
       bulk_g2s(ring + (size_t)s * a.chunk_bytes,
@@ -399,17 +419,12 @@ __device__ bool send_bulk(const MoonepDevCtx& c, const DispatchArgs& a, int epoc
   };
   // the stores of item j are complete: if it was the last piece of its token, the helper warp flags the token's rows
   auto flag_item = [&](int j) {
-    const int fs = j % (kBulkStages + 1);
-    int ch = 0, ftok = 0;
-#pragma unroll
-    for (int q = 0; q < kBulkStages + 1; ++q)
-      if (q == fs) {
-        ch = flag_chunk[q];
-        ftok = flag_tok[q];
+    if (lane == 0) {
+      const int ftok = fq.lagged[warp][j % (kFlagLag + 2)];
+      if (ftok >= 0 && !flagq_push(c, fq, warp, pushed, ftok)) {
+        record_status(c, MOONEP_STATUS_TIMEOUT, MOONEP_K_DISPATCH_SEND, 101, warp, pushed, ftok);
+        failed = true;  // lane 0 only; the loop condition below is evaluated after a warp-wide exchange
       }
-    if (ch == a.nchunks - 1 && lane == 0 && !flagq_push(c, fq, warp, pushed, ftok)) {
-      record_status(c, MOONEP_STATUS_TIMEOUT, MOONEP_K_DISPATCH_SEND, 101, warp, pushed, ftok);
-      failed = true;  // lane 0 only; the loop condition below is evaluated after a warp-wide exchange
     }
   };
 
@@ -467,17 +482,17 @@ __device__ bool send_bulk(const MoonepDevCtx& c, const DispatchArgs& a, int epoc
     }
     if (lane == 0) bulk_commit();
     ++done;
-    if (done >= kBulkStages) {
-      // all but the two most recent groups have completed: item done-3 is in its destinations' memory
-      if (lane == 0) bulk_wait<kBulkStages - 1>();
-      flag_item(done - kBulkStages);
+    if (done > kFlagLag) {
+      // all but the kFlagLag most recent groups have completed: item done-1-kFlagLag is in its destinations' memory
+      if (lane == 0) bulk_wait<kFlagLag>();
+      flag_item(done - 1 - kFlagLag);
       failed = __shfl_sync(0xffffffffu, failed ? 1 : 0, 0) != 0;
     }
   }
   if (lane == 0) bulk_wait<0>();
   __syncwarp();
   if (!failed)
-    for (int j = done >= kBulkStages ? done - kBulkStages + 1 : 0; j < done; ++j) flag_item(j);
+    for (int j = done > kFlagLag ? done - kFlagLag : 0; j < done; ++j) flag_item(j);
   if (lane == 0) sts_release(&fq.done[warp], 1);
   __syncwarp();
   return !failed;
@@ -519,8 +534,13 @@ __device__ void expand_group(const MoonepDevCtx& c, int primary, int my_dup, int
       for (int i = lane; i < H; i += 32) o[i] = src[i];
     }
   }
+  // one fence for the group (a fence waits for everything the warp has in flight), then its rows' flags
   __syncwarp();
-  if (lane < dn && my_dup >= 0 && my_dup < c.NvS) st_release_gpu(c.meta_peer[c.rank] + c.rowflag_off + my_dup, epoch);
+  if (lane == 0) fence_gpu();
+  for (int q = 0; q < dn && q < 32; ++q) {
+    const int row = __shfl_sync(0xffffffffu, my_dup, q);
+    if (lane == 0 && row >= 0 && row < c.NvS) st_relaxed_gpu(c.meta_peer[c.rank] + c.rowflag_off + row, epoch);
+  }
 }
 
 // Warp-wide bounded wait until row `loff` of the local shard carries `epoch`.
