@@ -34,7 +34,7 @@ namespace moonep {
 namespace {
 
 constexpr int kPushThreads = 512;
-constexpr int kPushMaxChunk = 16384;    // bytes of a row piece (one ring stage)
+constexpr int kPushMaxChunk = 8192;     // bytes of a row piece (one ring stage): 8 warps x 3 stages x 7 KB for H=7168
 constexpr int kPushRowBatch = 32;       // rows handed out per grab (the primaries without duplicates among them are sent)
 constexpr int kPushGroupBatch = 8;      // duplicate groups handed out per grab
 constexpr int kFoldVec = 4;             // int4 per lane per inner step (2 KB per warp)
@@ -294,7 +294,7 @@ __device__ void fold_role(const MoonepDevCtx& c, const PushArgs& a) {
 // counter: first batches of rows, of which the primaries without duplicates are sent as they are (they depend on
 // nothing), then the duplicate groups in the order the FOLD role finishes them.
 
-constexpr int kMoveWarps = 4;
+constexpr int kMoveWarps = 8;
 constexpr int kMoveStages = 3;
 constexpr int kMoveQ = 32;
 // A row is flagged once its bulk group has completed on the home rank, which takes several microseconds over NVLink;
@@ -718,8 +718,15 @@ __device__ void sum_role(const MoonepDevCtx& c, const PushArgs& a) {
   }
 }
 
-__global__ void __launch_bounds__(kPushThreads, 1) combine_push_kernel(const MoonepDevCtx c, const PushArgs a) {
+__global__ void __launch_bounds__(kPushThreads, 1) combine_push_kernel(const MoonepDevCtx c_in, const PushArgs a) {
   extern __shared__ __align__(128) unsigned char s_dyn[];  // PUSH: [kMoveWarps][kMoveStages][chunk_bytes]
+  // base addresses of every rank's staging chunk in shared memory: looked up per row, and a lookup in global memory
+  // is a dependent load of several hundred nanoseconds
+  __shared__ unsigned char* s_stage_peer[MOONEP_MAX_RANKS];
+  if (c_in.stage_peer != nullptr)
+    for (int r = threadIdx.x; r < c_in.R; r += blockDim.x) s_stage_peer[r] = c_in.stage_peer[r];
+  MoonepDevCtx c = c_in;
+  if (c_in.stage_peer != nullptr) c.stage_peer = s_stage_peer;
   __shared__ __align__(8) unsigned long long s_bar[kMoveWarps * kMoveStages];
   __shared__ MoveQueue s_mq;
   const int warp = threadIdx.x >> 5;

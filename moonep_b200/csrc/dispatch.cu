@@ -47,7 +47,15 @@ constexpr int kBulkStages = 3;   // ring depth per warp
 constexpr int kTokenBatch = 4;   // tokens handed out per grab
 constexpr int kVecPerLane = 8;   // int4 per lane per register chunk (4 KB per warp)
 constexpr int kMaxChunkBytes = 16 * 1024;
+constexpr int kExpandVec = 14;   // int4 per lane in flight while a row is expanded (a 14 KB row in two steps)
 constexpr int kExpandSlice = 2048;  // rows whose duplicate groups an expander CTA lists in shared memory at a time
+
+// Base addresses of every rank's shard and meta chunk, copied into shared memory at kernel start: the copy loops
+// look them up per destination, and a lookup in global memory is a dependent load of several hundred nanoseconds.
+struct PeerTables {
+  uint16_t* hidden[MOONEP_MAX_RANKS];
+  int* meta[MOONEP_MAX_RANKS];
+};
 
 struct DispatchArgs {
   // planner (fresh plans)
@@ -508,10 +516,10 @@ __device__ void expand_group(const MoonepDevCtx& c, int primary, int my_dup, int
   if (vec_ok) {
     const int nvec = H / 8;
     const int4* s4 = reinterpret_cast<const int4*>(src);
-    for (int c0 = 0; c0 < nvec; c0 += 32 * kVecPerLane) {
-      int4 v[kVecPerLane];
+    for (int c0 = 0; c0 < nvec; c0 += 32 * kExpandVec) {
+      int4 v[kExpandVec];
 #pragma unroll
-      for (int j = 0; j < kVecPerLane; ++j) {
+      for (int j = 0; j < kExpandVec; ++j) {
         const int i = c0 + j * 32 + lane;
         if (i < nvec) v[j] = ld16(s4 + i);
       }
@@ -520,7 +528,7 @@ __device__ void expand_group(const MoonepDevCtx& c, int primary, int my_dup, int
         if (row < 0 || row >= c.NvS) continue;
         int4* o4 = reinterpret_cast<int4*>(shard + (long long)row * H);
 #pragma unroll
-        for (int j = 0; j < kVecPerLane; ++j) {
+        for (int j = 0; j < kExpandVec; ++j) {
           const int i = c0 + j * 32 + lane;
           if (i < nvec) st16(o4 + i, v[j]);
         }
@@ -697,8 +705,16 @@ __device__ bool expand_role(const MoonepDevCtx& c, const DispatchArgs& a, int xi
 
 // ---- the kernel ------------------------------------------------------------------------------------
 
-__global__ void __launch_bounds__(kDispatchThreads, 1) dispatch_kernel(const MoonepDevCtx c, const DispatchArgs a) {
+__global__ void __launch_bounds__(kDispatchThreads, 1) dispatch_kernel(const MoonepDevCtx c_in, const DispatchArgs a) {
   extern __shared__ __align__(128) unsigned char s_dyn[];  // sender ring / planner tables / expert histogram
+  __shared__ PeerTables s_peer;
+  for (int r = threadIdx.x; r < c_in.R; r += blockDim.x) {
+    s_peer.hidden[r] = c_in.hidden_peer[r];
+    s_peer.meta[r] = c_in.meta_peer[r];
+  }
+  MoonepDevCtx c = c_in;  // same context, peer tables read from shared memory
+  c.hidden_peer = s_peer.hidden;
+  c.meta_peer = s_peer.meta;
   __shared__ __align__(8) unsigned long long s_bar[kBulkWarps * kBulkStages];
   __shared__ TokenScratch s_tok;
   __shared__ FlagQueue s_fq;
@@ -755,12 +771,13 @@ __global__ void __launch_bounds__(kDispatchThreads, 1) dispatch_kernel(const Moo
     }
   }
 
-  if (is_sender && (roles & MOONEP_ROLE_TOKENS)) {
+  if (roles & MOONEP_ROLE_TOKENS) {
+    // every CTA of the launch plans blocks of tokens (the expanders have nothing else to do yet)
     ok = wait_local_epoch(c, MOONEP_CTR_TABLES_READY, plan_epoch, MOONEP_K_PLAN_TOKENS) && ok;
     if (ok)
-      for (int b = sidx; b < a.n_blocks; b += scnt)
+      for (int b = blockIdx.x; b < a.n_blocks; b += gridDim.x)
         plan_tokens_block(c, a.topk, a.dst, a.tokens_per_block, b, reinterpret_cast<int*>(s_dyn), s_tok);
-    if (role_tail(c, MOONEP_CTR_PLAN_ARRIVE, scnt) && !poisoned(c)) {
+    if (role_tail(c, MOONEP_CTR_PLAN_ARRIVE, gridDim.x) && !poisoned(c)) {
       if (threadIdx.x == 0) st_release_gpu(c.counters + MOONEP_CTR_PLAN_DONE, plan_epoch);
       for (int r = threadIdx.x; r < c.R; r += blockDim.x) st_release_sys(flag_ptr(c, r, MOONEP_FLAG_PLAN, c.rank), plan_epoch);
     }
