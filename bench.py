@@ -333,6 +333,8 @@ def run_moe_step(args, rank, n):
     # every rank's outputs, input gradients, gate gradients and owned weight gradients must be finite
     finite = all(bool(torch.isfinite(t.float()).all()) for t in (out, last["dx"], last["dgates"], *layer.owner_grads()))
     finite = max_over_ranks(0.0 if finite else 1.0, n) == 0.0
+    layer.destroy()
+    buf.destroy()
     flops_fwd = 2.0 * S * K * H * inter * 3  # per rank, real rows
     return {
         "metric": "moe_layer_train_tokens_per_s", "value": n * S / (t_all / 1e3), "unit": "tokens/s", "n_gpus": n,

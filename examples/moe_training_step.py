@@ -81,6 +81,7 @@ def main():
                   f"hosts {st['remote_experts_hosted']} remote experts, |dx| {dx.float().abs().mean().item():.3e}",
                   flush=True)  # fmt: skip
     dist.barrier()
+    layer.destroy()
     buf.destroy()
     dist.destroy_process_group()
     if rank == 0:

@@ -218,6 +218,12 @@ class Buffer:
                 })  # fmt: skip
         return out
 
+    def gemm_hooks(self, **kw):
+        """Hand-off hooks for ``ops.grouped_gemm.grouped_gemm(..., hooks=...)`` on this Buffer's shard (CUDA only; see
+        ``CudaBackend.gemm_hooks``).  Returns None on the host backend."""
+        be = self._require_ctx()["_backend"]
+        return be.gemm_hooks(**kw) if hasattr(be, "gemm_hooks") else None
+
     # -- CUDA graphs ---------------------------------------------------------------
     def capture(self, fn, *, warmup: int = 1):
         """Capture ``fn()`` — any sequence of this Buffer's operations on fixed tensors, plus whatever
@@ -355,10 +361,12 @@ class Buffer:
 
     # -- combine ------------------------------------------------------------------------
     def _run_combine(self, ctx, hidden_sh, plan, hidden_nvsh, route_weights_nvs, route_weights_sk,
-                     *, inter_rank_sync, zero_copy):  # fmt: skip
+                     *, inter_rank_sync, zero_copy, ready=None):  # fmt: skip
         be = ctx["_backend"]
         if hasattr(be, "combine_all"):
-            be.combine_all(plan, hidden_nvsh, route_weights_nvs, hidden_sh, route_weights_sk, inter_rank_sync, zero_copy)
+            rdy, expect = ready if ready is not None else (None, 0)
+            be.combine_all(plan, hidden_nvsh, route_weights_nvs, hidden_sh, route_weights_sk, inter_rank_sync, zero_copy,
+                           ready=rdy, ready_expect=expect)  # fmt: skip
             return
         wait = None
         # The barrier protects the shard from being rewritten while a peer still pulls from it.  A
@@ -378,10 +386,14 @@ class Buffer:
         inter_rank_sync=True,
         *,
         zero_copy=False,
+        ready=None,
     ):
         """Bring expert outputs home: ``out[token] = bf16(sum_k row(token, k))`` (unweighted).
 
-        Returns ``(hidden_sh[S,H], route_weights_sk[S,K] | None, event | None)``.
+        Returns ``(hidden_sh[S,H], route_weights_sk[S,K] | None, event | None)``.  ``ready=(counter, value)`` (CUDA,
+        push path): ``counter[b]`` reaches ``value`` when the producer of ``hidden_nvsh`` (a grouped GEMM with a
+        ``done_counter`` hook) has finished the 128-row block ``b``; rows are then taken block by block instead of
+        after the whole producer.
         """
         ctx = self._require_ctx()
         S, H, K, NvS = ctx["S"], ctx["H"], ctx["K"], ctx["NvS"]
@@ -409,7 +421,7 @@ class Buffer:
         def run():
             self._run_combine(
                 ctx, hidden_sh, plan, hidden_nvsh, route_weights_nvs, route_weights_sk,
-                inter_rank_sync=inter_rank_sync, zero_copy=zero_copy,
+                inter_rank_sync=inter_rank_sync, zero_copy=zero_copy, ready=ready,
             )  # fmt: skip
 
         if not async_finish:

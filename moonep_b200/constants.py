@@ -45,6 +45,7 @@ FLAG_SENT = 3  # peer pushed all hidden rows / route weights
 FLAG_COMB = 4  # peer's shard is final and may be pulled by combine
 FLAG_GRAD_READY = 5  # peer's reduce buffers are final
 FLAG_GRAD_DONE = 6  # peer finished pulling gradient slots
+FLAG_PREFETCH = 7  # no cross-rank flag: epoch of the prefetch_weight calls (their per-slot flags are local)
 NUM_FLAG_FAMILIES = 8
 
 # Status codes written by kernels into the host-visible status block.

@@ -29,6 +29,8 @@
 // The reference has no GEMM; this kernel serves the MoE-layer benchmark configuration (dispatch ->
 // prefetch_weight -> grouped GEMM -> combine) named beside the reference's Buffer API
 // (reference README.md:46-48).
+#include <cstring>
+
 #include "umma.cuh"
 
 namespace moonep {
@@ -91,7 +93,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           if (a.cu_seqlens[mid] > row0) hi = mid; else lo = mid + 1;
         }
         int wslot = a.group_map != nullptr ? a.group_map[lo] : lo;
-        if (wslot < 0 || wslot >= a.w_slots) wslot = 0;  // a group without weights here: result is meaningless but in bounds
+        if (wslot < 0 || wslot >= a.w_slots) {
+          // a group whose weights this rank does not hold: reported, computed with slot 0 (in bounds), never trusted
+          gemm_bad_index(a.status, 13, 13, lo, wslot);
+          wslot = 0;
+        }
         const int wrow0 = wslot * a.n_per_group + nb * b_rows_per_tile;
         for (int kb = 0; kb < a.k_blocks; ++kb) {
           if (!mbar_wait(s_empty + stage, phase ^ 1u, a.timeout_ns)) {
@@ -592,6 +598,7 @@ extern "C" int moonep_grouped_gemm(const void* x, const void* w0, const void* w1
   a.pre_up = (uint16_t*)pre_up;
   a.b_kn = 0;
   a.k_split = a.k_blocks;
+  memset(&a.hooks, 0, sizeof(a.hooks));
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

@@ -28,6 +28,8 @@
 // MMA lane first waits (bounded) for its own last MMA, so no CTA leaves while the pair still works on it.
 //
 // No counterpart in the reference, which has no GEMM.
+#include <cstring>
+
 #include "umma.cuh"
 
 namespace moonep {
@@ -82,6 +84,36 @@ struct PairSched {
   }
 };
 
+// Bounded wait until *p (+ *bias) reaches `want`; false when the budget ran out.
+__device__ __forceinline__ bool hook_wait(const int* p, const int* bias, int want, unsigned long long timeout_ns) {
+  if (bias != nullptr) want += ld_volatile(bias);
+  if (ld_acquire_sys(p) - want >= 0) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  unsigned spins = 0;
+  while (ld_acquire_sys(p) - want < 0) {
+    if ((++spins & 63u) == 0 && globaltimer_ns() - t0 > timeout_ns) return false;
+    __nanosleep(200);
+  }
+  return true;
+}
+
+// Warp-wide: all 128 row flags of the block that starts at row0 have reached the epoch.
+__device__ __forceinline__ bool rows_arrived(const MoonepGemmHooks& h, int row0, int lane, unsigned long long timeout_ns) {
+  const int want = h.row_epoch + (h.row_bias != nullptr ? ld_volatile(h.row_bias) : 0);
+  const int4* f4 = reinterpret_cast<const int4*>(h.row_flags + row0) + lane;  // 4 flags per lane; row0 is a multiple of 128
+  const unsigned long long t0 = globaltimer_ns();
+  unsigned spins = 0;
+  for (;;) {
+    int4 v;
+    asm volatile("ld.acquire.sys.global.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(f4) : "memory");
+    const bool ok = v.x - want >= 0 && v.y - want >= 0 && v.z - want >= 0 && v.w - want >= 0;
+    if (__all_sync(0xffffffffu, ok)) return true;
+    const bool late = (++spins & 63u) == 0 && globaltimer_ns() - t0 > timeout_ns;
+    if (__any_sync(0xffffffffu, late)) return false;
+    __nanosleep(500);
+  }
+}
+
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
     grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b0,
                              const __grid_constant__ CUtensorMap tmap_b1, const GemmArgs a) {
@@ -94,6 +126,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
   const unsigned rank = cluster_ctarank();  // 0: leader (issues the MMAs), 1: its peer
   // every role walks the groups once; from shared memory a group costs a few cycles instead of an L2 round trip
   const int* cu = a.G <= kPairGroupsInSmem ? s_cu : a.cu_seqlens;
+  __shared__ int s_hook_ok;
+  if (threadIdx.x == 0) {
+    s_hook_ok = 1;
+    // the group ends may still be on their way out of the dispatch kernel's table stage
+    if (a.hooks.tables_ready != nullptr &&
+        !hook_wait(a.hooks.tables_ready, a.hooks.tables_bias, a.hooks.tables_epoch, a.timeout_ns)) {
+      gemm_fail(a.status, kPairKernelId, 10, 0, 0);
+      s_hook_ok = 0;
+    }
+  }
+  __syncthreads();
   if (a.G <= kPairGroupsInSmem)
     for (int g = threadIdx.x; g < a.G; g += blockDim.x) s_cu[g] = a.cu_seqlens[g];
   const long long pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
@@ -121,46 +164,78 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
   const unsigned tmem_base = s_tmem_base;
   // Both CTAs own their whole TMEM, so both accumulators start at column 0; the MMA addresses the peer's
   // TMEM with the leader's address.  Anything else means the SM is shared with another TMEM user: give up.
-  const bool tmem_ok = (tmem_base & 0xFFFFu) == 0;
-  if (!tmem_ok && threadIdx.x == 0) gemm_fail(a.status, kPairKernelId, 9, (int)tmem_base, 0);
+  const bool tmem_ok = (tmem_base & 0xFFFFu) == 0 && s_hook_ok != 0;
+  if ((tmem_base & 0xFFFFu) != 0 && threadIdx.x == 0) gemm_fail(a.status, kPairKernelId, 9, (int)tmem_base, 0);
   const int b_rows_per_tile = (a.mode == kSwiglu) ? 128 : 256;
 
   if (warp == 0) {
     // ---------------- TMA producer (both CTAs) ----------------
-    if (lane == 0 && tmem_ok) {
+    // Lane 0 issues the copies; the whole warp takes part in the (bounded) waits for rows that the dispatch kernel is
+    // still delivering and for weight slots the prefetch kernel is still filling.
+    if (tmem_ok) {
       PairSched sched(a, cu);
       int stage = 0;
       unsigned phase = 0;
       bool failed = false;
       int pig, nb;
+      int checked_blk = -1, checked_slot = -1;
       for (long long t = pair; !failed && sched.locate(t, pig, nb); t += npairs) {
-        const int row0 = (sched.blk0 + 2 * pig + (int)rank) * BM;  // beyond the group for the odd last block: loaded, never stored
+        const int blk = sched.blk0 + 2 * pig + (int)rank;
+        const int row0 = blk * BM;  // beyond the group for the odd last block: loaded, never stored
+        if (a.hooks.row_flags != nullptr && 2 * pig + (int)rank < sched.nblk && blk != checked_blk) {
+          if (!rows_arrived(a.hooks, row0, lane, a.timeout_ns)) {
+            if (lane == 0) gemm_fail(a.status, kPairKernelId, 11, blk, sched.g);
+            failed = true;
+            break;
+          }
+          checked_blk = blk;
+        }
+        if (a.hooks.slot_flags != nullptr && sched.g >= a.hooks.slot_first_group && sched.g != checked_slot) {
+          int ok = 1;
+          if (lane == 0)
+            ok = hook_wait(a.hooks.slot_flags + (sched.g - a.hooks.slot_first_group), a.hooks.slot_bias, a.hooks.slot_epoch,
+                           a.timeout_ns) ? 1 : 0;
+          if (!__shfl_sync(0xffffffffu, ok, 0)) {
+            if (lane == 0) gemm_fail(a.status, kPairKernelId, 12, sched.g, 0);
+            failed = true;
+            break;
+          }
+          checked_slot = sched.g;
+        }
         int wslot = a.group_map != nullptr ? a.group_map[sched.g] : sched.g;
-        if (wslot < 0 || wslot >= a.w_slots) wslot = 0;
+        if (wslot < 0 || wslot >= a.w_slots) {
+          // a group whose weights this rank does not hold: reported once, computed with slot 0 (in bounds), never trusted
+          if (lane == 0 && sched.nblk > 0) gemm_bad_index(a.status, kPairKernelId, 13, sched.g, wslot);
+          wslot = 0;
+        }
         const int wrow0 = wslot * a.n_per_group + nb * b_rows_per_tile;
         const CUtensorMap* tb = (a.mode == kSwiglu && rank == 1) ? &tmap_b1 : &tmap_b0;
         const int brow = (a.mode == kSwiglu) ? wrow0 : wrow0 + (int)rank * 128;
         for (int kb = 0; kb < a.k_blocks; ++kb) {
-          if (!mbar_wait_cluster(s_empty + stage, phase ^ 1u, a.timeout_ns)) {
-            gemm_fail(a.status, kPairKernelId, 1, stage, kb);
+          int got = 1;
+          if (lane == 0) got = mbar_wait_cluster(s_empty + stage, phase ^ 1u, a.timeout_ns) ? 1 : 0;
+          if (!__shfl_sync(0xffffffffu, got, 0)) {
+            if (lane == 0) gemm_fail(a.status, kPairKernelId, 1, stage, kb);
             failed = true;
             break;
           }
-          unsigned char* st = s_tiles + (size_t)stage * kPairStageBytes;
-          if (rank == 0) mbar_expect_tx(s_full + stage, 2 * kPairStageBytes);
-          const unsigned full_of_leader = mapa_u32(s_full + stage, 0);
-          tma_load_2d_pair(st, &tmap_a, kb * BK, row0, full_of_leader);
-          if (a.b_kn) {
-            // W is [slots, K, N]: this CTA's 128 columns of the tile as two boxes of 64 columns x 64 k
-            const bool second = kb >= a.k_split;
-            const int kdim = (second ? a.k_blocks - a.k_split : a.k_split) * BK;  // K rows per expert in that tensor
-            const int y = wslot * kdim + (second ? kb - a.k_split : kb) * BK;
-            const int x0 = nb * BN + (int)rank * 128;
-            const CUtensorMap* tw = second ? &tmap_b1 : &tmap_b0;
-            tma_load_2d_pair(st + kPairATileBytes, tw, x0, y, full_of_leader);
-            tma_load_2d_pair(st + kPairATileBytes + kMnBoxBytes, tw, x0 + 64, y, full_of_leader);
-          } else {
-            tma_load_2d_pair(st + kPairATileBytes, tb, kb * BK, brow, full_of_leader);
+          if (lane == 0) {
+            unsigned char* st = s_tiles + (size_t)stage * kPairStageBytes;
+            if (rank == 0) mbar_expect_tx(s_full + stage, 2 * kPairStageBytes);
+            const unsigned full_of_leader = mapa_u32(s_full + stage, 0);
+            tma_load_2d_pair(st, &tmap_a, kb * BK, row0, full_of_leader);
+            if (a.b_kn) {
+              // W is [slots, K, N]: this CTA's 128 columns of the tile as two boxes of 64 columns x 64 k
+              const bool second = kb >= a.k_split;
+              const int kdim = (second ? a.k_blocks - a.k_split : a.k_split) * BK;  // K rows per expert in that tensor
+              const int y = wslot * kdim + (second ? kb - a.k_split : kb) * BK;
+              const int x0 = nb * BN + (int)rank * 128;
+              const CUtensorMap* tw = second ? &tmap_b1 : &tmap_b0;
+              tma_load_2d_pair(st + kPairATileBytes, tw, x0, y, full_of_leader);
+              tma_load_2d_pair(st + kPairATileBytes + kMnBoxBytes, tw, x0 + 64, y, full_of_leader);
+            } else {
+              tma_load_2d_pair(st + kPairATileBytes, tb, kb * BK, brow, full_of_leader);
+            }
           }
           if (++stage == kPairStages) {
             stage = 0;
@@ -296,7 +371,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(tempty_of_leader[buf]);
+      if (lane == 0) {
+        mbar_arrive_cluster(tempty_of_leader[buf]);
+        if (valid && a.hooks.done_counter != nullptr) {
+          // this warp's 32 rows x 256 columns of the block are in memory: a consumer counts 4 * column tiles per block
+          __threadfence();
+          atomicAdd(a.hooks.done_counter + (sched.blk0 + blk_in_group), 1);
+        }
+      }
     }
   }
 
@@ -324,6 +406,15 @@ extern "C" int moonep_grouped_gemm_pair(const void* x, const void* w0, const voi
                                         const int* cu_seqlens, int G, int rows_cap, int K, int n_per_group, int mode,
                                         int* status, long long timeout_ms, int num_sms, const int* group_map,
                                         int w_slots, void* pre_gate, void* pre_up, void* stream) {
+  return moonep_grouped_gemm_pair_hooked(x, w0, w1, out, row_scale, cu_seqlens, G, rows_cap, K, n_per_group, mode, status,
+                                         timeout_ms, num_sms, group_map, w_slots, pre_gate, pre_up, nullptr, stream);
+}
+
+extern "C" int moonep_grouped_gemm_pair_hooked(const void* x, const void* w0, const void* w1, void* out,
+                                               const float* row_scale, const int* cu_seqlens, int G, int rows_cap, int K,
+                                               int n_per_group, int mode, int* status, long long timeout_ms, int num_sms,
+                                               const int* group_map, int w_slots, void* pre_gate, void* pre_up,
+                                               const MoonepGemmHooks* hooks, void* stream) {
   if (group_map == nullptr || w_slots <= 0) w_slots = G;
   if ((pre_gate != nullptr) != (pre_up != nullptr) || (pre_gate != nullptr && mode != kSwiglu)) {
     set_error("moonep_grouped_gemm_pair: pre_gate and pre_up go together and only with SwiGLU");
@@ -367,6 +458,11 @@ extern "C" int moonep_grouped_gemm_pair(const void* x, const void* w0, const voi
   a.pre_up = (uint16_t*)pre_up;
   a.b_kn = 0;
   a.k_split = a.k_blocks;
+  if (hooks != nullptr) a.hooks = *hooks; else memset(&a.hooks, 0, sizeof(a.hooks));
+  if (a.hooks.row_flags != nullptr && (reinterpret_cast<uintptr_t>(a.hooks.row_flags) & 15u) != 0) {
+    set_error("moonep_grouped_gemm_pair_hooked: row_flags must be 16-byte aligned");
+    return 1;
+  }
   return launch_pair(ta, tb0, tb1, a, num_sms, stream);
 }
 
@@ -406,6 +502,7 @@ extern "C" int moonep_grouped_gemm_pair_kn(const void* x, const void* w0, int K0
   a.pre_up = nullptr;
   a.b_kn = 1;
   a.k_split = K0 / BK;
+  memset(&a.hooks, 0, sizeof(a.hooks));
   return launch_pair(ta, tb0, tb1, a, num_sms, stream);
 }
 

@@ -31,6 +31,7 @@
 #define MOONEP_FLAG_COMB 4
 #define MOONEP_FLAG_GRAD_READY 5
 #define MOONEP_FLAG_GRAD_DONE 6
+#define MOONEP_FLAG_PREFETCH 7  // no cross-rank flag: the epoch of prefetch_weight calls (per-slot flags are local)
 #define MOONEP_NUM_FLAG_FAMILIES 8
 
 // Status block (int32 words, device memory, zero = healthy).
@@ -203,12 +204,40 @@ int moonep_combine_push(void* ctx, int roles, const int* src_info, const int* li
                         void* stream);
 
 // Expert weights: src[i] is [nexperts, H, Hp] bf16 (peer mapped), dst[i] is [nslots, H, Hp] bf16 (local).
+// slot_flags / slot_done ([nslots] int32 each, zero-initialised once, optional): slot b's flag receives the prefetch
+// epoch when all tensors of the slot have been copied (or at once when the slot stays empty).
 int moonep_prefetch(void* ctx, void* const* src3, void* const* dst3, int n_tensors, const int* experts_to_copy_row,
-                    long long elems, int nslots, int nexperts, int path, void* stream);
+                    long long elems, int nslots, int nexperts, int path, int* slot_flags, int* slot_done, int epoch,
+                    void* stream);
 // grads[i]: [E, H, Hp] fp32 (local), reduce[i]: [R, B, H, Hp] fp32 (slot (src, b) lives on rank src).
 int moonep_grad_reduce(void* ctx, float* const* grads, float* const* reduce, int n_tensors,
                        const int* experts_to_copy, int Bcols, long long elems, int epoch_ready, int epoch_done,
                        int phase, int path, void* stream);
+
+// Hand-off between the communication kernels and the grouped GEMM on CTA pairs, tile by tile.  Every pointer may be
+// null.  Epochs are compared as (value + *bias) when bias is given (graph replay, see moonep_epoch_bias).
+//   row_flags    [rows] the dispatch kernel's per-row arrival flags: the TMA producer waits (bounded) until all 128
+//                rows of a block carry row_epoch before it loads the block, so the GEMM can run beside the dispatch.
+//   tables_ready one word the dispatch kernel's table stage publishes: cu_seqlens is read only after it reached
+//                tables_epoch.
+//   slot_flags   [G - slot_first_group] the prefetch kernel's per-slot flags: the weights of a group
+//                g >= slot_first_group are loaded only after slot_flags[g - slot_first_group] reached slot_epoch.
+//   done_counter [rows / 128] bumped by every epilogue warp after it stored its part of a tile of the block
+//                (4 * column tiles per call and block), for a consumer that starts on finished row blocks
+//                (moonep_combine_push: ready / ready_expect).
+typedef struct MoonepGemmHooks {
+  const int* row_flags;
+  const int* row_bias;
+  int row_epoch;
+  int tables_epoch;
+  const int* tables_ready;
+  const int* tables_bias;
+  const int* slot_flags;
+  const int* slot_bias;
+  int slot_epoch;
+  int slot_first_group;
+  int* done_counter;
+} MoonepGemmHooks;
 
 // Expert computation (tcgen05 tensor cores).  None of these has a counterpart in the reference, which has no GEMM.
 // y[rows of g] = x[rows of g] @ w[g]^T for the padded row groups of a dispatched shard; mode 0 plain, 1 SwiGLU
@@ -224,6 +253,11 @@ int moonep_grouped_gemm_pair(const void* x, const void* w0, const void* w1, void
                              const int* cu_seqlens, int G, int rows_cap, int K, int n_per_group, int mode, int* status,
                              long long timeout_ms, int num_sms, const int* group_map, int w_slots, void* pre_gate,
                              void* pre_up, void* stream);
+// moonep_grouped_gemm_pair with the hand-off hooks above (hooks may be null).
+int moonep_grouped_gemm_pair_hooked(const void* x, const void* w0, const void* w1, void* out, const float* row_scale,
+                                    const int* cu_seqlens, int G, int rows_cap, int K, int n_per_group, int mode,
+                                    int* status, long long timeout_ms, int num_sms, const int* group_map, int w_slots,
+                                    void* pre_gate, void* pre_up, const MoonepGemmHooks* hooks, void* stream);
 // y[rows of g] = x[rows of g] @ W[g] with W as [slots, K, N] (N contiguous) on CTA pairs; w1 (optional) continues
 // the contraction: x = [a | b], W = [w0; w1].  This is the layout in which activation gradients need the forward
 // weights, so no transposed copies are made.  K0, K1 multiples of 64, N a multiple of 256.

@@ -27,6 +27,17 @@ __device__ __forceinline__ void gemm_fail(int* status, int kernel, int where, in
   }
 }
 
+// A group's weights are not on this rank (group_map says -1): an index error, recorded once.
+__device__ __forceinline__ void gemm_bad_index(int* status, int kernel, int kind, int x, int y) {
+  if (status != nullptr && atomicCAS(status + MOONEP_ST_CODE, 0, MOONEP_STATUS_BAD_INDEX) == 0) {
+    status[MOONEP_ST_KERNEL] = kernel;
+    status[MOONEP_ST_FAMILY] = kind;
+    status[MOONEP_ST_PEER] = x;
+    status[MOONEP_ST_EXPECT] = y;
+    __threadfence();
+  }
+}
+
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* tmap, int c0, int c1,
                                             unsigned long long* bar) {
   asm volatile(
@@ -142,6 +153,7 @@ struct GemmArgs {
   int k_split;           // with b_kn: K blocks served by the first W tensor, the rest come from the second
   uint16_t* pre_gate;    // SwiGLU only, optional: the pre-activations x Wg^T and x Wu^T, [rows, ldo] bf16 each,
   uint16_t* pre_up;      // kept for the backward pass so that it need not recompute them
+  MoonepGemmHooks hooks; // CTA-pair kernel only: hand-off with the communication kernels (all null = none)
 };
 
 // ---- CTA pairs (cta_group::2): the two CTAs of a cluster share one MMA --------------------------------

@@ -23,7 +23,7 @@ namespace {
 constexpr int kMaxTensors = 3;
 constexpr int kMaxSlots = 4096;     // R*B entries owned by one rank that grad_accum can list
 constexpr int kMaxLocalExperts = 2048;
-constexpr int kPieceVec = 1024;     // 16-byte vectors per work item (16 KB)
+constexpr int kPieceVec = 4096;     // 16-byte vectors per work item (64 KB)
 
 struct TensorSet {
   void* p[kMaxTensors];
@@ -51,18 +51,30 @@ __global__ void epoch_bias_kernel(const MoonepDevCtx c, const BiasValues b, int 
   if (f < MOONEP_NUM_FLAG_FAMILIES) c.counters[MOONEP_BIAS_OFF + f] = (mode ? c.counters[MOONEP_BIAS_OFF + f] : 0) + b.v[f];
 }
 
+// Work items are ordered slot-major, so that the slots fill one after the other; when the last piece of a slot
+// (over all tensors) has been copied, the slot's flag is released with the prefetch epoch and a grouped GEMM that
+// runs beside this kernel may load that slot's weights (moonep_grouped_gemm_pair_hooked: slot_flags).
 __global__ void __launch_bounds__(512)
     prefetch_kernel(const MoonepDevCtx c, const TensorSet w, const int* __restrict__ experts, long long elems,
-                    int nslots, int nexperts) {
+                    int nslots, int nexperts, int* slot_flags, int* slot_done, int epoch) {
   if (poisoned(c)) return;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const long long nvec = elems / 8;  // bf16: 8 elements per 16 bytes
   const long long pieces = (nvec + kPieceVec - 1) / kPieceVec;
-  const long long total = (long long)w.n * nslots * pieces;
+  const long long per_slot = (long long)w.n * pieces;
+  const long long total = (long long)nslots * per_slot;
+  if (slot_flags != nullptr) {
+    epoch = abs_epoch(c, MOONEP_FLAG_PREFETCH, epoch);
+    // slots that receive nothing are ready at once
+    if (blockIdx.x == 0)
+      for (int b = threadIdx.x; b < nslots; b += blockDim.x)
+        if (experts[b] < 0 || experts[b] >= nexperts) st_release_gpu(slot_flags + b, epoch);
+  }
   for (long long item = (long long)blockIdx.x * nwarps + warp; item < total; item += (long long)gridDim.x * nwarps) {
-    const long long piece = item % pieces;
-    const int b = (int)((item / pieces) % nslots);
-    const int t = (int)(item / (pieces * nslots));
+    const int b = (int)(item / per_slot);
+    const long long rest = item - (long long)b * per_slot;
+    const int t = (int)(rest / pieces);
+    const long long piece = rest - (long long)t * pieces;
     const int e = experts[b];
     if (e < 0) continue;
     if (e >= nexperts) {
@@ -84,6 +96,17 @@ __global__ void __launch_bounds__(512)
       for (int j = 0; j < 8; ++j) {
         const long long i = i0 + j * 32 + lane;
         if (i < v1) st16(dstp + i, v[j]);
+      }
+    }
+    if (slot_flags != nullptr) {
+      __syncwarp();
+      if (lane == 0) {
+        fence_gpu();
+        if (atomicAdd(slot_done + b, 1) == (int)per_slot - 1) {
+          slot_done[b] = 0;
+          fence_gpu();
+          st_relaxed_gpu(slot_flags + b, epoch);
+        }
       }
     }
   }
@@ -433,7 +456,7 @@ extern "C" int moonep_epoch_bias(void* ctx, const int* values, int mode, void* s
 
 extern "C" int moonep_prefetch(void* ctx, void* const* src3, void* const* dst3, int n_tensors,
                                const int* experts_to_copy_row, long long elems, int nslots, int nexperts, int path,
-                               void* stream) {
+                               int* slot_flags, int* slot_done, int epoch, void* stream) {
   (void)path;
   auto* h = (HostCtx*)ctx;
   const MoonepDevCtx& c = h->dev;
@@ -449,7 +472,8 @@ extern "C" int moonep_prefetch(void* ctx, void* const* src3, void* const* dst3, 
     w.q[i] = i < n_tensors ? dst3[i] : nullptr;
   }
   const int grid = imax(1, imin(c.num_sms, h->sm_count));
-  prefetch_kernel<<<grid, 512, 0, (cudaStream_t)stream>>>(c, w, experts_to_copy_row, elems, nslots, nexperts);
+  prefetch_kernel<<<grid, 512, 0, (cudaStream_t)stream>>>(c, w, experts_to_copy_row, elems, nslots, nexperts, slot_flags,
+                                                         slot_done, epoch);
   return check_launch("prefetch_kernel");
 }
 

@@ -95,7 +95,7 @@ def compute_layout(S, H, K, E, R, *, B=None, num_sms=None, token_padding=128, gr
     R32 = align_up(R, 32)
     SYNC_OFF = align_up(SRC_INFO_OFF + NvS, 32)
     LINK_OFF = SYNC_OFF + NUM_FLAG_FAMILIES * R32
-    ROWFLAG_OFF = LINK_OFF + NvS
+    ROWFLAG_OFF = align_up(LINK_OFF + NvS, 32)  # 16-byte aligned: consumers read four flags per load
     meta_chunk_logical = ROWFLAG_OFF + NvS
     meta_chunk_padded = align_up(meta_chunk_logical * 4, gran_bytes) // 4
 

@@ -75,3 +75,7 @@ class MoEBlock(nn.Module):
     def forward(self, x):
         gates, topk, tpe = self.router(x)
         return MoEFunction.apply(x, gates, topk, tpe, self.experts)
+
+    def destroy(self):
+        """Collective: free what the expert layer allocated beyond the caller's Buffer."""
+        self.experts.destroy()

@@ -32,6 +32,7 @@ import torch
 from .. import config
 from ..api import Buffer
 from ..ops.grouped_gemm import (
+    kernel_supports,
     WGRAD_ACCUMULATE,
     WGRAD_STORE,
     WGRAD_STORE_NONEMPTY,
@@ -48,10 +49,22 @@ from ..parallel.symm import create_full_expert_weight, create_nvl_dist_tensor, v
 
 
 class ExpertParallelMoE:
-    def __init__(self, buffer: Buffer, inter: int, *, init_std: float = 0.02, seed: int = 0):
+    def __init__(self, buffer: Buffer, inter: int, *, init_std: float = 0.02, seed: int = 0, backward_buffer: bool = True):
+        """``backward_buffer`` (CUDA): a second ``Buffer`` of the same shape carries the backward pass, so the rows the
+        forward dispatch delivered stay in the first one until the weight gradients need them and nothing is copied
+        (about one more shard plus staging per rank).  Without it the forward keeps a copy of the dispatched rows."""
         ctx = buffer._require_ctx()
         self.buffer = buffer
         self.world = ctx["world"]
+        # the copy-free path: push combine reads the expert output where it is, the backward has its own Buffer
+        self.fast = bool(ctx["world"].is_cuda and ctx["_backend"].combine_mode == "push")
+        self.bwd_buffer = None
+        if self.fast and backward_buffer:
+            self.bwd_buffer = Buffer(ctx["S"], ctx["H"], ctx["K"], ctx["E"], ctx["R"], num_sms=ctx["num_sms"],
+                                     token_padding=ctx["token_padding"], B=ctx["B"], world=ctx["world"])  # fmt: skip
+        self._y = None      # expert output rows [NvS, H]
+        self._done = None   # per 128-row block: output tiles the down projection has finished
+        self._down_calls = 0
         self.E, self.B, self.R, self.H, self.K, self.S = ctx["E"], ctx["B"], ctx["R"], ctx["H"], ctx["K"], ctx["S"]
         self.I = int(inter)
         self.rank, self.epn = ctx["rank"], ctx["epn"]
@@ -106,11 +119,58 @@ class ExpertParallelMoE:
                              False: torch.tensor(later, dtype=torch.int32).to(dev)}  # fmt: skip
         w.host_barrier()
 
+    def destroy(self):
+        """Collective: free the backward Buffer (the forward Buffer belongs to the caller)."""
+        if self.bwd_buffer is not None:
+            self.bwd_buffer.destroy()
+            self.bwd_buffer = None
+
     # -- forward -------------------------------------------------------------------------------
+    def _forward_fast(self, x, gates, topk, tokens_per_expert, save_for_backward):
+        """CUDA: dispatch -> prefetch (on the communication stream, beside the GEMMs) -> SwiGLU GEMM -> down projection
+        into a separate tensor -> push combine that reads it in place.  The GEMMs take their hand-off from the
+        communication kernels tile by tile: row flags of the dispatch, per-slot flags of the prefetch (so only the
+        groups that use a prefetched expert wait for it), and a per-row-block counter of finished output tiles that the
+        combine's push role consumes.  Nothing is copied and nothing synchronises with the host."""
+        buf = self.buffer
+        x_nvs, w_nvs, cu, plan = buf.dispatch(x, gates, topk, tokens_per_expert, zero_copy=True)
+        fetched = buf.prefetch_weight(plan, async_finish=True, full_gate_weight=self.w_gate,
+                                      full_up_weight=self.w_up, full_down_weight=self.w_down)  # fmt: skip
+        rows, dev = int(x_nvs.shape[0]), x_nvs.device
+        if self._y is None:
+            self._y = torch.empty(rows, self.H, dtype=torch.bfloat16, device=dev)
+            self._done = torch.zeros(-(-rows // 128), dtype=torch.int32, device=dev)
+        status = buf._require_ctx()["_backend"].status
+        a = u = None
+        if save_for_backward:
+            a = torch.empty(rows, self.I, dtype=torch.bfloat16, device=dev)
+            u = torch.empty_like(a)
+        # the hand-off hooks need the CTA-pair kernel's tiling; other shapes run after the prefetch, in stream order
+        hooked = rows >= 128 and self.H % 256 == 0 and self.I % 128 == 0
+        if not hooked:
+            torch.cuda.current_stream().wait_event(fetched)
+        h = grouped_gemm(x_nvs, self.w_gate, cu, w_up=self.w_up, mode="swiglu", status=status,
+                         save_pre=None if a is None else (a, u),
+                         hooks=buf.gemm_hooks(rows=True, slots=True) if hooked else None)  # fmt: skip
+        ready = None
+        if hooked:
+            self._down_calls += 1
+            ready = (self._done, self._down_calls * 4 * (self.H // 256))
+        grouped_gemm(h, self.w_down, cu, row_scale=w_nvs, mode="scale", out=self._y, status=status,
+                     hooks=buf.gemm_hooks(slots=True, done_counter=self._done) if hooked else None)  # fmt: skip
+        out, _, _ = buf.combine(plan, self._y, None, ready=ready)
+        if hooked:
+            torch.cuda.current_stream().wait_event(fetched)  # later users of the weight slots come after the copy
+        if not save_for_backward:
+            return out, None
+        return out, {"plan": plan, "cu": cu, "x_nvs": x_nvs, "w_nvs": w_nvs, "h": h, "a": a, "u": u}
+
     def forward(self, x, gates, topk, tokens_per_expert, save_for_backward: bool = True):
         """Returns ``(out[S, H], saved)``.  ``save_for_backward=False`` (inference): nothing is kept, the expert
         GEMMs read the dispatched rows in place, ``saved`` is None."""
         buf = self.buffer
+        if self.fast and (self.bwd_buffer is not None or not save_for_backward) and config.gemm_on_cta_pairs():
+            return self._forward_fast(x, gates, topk, tokens_per_expert, save_for_backward)
         x_nvs, w_nvs, cu, plan = buf.dispatch(x, gates, topk, tokens_per_expert, zero_copy=True)
         # the weight copies run on the communication stream while this stream saves the dispatched rows
         fetched = buf.prefetch_weight(plan, async_finish=True, full_gate_weight=self.w_gate,
@@ -170,7 +230,10 @@ class ExpertParallelMoE:
         straight into the gradient of an owned expert or into the reduce-buffer slot of a prefetched copy.  The
         pre-activations come from the forward pass.  On the kernel paths nothing synchronises with the host.
         """
-        buf, I = self.buffer, self.I
+        I = self.I
+        # the backward Buffer (when there is one) receives the output gradient, so the forward Buffer still holds x
+        buf = self.bwd_buffer if (self.bwd_buffer is not None and saved["x_nvs"].data_ptr() ==
+                                  self.buffer._require_ctx()["hidden_buf_local"].data_ptr()) else self.buffer
         ctx = buf._require_ctx()
         plan, cu, x_nvs, w_nvs = saved["plan"], saved["cu"], saved["x_nvs"], saved["w_nvs"]
         dy_nvs, _, _, _ = buf.dispatch(grad_out.contiguous(), None, plan=plan, zero_copy=True)
@@ -185,7 +248,7 @@ class ExpertParallelMoE:
             self._weight_grads_per_group(x_nvs, dy_nvs, dadu, hsw, cu)
         self._times_weights(dadu, [self.w_gate, self.w_up], cu, plan, out=dy_nvs)  # dx rows = da Wg + du Wu
         dx, dgates, _ = buf.combine(plan, dy_nvs, dgate_nvs, zero_copy=True)
-        buf.reduce_grad(plan, False, self.g_gate, self.g_up, self.g_down, self.red[0], self.red[1], self.red[2],
+        self.buffer.reduce_grad(plan, False, self.g_gate, self.g_up, self.g_down, self.red[0], self.red[1], self.red[2],
                         owner_local=True)  # fmt: skip
         return dx, dgates
 
@@ -195,7 +258,8 @@ class ExpertParallelMoE:
         MN-major tiles; elsewhere K-major copies of the local experts feed the ordinary grouped GEMM."""
         if kn_kernel_supports(x, ws):
             return grouped_gemm_kn(x, ws, cu, out=out)
-        return grouped_gemm(x, self._local_transposed(ws, plan), cu, group_map=self.group_map, out=out)
+        return grouped_gemm(x, self._local_transposed(ws, plan), cu, group_map=self.group_map, out=out,
+                            status=self.buffer._require_ctx()["_backend"].status if x.is_cuda else None)
 
     def _weight_grads_on_kernel(self, x_nvs, dy_nvs, dadu, hsw, cu) -> bool:
         """All weight gradients with three launches of the grouped tcgen05 kernel (no host synchronisation); every

@@ -113,10 +113,11 @@ _SIGNATURES = {
     "moonep_combine_push": (_i, [_vp, _i] + [_vp] * 7 + [_i, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "moonep_combine_prologue": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "moonep_combine_pull": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp]),
-    "moonep_prefetch": (_i, [_vp, ctypes.POINTER(_vp), ctypes.POINTER(_vp), _i, _vp, _ll, _i, _i, _i, _vp]),
+    "moonep_prefetch": (_i, [_vp, ctypes.POINTER(_vp), ctypes.POINTER(_vp), _i, _vp, _ll, _i, _i, _i, _vp, _vp, _i, _vp]),
     "moonep_grad_reduce": (_i, [_vp, ctypes.POINTER(_vp), ctypes.POINTER(_vp), _i, _vp, _i, _ll, _i, _i, _i, _i, _vp]),
     "moonep_grouped_gemm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _ll, _i, _vp, _i, _vp, _vp, _vp]),
     "moonep_grouped_gemm_pair": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _ll, _i, _vp, _i, _vp, _vp, _vp]),
+    "moonep_grouped_gemm_pair_hooked": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _ll, _i, _vp, _i, _vp, _vp, _vp, _vp]),
     "moonep_grouped_gemm_pair_kn": (_i, [_vp, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _ll, _i, _vp]),
     "moonep_pair_schedule": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _i]),
     "moonep_grouped_wgrad": (_i, [_vp, _vp, _ll, _i, _i, _vp, _i, _vp, _vp, _i, _vp, _ll, _i, _vp]),

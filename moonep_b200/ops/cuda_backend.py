@@ -27,6 +27,7 @@ from ..constants import (
     FLAG_GRAD_DONE,
     FLAG_GRAD_READY,
     FLAG_PLAN,
+    FLAG_PREFETCH,
     FLAG_READY,
     FLAG_SENT,
     FLAG_TPE,
@@ -45,7 +46,8 @@ _KERNEL_NAMES = {
 }  # fmt: skip
 ROLE_TABLES, ROLE_TOKENS, ROLE_SEND, ROLE_EXPAND = 1, 2, 4, 8
 ROLE_PUSH, ROLE_SUM, ROLE_FOLD = 1, 2, 4
-_FAMILY_NAMES = {0: "READY", 1: "TPE", 2: "PLAN", 3: "SENT", 4: "COMB", 5: "GRAD_READY", 6: "GRAD_DONE"}
+_FAMILY_NAMES = {0: "READY", 1: "TPE", 2: "PLAN", 3: "SENT", 4: "COMB", 5: "GRAD_READY", 6: "GRAD_DONE", 7: "PREFETCH"}
+_BIAS_OFF, _CTR_TABLES_READY = 32, 18  # words of the counters block (csrc/moonep.h)
 
 
 def _ptr(t: torch.Tensor | None) -> int | None:
@@ -534,7 +536,46 @@ class CudaBackend:
         assert H % 128 == 0 and Hp % 128 == 0, f"H and H' must be multiples of 128, got ({H}, {Hp})"
         src = (ctypes.c_void_p * n)(*[t.data_ptr() for t in remote_experts])
         dst = (ctypes.c_void_p * n)(*[t.data_ptr() for t in prefetch_buffers])
-        self._call("moonep_prefetch", src, dst, n, _ptr(experts_row), H * Hp, nslots, nexp, self.path, _stream())
+        flags = done = None
+        epoch = 0
+        if nslots == self.ctx["B"]:  # the Buffer's own prefetch slots: per-slot flags for a GEMM that runs beside the copy
+            flags, done = self._slot_scratch()
+            epoch = self._next(FLAG_PREFETCH)
+        self._call("moonep_prefetch", src, dst, n, _ptr(experts_row), H * Hp, nslots, nexp, self.path, _ptr(flags),
+                   _ptr(done), epoch, _stream())  # fmt: skip
+
+    def gemm_hooks(self, *, rows=False, tables=False, slots=False, done_counter=None):
+        """``GemmHooks`` for a grouped GEMM on this Buffer's shard, each part optional: ``rows`` waits per 128-row block
+        for the row flags of the latest dispatch; ``tables`` delays reading ``cu_seqlens`` until that dispatch's planner
+        tables are out; ``slots`` waits per prefetch slot for the latest ``prefetch_weight``; ``done_counter`` (int32
+        ``[ceil(NvS / 128)]``, zero-initialised once) is bumped 4 x column tiles times per row block and call."""
+        from .grouped_gemm import GemmHooks
+
+        c, h = self.ctx, GemmHooks()
+        ctr = self.counters.data_ptr()
+        if rows:
+            h.row_flags = c["meta_buf"].data_ptr() + 4 * (c["rank"] * c["meta_chunk_padded"] + c["ROWFLAG_OFF"])
+            h.row_bias = ctr + 4 * (_BIAS_OFF + FLAG_SENT)
+            h.row_epoch = self._cur(FLAG_SENT)
+        if tables:
+            h.tables_ready = ctr + 4 * _CTR_TABLES_READY
+            h.tables_bias = ctr + 4 * (_BIAS_OFF + FLAG_PLAN)
+            h.tables_epoch = self._cur(FLAG_PLAN)
+        if slots and c["B"] > 0:
+            h.slot_flags = self._slot_scratch()[0].data_ptr()
+            h.slot_bias = ctr + 4 * (_BIAS_OFF + FLAG_PREFETCH)
+            h.slot_epoch = self._cur(FLAG_PREFETCH)
+            h.slot_first_group = c["E"]
+        if done_counter is not None:
+            assert done_counter.dtype == torch.int32 and done_counter.numel() >= -(-c["NvS"] // 128)
+            h.done_counter = done_counter.data_ptr()
+        return h
+
+    def _slot_scratch(self):
+        if getattr(self, "_slots", None) is None:
+            dev, B = self.ctx["device"], max(1, self.ctx["B"])
+            self._slots = (torch.zeros(B, dtype=torch.int32, device=dev), torch.zeros(B, dtype=torch.int32, device=dev))
+        return self._slots
 
     def reduce_grad(self, experts_to_copy, grads, reduce_buffers, local=False):
         """``local=True``: ``grads[i]`` holds only this rank's experts, ``[E/R, H, H']``."""

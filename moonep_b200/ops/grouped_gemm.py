@@ -11,12 +11,27 @@ On CPU tensors, or when the shapes do not fit the kernel's tiling, a per-group f
 
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
 from .. import config
 from . import _lib
 
 _MODES = {"plain": 0, "swiglu": 1, "scale": 2}
+
+
+class GemmHooks(ctypes.Structure):
+    """Tile-by-tile hand-off between the communication kernels and the CTA-pair GEMM (``MoonepGemmHooks`` in
+    ``csrc/moonep.h``): per-row arrival flags of a dispatch, the dispatch's "tables ready" word, per-slot flags of a
+    weight prefetch, and a per-row-block counter of finished output tiles.  Build one with ``Buffer.gemm_hooks``."""
+
+    _fields_ = [
+        ("row_flags", ctypes.c_void_p), ("row_bias", ctypes.c_void_p), ("row_epoch", ctypes.c_int),
+        ("tables_epoch", ctypes.c_int), ("tables_ready", ctypes.c_void_p), ("tables_bias", ctypes.c_void_p),
+        ("slot_flags", ctypes.c_void_p), ("slot_bias", ctypes.c_void_p), ("slot_epoch", ctypes.c_int),
+        ("slot_first_group", ctypes.c_int), ("done_counter", ctypes.c_void_p),
+    ]  # fmt: skip
 
 
 def grouped_gemm_reference(x, w, cu_seqlens, *, w_up=None, row_scale=None, mode="plain", group_map=None):
@@ -31,7 +46,9 @@ def grouped_gemm_reference(x, w, cu_seqlens, *, w_up=None, row_scale=None, mode=
         end = int(ends[g])
         if end > start:
             xs = x[start:end].float()
-            ws = max(0, int(gmap[g]))
+            ws = int(gmap[g])
+            if ws < 0:
+                raise IndexError(f"grouped_gemm: group {g} has rows but no weights on this rank (group_map[{g}] = {ws})")
             y = xs @ w[ws].float().t()
             if mode == "swiglu":
                 y = torch.nn.functional.silu(y) * (xs @ w_up[ws].float().t())
@@ -49,7 +66,7 @@ def kernel_supports(x, w, mode: str) -> bool:
 
 
 def grouped_gemm(x, w, cu_seqlens, *, w_up=None, row_scale=None, mode="plain", out=None, status=None, num_sms=0,
-                 group_map=None, save_pre=None, pair=None):
+                 group_map=None, save_pre=None, pair=None, hooks=None):
     """See module docstring.  ``x``: ``[rows, K]`` bf16, ``w``: ``[G, N, K]`` bf16, returns ``[rows, N]`` bf16.
 
     Rows beyond ``cu_seqlens[-1]`` are not written.  Group ends must be multiples of 128.  With
@@ -57,6 +74,8 @@ def grouped_gemm(x, w, cu_seqlens, *, w_up=None, row_scale=None, mode="plain", o
     than there are groups (e.g. only the experts a rank owns or has prefetched).  ``save_pre=(a, u)`` (SwiGLU
     only, two ``[rows, N]`` bf16 tensors) also stores the pre-activations ``x @ w.T`` and ``x @ w_up.T``.
     ``pair`` selects the kernel: True = CTA pairs (``cta_group::2``), False = one CTA per tile, None = ``MOONEP_GEMM_PAIR``.
+    ``hooks`` (a ``GemmHooks``, CTA-pair kernel only) lets the kernel run beside the communication kernels: it waits
+    per row block / weight slot for their flags and counts finished output tiles per row block.
     """
     assert mode in _MODES
     W, N, K = (int(v) for v in w.shape)
@@ -92,16 +111,21 @@ def grouped_gemm(x, w, cu_seqlens, *, w_up=None, row_scale=None, mode="plain", o
         for t in save_pre:
             assert t.is_contiguous() and t.shape == out.shape and t.dtype == torch.bfloat16 and t.device == out.device
     lib = _lib.load()
+    use_pair = config.gemm_on_cta_pairs() if pair is None else pair
+    assert hooks is None or use_pair, "hooks need the CTA-pair kernel"
     with torch.cuda.device(x.device):
-        fn = lib.moonep_grouped_gemm_pair if (config.gemm_on_cta_pairs() if pair is None else pair) else lib.moonep_grouped_gemm
-        rc = fn(
+        args = (
             x.data_ptr(), w.data_ptr(), None if w_up is None else w_up.data_ptr(), out.data_ptr(),
             None if row_scale is None else row_scale.data_ptr(), cu_seqlens.data_ptr(), G, int(x.shape[0]), K, N,
             _MODES[mode], None if status is None else status.data_ptr(), config.timeout_ms(), int(num_sms),
             None if group_map is None else group_map.data_ptr(), W,
             None if save_pre is None else save_pre[0].data_ptr(), None if save_pre is None else save_pre[1].data_ptr(),
-            torch.cuda.current_stream().cuda_stream,
         )  # fmt: skip
+        st = torch.cuda.current_stream().cuda_stream
+        if hooks is not None:
+            rc = lib.moonep_grouped_gemm_pair_hooked(*args, ctypes.byref(hooks), st)
+        else:
+            rc = (lib.moonep_grouped_gemm_pair if use_pair else lib.moonep_grouped_gemm)(*args, st)
     _lib.check(rc, "moonep_grouped_gemm")
     return out
 

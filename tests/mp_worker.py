@@ -259,6 +259,7 @@ def scenario_moe_layer(rank, R, dev):
     close(mine[3][1], wu.grad[sl], "grad W_up")
     close(mine[3][2], wd.grad[sl], "grad W_down")
     barrier(dev)
+    layer.destroy()
     buf.destroy()
     if rank == 0:
         print("  moe layer ok", flush=True)
@@ -330,6 +331,7 @@ def scenario_moe_block(rank, R, dev):
         err = (got.float() - want.float()).abs().max().item()
         assert err <= 6e-2 * max(1e-3, want.abs().max().item()), f"moe block rank {rank}: {what} err {err}"
     barrier(dev)
+    block.destroy()
     buf.destroy()
     if rank == 0:
         print("  moe block ok", flush=True)

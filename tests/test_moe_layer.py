@@ -64,6 +64,7 @@ def test_moe_layer_forward_backward_matches_dense_reference(device, R, routing):
         close(res[r][3][0], wg.grad[s], f"rank {r} grad W_gate")
         close(res[r][3][1], wu.grad[s], f"rank {r} grad W_up")
         close(res[r][3][2], wd.grad[s], f"rank {r} grad W_down")
+    lw.run(lambda r: layers[r].destroy())
     lw.run(lambda r: bufs[r].destroy())
 
 
@@ -144,6 +145,7 @@ def test_moe_block_autograd_matches_dense_reference(device):
     close(block.router.weight.grad, wr.grad, "router gradient", tol=6e-2)
     # the input gradient has two parts: through the experts (from the layer) and through the router (from autograd)
     close(x.grad, xr.grad, "input gradient", tol=6e-2)
+    block.destroy()
     buf.destroy()
 
 
@@ -172,6 +174,8 @@ def test_expert_shards_save_and_load(device, tmp_path):
         bad = layers[0].state_dict()
         bad["first_expert"] = 1
         layers[0].load_state_dict(bad)
+    lw.run(lambda r: layers[r].destroy())
+    lw.run(lambda r: others[r].destroy())
     lw.run(lambda r: bufs[r].destroy())
 
 
@@ -199,6 +203,7 @@ def test_owned_expert_updates_reach_the_other_ranks_copies(device):
     res = lw.run(body)
     assert torch.equal(res[0][1], res[1][1]) and torch.equal(res[0][2], res[1][2]), "the ranks' copies diverged"
     assert not torch.equal(res[0][0], res[0][1]), "the step changed nothing"
+    lw.run(lambda r: layers[r].destroy())
     lw.run(lambda r: bufs[r].destroy())
 
 
@@ -226,6 +231,7 @@ def test_expert_adamw_matches_torch_adamw():
     opt2 = ExpertAdamW(layer)
     opt2.load_state_dict(state)
     assert opt2.steps == 3 and torch.equal(opt2.exp_avg[0], opt.exp_avg[0])
+    layer.destroy()
     buf.destroy()
 
 
@@ -247,4 +253,5 @@ def test_inference_forward_equals_training_forward(device, R):
         return saved is not None and none is None and torch.equal(a, b)
 
     assert all(lw.run(body))
+    lw.run(lambda r: layers[r].destroy())
     lw.run(lambda r: bufs[r].destroy())
