@@ -121,6 +121,9 @@ class Buffer:
         w = self._ctx["world"]
         if w.is_cuda:
             max_sms = torch.cuda.get_device_properties(w.device).multi_processor_count
+            # enable_pdl: the dispatch and combine kernels are launched with programmatic dependent launch, so their
+            # set-up overlaps the tail of the kernel before them (the reference accepts the flag and drops it)
+            self._ctx["_backend"].set_pdl(bool(enable_pdl) and config.pdl_allowed())
             self._ctx["num_sms_dedup"] = config.num_sms_dedup(max_sms)  # CTAs of the destination-side dedup/expand role
             self._ctx["_backend"].n_expand = self._ctx["num_sms_dedup"] if config.num_sms_dedup_is_set() else 0
             assert 1 <= self._ctx["num_sms"] <= max_sms, f"num_sms must be in [1, {max_sms}]"

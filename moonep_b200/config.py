@@ -9,6 +9,7 @@ MOONEP_COMBINE        ``push`` (default: the expert side folds duplicates and pu
                       which sum them as they arrive) or ``pull`` (fold pass, then the home ranks pull).
 MOONEP_PHASED         ``1``: launch the dispatch and combine kernels one role at a time even on real multi-GPU worlds
                       (what emulated ranks always do); for per-role timing and debugging.
+MOONEP_PDL            ``0`` turns programmatic dependent launch off even for Buffers created with ``enable_pdl=True``.
 MOONEP_LOCAL_SMS      CTAs of the kernels that only touch local memory (default: all SMs); ``num_sms`` of
                       the Buffer bounds the kernels that move data between ranks.
 MOONEP_NUM_SMS_DEDUP  CTAs of the dispatch kernel's destination-side role (zero fill, dedup builder, duplicate
@@ -64,6 +65,10 @@ def local_sms(sm_count: int) -> int:
     if raw is None or raw == "":
         return sm_count
     return max(1, min(int(raw), sm_count))
+
+
+def pdl_allowed() -> bool:
+    return os.environ.get("MOONEP_PDL", "1") not in _FALSE
 
 
 def force_phased() -> bool:

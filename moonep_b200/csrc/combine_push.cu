@@ -737,6 +737,7 @@ __global__ void __launch_bounds__(kPushThreads, 1) combine_push_kernel(const Moo
     s_mq.done[threadIdx.x] = 0;
   }
   fence_barrier_init();
+  griddep_wait();  // the set-up above may overlap the previous kernel's tail; its results are needed from here on
   __syncthreads();
   const bool has_push = (a.roles & MOONEP_ROLE_PUSH) != 0;
   const bool has_local = (a.roles & (MOONEP_ROLE_FOLD | MOONEP_ROLE_SUM)) != 0;
@@ -855,6 +856,9 @@ extern "C" int moonep_combine_push(void* ctx, int roles, const int* src_info, co
     const int room = imax(1, imin(c.local_sms, h->sm_count) - a.n_push);
     grid += n_local > 0 ? imin(n_local, room) : room;
   }
-  combine_push_kernel<<<grid, kPushThreads, smem, (cudaStream_t)stream>>>(c, a);
+  if (int rc = check_cuda(launch_maybe_pdl(combine_push_kernel, grid, kPushThreads, smem, (cudaStream_t)stream,
+                                           h->enable_pdl != 0, c, a),
+                          "launch combine_push_kernel"))
+    return rc;
   return check_launch("combine_push_kernel");
 }

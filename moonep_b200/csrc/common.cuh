@@ -89,6 +89,10 @@ __device__ __forceinline__ void record_status(const MoonepDevCtx& c, int code, i
   }
 }
 
+// Programmatic dependent launch: everything before this call may run while the previous kernel of the stream is
+// still finishing; after it, that kernel has completed and its writes are visible.  A no-op for ordinary launches.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // Absolute epoch of a launch argument: argument + this family's bias (see the header comment).
 __device__ __forceinline__ int abs_epoch(const MoonepDevCtx& c, int family, int epoch) {
   return epoch + ld_volatile(c.counters + MOONEP_BIAS_OFF + family);

@@ -727,6 +727,7 @@ __global__ void __launch_bounds__(kDispatchThreads, 1) dispatch_kernel(const Moo
     s_fq.done[threadIdx.x] = 0;
   }
   fence_barrier_init();
+  griddep_wait();  // the set-up above may overlap the previous kernel's tail; its results are needed from here on
   __syncthreads();
   bool ok = !poisoned(c);
 
@@ -903,6 +904,9 @@ extern "C" int moonep_dispatch(void* ctx, int roles, int fresh, const int* topk,
     const int nx = n_expand > 0 ? imin(n_expand, room) : room;
     grid = a.n_send + imax(1, nx);
   }
-  dispatch_kernel<<<grid, kDispatchThreads, smem, (cudaStream_t)stream>>>(c, a);
+  if (int rc = check_cuda(launch_maybe_pdl(dispatch_kernel, grid, kDispatchThreads, smem, (cudaStream_t)stream,
+                                           h->enable_pdl != 0, c, a),
+                          "launch dispatch_kernel"))
+    return rc;
   return check_launch("dispatch_kernel");
 }

@@ -157,6 +157,8 @@ void* moonep_ctx_create(const long long* params, int nparams, const unsigned lon
                         const unsigned long long* meta_peers, const unsigned long long* stage_peers);
 void moonep_ctx_destroy(void* ctx);
 int moonep_ctx_set_timeout_ms(void* ctx, long long ms);
+// Programmatic dependent launch for the dispatch and combine kernels of this context (off by default).
+int moonep_ctx_set_pdl(void* ctx, int on);
 
 // Cross-rank flags.  signal: store `epoch` into flag[family][rank] of every peer.
 // wait: spin (bounded) until every peer's flag[wait_family] >= wait_epoch.  Either part

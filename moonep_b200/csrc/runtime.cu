@@ -124,6 +124,13 @@ extern "C" void moonep_ctx_destroy(void* ctx) {
   delete h;
 }
 
+extern "C" int moonep_ctx_set_pdl(void* ctx, int on) {
+  auto* h = (HostCtx*)ctx;
+  if (!h) return 1;
+  h->enable_pdl = on ? 1 : 0;
+  return 0;
+}
+
 extern "C" int moonep_ctx_set_timeout_ms(void* ctx, long long ms) {
   auto* h = (HostCtx*)ctx;
   if (!h || ms < 1) return 1;

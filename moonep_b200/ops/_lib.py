@@ -104,6 +104,7 @@ _SIGNATURES = {
     "moonep_ctx_create": (_vp, [ctypes.POINTER(_ll), _i, ctypes.POINTER(_ull), ctypes.POINTER(_ull), ctypes.POINTER(_ull)]),
     "moonep_ctx_destroy": (None, [_vp]),
     "moonep_ctx_set_timeout_ms": (_i, [_vp, _ll]),
+    "moonep_ctx_set_pdl": (_i, [_vp, _i]),
     "moonep_signal_wait": (_i, [_vp, _i, _i, _i, _i, _vp]),
     "moonep_epoch_bias": (_i, [_vp, _vp, _i, _vp]),
     "moonep_plan_publish": (_i, [_vp, _vp, _vp, _i, _i, _vp]),

@@ -131,6 +131,9 @@ class CudaBackend:
             self.lib.moonep_ctx_destroy(self.handle)
             self.handle = None
 
+    def set_pdl(self, on: bool):
+        _lib.check(self.lib.moonep_ctx_set_pdl(self.handle, int(bool(on))), "set_pdl")
+
     def set_timeout_ms(self, ms: int):
         _lib.check(self.lib.moonep_ctx_set_timeout_ms(self.handle, int(ms)), "set_timeout_ms")
 

@@ -104,3 +104,61 @@ def test_round_trip_on_the_alternative_copy_paths(case, paths, monkeypatch):
     for r in range(R):
         assert_within_ulp(recs[r]["out"], want[r], max_ulps=1, what=f"rank {r} combine")
         assert torch.equal(recs[r]["weights_back"], recs[r]["w"]), f"rank {r}: weights did not round-trip"
+
+
+@pytest.mark.gpu
+def test_large_stride_dispatch_and_identity_combine():
+    """S=8192, K=16, H=7168 on two emulated ranks: every rank's shard is 1.9 GB, so element offsets inside the mapped
+    range pass 2**31 and byte offsets inside one shard pass 2**30 by far (parity: reference tests/test_dispatch.py:124-134
+    spot check and tests/test_combine.py:321-329 large identity combine).  Plan against the host planner, landed rows
+    spot-checked through src_info, weights bit-exact, combine = K * x within the two bf16 roundings."""
+    import numpy as np
+
+    from moonep_b200 import Buffer
+    from moonep_b200.cpu import planner as P
+    from moonep_b200.models.routing import make_routing
+    from moonep_b200.parallel.world import LocalWorld
+
+    R, S, K, H, epn = 2, 8192, 16, 7168, 8
+    E = R * epn
+    lw = LocalWorld(R, "cuda")
+    bufs = lw.run(lambda r: Buffer(S, H, K, E, R, num_sms=32, token_padding=128, B=2, world=lw.view(r)))
+    routes = [make_routing("biased", S, K, E, R, r, bias=1.0, seed=77, device="cuda") for r in range(R)]
+    xs = [(torch.randn(S, H, generator=torch.Generator().manual_seed(5 + r)) * 0.5).to(torch.bfloat16).cuda() for r in range(R)]
+
+    def body(r):
+        topk, tpe, gates = routes[r]
+        xn, wn, cu, plan = bufs[r].dispatch(xs[r], gates, topk, tpe, zero_copy=True)
+        torch.cuda.synchronize()
+        lw.view(r).step()
+        ctx = bufs[r]._require_ctx()
+        src_info = plan.src_info.cpu().numpy().astype(np.int64)
+        occupied = np.nonzero(src_info >= 0)[0]
+        pick = occupied[np.random.default_rng(r).choice(len(occupied), 256, replace=False)]
+        pick = np.concatenate([pick, occupied[-8:]])  # the highest rows of the shard too
+        rows = xn[torch.from_numpy(pick).cuda()].cpu()
+        wts = wn[torch.from_numpy(pick).cuda()].cpu()
+        out, wb, _ = bufs[r].combine(plan, xn, wn, zero_copy=True)
+        torch.cuda.synchronize()
+        bufs[r].check_status()
+        return {"dst": plan.dst.cpu().numpy(), "cu": cu.cpu().numpy(), "pick": pick, "info": src_info[pick], "rows": rows,
+                "wts": wts, "out_err": float((out.float() - K * xs[r].float()).abs().max()), "wb_ok": torch.equal(wb, gates),
+                "NvS": ctx["NvS"], "B": ctx["B"]}  # fmt: skip
+
+    recs = lw.run(body)
+    NvS = recs[0]["NvS"]
+    tpe = np.stack([routes[r][1].cpu().numpy() for r in range(R)]).astype(np.int64)
+    tabs = P.global_tables(tpe, S=S, K=K, B=recs[0]["B"], token_padding=128, NvS=NvS)
+    for r in range(R):
+        dst_pos = P.local_destinations(routes[r][0].cpu().numpy().reshape(-1), r, tabs, NvS)
+        assert np.array_equal(recs[r]["dst"], P.mark_duplicates(dst_pos, S, K, NvS)), f"rank {r}: dst"
+        assert np.array_equal(recs[r]["cu"], tabs["cu_seqlens"][r]), f"rank {r}: cu_seqlens"
+        info = recs[r]["info"]
+        src, slot = info // NvS, info % NvS
+        for i in range(len(info)):
+            s, t, k = int(src[i]), int(slot[i]) // K, int(slot[i]) % K
+            assert torch.equal(recs[r]["rows"][i], xs[s][t].cpu()), f"rank {r}: row {recs[r]['pick'][i]} is not token {t} of rank {s}"
+            assert float(recs[r]["wts"][i]) == float(routes[s][2][t, k]), f"rank {r}: weight of row {recs[r]['pick'][i]}"
+        assert recs[r]["wb_ok"], f"rank {r}: gate weights did not come back bit-exact"
+        assert recs[r]["out_err"] <= 0.25, f"rank {r}: combine error {recs[r]['out_err']}"
+    lw.run(lambda r: bufs[r].destroy())
