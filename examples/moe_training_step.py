@@ -69,9 +69,7 @@ def main():
         dx, dgates = layer.backward(saved, grad_out)
         layer.sgd_step(a.lr)
         layer.zero_grad()
-        if dev.type == "cuda":
-            torch.cuda.synchronize()
-            buf.check_status()
+        layer.check()  # the loss is read below anyway: raise here if a kernel gave up a wait or met a bad index
         loss_all = loss.detach().clone()
         dist.all_reduce(loss_all)
         st = buf.stats(saved["plan"])

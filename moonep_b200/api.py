@@ -151,6 +151,10 @@ class Buffer:
             if self._comm_stream is not None:
                 self._comm_stream.synchronize()
             torch.cuda.synchronize(w.device)
+            try:  # a failure nobody asked about must not disappear with the Buffer
+                ctx["_backend"].check_status()
+            except Exception as exc:  # noqa: BLE001 - destroy() still has to free the memory on every rank
+                warnings.warn(f"Buffer destroyed with an unreported device-side failure: {exc}", RuntimeWarning)
         if _collective:
             w.host_barrier()
         ctx["_backend"].destroy()
@@ -177,8 +181,21 @@ class Buffer:
             warnings.warn(f"Buffer destructor failed: {exc!r}", ResourceWarning)
 
     def check_status(self) -> None:
-        """Raise ``MoonEPTimeoutError`` if a device-side wait of an earlier operation ran out."""
+        """Raise ``MoonEPTimeoutError`` / ``MoonEPIndexError`` if a kernel of an earlier operation gave up a wait or met
+        an index out of range (reads a few words from the device: synchronises).  Kernels never trap or hang: after a
+        failure they record it and every later kernel of this Buffer returns at once, so **the results of all
+        operations since the last successful ``check_status()`` are undefined until it passes**.  Call it where a host
+        synchronisation is acceptable anyway (after the optimiser step, when a loss is read, before a checkpoint)."""
         self._require_ctx()["_backend"].check_status()
+
+    def synchronize(self) -> None:
+        """Wait for every operation of this Buffer (both streams) and raise if one of them failed on the device."""
+        ctx = self._require_ctx()
+        if ctx["world"].is_cuda:
+            if self._comm_stream is not None:
+                self._comm_stream.synchronize()
+            torch.cuda.synchronize(ctx["device"])
+        self.check_status()
 
     def stats(self, plan: MoonEPCommPlan | None = None) -> dict:
         """Runtime figures.  With ``plan``: rows this rank sends (primary entries), how many of them leave
@@ -228,19 +245,21 @@ class Buffer:
         return be.gemm_hooks(**kw) if hasattr(be, "gemm_hooks") else None
 
     # -- CUDA graphs ---------------------------------------------------------------
-    def capture(self, fn, *, warmup: int = 1):
+    def capture(self, fn, *, warmup: int = 1, check_every: int = 0):
         """Capture ``fn()`` — any sequence of this Buffer's operations on fixed tensors, plus whatever
         else is capturable — into a CUDA graph and return a ``CapturedStep``; ``step.replay()`` then
         runs the whole sequence with one launch.  Collective: every rank captures the same sequence and
         replays it the same number of times.  ``fn`` runs ``warmup`` times for real before the capture
         (lazy initialisation, allocator warm-up); its return value of the captured run is ``step.outputs``
         (tensors that every replay overwrites).  Ordinary calls and replays can be mixed, in stream order: wait for an
-        ``async_finish`` operation of this Buffer before replaying.
+        ``async_finish`` operation of this Buffer before replaying.  A replay does not look at the device-side status
+        block (that would synchronise); pass ``check_every=N`` to synchronise and raise on a failure every N replays, or
+        call ``Buffer.synchronize()`` yourself.
         No counterpart in the reference, whose barriers are host-driven."""
         ctx = self._require_ctx()
         if not ctx["world"].is_cuda:
             return _EagerStep(fn)  # host backend: same interface, every replay simply runs ``fn``
-        return CapturedStep(self, fn, warmup)
+        return CapturedStep(self, fn, warmup, check_every)
 
     # -- stream helpers ------------------------------------------------------------
     def _on_comm_stream(self, tensors, fn):
@@ -473,8 +492,9 @@ class Buffer:
 class CapturedStep:
     """A CUDA graph of Buffer operations (see ``Buffer.capture``)."""
 
-    def __init__(self, buffer: Buffer, fn, warmup: int = 1):
+    def __init__(self, buffer: Buffer, fn, warmup: int = 1, check_every: int = 0):
         self._buffer = buffer
+        self.check_every = int(check_every)  # every so many replays, synchronise and raise on a device-side failure
         be = buffer._require_ctx()["_backend"]
         for _ in range(max(0, warmup)):
             fn()
@@ -498,6 +518,8 @@ class CapturedStep:
         self.graph.replay()
         be.replay_done(self._end)
         self.replays += 1
+        if self.check_every > 0 and self.replays % self.check_every == 0:
+            self._buffer.synchronize()
         return self.outputs
 
 

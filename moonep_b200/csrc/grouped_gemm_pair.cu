@@ -167,6 +167,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
   const bool tmem_ok = (tmem_base & 0xFFFFu) == 0 && s_hook_ok != 0;
   if ((tmem_base & 0xFFFFu) != 0 && threadIdx.x == 0) gemm_fail(a.status, kPairKernelId, 9, (int)tmem_base, 0);
   const int b_rows_per_tile = (a.mode == kSwiglu) ? 128 : 256;
+  // The producer may legitimately spend a whole budget waiting for another kernel's flag; the roles behind it wait
+  // longer, so that the status block names the wait that actually ran out.
+  const bool hooked = a.hooks.row_flags != nullptr || a.hooks.slot_flags != nullptr;
+  const unsigned long long pipe_timeout_ns = hooked ? 3 * a.timeout_ns : a.timeout_ns;
 
   if (warp == 0) {
     // ---------------- TMA producer (both CTAs) ----------------
@@ -213,7 +217,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
         const int brow = (a.mode == kSwiglu) ? wrow0 : wrow0 + (int)rank * 128;
         for (int kb = 0; kb < a.k_blocks; ++kb) {
           int got = 1;
-          if (lane == 0) got = mbar_wait_cluster(s_empty + stage, phase ^ 1u, a.timeout_ns) ? 1 : 0;
+          if (lane == 0) got = mbar_wait_cluster(s_empty + stage, phase ^ 1u, pipe_timeout_ns) ? 1 : 0;
           if (!__shfl_sync(0xffffffffu, got, 0)) {
             if (lane == 0) gemm_fail(a.status, kPairKernelId, 1, stage, kb);
             failed = true;
@@ -260,7 +264,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
       int pig, nb;
       for (long long t = pair; !failed && sched.locate(t, pig, nb); t += npairs, ++it) {
         const int buf = it & 1;
-        if (!mbar_wait_cluster(s_tempty + buf, tphase[buf] ^ 1u, a.timeout_ns)) {
+        if (!mbar_wait_cluster(s_tempty + buf, tphase[buf] ^ 1u, pipe_timeout_ns)) {
           gemm_fail(a.status, kPairKernelId, 2, buf, it);
           failed = true;
           break;
@@ -269,7 +273,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
         tc_fence_after();
         const unsigned d_tmem = tmem_base + (unsigned)(buf * BN);
         for (int kb = 0; kb < a.k_blocks; ++kb) {
-          if (!mbar_wait_cluster(s_full + stage, phase, a.timeout_ns)) {
+          if (!mbar_wait_cluster(s_full + stage, phase, pipe_timeout_ns)) {
             gemm_fail(a.status, kPairKernelId, 3, stage, kb);
             failed = true;
             break;
@@ -292,7 +296,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
       }
       // the pair must not be torn down under a running MMA: wait for everything issued so far
       umma_commit_pair(&s_done, 1);
-      if (!mbar_wait_cluster(&s_done, 0, a.timeout_ns)) gemm_fail(a.status, kPairKernelId, 5, 0, 0);
+      if (!mbar_wait_cluster(&s_done, 0, pipe_timeout_ns)) gemm_fail(a.status, kPairKernelId, 5, 0, 0);
     }
     __syncwarp();
   } else {
@@ -308,7 +312,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
       const int blk_in_group = 2 * pig + (int)rank;
       const bool valid = blk_in_group < sched.nblk;
       int got = 1;
-      if (lane == 0) got = mbar_wait_cluster(s_tfull + buf, tphase[buf], a.timeout_ns) ? 1 : 0;
+      if (lane == 0) got = mbar_wait_cluster(s_tfull + buf, tphase[buf], pipe_timeout_ns) ? 1 : 0;
       got = __shfl_sync(0xffffffffu, got, 0);
       if (!got) {
         if (lane == 0) gemm_fail(a.status, kPairKernelId, 4, buf, it);

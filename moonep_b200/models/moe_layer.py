@@ -322,6 +322,14 @@ class ExpertParallelMoE:
                         gt[le].zero_()
             self._fresh = False
 
+    def check(self):
+        """Synchronise and raise if a kernel of the layer's Buffers failed on the device since the last check (nothing in
+        forward/backward looks at the status block, because that would synchronise with the host).  Call it once per
+        step where the loop synchronises anyway, e.g. when it reads the loss."""
+        self.buffer.synchronize()
+        if self.bwd_buffer is not None:
+            self.bwd_buffer.synchronize()
+
     def zero_grad(self):
         """Lazy: the next backward overwrites (instead of adding to) the gradients of the experts it visits
         and clears the others."""

@@ -43,6 +43,15 @@ class ClockSampler:
             pynvml.nvmlInit()
             self._nvml = pynvml
             self._handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            # the first call of each query is the slow one (tens of milliseconds): make it before the timed region
+            nv, h = pynvml, self._handle
+            nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+            nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            nv.nvmlDeviceGetPowerUsage(h)
+            try:
+                nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+            except AttributeError:
+                nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
         except Exception:  # noqa: BLE001 - sampling is best effort
             self._nvml = None
             return self
@@ -71,6 +80,10 @@ class ClockSampler:
         if self._thread is not None:
             self._thread.join(timeout=2)
         return False
+
+    def reset(self):
+        """Forget the samples taken so far (e.g. those of a warm-up inside the ``with`` block)."""
+        self.samples = []
 
     def summary(self) -> dict:
         if not self.samples:
