@@ -121,9 +121,13 @@ __device__ __forceinline__ void st16f(float4* p, const float4& f) {
   st16(p, make_int4(__float_as_int(f.x), __float_as_int(f.y), __float_as_int(f.z), __float_as_int(f.w)));
 }
 
-constexpr int kAccLd = 8;  // 16-byte loads per lane and slot in flight (4 KB per warp)
+constexpr int kAccLd = 6;  // 16-byte loads per lane and slot in flight (3 KB per warp; 8 would spill at 24 warps per SM)
 
-__global__ void __launch_bounds__(256, 3)
+// One CTA of 24 warps per SM, num_sms CTAs: remote reads are latency bound, so every resident warp counts, and the
+// grid stays within the SMs the Buffer was told to use for traffic between ranks.
+constexpr int kAccumThreads = 768;
+
+__global__ void __launch_bounds__(kAccumThreads, 1)
     grad_accum_kernel(const MoonepDevCtx c, const TensorSet ts, const int* __restrict__ etc, int Bcols, long long elems,
                       int wait_epoch, int signal_epoch) {
   __shared__ int s_rb[kMaxSlots];
@@ -512,8 +516,7 @@ extern "C" int moonep_grad_reduce(void* ctx, float* const* grads, float* const* 
                                                              epoch_done, nstages);
       return check_launch("grad_accum_bulk_kernel");
     }
-    // three CTAs of 8 warps per SM: remote reads are latency bound, more resident warps mean more loads in flight
-    grad_accum_kernel<<<3 * grid, 256, 0, st>>>(c, ts, experts_to_copy, Bcols, elems, epoch_ready, epoch_done);
+    grad_accum_kernel<<<grid, kAccumThreads, 0, st>>>(c, ts, experts_to_copy, Bcols, elems, epoch_ready, epoch_done);
     return check_launch("grad_accum_kernel");
   }
   if (phase == 2) {
