@@ -32,6 +32,8 @@
 // moves 2 bytes per thread per iteration, launches one CTA per (token, k) entry and re-reads the source
 // row for every destination.
 #include <climits>
+#include <cstdlib>
+#include <cstring>
 
 #include "common.cuh"
 #include "host.h"
@@ -48,6 +50,7 @@ constexpr int kTokenBatch = 4;   // tokens handed out per grab
 constexpr int kVecPerLane = 8;   // int4 per lane per register chunk (4 KB per warp)
 constexpr int kMaxChunkBytes = 16 * 1024;
 constexpr int kExpandVec = 14;   // int4 per lane in flight while a row is expanded (a 14 KB row in two steps)
+constexpr int kExpandCopyWarps = 12;  // warps of an expander CTA that own a shared-memory piece for bulk copies
 constexpr int kExpandSlice = 2048;  // rows whose duplicate groups an expander CTA lists in shared memory at a time
 
 // Base addresses of every rank's shard and meta chunk, copied into shared memory at kernel start: the copy loops
@@ -84,6 +87,7 @@ struct DispatchArgs {
   int vec_ok;                // rows are 16-byte aligned and a multiple of 16 bytes
   int chunk_bytes, nchunks;  // bulk path: a row is sent in nchunks pieces
   int bulk;
+  int expand_bulk;  // EXPAND copies through shared memory with bulk copies (needs (kExpandCopyWarps + 1) pieces of smem)
   int build_only;  // EXPAND: only build the duplicate map (no zero fill, no copies)
 };
 
@@ -125,8 +129,11 @@ __device__ __forceinline__ bool role_tail(const MoonepDevCtx& c, int counter, in
 
 // Reads the (start, count) pairs of 32 groups at a time, then spreads the pad rows of every
 // non-empty range over all participating warps.  Every cleared row gets its row flag.
+// With `zeros` (a shared-memory piece of chunk_bytes zeros, visible to the async proxy) the rows are cleared by bulk
+// stores from it, one instruction per piece of a row, instead of by register stores.
 __device__ void zero_fill_rows(const MoonepDevCtx& c, const int* __restrict__ zero_fill, int with_weights, int vec_ok,
-                               int epoch, int warp_global, int warps_total, int lane) {
+                               int epoch, int warp_global, int warps_total, int lane,
+                               const unsigned char* zeros = nullptr, int chunk_bytes = 0) {
   uint16_t* shard = c.hidden_peer[c.rank];
   float* wbuf = reinterpret_cast<float*>(c.meta_peer[c.rank] + c.weights_off);
   int* rowflag = c.meta_peer[c.rank] + c.rowflag_off;
@@ -152,7 +159,14 @@ __device__ void zero_fill_rows(const MoonepDevCtx& c, const int* __restrict__ ze
         const int row = s0 + r;
         if (row < 0 || row >= c.NvS) continue;
         uint16_t* p = shard + (long long)row * H;
-        if (vec_ok) {
+        if (zeros != nullptr) {
+          if (lane == 0) {
+            const long long row_bytes = (long long)H * 2;
+            for (long long off = 0; off < row_bytes; off += chunk_bytes)
+              bulk_s2g(reinterpret_cast<unsigned char*>(p) + off, zeros,
+                       (unsigned)(row_bytes - off < chunk_bytes ? row_bytes - off : chunk_bytes));
+          }
+        } else if (vec_ok) {
           const int nvec = H / 8;
           const int4 z = make_int4(0, 0, 0, 0);
           for (int i = lane; i < nvec; i += 32) st16(reinterpret_cast<int4*>(p) + i, z);
@@ -165,6 +179,10 @@ __device__ void zero_fill_rows(const MoonepDevCtx& c, const int* __restrict__ ze
       if (first < np) {
         __syncwarp();
         if (lane == 0) {
+          if (zeros != nullptr) {
+            bulk_commit();
+            bulk_wait<0>();
+          }
           fence_gpu();
           for (int r = first; r < np; r += warps_total) {
             const int row = s0 + r;
@@ -551,6 +569,45 @@ __device__ void expand_group(const MoonepDevCtx& c, int primary, int my_dup, int
   }
 }
 
+// The same through shared memory with bulk copies: the row piece is loaded once into this warp's stage and stored to
+// every duplicate row, no register traffic.  stage: chunk_bytes of shared memory of this warp; bar: its mbarrier
+// (count 1), phase: its parity, flipped per use.  Returns false after a timeout.
+__device__ bool expand_group_bulk(const MoonepDevCtx& c, int primary, int my_dup, int dn, int epoch, int lane,
+                                  unsigned char* stage, int chunk_bytes, unsigned long long* bar, unsigned& phase) {
+  const long long row_bytes = (long long)c.H * 2;
+  unsigned char* shard = reinterpret_cast<unsigned char*>(c.hidden_peer[c.rank]);
+  bool ok = true;
+  for (long long off = 0; off < row_bytes && ok; off += chunk_bytes) {
+    const unsigned len = (unsigned)(row_bytes - off < chunk_bytes ? row_bytes - off : chunk_bytes);
+    int got = 1;
+    if (lane == 0) {
+      bulk_wait_read<0>();  // the stage is free once the previous stores have read it
+      mbar_expect_tx(bar, len);
+      bulk_g2s(stage, shard + (long long)primary * row_bytes + off, len, bar);
+      got = mbar_wait(bar, phase, c.timeout_ns) ? 1 : 0;
+      if (!got) record_status(c, MOONEP_STATUS_TIMEOUT, MOONEP_K_DISPATCH_EXPAND, 100, primary, dn, 0);
+    }
+    phase ^= 1u;
+    ok = __shfl_sync(0xffffffffu, got, 0) != 0;
+    if (!ok) break;
+    for (int q = 0; q < dn && q < 32; ++q) {
+      const int row = __shfl_sync(0xffffffffu, my_dup, q);
+      if (lane == 0 && row >= 0 && row < c.NvS) bulk_s2g(shard + (long long)row * row_bytes + off, stage, len);
+    }
+    if (lane == 0) bulk_commit();
+  }
+  // the copies must be complete before the rows are flagged
+  if (lane == 0) {
+    bulk_wait<0>();
+    fence_gpu();
+  }
+  for (int q = 0; q < dn && q < 32; ++q) {
+    const int row = __shfl_sync(0xffffffffu, my_dup, q);
+    if (ok && lane == 0 && row >= 0 && row < c.NvS) st_relaxed_gpu(c.meta_peer[c.rank] + c.rowflag_off + row, epoch);
+  }
+  return ok;
+}
+
 // Warp-wide bounded wait until row `loff` of the local shard carries `epoch`.
 __device__ bool wait_row(const MoonepDevCtx& c, int loff, int epoch, int lane) {
   int ok = 1;
@@ -574,10 +631,25 @@ __device__ bool wait_row(const MoonepDevCtx& c, int loff, int epoch, int lane) {
 }
 
 // xidx of xcnt expander CTAs.  Returns false after a failed wait.
-__device__ bool expand_role(const MoonepDevCtx& c, const DispatchArgs& a, int xidx, int xcnt, bool ok) {
+//
+// With a.expand_bulk the copies go through shared memory with bulk copies: warps 0..kExpandCopyWarps-1 own one piece
+// of chunk_bytes each in s_dyn, followed by one piece of zeros that the zero fill stores from.
+__device__ bool expand_role(const MoonepDevCtx& c, const DispatchArgs& a, int xidx, int xcnt, bool ok, unsigned char* s_dyn,
+                            unsigned long long* s_xbar) {
   __shared__ int s_groups[kExpandSlice];  // group numbers found by this CTA in the current slice
   __shared__ int s_ngroups;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const bool bulk = a.expand_bulk != 0;
+  const int copy_warps = bulk ? kExpandCopyWarps : nwarps;  // warps that expand groups
+  unsigned char* my_stage = s_dyn + (size_t)warp * a.chunk_bytes;
+  unsigned char* zeros = bulk ? s_dyn + (size_t)kExpandCopyWarps * a.chunk_bytes : nullptr;
+  unsigned xphase = 0;
+  if (bulk) {
+    for (int i = threadIdx.x; i < a.chunk_bytes / 16; i += blockDim.x)
+      reinterpret_cast<int4*>(zeros)[i] = make_int4(0, 0, 0, 0);
+    fence_proxy_async();
+    __syncthreads();
+  }
   const int NvS = c.NvS;
   const int epoch = abs_epoch(c, MOONEP_FLAG_SENT, a.epoch_sent);
   // zero_fill comes from the table stage of this dispatch when the planner ran on the device
@@ -585,7 +657,8 @@ __device__ bool expand_role(const MoonepDevCtx& c, const DispatchArgs& a, int xi
     ok = wait_local_epoch(c, MOONEP_CTR_TABLES_READY, abs_epoch(c, MOONEP_FLAG_PLAN, a.epoch_plan),
                           MOONEP_K_DISPATCH_EXPAND) && ok;
   if (ok && a.zero_fill != nullptr && !a.build_only)
-    zero_fill_rows(c, a.zero_fill, a.with_weights, a.vec_ok, epoch, xidx * nwarps + warp, xcnt * nwarps, lane);
+    zero_fill_rows(c, a.zero_fill, a.with_weights, a.vec_ok, epoch, xidx * nwarps + warp, xcnt * nwarps, lane, zeros,
+                   a.chunk_bytes);
   if (a.fresh) ok = block_wait_flags(c, MOONEP_FLAG_PLAN, a.epoch_plan, MOONEP_K_DISPATCH_EXPAND) && ok;
   if (ok && a.fresh) {
     // Every source pushed, next to src_info, a link word per landed row: whether the row is the first of its
@@ -670,7 +743,7 @@ __device__ bool expand_role(const MoonepDevCtx& c, const DispatchArgs& a, int xi
       }
       __syncthreads();
       const int ng = a.build_only ? 0 : s_ngroups;
-      for (int i = warp; i < ng && ok; i += nwarps) {
+      for (int i = warp; i < ng && ok && warp < copy_warps; i += copy_warps) {
         const int g = s_groups[i];
         if (g < 0) continue;
         const int primary = a.dup_groups[3 * g], ds = a.dup_groups[3 * g + 1], dn = a.dup_groups[3 * g + 2];
@@ -679,7 +752,10 @@ __device__ bool expand_role(const MoonepDevCtx& c, const DispatchArgs& a, int xi
           ok = false;
           break;
         }
-        expand_group(c, primary, my_dup, dn, a.vec_ok, epoch, lane);
+        if (bulk)
+          ok = expand_group_bulk(c, primary, my_dup, dn, epoch, lane, my_stage, a.chunk_bytes, s_xbar + warp, xphase);
+        else
+          expand_group(c, primary, my_dup, dn, a.vec_ok, epoch, lane);
       }
       ok = __syncthreads_and(ok ? 1 : 0) != 0;
     }
@@ -687,7 +763,7 @@ __device__ bool expand_role(const MoonepDevCtx& c, const DispatchArgs& a, int xi
     // replayed plan: the groups are in the plan
     int ngroups = a.dup_counts[0];
     if (ngroups < 0 || ngroups > NvS) ngroups = 0;
-    for (int g = xidx * nwarps + warp; g < ngroups && ok; g += xcnt * nwarps) {
+    for (int g = xidx * copy_warps + warp; g < ngroups && ok && warp < copy_warps; g += xcnt * copy_warps) {
       const int primary = a.dup_groups[3 * g], ds = a.dup_groups[3 * g + 1], dn = a.dup_groups[3 * g + 2];
       if (primary < 0 || primary >= NvS || ds < 0 || dn < 0 || ds + dn > NvS) continue;
       const int my_dup = lane < dn ? a.dup_loffs[ds + lane] : -1;
@@ -695,7 +771,10 @@ __device__ bool expand_role(const MoonepDevCtx& c, const DispatchArgs& a, int xi
         ok = false;
         break;
       }
-      expand_group(c, primary, my_dup, dn, a.vec_ok, epoch, lane);
+      if (bulk)
+        ok = expand_group_bulk(c, primary, my_dup, dn, epoch, lane, my_stage, a.chunk_bytes, s_xbar + warp, xphase);
+      else
+        expand_group(c, primary, my_dup, dn, a.vec_ok, epoch, lane);
     }
     ok = __syncthreads_and(ok ? 1 : 0) != 0;
   }
@@ -718,9 +797,11 @@ __global__ void __launch_bounds__(kDispatchThreads, 1) dispatch_kernel(const Moo
   __shared__ __align__(8) unsigned long long s_bar[kBulkWarps * kBulkStages];
   __shared__ TokenScratch s_tok;
   __shared__ FlagQueue s_fq;
+  __shared__ __align__(8) unsigned long long s_xbar[kExpandCopyWarps];
   const int roles = a.roles;
   const int warp = threadIdx.x >> 5;
   if (threadIdx.x < kBulkWarps * kBulkStages) mbar_init(s_bar + threadIdx.x, 1);
+  if (threadIdx.x < kExpandCopyWarps) mbar_init(s_xbar + threadIdx.x, 1);
   if (threadIdx.x < kBulkWarps) {
     s_fq.head[threadIdx.x] = 0;
     s_fq.tail[threadIdx.x] = 0;
@@ -809,7 +890,7 @@ __global__ void __launch_bounds__(kDispatchThreads, 1) dispatch_kernel(const Moo
     }
   }
 
-  if (is_expander) expand_role(c, a, xidx, xcnt, ok);
+  if (is_expander) expand_role(c, a, xidx, xcnt, ok, s_dyn, s_xbar);
 }
 
 }  // namespace
@@ -870,6 +951,12 @@ extern "C" int moonep_dispatch(void* ctx, int roles, int fresh, const int* topk,
   const size_t limit = (size_t)imax(0, h->max_smem_optin - 20 * 1024);  // static arrays take about 17 KB
   a.bulk = (path == MOONEP_PATH_BULK && a.vec_ok && ring_bytes <= limit) ? 1 : 0;
   if ((roles & MOONEP_ROLE_SEND) && a.bulk) smem = ring_bytes;
+  const size_t expand_bytes = (size_t)(kExpandCopyWarps + 1) * a.chunk_bytes;
+  // MOONEP_EXPAND_PATH=bulk: duplicate expansion and zero fill through shared memory with bulk copies (default: registers)
+  const char* xp = getenv("MOONEP_EXPAND_PATH");
+  const bool want_bulk = xp != nullptr && strcmp(xp, "bulk") == 0;
+  a.expand_bulk = (want_bulk && (roles & MOONEP_ROLE_EXPAND) && a.vec_ok && a.chunk_bytes % 16 == 0 && expand_bytes <= limit) ? 1 : 0;
+  if (a.expand_bulk && expand_bytes > smem) smem = expand_bytes;
   a.tables_in_smem = 0;
   if (roles & MOONEP_ROLE_TABLES) {
     const size_t tb = (size_t)table_words(c.R, c.E) * sizeof(int);
