@@ -5,6 +5,8 @@ MOONEP_TIMEOUT_MS     budget of every device-side wait (default 10000).
 MOONEP_COPY_PATH      ``bulk`` (default: TMA bulk copies through shared memory) or ``ldst``
                       (plain 16-byte loads/stores) for dispatch/combine/prefetch;
                       ``MOONEP_SEND_PATH`` / ``MOONEP_PULL_PATH`` / ``MOONEP_GRAD_PATH`` set one kernel only.
+MOONEP_EXPAND_PATH    ``bulk`` (default) or ``ldst``: how the destination side of dispatch copies duplicate rows and clears
+                      pad rows (read by the native library).
 MOONEP_COMBINE        ``push`` (default: the expert side folds duplicates and pushes rows to the tokens' home ranks,
                       which sum them as they arrive) or ``pull`` (fold pass, then the home ranks pull).
 MOONEP_PHASED         ``1``: launch the dispatch and combine kernels one role at a time even on real multi-GPU worlds

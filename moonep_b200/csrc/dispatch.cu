@@ -952,9 +952,10 @@ extern "C" int moonep_dispatch(void* ctx, int roles, int fresh, const int* topk,
   a.bulk = (path == MOONEP_PATH_BULK && a.vec_ok && ring_bytes <= limit) ? 1 : 0;
   if ((roles & MOONEP_ROLE_SEND) && a.bulk) smem = ring_bytes;
   const size_t expand_bytes = (size_t)(kExpandCopyWarps + 1) * a.chunk_bytes;
-  // MOONEP_EXPAND_PATH=bulk: duplicate expansion and zero fill through shared memory with bulk copies (default: registers)
+  // duplicate expansion and zero fill go through shared memory with bulk copies; MOONEP_EXPAND_PATH=ldst selects the
+  // register copies (measured on one B200, S=4096: 0.343 vs 0.359 ms per round trip; both are bound by HBM writes)
   const char* xp = getenv("MOONEP_EXPAND_PATH");
-  const bool want_bulk = xp != nullptr && strcmp(xp, "bulk") == 0;
+  const bool want_bulk = !(xp != nullptr && strcmp(xp, "ldst") == 0);
   a.expand_bulk = (want_bulk && (roles & MOONEP_ROLE_EXPAND) && a.vec_ok && a.chunk_bytes % 16 == 0 && expand_bytes <= limit) ? 1 : 0;
   if (a.expand_bulk && expand_bytes > smem) smem = expand_bytes;
   a.tables_in_smem = 0;
