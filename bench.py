@@ -207,11 +207,15 @@ def run_steps(args, BufferCls, rank, n, reference=False):
     if not reference:
         be = buf._require_ctx()["_backend"]
         be.profile(True)
+        be.reset_wait_stats()
         for _ in range(10):
             flush.zero_()
             step(x, gates, topk, tpe)
         phases = {k: round(max_over_ranks(v, n), 1) for k, v in sorted(be.phase_times().items())}
         be.profile(False)
+        # inside the fused kernels: longest duration of each role's phases over the CTAs (device clock)
+        inner = be.stats().get("kernel_phase_max_us", {})
+        phases["inside_kernels_max_us"] = {k: round(max_over_ranks(v, n), 1) for k, v in sorted(inner.items())}
 
     # the same step as one CUDA graph replay (one launch from the host per step)
     graph_ms = None

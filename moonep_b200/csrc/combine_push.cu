@@ -745,6 +745,7 @@ __global__ void __launch_bounds__(kPushThreads, 1) combine_push_kernel(const Moo
   const bool pusher = has_push && (!has_local || (int)blockIdx.x >= (int)gridDim.x - a.n_push);
   if (pusher) {
     if (block_wait_flags(c, a.wait_family, a.wait_epoch, MOONEP_K_COMBINE_PUSH)) {
+      const unsigned long long t0 = globaltimer_ns();
       if (!a.vec_ok) {
         push_role_plain(c, a);
       } else if (warp < kMoveWarps) {
@@ -753,10 +754,21 @@ __global__ void __launch_bounds__(kPushThreads, 1) combine_push_kernel(const Moo
       } else if (warp < 2 * kMoveWarps) {
         move_helper(c, abs_epoch(c, MOONEP_FLAG_COMB, a.epoch_comb), s_mq, warp - kMoveWarps);
       }
+      if ((threadIdx.x & 31) == 0 && warp < kMoveWarps) stat_phase(c, MOONEP_PH_PUSH, t0);
     }
   } else if (has_local && !poisoned(c)) {
-    if (a.roles & MOONEP_ROLE_FOLD) fold_role(c, a);
-    if (a.roles & MOONEP_ROLE_SUM) sum_role(c, a);
+    unsigned long long t0 = globaltimer_ns();
+    if (a.roles & MOONEP_ROLE_FOLD) {
+      fold_role(c, a);
+      __syncthreads();
+      if (threadIdx.x == 0) stat_phase(c, MOONEP_PH_FOLD, t0);
+      t0 = globaltimer_ns();
+    }
+    if (a.roles & MOONEP_ROLE_SUM) {
+      sum_role(c, a);
+      __syncthreads();
+      if (threadIdx.x == 0) stat_phase(c, MOONEP_PH_SUM, t0);
+    }
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -836,12 +848,14 @@ extern "C" int moonep_combine_push(void* ctx, int roles, const int* src_info, co
   size_t smem = 0;
   if ((roles & MOONEP_ROLE_PUSH) && a.vec_ok)
     smem = (size_t)kMoveWarps * kMoveStages * ((size_t)(a.chunk_bytes + 127) / 128 * 128);
-  if ((int)smem + 4096 > h->max_smem_optin) {
+  if ((int)smem + 8192 > h->max_smem_optin) {
     set_error("moonep_combine_push: staging ring does not fit shared memory");
     return 1;
   }
+  // The attribute belongs to the kernel, not to the launch, and emulated ranks launch from several threads with
+  // different sizes: always allow the same maximum, so that no thread lowers it under another one's launch.
   if (int rc = check_cuda(cudaFuncSetAttribute(combine_push_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               (int)imax((int)smem, 1024)),
+                                               h->max_smem_optin - 8192),
                           "cudaFuncSetAttribute(combine_push_kernel)"))
     return rc;
   const bool local = (roles & (MOONEP_ROLE_FOLD | MOONEP_ROLE_SUM)) != 0;

@@ -89,6 +89,11 @@ __device__ __forceinline__ void record_status(const MoonepDevCtx& c, int code, i
   }
 }
 
+// Phase statistics: one thread of a CTA reports how long a phase took; the longest one over the CTAs is kept.
+__device__ __forceinline__ void stat_phase(const MoonepDevCtx& c, int phase, unsigned long long t0) {
+  atomicMax(reinterpret_cast<unsigned long long*>(c.stats) + MOONEP_STAT_PHASE_NS + phase, globaltimer_ns() - t0);
+}
+
 // Programmatic dependent launch: everything before this call may run while the previous kernel of the stream is
 // still finishing; after it, that kernel has completed and its writes are visible.  A no-op for ordinary launches.
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }

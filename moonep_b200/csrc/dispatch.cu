@@ -127,37 +127,60 @@ __device__ __forceinline__ bool role_tail(const MoonepDevCtx& c, int counter, in
 
 // ---- zero fill of pad rows ---------------------------------------------------------------------
 
-// Reads the (start, count) pairs of 32 groups at a time, then spreads the pad rows of every
-// non-empty range over all participating warps.  Every cleared row gets its row flag.
-// With `zeros` (a shared-memory piece of chunk_bytes zeros, visible to the async proxy) the rows are cleared by bulk
-// stores from it, one instruction per piece of a row, instead of by register stores.
+// Block-wide.  The (first pad row, pad rows) pairs of up to kZfChunk groups at a time go to shared memory together
+// with the running total of pad rows, so that pad row j of the rank is found by a binary search; the pad rows are
+// dealt round-robin to all participating warps (warp_global of warps_total).  A warp first clears its rows, then
+// (after one completion wait and one fence for all of them) releases their row flags.  With `zeros` (a shared-memory
+// piece of chunk_bytes zeros, visible to the async proxy) the rows are cleared by bulk stores from it, one
+// instruction per piece of a row, instead of by register stores.  s_start / s_cum: kZfChunk words of shared memory each.
+constexpr int kZfChunk = 1024;
+
 __device__ void zero_fill_rows(const MoonepDevCtx& c, const int* __restrict__ zero_fill, int with_weights, int vec_ok,
-                               int epoch, int warp_global, int warps_total, int lane,
+                               int epoch, int warp_global, int warps_total, int* s_start, int* s_cum,
                                const unsigned char* zeros = nullptr, int chunk_bytes = 0) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   uint16_t* shard = c.hidden_peer[c.rank];
   float* wbuf = reinterpret_cast<float*>(c.meta_peer[c.rank] + c.weights_off);
   int* rowflag = c.meta_peer[c.rank] + c.rowflag_off;
   const int ngroups = c.E + c.B;
   const int H = c.H;
-  int seen = 0;  // pad rows of the ranges before this one: rows are dealt round-robin across ranges
-  for (int base = 0; base < ngroups; base += 32) {
-    const int g = base + lane;
-    int n_pad = 0, start = 0;
-    if (g < ngroups) {
-      n_pad = zero_fill[2 * g + 1];
-      start = zero_fill[2 * g];
+  for (int gbase = 0; gbase < ngroups; gbase += kZfChunk) {
+    const int n = min(kZfChunk, ngroups - gbase);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      const int np = zero_fill[2 * (gbase + i) + 1];
+      s_start[i] = zero_fill[2 * (gbase + i)];
+      s_cum[i] = np > 0 ? np : 0;
     }
-    unsigned m = __ballot_sync(0xffffffffu, n_pad > 0);
-    while (m) {
-      const int src = __ffs(m) - 1;
-      m &= m - 1;
-      const int s0 = __shfl_sync(0xffffffffu, start, src);
-      const int np = __shfl_sync(0xffffffffu, n_pad, src);
-      const int first = ((warp_global - seen) % warps_total + warps_total) % warps_total;
-      seen = (seen + np) % warps_total;
-      for (int r = first; r < np; r += warps_total) {
-        const int row = s0 + r;
+    __syncthreads();
+    if (warp == 0) {  // inclusive running total, 32 groups per step
+      int carry = 0;
+      for (int i0 = 0; i0 < n; i0 += 32) {
+        const int i = i0 + lane;
+        int v = i < n ? s_cum[i] : 0;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int u = __shfl_up_sync(0xffffffffu, v, o);
+          if (lane >= o) v += u;
+        }
+        if (i < n) s_cum[i] = carry + v;
+        carry += __shfl_sync(0xffffffffu, v, 31);
+      }
+    }
+    __syncthreads();
+    const int total = s_cum[n - 1];
+    for (int pass = 0; pass < 2; ++pass) {
+      for (int j = warp_global; j < total; j += warps_total) {
+        int lo = 0, hi = n - 1;  // first group whose running total exceeds j
+        while (lo < hi) {
+          const int mid = (lo + hi) >> 1;
+          if (s_cum[mid] > j) hi = mid; else lo = mid + 1;
+        }
+        const int row = s_start[lo] + (j - (lo > 0 ? s_cum[lo - 1] : 0));
         if (row < 0 || row >= c.NvS) continue;
+        if (pass == 1) {
+          if (lane == 0) st_relaxed_gpu(rowflag + row, epoch);
+          continue;
+        }
         uint16_t* p = shard + (long long)row * H;
         if (zeros != nullptr) {
           if (lane == 0) {
@@ -175,8 +198,8 @@ __device__ void zero_fill_rows(const MoonepDevCtx& c, const int* __restrict__ ze
         }
         if (with_weights && lane == 0) wbuf[row] = 0.f;
       }
-      // one fence for the rows this warp cleared in the range, then their flags
-      if (first < np) {
+      if (pass == 0) {
+        // everything this warp cleared must be in memory before the first flag goes out
         __syncwarp();
         if (lane == 0) {
           if (zeros != nullptr) {
@@ -184,13 +207,11 @@ __device__ void zero_fill_rows(const MoonepDevCtx& c, const int* __restrict__ ze
             bulk_wait<0>();
           }
           fence_gpu();
-          for (int r = first; r < np; r += warps_total) {
-            const int row = s0 + r;
-            if (row >= 0 && row < c.NvS) st_relaxed_gpu(rowflag + row, epoch);
-          }
         }
+        __syncwarp();
       }
     }
+    __syncthreads();  // the shared-memory tables are rewritten by the next chunk of groups
   }
 }
 
@@ -569,11 +590,28 @@ __device__ void expand_group(const MoonepDevCtx& c, int primary, int my_dup, int
   }
 }
 
+// Rows whose copies have been issued but not yet flagged (lane q holds the q-th row).
+struct PendingRows {
+  int dup, dn;
+};
+
+// Lane 0 has waited for the copies of `p` to complete: fence once, then release the rows' flags.
+__device__ __forceinline__ void flag_pending(const MoonepDevCtx& c, const PendingRows& p, int epoch, int lane) {
+  if (lane == 0) fence_gpu();
+  for (int q = 0; q < p.dn && q < 32; ++q) {
+    const int row = __shfl_sync(0xffffffffu, p.dup, q);
+    if (lane == 0 && row >= 0 && row < c.NvS) st_relaxed_gpu(c.meta_peer[c.rank] + c.rowflag_off + row, epoch);
+  }
+}
+
 // The same through shared memory with bulk copies: the row piece is loaded once into this warp's stage and stored to
 // every duplicate row, no register traffic.  stage: chunk_bytes of shared memory of this warp; bar: its mbarrier
-// (count 1), phase: its parity, flipped per use.  Returns false after a timeout.
+// (count 1), phase: its parity, flipped per use.  The rows of this group are flagged one group late (`pend`: the
+// previous group's rows), so that waiting for the completion of a group's stores overlaps the next group's load;
+// the caller flushes the last group with expand_flush().  Returns false after a timeout.
 __device__ bool expand_group_bulk(const MoonepDevCtx& c, int primary, int my_dup, int dn, int epoch, int lane,
-                                  unsigned char* stage, int chunk_bytes, unsigned long long* bar, unsigned& phase) {
+                                  unsigned char* stage, int chunk_bytes, unsigned long long* bar, unsigned& phase,
+                                  PendingRows& pend) {
   const long long row_bytes = (long long)c.H * 2;
   unsigned char* shard = reinterpret_cast<unsigned char*>(c.hidden_peer[c.rank]);
   bool ok = true;
@@ -594,18 +632,31 @@ __device__ bool expand_group_bulk(const MoonepDevCtx& c, int primary, int my_dup
       const int row = __shfl_sync(0xffffffffu, my_dup, q);
       if (lane == 0 && row >= 0 && row < c.NvS) bulk_s2g(shard + (long long)row * row_bytes + off, stage, len);
     }
-    if (lane == 0) bulk_commit();
+    if (lane == 0) bulk_commit();  // one bulk group per piece: the next piece waits for this one to have read the stage
   }
-  // the copies must be complete before the rows are flagged
-  if (lane == 0) {
-    bulk_wait<0>();
-    fence_gpu();
+  if (row_bytes > chunk_bytes) {
+    // rows of several pieces (several bulk groups): no lag, everything completes here
+    if (lane == 0) bulk_wait<0>();
+    if (pend.dn > 0) flag_pending(c, pend, epoch, lane);
+    pend.dup = ok ? my_dup : -1;
+    pend.dn = ok ? dn : 0;
+    if (pend.dn > 0) flag_pending(c, pend, epoch, lane);
+    pend.dn = 0;
+    return ok;
   }
-  for (int q = 0; q < dn && q < 32; ++q) {
-    const int row = __shfl_sync(0xffffffffu, my_dup, q);
-    if (ok && lane == 0 && row >= 0 && row < c.NvS) st_relaxed_gpu(c.meta_peer[c.rank] + c.rowflag_off + row, epoch);
+  if (pend.dn > 0) {
+    if (lane == 0) bulk_wait<1>();  // everything but the group just committed has completed
+    flag_pending(c, pend, epoch, lane);
   }
+  pend.dup = ok ? my_dup : -1;
+  pend.dn = ok ? dn : 0;
   return ok;
+}
+
+__device__ __forceinline__ void expand_flush(const MoonepDevCtx& c, PendingRows& pend, int epoch, int lane) {
+  if (lane == 0) bulk_wait<0>();
+  if (pend.dn > 0) flag_pending(c, pend, epoch, lane);
+  pend.dn = 0;
 }
 
 // Warp-wide bounded wait until row `loff` of the local shard carries `epoch`.
@@ -635,7 +686,7 @@ __device__ bool wait_row(const MoonepDevCtx& c, int loff, int epoch, int lane) {
 // With a.expand_bulk the copies go through shared memory with bulk copies: warps 0..kExpandCopyWarps-1 own one piece
 // of chunk_bytes each in s_dyn, followed by one piece of zeros that the zero fill stores from.
 __device__ bool expand_role(const MoonepDevCtx& c, const DispatchArgs& a, int xidx, int xcnt, bool ok, unsigned char* s_dyn,
-                            unsigned long long* s_xbar) {
+                            unsigned long long* s_xbar, int* s_scratch) {
   __shared__ int s_groups[kExpandSlice];  // group numbers found by this CTA in the current slice
   __shared__ int s_ngroups;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
@@ -644,6 +695,7 @@ __device__ bool expand_role(const MoonepDevCtx& c, const DispatchArgs& a, int xi
   unsigned char* my_stage = s_dyn + (size_t)warp * a.chunk_bytes;
   unsigned char* zeros = bulk ? s_dyn + (size_t)kExpandCopyWarps * a.chunk_bytes : nullptr;
   unsigned xphase = 0;
+  PendingRows pend = {-1, 0};
   if (bulk) {
     for (int i = threadIdx.x; i < a.chunk_bytes / 16; i += blockDim.x)
       reinterpret_cast<int4*>(zeros)[i] = make_int4(0, 0, 0, 0);
@@ -656,10 +708,16 @@ __device__ bool expand_role(const MoonepDevCtx& c, const DispatchArgs& a, int xi
   if (a.fresh && a.wait_family < 0)
     ok = wait_local_epoch(c, MOONEP_CTR_TABLES_READY, abs_epoch(c, MOONEP_FLAG_PLAN, a.epoch_plan),
                           MOONEP_K_DISPATCH_EXPAND) && ok;
+  unsigned long long t0 = globaltimer_ns();
   if (ok && a.zero_fill != nullptr && !a.build_only)
-    zero_fill_rows(c, a.zero_fill, a.with_weights, a.vec_ok, epoch, xidx * nwarps + warp, xcnt * nwarps, lane, zeros,
-                   a.chunk_bytes);
+    zero_fill_rows(c, a.zero_fill, a.with_weights, a.vec_ok, epoch, xidx * nwarps + warp, xcnt * nwarps, s_groups,
+                   s_scratch, zeros, a.chunk_bytes);
+  __syncthreads();
+  if (threadIdx.x == 0) stat_phase(c, MOONEP_PH_ZERO, t0);
+  t0 = globaltimer_ns();
   if (a.fresh) ok = block_wait_flags(c, MOONEP_FLAG_PLAN, a.epoch_plan, MOONEP_K_DISPATCH_EXPAND) && ok;
+  if (threadIdx.x == 0) stat_phase(c, MOONEP_PH_WAIT_PLAN, t0);
+  t0 = globaltimer_ns();
   if (ok && a.fresh) {
     // Every source pushed, next to src_info, a link word per landed row: whether the row is the first of its
     // (source, token) on this rank and which row holds the next entry of the same token.  A primary row that
@@ -753,10 +811,11 @@ __device__ bool expand_role(const MoonepDevCtx& c, const DispatchArgs& a, int xi
           break;
         }
         if (bulk)
-          ok = expand_group_bulk(c, primary, my_dup, dn, epoch, lane, my_stage, a.chunk_bytes, s_xbar + warp, xphase);
+          ok = expand_group_bulk(c, primary, my_dup, dn, epoch, lane, my_stage, a.chunk_bytes, s_xbar + warp, xphase, pend);
         else
           expand_group(c, primary, my_dup, dn, a.vec_ok, epoch, lane);
       }
+      if (bulk && warp < copy_warps) expand_flush(c, pend, epoch, lane);
       ok = __syncthreads_and(ok ? 1 : 0) != 0;
     }
   } else if (ok) {
@@ -772,14 +831,20 @@ __device__ bool expand_role(const MoonepDevCtx& c, const DispatchArgs& a, int xi
         break;
       }
       if (bulk)
-        ok = expand_group_bulk(c, primary, my_dup, dn, epoch, lane, my_stage, a.chunk_bytes, s_xbar + warp, xphase);
+        ok = expand_group_bulk(c, primary, my_dup, dn, epoch, lane, my_stage, a.chunk_bytes, s_xbar + warp, xphase, pend);
       else
         expand_group(c, primary, my_dup, dn, a.vec_ok, epoch, lane);
     }
+    if (bulk && warp < copy_warps) expand_flush(c, pend, epoch, lane);
     ok = __syncthreads_and(ok ? 1 : 0) != 0;
   }
+  __syncthreads();
+  if (threadIdx.x == 0) stat_phase(c, MOONEP_PH_BUILD_EXPAND, t0);
+  t0 = globaltimer_ns();
   // the kernel ends when every row of the shard is present
-  return block_wait_flags(c, MOONEP_FLAG_SENT, a.epoch_sent, MOONEP_K_DISPATCH_EXPAND) && ok;
+  ok = block_wait_flags(c, MOONEP_FLAG_SENT, a.epoch_sent, MOONEP_K_DISPATCH_EXPAND) && ok;
+  if (threadIdx.x == 0) stat_phase(c, MOONEP_PH_WAIT_SENT, t0);
+  return ok;
 }
 
 // ---- the kernel ------------------------------------------------------------------------------------
@@ -829,6 +894,7 @@ __global__ void __launch_bounds__(kDispatchThreads, 1) dispatch_kernel(const Moo
   const int plan_epoch = abs_epoch(c, MOONEP_FLAG_PLAN, a.epoch_plan);
 
   if ((roles & MOONEP_ROLE_TABLES) && blockIdx.x == 0) {
+    const unsigned long long t0 = globaltimer_ns();
     ok = block_wait_flags(c, MOONEP_FLAG_TPE, a.epoch_tpe, MOONEP_K_PLAN_TABLES) && ok;
     if (ok) {
       TablesIO io;
@@ -849,6 +915,7 @@ __global__ void __launch_bounds__(kDispatchThreads, 1) dispatch_kernel(const Moo
       if (threadIdx.x == 0) {
         __threadfence();
         st_release_gpu(c.counters + MOONEP_CTR_TABLES_READY, plan_epoch);
+        stat_phase(c, MOONEP_PH_TABLES, t0);
       }
     }
   }
@@ -856,9 +923,11 @@ __global__ void __launch_bounds__(kDispatchThreads, 1) dispatch_kernel(const Moo
   if (roles & MOONEP_ROLE_TOKENS) {
     // every CTA of the launch plans blocks of tokens (the expanders have nothing else to do yet)
     ok = wait_local_epoch(c, MOONEP_CTR_TABLES_READY, plan_epoch, MOONEP_K_PLAN_TOKENS) && ok;
+    const unsigned long long t0 = globaltimer_ns();
     if (ok)
       for (int b = blockIdx.x; b < a.n_blocks; b += gridDim.x)
         plan_tokens_block(c, a.topk, a.dst, a.tokens_per_block, b, reinterpret_cast<int*>(s_dyn), s_tok);
+    if (threadIdx.x == 0 && (int)blockIdx.x < a.n_blocks) stat_phase(c, MOONEP_PH_TOKENS, t0);
     if (role_tail(c, MOONEP_CTR_PLAN_ARRIVE, gridDim.x) && !poisoned(c)) {
       if (threadIdx.x == 0) st_release_gpu(c.counters + MOONEP_CTR_PLAN_DONE, plan_epoch);
       for (int r = threadIdx.x; r < c.R; r += blockDim.x) st_release_sys(flag_ptr(c, r, MOONEP_FLAG_PLAN, c.rank), plan_epoch);
@@ -873,6 +942,7 @@ __global__ void __launch_bounds__(kDispatchThreads, 1) dispatch_kernel(const Moo
     else
       ok = block_wait_flags(c, a.wait_family, a.wait_epoch, MOONEP_K_DISPATCH_SEND) && ok;
     const int epoch = abs_epoch(c, MOONEP_FLAG_SENT, a.epoch_sent);
+    const unsigned long long t_send = globaltimer_ns();
     if (ok) {
       if (a.bulk) {
         if (warp < kBulkWarps)
@@ -883,6 +953,8 @@ __global__ void __launch_bounds__(kDispatchThreads, 1) dispatch_kernel(const Moo
         send_ldst(c, a, epoch);
       }
     }
+    __syncthreads();
+    if (threadIdx.x == 0) stat_phase(c, MOONEP_PH_SEND, t_send);
     if (role_tail(c, MOONEP_CTR_SEND_ARRIVE, scnt)) {
       if (threadIdx.x == 0) c.counters[MOONEP_CTR_SEND_WORK] = 0;
       if (ok && !poisoned(c))
@@ -890,7 +962,9 @@ __global__ void __launch_bounds__(kDispatchThreads, 1) dispatch_kernel(const Moo
     }
   }
 
-  if (is_expander) expand_role(c, a, xidx, xcnt, ok, s_dyn, s_xbar);
+  // the token stage's scratch (>= kZfChunk words) is free by now: the zero fill keeps its tables there
+  static_assert(sizeof(TokenScratch) >= kZfChunk * sizeof(int) && kExpandSlice >= kZfChunk, "scratch too small");
+  if (is_expander) expand_role(c, a, xidx, xcnt, ok, s_dyn, s_xbar, reinterpret_cast<int*>(&s_tok));
 }
 
 }  // namespace
@@ -974,8 +1048,9 @@ extern "C" int moonep_dispatch(void* ctx, int roles, int fresh, const int* topk,
     }
     if (hb > smem) smem = hb;
   }
-  if (int rc = check_cuda(cudaFuncSetAttribute(dispatch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               (int)imax((int)smem, 1024)),
+  // The attribute belongs to the kernel, not to the launch, and emulated ranks launch from several threads with
+  // different sizes: always allow the same maximum, so that no thread lowers it under another one's launch.
+  if (int rc = check_cuda(cudaFuncSetAttribute(dispatch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)limit),
                           "cudaFuncSetAttribute(dispatch_kernel)"))
     return rc;
 

@@ -82,6 +82,20 @@
 // stats[MOONEP_STAT_WAIT_COUNT + family]: number of such waits that did not find the flag already set.
 #define MOONEP_STAT_WAIT_MAX_NS 0
 #define MOONEP_STAT_WAIT_COUNT 8
+// stats[MOONEP_STAT_PHASE_NS + p]: longest time (ns, over the CTAs of a role, since the statistics were last reset) of
+// phase p of the dispatch and combine kernels, stamped with %globaltimer:
+#define MOONEP_STAT_PHASE_NS 16
+#define MOONEP_PH_TABLES 0        // TABLES role: wait for the tokens-per-expert rows + table stage
+#define MOONEP_PH_TOKENS 1        // TOKENS stage of one CTA (all its blocks)
+#define MOONEP_PH_SEND 2          // SEND role: first token grabbed .. all copies of the CTA complete
+#define MOONEP_PH_ZERO 3          // EXPAND role: zero fill
+#define MOONEP_PH_WAIT_PLAN 4     // EXPAND role: wait for every peer's FLAG_PLAN
+#define MOONEP_PH_BUILD_EXPAND 5  // EXPAND role: duplicate map + expansion (includes waiting for rows to land)
+#define MOONEP_PH_WAIT_SENT 6     // EXPAND role: final wait for every peer's FLAG_SENT
+#define MOONEP_PH_FOLD 7          // combine FOLD role
+#define MOONEP_PH_PUSH 8          // combine PUSH role (a copy warp)
+#define MOONEP_PH_SUM 9           // combine SUM role
+#define MOONEP_STAT_WORDS 32
 // counters[MOONEP_BIAS_OFF + family]: epoch bias added to every epoch argument of that family.
 #define MOONEP_BIAS_OFF 32
 
@@ -136,7 +150,7 @@ struct MoonepDevCtx {
   int* tpe_prev;      // [E]      tokens of expert e on source ranks < rank
   int* tables;        // planner work area, see planner.cu
   int* block_hist;    // [planner blocks, E] per-block expert histograms of the local routing
-  long long* stats;     // [16] flag-wait statistics, see MOONEP_STAT_*
+  long long* stats;     // [MOONEP_STAT_WORDS] flag-wait and phase statistics, see MOONEP_STAT_*
 };
 
 #ifdef __cplusplus

@@ -44,6 +44,7 @@ _KERNEL_NAMES = {
     7: "combine_prologue", 8: "combine_pull", 9: "prefetch", 10: "grad_accum", 11: "grad_clear", 12: "wait",
     13: "grouped_gemm", 14: "grouped_wgrad", 15: "grouped_gemm_pair", 16: "combine_push", 17: "combine_sum",
 }  # fmt: skip
+_PHASE_NAMES = ("tables", "tokens", "send", "zero_fill", "wait_plan", "build_expand", "wait_sent", "fold", "push", "sum")
 ROLE_TABLES, ROLE_TOKENS, ROLE_SEND, ROLE_EXPAND = 1, 2, 4, 8
 ROLE_PUSH, ROLE_SUM, ROLE_FOLD = 1, 2, 4
 _FAMILY_NAMES = {0: "READY", 1: "TPE", 2: "PLAN", 3: "SENT", 4: "COMB", 5: "GRAD_READY", 6: "GRAD_DONE", 7: "PREFETCH"}
@@ -89,7 +90,7 @@ class CudaBackend:
         self.expert_off = i32(R * E)
         self.tpe_prev = i32(E)
         self.tables = i32(self.lib.moonep_planner_table_words(R, E, B))
-        self.stats_buf = torch.zeros(16, dtype=torch.int64, device=dev)
+        self.stats_buf = torch.zeros(32, dtype=torch.int64, device=dev)
         tokens_per_block = max(1, PLAN_BLOCK // K)
         self.block_hist = i32(-(-S // tokens_per_block) * E)
         sm_count = torch.cuda.get_device_properties(dev).multi_processor_count
@@ -163,6 +164,8 @@ class CudaBackend:
         st = self.stats_buf.cpu().tolist()
         out["flag_wait_max_us"] = {_FAMILY_NAMES[f]: st[f] / 1e3 for f in _FAMILY_NAMES if st[8 + f]}
         out["flag_waits_that_spun"] = {_FAMILY_NAMES[f]: st[8 + f] for f in _FAMILY_NAMES if st[8 + f]}
+        # longest duration of each phase of the dispatch / combine kernels over their CTAs since reset_wait_stats()
+        out["kernel_phase_max_us"] = {name: st[16 + i] / 1e3 for i, name in enumerate(_PHASE_NAMES) if st[16 + i]}
         if self._profile:
             out["phase_times_us"] = self.phase_times()
         return out
