@@ -470,13 +470,17 @@ class Buffer:
 
         ``full_*_grad`` are ``[>=E, H, H']`` fp32 indexed by global expert id (only this rank's experts
         are touched).  With ``owner_local=True`` they are ``[E/R, H, H']`` and hold this rank's experts
-        only, which saves the memory of the other ranks' rows.
+        only, which saves the memory of the other ranks' rows.  A weight whose gradient and reduce buffer are both
+        ``None`` is left out (every rank must leave out the same ones), so that the weights can be reduced one by one
+        as their gradients become ready.
         """
         ctx = self._require_ctx()
         assert isinstance(plan, MoonEPCommPlan), "reduce_grad: plan is required"
-        grads = (full_gate_grad, full_up_grad, full_down_grad)
-        bufs = (gate_reduce_buffer, up_reduce_buffer, down_reduce_buffer)
-        assert all(t is not None for t in (*grads, *bufs)), "reduce_grad needs three gradients and three reduce buffers"
+        pairs = [(g, b) for g, b in ((full_gate_grad, gate_reduce_buffer), (full_up_grad, up_reduce_buffer),
+                                     (full_down_grad, down_reduce_buffer)) if g is not None or b is not None]  # fmt: skip
+        assert pairs and all(g is not None and b is not None for g, b in pairs), \
+            "reduce_grad needs a gradient together with its reduce buffer, for at least one weight"
+        grads, bufs = [g for g, _ in pairs], [b for _, b in pairs]
 
         def run():
             E = ctx["E"]

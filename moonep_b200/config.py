@@ -4,7 +4,8 @@ MOONEP_PLANNER        ``gpu`` (default) or ``cpu``: run the planner kernels or t
 MOONEP_TIMEOUT_MS     budget of every device-side wait (default 10000).
 MOONEP_COPY_PATH      ``bulk`` (default: TMA bulk copies through shared memory) or ``ldst``
                       (plain 16-byte loads/stores) for dispatch/combine/prefetch;
-                      ``MOONEP_SEND_PATH`` / ``MOONEP_PULL_PATH`` / ``MOONEP_GRAD_PATH`` set one kernel only.
+                      ``MOONEP_SEND_PATH`` / ``MOONEP_PULL_PATH`` / ``MOONEP_GRAD_PATH`` / ``MOONEP_PREFETCH_PATH`` set one
+                      kernel only; the last two also take ``async`` (cp.async rings in shared memory).
 MOONEP_EXPAND_PATH    ``bulk`` (default) or ``ldst``: how the destination side of dispatch copies duplicate rows and clears
                       pad rows (read by the native library).
 MOONEP_COMBINE        ``push`` (default: the expert side folds duplicates and pushes rows to the tokens' home ranks,
@@ -46,18 +47,22 @@ def timeout_ms() -> int:
 
 
 def copy_path(which: str = "") -> str:
-    """Copy path of the send (``which="send"``) or pull (``"pull"``) kernel.
+    """Copy path of the send (``which="send"``), pull (``"pull"``), gradient accumulation (``"grad"``) or prefetch
+    (``"prefetch"``) kernel.
 
-    ``MOONEP_SEND_PATH`` / ``MOONEP_PULL_PATH`` override ``MOONEP_COPY_PATH`` for one direction.
+    ``MOONEP_SEND_PATH`` / ``MOONEP_PULL_PATH`` / ``MOONEP_GRAD_PATH`` / ``MOONEP_PREFETCH_PATH`` override
+    ``MOONEP_COPY_PATH`` for one kernel.
     """
     raw = os.environ.get(f"MOONEP_{which.upper()}_PATH") if which else None
     if not raw:
         # measured on 8 B200: bulk stores win for the send, register loads for the pull
         # (bulk loads from peer memory measured below LSU loads, bulk stores to peer memory above LSU stores)
-        raw = os.environ.get("MOONEP_COPY_PATH", "ldst" if which in ("pull", "grad") else "bulk")
+        raw = os.environ.get("MOONEP_COPY_PATH", "ldst" if which in ("pull", "grad", "prefetch") else "bulk")
     raw = raw.lower()
-    if raw not in ("bulk", "ldst"):
-        raise ValueError(f"copy path must be 'bulk' or 'ldst', got {raw!r}")
+    # "async": 16-byte cp.async copies into per-warp shared-memory rings (gradient accumulation and prefetch only)
+    allowed = ("bulk", "ldst", "async") if which in ("grad", "prefetch") else ("bulk", "ldst")
+    if raw not in allowed:
+        raise ValueError(f"copy path must be one of {allowed}, got {raw!r}")
     return raw
 
 
@@ -89,6 +94,13 @@ def wgrad_on_kernel() -> bool:
     """MOONEP_WGRAD=torch: the MoE layer computes weight gradients with per-group torch matmuls instead of the
     grouped tcgen05 kernel (for comparisons)."""
     return os.environ.get("MOONEP_WGRAD", "kernel").lower() != "torch"
+
+
+def backward_overlap() -> bool:
+    """The MoE layer's backward starts ``reduce_grad`` of each weight on the communication stream as soon as that
+    weight's gradients exist, beside the remaining GEMMs (which then leave ``num_sms`` SMs to it).
+    MOONEP_BWD_OVERLAP=0 runs one ``reduce_grad`` for all three weights after the backward's combine."""
+    return os.environ.get("MOONEP_BWD_OVERLAP", "0") not in _FALSE
 
 
 def gemm_on_cta_pairs() -> bool:

@@ -659,26 +659,70 @@ __device__ __forceinline__ void expand_flush(const MoonepDevCtx& c, PendingRows&
   pend.dn = 0;
 }
 
-// Warp-wide bounded wait until row `loff` of the local shard carries `epoch`.
-__device__ bool wait_row(const MoonepDevCtx& c, int loff, int epoch, int lane) {
-  int ok = 1;
-  if (lane == 0) {
-    const int* f = c.meta_peer[c.rank] + c.rowflag_off + loff;
-    if (ld_acquire_sys(f) - epoch < 0) {
-      const unsigned long long t0 = globaltimer_ns();
-      unsigned spins = 0;
-      int v;
-      while ((v = ld_acquire_sys(f)) - epoch < 0) {
-        if ((++spins & 63u) == 0 && (globaltimer_ns() - t0 > c.timeout_ns || poisoned(c))) {
-          record_status(c, MOONEP_STATUS_TIMEOUT, MOONEP_K_DISPATCH_EXPAND, 200, loff, epoch, v);
-          ok = 0;
-          break;
+// Expands the groups of this warp, `count` of them, group number `group_of(k)` (negative: nothing to do), in the
+// order in which their primary rows arrive rather than in list order: rows land in the senders' token order, which
+// has nothing to do with the order of the rows in the shard, and a warp that sat on its first missing row would push
+// all its copies to the end of the kernel.  Lane 0 polls the row flags of up to 32 pending groups per round; a round
+// without progress sleeps, and the usual time limit applies to the whole wait.
+template <class GroupOf>
+__device__ bool expand_as_rows_arrive(const MoonepDevCtx& c, const DispatchArgs& a, int count, GroupOf group_of, int epoch,
+                                      int lane, bool bulk, unsigned char* my_stage, unsigned long long* my_bar,
+                                      unsigned& xphase, PendingRows& pend) {
+  const int* rowflag = c.meta_peer[c.rank] + c.rowflag_off;
+  const int NvS = c.NvS;
+  for (int k0 = 0; k0 < count; k0 += 32) {
+    const int nk = min(32, count - k0);
+    unsigned pending = nk == 32 ? 0xffffffffu : ((1u << nk) - 1u);
+    unsigned long long t0 = 0;
+    unsigned idle = 0;
+    while (pending != 0) {
+      // lane k looks at group k0 + k: which of the pending groups have their primary row?
+      int g = -1, primary = -1;
+      bool ready = false;
+      if (lane < nk && ((pending >> lane) & 1u)) {
+        g = group_of(k0 + lane);
+        if (g >= 0) {
+          primary = a.dup_groups[3 * g];
+          if (primary < 0 || primary >= NvS) g = -1;
         }
-        __nanosleep(128);
+        ready = g < 0 || ld_acquire_sys(rowflag + primary) - epoch >= 0;
+      }
+      unsigned now = __ballot_sync(0xffffffffu, ready);
+      if (now == 0) {
+        if (idle++ == 0) {
+          t0 = globaltimer_ns();
+          if (bulk) expand_flush(c, pend, epoch, lane);  // nothing to copy: release the flags still held back
+        }
+        int give_up = 0;
+        if (lane == 0 && (idle & 15u) == 0 && (globaltimer_ns() - t0 > c.timeout_ns || poisoned(c))) {
+          const int k = __ffs(pending) - 1;
+          record_status(c, MOONEP_STATUS_TIMEOUT, MOONEP_K_DISPATCH_EXPAND, 200, group_of(k0 + k), epoch, (int)pending);
+          give_up = 1;
+        }
+        if (__shfl_sync(0xffffffffu, give_up, 0)) return false;
+        __nanosleep(256);
+        continue;
+      }
+      idle = 0;
+      pending &= ~now;
+      while (now != 0) {
+        const int k = __ffs(now) - 1;
+        now &= now - 1;
+        const int gk = __shfl_sync(0xffffffffu, g, k);
+        if (gk < 0) continue;
+        const int pk = __shfl_sync(0xffffffffu, primary, k);
+        const int ds = a.dup_groups[3 * gk + 1], dn = a.dup_groups[3 * gk + 2];
+        if (ds < 0 || dn < 0 || ds + dn > NvS) continue;
+        const int my_dup = lane < dn ? a.dup_loffs[ds + lane] : -1;
+        if (bulk) {
+          if (!expand_group_bulk(c, pk, my_dup, dn, epoch, lane, my_stage, a.chunk_bytes, my_bar, xphase, pend)) return false;
+        } else {
+          expand_group(c, pk, my_dup, dn, a.vec_ok, epoch, lane);
+        }
       }
     }
   }
-  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+  return true;
 }
 
 // xidx of xcnt expander CTAs.  Returns false after a failed wait.
@@ -801,20 +845,10 @@ __device__ bool expand_role(const MoonepDevCtx& c, const DispatchArgs& a, int xi
       }
       __syncthreads();
       const int ng = a.build_only ? 0 : s_ngroups;
-      for (int i = warp; i < ng && ok && warp < copy_warps; i += copy_warps) {
-        const int g = s_groups[i];
-        if (g < 0) continue;
-        const int primary = a.dup_groups[3 * g], ds = a.dup_groups[3 * g + 1], dn = a.dup_groups[3 * g + 2];
-        const int my_dup = lane < dn ? a.dup_loffs[ds + lane] : -1;
-        if (!wait_row(c, primary, epoch, lane)) {
-          ok = false;
-          break;
-        }
-        if (bulk)
-          ok = expand_group_bulk(c, primary, my_dup, dn, epoch, lane, my_stage, a.chunk_bytes, s_xbar + warp, xphase, pend);
-        else
-          expand_group(c, primary, my_dup, dn, a.vec_ok, epoch, lane);
-      }
+      if (ok && warp < copy_warps && warp < ng)
+        ok = expand_as_rows_arrive(
+            c, a, (ng - warp + copy_warps - 1) / copy_warps, [&](int k) { return s_groups[warp + k * copy_warps]; }, epoch,
+            lane, bulk, my_stage, s_xbar + warp, xphase, pend);
       if (bulk && warp < copy_warps) expand_flush(c, pend, epoch, lane);
       ok = __syncthreads_and(ok ? 1 : 0) != 0;
     }
@@ -822,19 +856,11 @@ __device__ bool expand_role(const MoonepDevCtx& c, const DispatchArgs& a, int xi
     // replayed plan: the groups are in the plan
     int ngroups = a.dup_counts[0];
     if (ngroups < 0 || ngroups > NvS) ngroups = 0;
-    for (int g = xidx * copy_warps + warp; g < ngroups && ok && warp < copy_warps; g += xcnt * copy_warps) {
-      const int primary = a.dup_groups[3 * g], ds = a.dup_groups[3 * g + 1], dn = a.dup_groups[3 * g + 2];
-      if (primary < 0 || primary >= NvS || ds < 0 || dn < 0 || ds + dn > NvS) continue;
-      const int my_dup = lane < dn ? a.dup_loffs[ds + lane] : -1;
-      if (!wait_row(c, primary, epoch, lane)) {
-        ok = false;
-        break;
-      }
-      if (bulk)
-        ok = expand_group_bulk(c, primary, my_dup, dn, epoch, lane, my_stage, a.chunk_bytes, s_xbar + warp, xphase, pend);
-      else
-        expand_group(c, primary, my_dup, dn, a.vec_ok, epoch, lane);
-    }
+    const int g0 = xidx * copy_warps + warp, gstride = xcnt * copy_warps;
+    if (warp < copy_warps && g0 < ngroups)
+      ok = expand_as_rows_arrive(
+          c, a, (ngroups - g0 + gstride - 1) / gstride, [&](int k) { return g0 + k * gstride; }, epoch, lane, bulk,
+          my_stage, s_xbar + warp, xphase, pend);
     if (bulk && warp < copy_warps) expand_flush(c, pend, epoch, lane);
     ok = __syncthreads_and(ok ? 1 : 0) != 0;
   }

@@ -244,27 +244,47 @@ class ExpertParallelMoE:
         dgate_nvs = ctx["weights_buf_local"].view(torch.float32)  # gate gradients ride the weights channel home
         swiglu_bwd(saved["a"], saved["u"], g, w_nvs, cu[-1:], dadu, hsw, dgate_nvs)
         del g
-        if not self._weight_grads_on_kernel(x_nvs, dy_nvs, dadu, hsw, cu):
+        # Weight by weight: as soon as the gradients of one weight exist, its reduce_grad starts on the communication
+        # stream and runs beside the GEMMs that follow, which leave the communication kernels their SMs.
+        reduced, grads = [], (self.g_gate, self.g_up, self.g_down)
+
+        def reduce_one(i):
+            sel = [None] * 6
+            sel[i], sel[3 + i] = grads[i], self.red[i]
+            reduced.append(self.buffer.reduce_grad(plan, True, *sel, owner_local=True))
+
+        overlap = config.backward_overlap() and x_nvs.is_cuda
+        sms = 0
+        if overlap:
+            total = torch.cuda.get_device_properties(dev).multi_processor_count
+            sms = max(2, (total - int(self.buffer._require_ctx()["num_sms"])) // 2 * 2)
+        if not self._weight_grads_on_kernel(x_nvs, dy_nvs, dadu, hsw, cu, after=reduce_one if overlap else None, num_sms=sms):
             self._weight_grads_per_group(x_nvs, dy_nvs, dadu, hsw, cu)
-        self._times_weights(dadu, [self.w_gate, self.w_up], cu, plan, out=dy_nvs)  # dx rows = da Wg + du Wu
+        self._times_weights(dadu, [self.w_gate, self.w_up], cu, plan, out=dy_nvs,
+                            num_sms=sms if reduced else 0)  # dx rows = da Wg + du Wu
         dx, dgates, _ = buf.combine(plan, dy_nvs, dgate_nvs, zero_copy=True)
-        self.buffer.reduce_grad(plan, False, self.g_gate, self.g_up, self.g_down, self.red[0], self.red[1], self.red[2],
-                        owner_local=True)  # fmt: skip
+        if reduced:
+            for ev in reduced:  # the gradients are complete, and the reduce slots cleared, for whatever comes next
+                torch.cuda.current_stream().wait_event(ev)
+        else:
+            self.buffer.reduce_grad(plan, False, *grads, self.red[0], self.red[1], self.red[2], owner_local=True)
         return dx, dgates
 
-    def _times_weights(self, x, ws, cu, plan, out=None):
+    def _times_weights(self, x, ws, cu, plan, out=None, num_sms=0):
         """``x[rows of g] @ cat(ws, dim=1)[g]`` per group: what an activation gradient needs from forward weights
         stored ``[E+B, out, in]`` (which is ``[G, K, N]`` for this product).  The CTA-pair kernel stages them as
         MN-major tiles; elsewhere K-major copies of the local experts feed the ordinary grouped GEMM."""
         if kn_kernel_supports(x, ws):
-            return grouped_gemm_kn(x, ws, cu, out=out)
+            return grouped_gemm_kn(x, ws, cu, out=out, num_sms=num_sms)
         return grouped_gemm(x, self._local_transposed(ws, plan), cu, group_map=self.group_map, out=out,
                             status=self.buffer._require_ctx()["_backend"].status if x.is_cuda else None)
 
-    def _weight_grads_on_kernel(self, x_nvs, dy_nvs, dadu, hsw, cu) -> bool:
+    def _weight_grads_on_kernel(self, x_nvs, dy_nvs, dadu, hsw, cu, after=None, num_sms=0) -> bool:
         """All weight gradients with three launches of the grouped tcgen05 kernel (no host synchronisation); every
         group's result goes straight to the owner's gradient or to the reduce-buffer slot of a prefetched copy.
-        Returns False (nothing done) when the shapes do not fit the kernel."""
+        Returns False (nothing done) when the shapes do not fit the kernel.  ``after(i)`` is called once the
+        gradients of weight ``i`` (0 gate, 1 up, 2 down) are enqueued; launches after the first such call use
+        ``num_sms`` SMs."""
         I, H = self.I, self.H
         rows = int(x_nvs.shape[0]) // 64 * 64
         dev = x_nvs.device
@@ -278,10 +298,15 @@ class ExpertParallelMoE:
         flags = self._wgrad_flags[bool(self._fresh)]
         status = self.buffer._require_ctx()["_backend"].status
         ptrs = self._wgrad_ptrs
+        done = after if after is not None else (lambda i: None)
+        later = num_sms if after is not None else 0
         if config.wgrad_layout() == "rows":  # the kernel stages MN-major tiles: the activations as they are
-            grouped_wgrad_rows(dadu[:, :I], x_nvs, cu, ptrs[0], flags, status=status)  # dW_gate = da^T x
-            grouped_wgrad_rows(dadu[:, I:], x_nvs, cu, ptrs[1], flags, status=status)  # dW_up   = du^T x
             grouped_wgrad_rows(dy_nvs, hsw, cu, ptrs[2], flags, status=status)  # dW_down = dy^T (h * gate weight)
+            done(2)
+            grouped_wgrad_rows(dadu[:, :I], x_nvs, cu, ptrs[0], flags, status=status, num_sms=later)  # dW_gate = da^T x
+            done(0)
+            grouped_wgrad_rows(dadu[:, I:], x_nvs, cu, ptrs[1], flags, status=status, num_sms=later)  # dW_up   = du^T x
+            done(1)
         else:  # K-major tiles from transposed copies
 
             def transposed(t):
@@ -289,9 +314,12 @@ class ExpertParallelMoE:
                 return transpose_experts(t[:rows].unsqueeze(0), out)[0]
 
             xt, dadut, dyt, hswt = transposed(x_nvs), transposed(dadu), transposed(dy_nvs), transposed(hsw)
-            grouped_wgrad(dadut[:I], xt, cu, ptrs[0], flags, status=status)
-            grouped_wgrad(dadut[I:], xt, cu, ptrs[1], flags, status=status)
             grouped_wgrad(dyt, hswt, cu, ptrs[2], flags, status=status)
+            done(2)
+            grouped_wgrad(dadut[:I], xt, cu, ptrs[0], flags, status=status, num_sms=later)
+            done(0)
+            grouped_wgrad(dadut[I:], xt, cu, ptrs[1], flags, status=status, num_sms=later)
+            done(1)
         self._fresh = False
         return True
 

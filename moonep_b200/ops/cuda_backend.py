@@ -38,7 +38,7 @@ from ..constants import (
 from ..errors import MoonEPIndexError, MoonEPTimeoutError
 from . import _lib
 
-_PATHS = {"ldst": 0, "bulk": 1}
+_PATHS = {"ldst": 0, "bulk": 1, "async": 2}
 _KERNEL_NAMES = {
     1: "signal", 2: "plan_publish", 3: "plan_tables", 4: "plan_tokens", 5: "dispatch_send", 6: "dispatch_expand",
     7: "combine_prologue", 8: "combine_pull", 9: "prefetch", 10: "grad_accum", 11: "grad_clear", 12: "wait",
@@ -77,6 +77,7 @@ class CudaBackend:
         self.send_path = _PATHS[config.copy_path("send")] if R > 1 else _PATHS["ldst"]
         self.pull_path = _PATHS[config.copy_path("pull")]
         self.grad_path = _PATHS[config.copy_path("grad")]
+        self.prefetch_path = _PATHS[config.copy_path("prefetch")]
         self._profile = None
         self._nvtx = config.nvtx()
         self._quiesced = False  # every peer is known to be past its last pull from this rank's shard
@@ -547,7 +548,7 @@ class CudaBackend:
         if nslots == self.ctx["B"]:  # the Buffer's own prefetch slots: per-slot flags for a GEMM that runs beside the copy
             flags, done = self._slot_scratch()
             epoch = self._next(FLAG_PREFETCH)
-        self._call("moonep_prefetch", src, dst, n, _ptr(experts_row), H * Hp, nslots, nexp, self.path, _ptr(flags),
+        self._call("moonep_prefetch", src, dst, n, _ptr(experts_row), H * Hp, nslots, nexp, self.prefetch_path, _ptr(flags),
                    _ptr(done), epoch, _stream())  # fmt: skip
 
     def gemm_hooks(self, *, rows=False, tables=False, slots=False, done_counter=None):

@@ -6,6 +6,17 @@ import torch
 from moonep_b200.ops.grouped_gemm import grouped_gemm, grouped_gemm_reference
 
 
+def grouped_gemm_reference_fp32(x, w, cu):
+    """``x[rows of g] @ w[g].T`` in fp32 without the final rounding to bf16."""
+    out = torch.zeros(x.shape[0], w.shape[1], dtype=torch.float32, device=x.device)
+    start = 0
+    for g, end in enumerate(cu.tolist()):
+        if end > start:
+            out[start:end] = x[start:end].float() @ w[g].float().t()
+        start = max(start, end)
+    return out
+
+
 def _case(G, rows_per_group, K, N, seed=0, device="cuda"):
     g = torch.Generator().manual_seed(seed)
     ends, total = [], 0
@@ -19,6 +30,48 @@ def _case(G, rows_per_group, K, N, seed=0, device="cuda"):
     cu = torch.tensor(ends, dtype=torch.int32, device=device)
     scale = torch.rand(rows_cap, generator=g).to(device)
     return x, w, w2, cu, scale, total
+
+
+def _group_of_rows(cu, total):
+    """Group index of every row below ``total`` (ends are cumulative)."""
+    ends = cu.to(torch.int64)
+    return torch.searchsorted(ends, torch.arange(total, device=cu.device), right=True)
+
+
+def _abs_dot(x, w, cu, total):
+    """``sum_k |x[r, k]| * |w[g(r), n, k]|``: the scale of the rounding error of one output element."""
+    out = torch.zeros(total, w.shape[1], dtype=torch.float32, device=x.device)
+    start = 0
+    for g, end in enumerate(cu.tolist()):
+        if end > start:
+            out[start:end] = x[start:end].float().abs() @ w[g].float().abs().t()
+        start = max(start, end)
+    return out
+
+
+# A bf16 result is within one rounding (2^-9 relative) of the exact value plus the error of the fp32 accumulation,
+# which over K / 16 tensor-core steps stays below (K / 16) * 2^-23 of the sum of absolute products: 1.6e-5 at K = 2048.
+BF16_REL = 2.0**-8
+ACC_REL = 5e-5
+
+
+def _assert_elementwise(got, want, scale, what):
+    """|got - want| <= 2^-8 |want| + ACC_REL * scale, element by element; a lost 64-wide K block is far outside."""
+    bound = BF16_REL * want.abs() + ACC_REL * scale + 1e-30
+    excess = ((got - want).abs() / bound).max().item()
+    assert excess <= 1.0, f"{what}: an element is {excess:.2f} times its error bound away from the fp32 reference"
+
+
+def test_elementwise_bound_catches_a_dropped_k_block():
+    x, w, w2, cu, scale, total = _case(2, [128, 128], 256, 128, device="cpu")
+    want = torch.cat([x[:128].float() @ w[0].float().t(), x[128:256].float() @ w[1].float().t()])
+    ad = _abs_dot(x, w, cu, total)
+    _assert_elementwise(want.to(torch.bfloat16).float(), want, ad, "exact")
+    xd = x.clone()
+    xd[:, 64:128] = 0  # the second K block never reaches the accumulator
+    bad = torch.cat([xd[:128].float() @ w[0].float().t(), xd[128:256].float() @ w[1].float().t()])
+    with pytest.raises(AssertionError):
+        _assert_elementwise(bad.to(torch.bfloat16).float(), want, ad, "dropped block")
 
 
 def test_reference_on_cpu_matches_dense():
@@ -52,10 +105,22 @@ def test_grouped_gemm_matches_fp32_reference(mode, G, rows, K, N, pair):
     kw.pop("pair")
     ref = grouped_gemm_reference(x, w, cu, mode=mode, **kw)
     kw["pair"] = pair
-    got, want = y[:total].float(), ref[:total].float()
-    err = (got - want).abs().max().item()
-    tol = 2e-2 * max(1.0, want.abs().max().item())
-    assert err <= tol, f"max abs err {err} > {tol}"
+    # the oracle in fp32 before its final rounding, and the error scale of every element
+    got = y[:total].float()
+    ad = _abs_dot(x, w, cu, total)
+    acc = grouped_gemm_reference_fp32(x, w, cu)[:total]
+    if mode == "plain":
+        want, scale_el = acc, ad
+    elif mode == "scale":
+        want, scale_el = acc * scale[:total, None], ad * scale[:total, None].abs()
+    else:
+        up = grouped_gemm_reference_fp32(x, w2, cu)[:total]
+        sig = torch.sigmoid(acc)
+        want = acc * sig * up
+        # d silu / d a is bounded by 1.1; the fast exponential adds a few 2^-22 relative
+        scale_el = 1.1 * ad * up.abs() + _abs_dot(x, w2, cu, total) * (acc * sig).abs() + 0.05 * want.abs()
+    _assert_elementwise(got, want, scale_el, mode)
+    assert (got - ref[:total].float()).abs().max().item() <= 2.0**-7 * max(1e-3, want.abs().max().item())
     # twice in a row on the same buffers (TMEM and barriers are re-initialised per launch)
     y2 = grouped_gemm(x, w, cu, mode=mode, status=status, **kw)
     torch.cuda.synchronize()
@@ -66,9 +131,8 @@ def test_grouped_gemm_matches_fp32_reference(mode, G, rows, K, N, pair):
         torch.cuda.synchronize()
         assert torch.equal(y3[:total], y[:total])
         for got_pre, wt in zip(pre, (w, w2)):
-            want_pre = grouped_gemm_reference(x, wt, cu)[:total].float()
-            err = (got_pre[:total].float() - want_pre).abs().max().item()
-            assert err <= 2e-2 * max(1.0, want_pre.abs().max().item()), f"pre-activation err {err}"
+            want_pre = grouped_gemm_reference_fp32(x, wt, cu)[:total]
+            _assert_elementwise(got_pre[:total].float(), want_pre, _abs_dot(x, wt, cu, total), "pre-activation")
 
 
 def _wgrad_case(rows, P, Q, seed=0, device="cpu"):
@@ -140,16 +204,23 @@ def test_grouped_wgrad_matches_fp32_reference(rows, P, Q, layout):
     want = init.clone().cpu()
     targets = [None if g == skipped else want[g] for g in range(G)]
     grouped_wgrad_reference(left.cpu(), right.cpu(), cu.cpu(), targets, flag_list)
-    err = (out.cpu() - want).abs().max().item()
-    tol = 2e-3 * max(1.0, want.abs().max().item())
-    assert err <= tol, f"max abs err {err} > {tol}"
+    # fp32 results: the accumulation error only, scaled by the sum of absolute products of each element
+    ad = torch.zeros(G, P, Q)
+    start = 0
+    for g, end in enumerate(cu.tolist()):
+        if end > start:
+            ad[g] = left[start:end].float().abs().cpu().t() @ right[start:end].float().abs().cpu()
+        start = max(start, end)
+    bound = ACC_REL * ad + 2.0**-22 * want.abs() + 1e-30
+    excess = ((out.cpu() - want).abs() / bound).max().item()
+    assert excess <= 1.0, f"an element is {excess:.2f} times its error bound away from the fp32 reference"
     # again on the same buffers: accumulating groups add a second time, the others give the same result
     run(torch.tensor(ptrs, dtype=torch.int64, device="cuda"), flags)
     torch.cuda.synchronize()
     assert status.tolist()[0] == 0
     grouped_wgrad_reference(left.cpu(), right.cpu(), cu.cpu(), targets, flag_list)
-    err = (out.cpu() - want).abs().max().item()
-    assert err <= 2 * tol, f"second launch: max abs err {err}"
+    excess = ((out.cpu() - want).abs() / (2 * bound)).max().item()
+    assert excess <= 1.0, f"second launch: an element is {excess:.2f} times its error bound away"
 
 
 def test_kn_reference_on_cpu():
@@ -188,9 +259,11 @@ def test_grouped_gemm_kn_matches_fp32_reference(rows, Ks, N):
     y = grouped_gemm_kn(x, ws, cu, status=status)
     torch.cuda.synchronize()
     assert status.tolist()[0] == 0, f"kernel reported status {status.tolist()}"
-    want = grouped_gemm_kn_reference(x, ws, cu)[:total].float()
-    err = (y[:total].float() - want).abs().max().item()
-    assert err <= 2e-2 * max(1.0, want.abs().max().item()), f"max abs err {err}"
+    wcat = torch.cat(ws, dim=1).transpose(1, 2).contiguous()  # [G, N, K]
+    want = grouped_gemm_reference_fp32(x, wcat, cu)[:total]
+    _assert_elementwise(y[:total].float(), want, _abs_dot(x, wcat, cu, total), "kn")
+    ref = grouped_gemm_kn_reference(x, ws, cu)[:total].float()
+    assert (y[:total].float() - ref).abs().max().item() <= 2.0**-7 * max(1e-3, want.abs().max().item())
 
 
 @pytest.mark.parametrize("seed", range(6))

@@ -77,13 +77,36 @@ def test_prefetch_and_reduce_grad(device, table, R):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("table", ["fan_in", "random"])
-def test_reduce_grad_on_the_bulk_copy_path(table, monkeypatch):
-    """The TMA-ring variant of the gradient accumulation (``MOONEP_GRAD_PATH=bulk``) keeps the bitwise order."""
-    monkeypatch.setenv("MOONEP_GRAD_PATH", "bulk")
+@pytest.mark.parametrize("path", ["bulk", "async", "ldst"])
+def test_reduce_grad_on_every_copy_path(table, path, monkeypatch):
+    """The TMA-ring (``MOONEP_GRAD_PATH=bulk``), cp.async-ring (``async``) and register (``ldst``) variants of the
+    gradient accumulation all keep the bitwise order of the additions."""
+    monkeypatch.setenv("MOONEP_GRAD_PATH", path)
+    monkeypatch.setenv("MOONEP_PREFETCH_PATH", path)  # "bulk" means the register kernel for the prefetch
     _prefetch_and_reduce_grad("cuda", table, 4)
 
 
-def _prefetch_and_reduce_grad(device, table, R, Hw=128, Hp=256, epn=4, B=3, num_sms=5):
+@pytest.mark.gpu
+@pytest.mark.parametrize("path", ["async", "ldst"])
+def test_reduce_grad_paths_on_odd_sizes(path, monkeypatch):
+    """Experts whose size is not a multiple of a 2 KB stage (384 x 128 fp32 = 96 stages; 128 x 128 with one SM) and
+    more slots per expert than ranks."""
+    monkeypatch.setenv("MOONEP_GRAD_PATH", path)
+    monkeypatch.setenv("MOONEP_PREFETCH_PATH", path)
+    _prefetch_and_reduce_grad("cuda", "fan_in", 4, Hw=384, Hp=128, epn=2, B=4, num_sms=3)
+    _prefetch_and_reduce_grad("cuda", "random_seed2", 2, Hw=128, Hp=128, epn=1, B=1, num_sms=1)
+    # 36 slots hold the same expert: the async variant lists 32 of them per pass over a piece
+    _prefetch_and_reduce_grad("cuda", "fan_in", 4, Hw=128, Hp=128, epn=2, B=12, num_sms=2)
+
+
+@pytest.mark.parametrize("device", DEVICES)
+def test_reduce_grad_one_weight_at_a_time(device):
+    """A weight whose gradient and reduce buffer are both None is left out; three calls with one weight each
+    (the first two asynchronous, on the communication stream) give what one call with all three gives."""
+    _prefetch_and_reduce_grad(device, "random", 2, one_by_one=True)
+
+
+def _prefetch_and_reduce_grad(device, table, R, Hw=128, Hp=256, epn=4, B=3, num_sms=5, one_by_one=False):
     S, H, K = 32, 64, 2
     E = R * epn
     lw, bufs = _world(R, device, S, H, K, epn, B, num_sms=num_sms)
@@ -116,6 +139,14 @@ def _prefetch_and_reduce_grad(device, table, R, Hw=128, Hp=256, epn=4, B=3, num_
             torch.cuda.synchronize()
         lw.view(r).step()
         for _rep in range(2):  # the second call finds the consumed slots cleared and must add zeros
+            if one_by_one:
+                for t in (2, 0, 1):
+                    sel = [None] * 6
+                    sel[t], sel[3 + t] = grads[t], shared_red[t]
+                    ev = bufs[r].reduce_grad(plan, t != 1, *sel)
+                    if ev is not None:
+                        ev.wait()
+                continue
             bufs[r].reduce_grad(plan, False, grads[0], grads[1], grads[2], shared_red[0], shared_red[1], shared_red[2])
         if device == "cuda":
             torch.cuda.synchronize()
