@@ -5,7 +5,10 @@ MOONEP_TIMEOUT_MS     budget of every device-side wait (default 10000).
 MOONEP_COPY_PATH      ``bulk`` (default: TMA bulk copies through shared memory) or ``ldst``
                       (plain 16-byte loads/stores) for dispatch/combine/prefetch;
                       ``MOONEP_SEND_PATH`` / ``MOONEP_PULL_PATH`` / ``MOONEP_GRAD_PATH`` / ``MOONEP_PREFETCH_PATH`` set one
-                      kernel only; the last two also take ``async`` (cp.async rings in shared memory).
+                      kernel only; the prefetch defaults to ``async`` (cp.async rings in shared memory; ``ldst`` for
+                      register copies) whatever ``MOONEP_COPY_PATH`` says.
+MOONEP_RING_STAGES    2..6 (default 4): 2 KB stages per warp of the prefetch kernel's cp.async ring (read by the native
+                      library).
 MOONEP_EXPAND_PATH    ``bulk`` (default) or ``ldst``: how the destination side of dispatch copies duplicate rows and clears
                       pad rows (read by the native library).
 MOONEP_COMBINE        ``push`` (default: the expert side folds duplicates and pushes rows to the tokens' home ranks,
@@ -57,10 +60,13 @@ def copy_path(which: str = "") -> str:
     if not raw:
         # measured on 8 B200: bulk stores win for the send, register loads for the pull
         # (bulk loads from peer memory measured below LSU loads, bulk stores to peer memory above LSU stores)
-        raw = os.environ.get("MOONEP_COPY_PATH", "ldst" if which in ("pull", "grad", "prefetch") else "bulk")
+        if which == "prefetch":
+            raw = "async"  # measured 668 GB/s against 629 GB/s of the register kernel on 2 B200
+        else:
+            raw = os.environ.get("MOONEP_COPY_PATH", "ldst" if which in ("pull", "grad") else "bulk")
     raw = raw.lower()
-    # "async": 16-byte cp.async copies into per-warp shared-memory rings (gradient accumulation and prefetch only)
-    allowed = ("bulk", "ldst", "async") if which in ("grad", "prefetch") else ("bulk", "ldst")
+    # "async": 16-byte cp.async copies into per-warp shared-memory rings (prefetch only)
+    allowed = ("bulk", "ldst", "async") if which == "prefetch" else ("bulk", "ldst")
     if raw not in allowed:
         raise ValueError(f"copy path must be one of {allowed}, got {raw!r}")
     return raw

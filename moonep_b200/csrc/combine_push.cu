@@ -302,7 +302,7 @@ constexpr int kMoveQ = 32;
 constexpr int kMoveLag = 12;
 
 struct MoveQueue {
-  int* lagged[kMoveWarps][kMoveLag + 2];  // flag of every item in flight that is the last piece of its row, else null
+  int* lagged[kMoveWarps][kMoveLag + 4];  // flag of every item in flight that is the last piece of its row, else null
   int* flag[kMoveWarps][kMoveQ];
   int head[kMoveWarps], tail[kMoveWarps], done[kMoveWarps];
 };
@@ -526,7 +526,7 @@ __device__ void push_role(const MoonepDevCtx& c, const PushArgs& a, unsigned cha
     return true;
   };
 
-  // three-stage ring, as in the dispatch send role: the load of item i+1 is in flight while item i is stored
+  // three-stage ring, as in the dispatch send role: the loads of items i+1 and i+2 are in flight while item i is stored
   unsigned char* r_dst[kMoveStages];
   unsigned r_len[kMoveStages];
   int loaded = 0, done = 0, pushed = 0;
@@ -539,14 +539,14 @@ __device__ void push_role(const MoonepDevCtx& c, const PushArgs& a, unsigned cha
         r_len[q] = len;
       }
     if (lane == 0) {
-      mq.lagged[w][loaded % (kMoveLag + 2)] = flag;
+      mq.lagged[w][loaded % (kMoveLag + 4)] = flag;
       mbar_expect_tx(s_bar + s, len);
       bulk_g2s(s_ring + (size_t)s * a.chunk_bytes, src, len, s_bar + s);
     }
     ++loaded;
   };
   auto flag_item = [&](int j) {
-    int* flag = lane == 0 ? mq.lagged[w][j % (kMoveLag + 2)] : nullptr;
+    int* flag = lane == 0 ? mq.lagged[w][j % (kMoveLag + 4)] : nullptr;
     if (flag != nullptr && lane == 0) {
       if (pushed - lds_acquire(&mq.tail[w]) >= kMoveQ) {
         const unsigned long long t0 = globaltimer_ns();
@@ -569,17 +569,13 @@ __device__ void push_role(const MoonepDevCtx& c, const PushArgs& a, unsigned cha
   unsigned char* dst;
   unsigned len;
   int* flag;
-  bool more = next_item(src, dst, len, flag);
-  if (more) issue_load(src, dst, len, flag);
+  // loads run two items ahead of the stores (see the dispatch send role)
+  bool more = true;
+  for (int q = 0; q < kMoveStages - 1 && more; ++q) {
+    more = next_item(src, dst, len, flag);
+    if (more) issue_load(src, dst, len, flag);
+  }
   while (done < loaded && !failed) {
-    if (more) {
-      more = next_item(src, dst, len, flag);
-      if (more) {
-        if (lane == 0) bulk_wait_read<1>();  // the stage to refill was read by the group committed two items ago
-        __syncwarp();
-        issue_load(src, dst, len, flag);
-      }
-    }
     const int s = done % kMoveStages;
     unsigned char* o = nullptr;
     unsigned olen = 0;
@@ -606,6 +602,14 @@ __device__ void push_role(const MoonepDevCtx& c, const PushArgs& a, unsigned cha
       if (lane == 0) bulk_wait<kMoveLag>();  // item done-1-kMoveLag has reached its home rank
       flag_item(done - 1 - kMoveLag);
       failed = __shfl_sync(0xffffffffu, failed ? 1 : 0, 0) != 0;
+    }
+    if (more && !failed) {
+      more = next_item(src, dst, len, flag);
+      if (more) {
+        if (lane == 0) bulk_wait_read<1>();  // every group but the one just committed has read its stage
+        __syncwarp();
+        issue_load(src, dst, len, flag);
+      }
     }
   }
   if (lane == 0) bulk_wait<0>();

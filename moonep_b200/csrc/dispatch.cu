@@ -260,7 +260,7 @@ constexpr int kFlagQ = 32;  // tokens a bulk warp may be ahead of its helper
 constexpr int kFlagLag = 12;
 
 struct FlagQueue {
-  int lagged[kBulkWarps][kFlagLag + 2];  // token of every item in flight whose last piece it is, else -1
+  int lagged[kBulkWarps][kFlagLag + 4];  // token of every item in flight whose last piece it is, else -1
   int tok[kBulkWarps][kFlagQ];
   int head[kBulkWarps];  // tokens pushed so far (written by the bulk warp)
   int tail[kBulkWarps];  // tokens consumed so far (written by the helper)
@@ -455,7 +455,7 @@ __device__ bool send_bulk(const MoonepDevCtx& c, const DispatchArgs& a, int epoc
         ring_d[q] = d;
       }
     if (lane == 0) {
-      fq.lagged[warp][loaded % (kFlagLag + 2)] = (ch == a.nchunks - 1) ? tok : -1;
+      fq.lagged[warp][loaded % (kFlagLag + 4)] = (ch == a.nchunks - 1) ? tok : -1;
       const unsigned len = chunk_len(ch);
       mbar_expect_tx(bar + s, len);
       bulk_g2s(ring + (size_t)s * a.chunk_bytes,
@@ -467,7 +467,7 @@ __device__ bool send_bulk(const MoonepDevCtx& c, const DispatchArgs& a, int epoc
   // the stores of item j are complete: if it was the last piece of its token, the helper warp flags the token's rows
   auto flag_item = [&](int j) {
     if (lane == 0) {
-      const int ftok = fq.lagged[warp][j % (kFlagLag + 2)];
+      const int ftok = fq.lagged[warp][j % (kFlagLag + 4)];
       if (ftok >= 0 && !flagq_push(c, fq, warp, pushed, ftok)) {
         record_status(c, MOONEP_STATUS_TIMEOUT, MOONEP_K_DISPATCH_SEND, 101, warp, pushed, ftok);
         failed = true;  // lane 0 only; the loop condition below is evaluated after a warp-wide exchange
@@ -475,20 +475,14 @@ __device__ bool send_bulk(const MoonepDevCtx& c, const DispatchArgs& a, int epoc
     }
   };
 
+  // Loads run two items ahead of the stores: while the stores of item n drain, the loads of n+1 and n+2 are in
+  // flight, so an iteration does not wait a whole HBM latency for the row it is about to send.
   int tok, ch;
-  more = next_item(tok, ch);
-  if (more) issue_load(tok, ch);
+  for (int q = 0; q < kBulkStages - 1 && more; ++q) {
+    more = next_item(tok, ch);
+    if (more) issue_load(tok, ch);
+  }
   while (done < loaded && !failed) {
-    if (more) {
-      more = next_item(tok, ch);
-      if (more) {
-        // the stage about to be refilled belongs to item loaded-3, whose stores are complete (and flagged) by now:
-        // item done-2 at the latest was retired by the wait below in the previous iteration
-        if (lane == 0) bulk_wait_read<1>();
-        __syncwarp();
-        issue_load(tok, ch);
-      }
-    }
     const int s = done % kBulkStages;
     int ctok = 0, cch = 0, d = 0;
 #pragma unroll
@@ -534,6 +528,15 @@ __device__ bool send_bulk(const MoonepDevCtx& c, const DispatchArgs& a, int epoc
       if (lane == 0) bulk_wait<kFlagLag>();
       flag_item(done - 1 - kFlagLag);
       failed = __shfl_sync(0xffffffffu, failed ? 1 : 0, 0) != 0;
+    }
+    if (more && !failed) {
+      more = next_item(tok, ch);
+      if (more) {
+        // the stage to refill held item done-2: every group but the one just committed has read its stage
+        if (lane == 0) bulk_wait_read<1>();
+        __syncwarp();
+        issue_load(tok, ch);  // overwrites the `lagged` entry of item loaded-(kFlagLag+4), flagged long ago
+      }
     }
   }
   if (lane == 0) bulk_wait<0>();

@@ -122,7 +122,7 @@
 // Copy paths of dispatch/combine/prefetch.
 #define MOONEP_PATH_LDST 0  // 16-byte loads/stores from registers
 #define MOONEP_PATH_BULK 1  // cp.async.bulk through shared memory (mbarrier pipeline)
-#define MOONEP_PATH_ASYNC 2  // 16-byte cp.async into per-warp shared-memory rings (gradient accumulation only)
+#define MOONEP_PATH_ASYNC 2  // 16-byte cp.async into per-warp shared-memory rings (prefetch only)
 
 // Everything a kernel needs to know about one Buffer; passed by value.
 struct MoonepDevCtx {

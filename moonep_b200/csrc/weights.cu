@@ -13,6 +13,8 @@
 //
 // Parity: reference moonep_td/prefetch.py:22-64, moonep_td/grad_reduce.py:14-178 (host prescan with
 // argsort/bincount and a host sync per tensor, two barriers and two kernels per tensor).
+#include <cstdlib>
+
 #include "common.cuh"
 #include "host.h"
 
@@ -225,166 +227,24 @@ __global__ void __launch_bounds__(kAccumThreads, 1)
   grid_tail_signal(c, MOONEP_K_GRAD_ACCUM, ok ? MOONEP_FLAG_GRAD_DONE : -1, signal_epoch);
 }
 
-// Deep-pipeline variant of grad_accum (MOONEP_GRAD_PATH=async).  Register loads keep at most a few KB per warp in
-// flight, which over NVLink (several microseconds per round trip) bounds the pull below the link rate.  Here every
-// warp owns a ring of kCaStages shared-memory stages of 2 KB and fills them with 16-byte cp.async copies (the same
-// load path as register loads, but the data waits in shared memory, not in registers), so a CTA of 16 warps keeps
-// 16 x kCaStages x 2 KB in flight.  A lane reads back only what it copied itself, so the warps need no barrier.
-// The sources of one 2 KB chunk follow each other through the ring: first the local gradient, then the slots in
-// ascending slot order, which is the order of the additions of the register kernel (bitwise the same result).
+// prefetch_weight through per-warp cp.async rings (MOONEP_PREFETCH_PATH=async, the default).  Register loads keep at
+// most a few KB per warp in flight, which over NVLink (several microseconds per round trip) bounds a pull below the
+// link rate.  Here every warp owns a ring of 2 KB shared-memory stages and fills them with 16-byte cp.async copies
+// (the same load path as register loads, but the data waits in shared memory, not in registers); every lane stores
+// what it copied itself, so the warps need no barrier.  Work items are 256 KB pieces in slot-major order, so the
+// first slots complete (and are flagged) first.  Measured on 2 B200 (2.8 GB per rank): 668 GB/s against 629 GB/s of
+// the register kernel, the same with 3, 4, 5 or 6 stages.  The same ring under grad_accum measured half the rate of
+// its register kernel (244 against 489 GB/s), whatever the ring depth, the piece size, the completion mechanism
+// (cp.async groups or an mbarrier per stage) and whether the data was consumed at all; that variant was dropped.
 constexpr int kCaThreads = 512;
 constexpr int kCaWarps = kCaThreads / 32;
-constexpr int kCaStages = 6;
+constexpr int kCaStages = 4;
+constexpr int kCaMaxStages = 6;
 constexpr int kCaLaneVec = 4;                  // 16-byte vectors per lane and stage
 constexpr int kCaChunkVec = 32 * kCaLaneVec;   // a stage: 128 vectors = 2 KB
 constexpr int kCaPieceVec = 16384;             // work item: 256 KB of one expert
-constexpr int kCaMaxFan = 32;                  // slots of one expert handled per pass over a piece
 
-__global__ void __launch_bounds__(kCaThreads, 1)
-    grad_accum_async_kernel(const MoonepDevCtx c, const TensorSet ts, const int* __restrict__ etc, int Bcols,
-                            long long elems, int wait_epoch, int signal_epoch) {
-  extern __shared__ __align__(16) unsigned char s_ca_ring[];  // [kCaWarps][kCaStages][kCaLaneVec][32] float4
-  __shared__ int s_rb[kMaxSlots];
-  __shared__ short s_le[kMaxSlots];
-  __shared__ short s_active[kMaxLocalExperts];
-  __shared__ unsigned char s_has[kMaxLocalExperts];
-  __shared__ int s_fan[kCaWarps][kCaMaxFan];
-  __shared__ int s_n, s_nactive;
-  const bool ok = block_wait_flags(c, MOONEP_FLAG_GRAD_READY, wait_epoch, MOONEP_K_GRAD_ACCUM);
-  if (ok) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int epn = c.epn, owner0 = c.rank * epn, nslots = c.R * Bcols;
-    for (int i = threadIdx.x; i < epn; i += blockDim.x) s_has[i] = 0;
-    __syncthreads();
-    if (warp == 0) {
-      int n = 0;
-      for (int base = 0; base < nslots; base += 32) {
-        const int rb = base + lane;
-        const int e = rb < nslots ? etc[rb] : -1;
-        const bool mine = e >= owner0 && e < owner0 + epn;
-        const unsigned m = __ballot_sync(0xffffffffu, mine);
-        if (mine) {
-          const int pos = n + __popc(m & ((1u << lane) - 1u));
-          if (pos < kMaxSlots) {
-            s_rb[pos] = rb;
-            s_le[pos] = (short)(e - owner0);
-          }
-          s_has[e - owner0] = 1;
-        }
-        n += __popc(m);
-      }
-      __syncwarp();
-      int na = 0;
-      for (int base = 0; base < epn; base += 32) {
-        const int le = base + lane;
-        const bool has = le < epn && s_has[le];
-        const unsigned m = __ballot_sync(0xffffffffu, has);
-        if (has) s_active[na + __popc(m & ((1u << lane) - 1u))] = (short)le;
-        na += __popc(m);
-      }
-      if (lane == 0) {
-        s_n = n < kMaxSlots ? n : kMaxSlots;
-        s_nactive = na;
-        if (n > kMaxSlots) record_status(c, MOONEP_STATUS_BAD_INDEX, MOONEP_K_GRAD_ACCUM, 8, n, kMaxSlots, 0);
-      }
-    }
-    __syncthreads();
-    const int n = s_n, na = s_nactive;
-    const long long nvec = elems / 4;  // fp32: 4 elements per 16 bytes
-    const long long pieces = (nvec + kCaPieceVec - 1) / kCaPieceVec;
-    const long long total = (long long)ts.n * na * pieces;
-    float4* ring = reinterpret_cast<float4*>(s_ca_ring) + (size_t)warp * kCaStages * kCaChunkVec;
-    int* fan = s_fan[warp];
-    for (long long item = (long long)blockIdx.x * kCaWarps + warp; item < total; item += (long long)gridDim.x * kCaWarps) {
-      const long long piece = item % pieces;
-      const int ai = (int)((item / pieces) % na);
-      const int t = (int)(item / (pieces * na));
-      const int le = s_active[ai];
-      float4* g = reinterpret_cast<float4*>(ts.p[t]) + (long long)(owner0 + le) * nvec;
-      const float4* red = reinterpret_cast<const float4*>(ts.q[t]);
-      const long long v0 = piece * kCaPieceVec;
-      const long long v1 = v0 + kCaPieceVec < nvec ? v0 + kCaPieceVec : nvec;
-      const int nchunks = (int)((v1 - v0 + kCaChunkVec - 1) / kCaChunkVec);
-      // passes over the piece: kCaMaxFan slots of this expert at a time, in ascending slot order
-      for (int first = 0; first < n;) {
-        int m = 0, s = first;
-        __syncwarp();  // the previous pass no longer reads the list
-        for (; s < n && m < kCaMaxFan; s += 32) {
-          const int idx = s + lane;
-          const bool hit = idx < n && s_le[idx] == le;
-          const unsigned mask = __ballot_sync(0xffffffffu, hit);
-          const int pos = m + __popc(mask & ((1u << lane) - 1u));
-          if (hit && pos < kCaMaxFan) fan[pos] = s_rb[idx];
-          const int cnt = __popc(mask);
-          if (m + cnt > kCaMaxFan) {
-            // the list is full inside this group of 32: resume right after the last slot taken
-            int taken = kCaMaxFan - m, last = -1;
-            unsigned mm = mask;
-            while (taken-- > 0) {
-              last = __ffs(mm) - 1;
-              mm &= mm - 1;
-            }
-            s += last + 1 - 32;  // the loop adds 32
-            m = kCaMaxFan;
-          } else {
-            m += cnt;
-          }
-        }
-        first = s < n ? s : n;
-        __syncwarp();
-        if (m == 0) break;
-        const int per = m + 1;  // sources of a chunk: the gradient itself, then the slots
-        const int steps = nchunks * per;
-        auto issue = [&](int q) {
-          const int chunk = q / per, j = q - chunk * per;
-          const float4* src = j == 0 ? g : red + (long long)fan[j - 1] * nvec;
-          float4* dst = ring + (size_t)(q % kCaStages) * kCaChunkVec;
-          const long long base = v0 + (long long)chunk * kCaChunkVec;
-#pragma unroll
-          for (int k = 0; k < kCaLaneVec; ++k) {
-            const long long i = base + k * 32 + lane;
-            if (i < v1) cp_async16(dst + k * 32 + lane, src + i);
-          }
-        };
-        for (int q = 0; q < kCaStages; ++q) {
-          if (q < steps) issue(q);
-          cp_async_commit();
-        }
-        float4 acc[kCaLaneVec];
-        for (int q = 0; q < steps; ++q) {
-          cp_async_wait<kCaStages - 1>();  // all but the newest kCaStages - 1 groups have landed: step q is here
-          const int chunk = q / per, j = q - chunk * per;
-          const float4* st = ring + (size_t)(q % kCaStages) * kCaChunkVec;
-          const long long base = v0 + (long long)chunk * kCaChunkVec;
-#pragma unroll
-          for (int k = 0; k < kCaLaneVec; ++k) {
-            const long long i = base + k * 32 + lane;
-            if (i < v1) {
-              const float4 v = st[k * 32 + lane];
-              if (j == 0) {
-                acc[k] = v;
-              } else {
-                acc[k].x += v.x;
-                acc[k].y += v.y;
-                acc[k].z += v.z;
-                acc[k].w += v.w;
-              }
-              if (j == per - 1) st16f(g + i, acc[k]);
-            }
-          }
-          if (q + kCaStages < steps) issue(q + kCaStages);  // into the stage just read
-          cp_async_commit();
-        }
-        cp_async_wait<0>();
-      }
-    }
-  }
-  grid_tail_signal(c, MOONEP_K_GRAD_ACCUM, ok ? MOONEP_FLAG_GRAD_DONE : -1, signal_epoch);
-}
-
-// prefetch_weight on the same per-warp cp.async rings (MOONEP_PREFETCH_PATH=async): the remote expert waits in
-// shared memory instead of in registers, six 2 KB stages per warp, and every lane stores what it copied itself.
-// Work items are 256 KB pieces in slot-major order, so the first slots complete (and are flagged) first.
+template <int kStages>
 __global__ void __launch_bounds__(kCaThreads, 1)
     prefetch_async_kernel(const MoonepDevCtx c, const TensorSet w, const int* __restrict__ experts, long long elems,
                           int nslots, int nexperts, int* slot_flags, int* slot_done, int epoch) {
@@ -401,7 +261,7 @@ __global__ void __launch_bounds__(kCaThreads, 1)
       for (int b = threadIdx.x; b < nslots; b += blockDim.x)
         if (experts[b] < 0 || experts[b] >= nexperts) st_release_gpu(slot_flags + b, epoch);
   }
-  int4* ring = reinterpret_cast<int4*>(s_ca_ring) + (size_t)warp * kCaStages * kCaChunkVec;
+  int4* ring = reinterpret_cast<int4*>(s_ca_ring) + (size_t)warp * kStages * kCaChunkVec;
   for (long long item = (long long)blockIdx.x * kCaWarps + warp; item < total; item += (long long)gridDim.x * kCaWarps) {
     const int b = (int)(item / per_slot);
     const long long rest = item - (long long)b * per_slot;
@@ -419,7 +279,7 @@ __global__ void __launch_bounds__(kCaThreads, 1)
     const long long v1 = v0 + kCaPieceVec < nvec ? v0 + kCaPieceVec : nvec;
     const int steps = (int)((v1 - v0 + kCaChunkVec - 1) / kCaChunkVec);
     auto issue = [&](int q) {
-      int4* dst = ring + (size_t)(q % kCaStages) * kCaChunkVec;
+      int4* dst = ring + (size_t)(q % kStages) * kCaChunkVec;
       const long long base = v0 + (long long)q * kCaChunkVec;
 #pragma unroll
       for (int k = 0; k < kCaLaneVec; ++k) {
@@ -427,20 +287,20 @@ __global__ void __launch_bounds__(kCaThreads, 1)
         if (i < v1) cp_async16(dst + k * 32 + lane, src + i);
       }
     };
-    for (int q = 0; q < kCaStages; ++q) {
+    for (int q = 0; q < kStages; ++q) {
       if (q < steps) issue(q);
       cp_async_commit();
     }
     for (int q = 0; q < steps; ++q) {
-      cp_async_wait<kCaStages - 1>();
-      const int4* st = ring + (size_t)(q % kCaStages) * kCaChunkVec;
+      cp_async_wait<kStages - 1>();
+      const int4* st = ring + (size_t)(q % kStages) * kCaChunkVec;
       const long long base = v0 + (long long)q * kCaChunkVec;
 #pragma unroll
       for (int k = 0; k < kCaLaneVec; ++k) {
         const long long i = base + k * 32 + lane;
         if (i < v1) st16(dstp + i, st[k * 32 + lane]);
       }
-      if (q + kCaStages < steps) issue(q + kCaStages);
+      if (q + kStages < steps) issue(q + kStages);
       cp_async_commit();
     }
     cp_async_wait<0>();
@@ -691,6 +551,13 @@ extern "C" int moonep_epoch_bias(void* ctx, const int* values, int mode, void* s
   return check_launch("epoch_bias_kernel");
 }
 
+// Ring depth of the cp.async kernels: MOONEP_RING_STAGES (2..6), default kCaStages.
+static int ring_stages() {
+  const char* v = getenv("MOONEP_RING_STAGES");
+  const int n = v != nullptr ? atoi(v) : kCaStages;
+  return n >= 2 && n <= kCaMaxStages ? n : kCaStages;
+}
+
 extern "C" int moonep_prefetch(void* ctx, void* const* src3, void* const* dst3, int n_tensors,
                                const int* experts_to_copy_row, long long elems, int nslots, int nexperts, int path,
                                int* slot_flags, int* slot_done, int epoch, void* stream) {
@@ -709,14 +576,23 @@ extern "C" int moonep_prefetch(void* ctx, void* const* src3, void* const* dst3, 
   }
   const int grid = imax(1, imin(c.num_sms, h->sm_count));
   if (path == MOONEP_PATH_ASYNC) {
-    const size_t smem = (size_t)kCaWarps * kCaStages * kCaChunkVec * 16;
-    if (int rc = check_cuda(cudaFuncSetAttribute(prefetch_async_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 (int)smem),
-                            "cudaFuncSetAttribute(prefetch_async_kernel)"))
-      return rc;
-    prefetch_async_kernel<<<grid, kCaThreads, smem, (cudaStream_t)stream>>>(c, w, experts_to_copy_row, elems, nslots,
-                                                                          nexperts, slot_flags, slot_done, epoch);
-    return check_launch("prefetch_async_kernel");
+    const int stages = ring_stages();
+    const size_t smem = (size_t)kCaWarps * stages * kCaChunkVec * 16;
+    auto launch = [&](auto kernel) -> int {
+      if (int rc = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                              "cudaFuncSetAttribute(prefetch_async_kernel)"))
+        return rc;
+      kernel<<<grid, kCaThreads, smem, (cudaStream_t)stream>>>(c, w, experts_to_copy_row, elems, nslots, nexperts,
+                                                               slot_flags, slot_done, epoch);
+      return check_launch("prefetch_async_kernel");
+    };
+    switch (stages) {
+      case 2: return launch(prefetch_async_kernel<2>);
+      case 4: return launch(prefetch_async_kernel<4>);
+      case 5: return launch(prefetch_async_kernel<5>);
+      case 6: return launch(prefetch_async_kernel<6>);
+      default: return launch(prefetch_async_kernel<3>);
+    }
   }
   prefetch_kernel<<<grid, 512, 0, (cudaStream_t)stream>>>(c, w, experts_to_copy_row, elems, nslots, nexperts, slot_flags,
                                                          slot_done, epoch);
@@ -757,16 +633,6 @@ extern "C" int moonep_grad_reduce(void* ctx, float* const* grads, float* const* 
       grad_accum_bulk_kernel<<<grid, kAccThreads, smem, st>>>(c, ts, experts_to_copy, Bcols, elems, epoch_ready,
                                                              epoch_done, nstages);
       return check_launch("grad_accum_bulk_kernel");
-    }
-    if (path == MOONEP_PATH_ASYNC) {
-      const size_t smem = (size_t)kCaWarps * kCaStages * kCaChunkVec * 16;
-      if (int rc = check_cuda(cudaFuncSetAttribute(grad_accum_async_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                   (int)smem),
-                              "cudaFuncSetAttribute(grad_accum_async_kernel)"))
-        return rc;
-      grad_accum_async_kernel<<<grid, kCaThreads, smem, st>>>(c, ts, experts_to_copy, Bcols, elems, epoch_ready,
-                                                             epoch_done);
-      return check_launch("grad_accum_async_kernel");
     }
     grad_accum_kernel<<<grid, kAccumThreads, 0, st>>>(c, ts, experts_to_copy, Bcols, elems, epoch_ready, epoch_done);
     return check_launch("grad_accum_kernel");

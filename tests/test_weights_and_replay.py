@@ -77,25 +77,26 @@ def test_prefetch_and_reduce_grad(device, table, R):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("table", ["fan_in", "random"])
-@pytest.mark.parametrize("path", ["bulk", "async", "ldst"])
+@pytest.mark.parametrize("path", ["bulk", "ldst"])
 def test_reduce_grad_on_every_copy_path(table, path, monkeypatch):
-    """The TMA-ring (``MOONEP_GRAD_PATH=bulk``), cp.async-ring (``async``) and register (``ldst``) variants of the
-    gradient accumulation all keep the bitwise order of the additions."""
+    """The TMA-ring (``MOONEP_GRAD_PATH=bulk``) and register (``ldst``) variants of the gradient accumulation keep the
+    bitwise order of the additions; the prefetch runs on its register kernel (``ldst``) and its cp.async ring."""
     monkeypatch.setenv("MOONEP_GRAD_PATH", path)
-    monkeypatch.setenv("MOONEP_PREFETCH_PATH", path)  # "bulk" means the register kernel for the prefetch
+    monkeypatch.setenv("MOONEP_PREFETCH_PATH", "ldst" if path == "ldst" else "async")
     _prefetch_and_reduce_grad("cuda", table, 4)
 
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("path", ["async", "ldst"])
-def test_reduce_grad_paths_on_odd_sizes(path, monkeypatch):
-    """Experts whose size is not a multiple of a 2 KB stage (384 x 128 fp32 = 96 stages; 128 x 128 with one SM) and
-    more slots per expert than ranks."""
-    monkeypatch.setenv("MOONEP_GRAD_PATH", path)
+@pytest.mark.parametrize("stages", ["2", "4", "6"])
+def test_prefetch_paths_on_odd_sizes(path, stages, monkeypatch):
+    """Experts that are a few 2 KB stages long (fewer than the ring is deep, with one SM) and many slots per expert,
+    on the register kernel and on cp.async rings of several depths."""
     monkeypatch.setenv("MOONEP_PREFETCH_PATH", path)
+    monkeypatch.setenv("MOONEP_RING_STAGES", stages)
     _prefetch_and_reduce_grad("cuda", "fan_in", 4, Hw=384, Hp=128, epn=2, B=4, num_sms=3)
     _prefetch_and_reduce_grad("cuda", "random_seed2", 2, Hw=128, Hp=128, epn=1, B=1, num_sms=1)
-    # 36 slots hold the same expert: the async variant lists 32 of them per pass over a piece
+    # 36 slots hold the same expert
     _prefetch_and_reduce_grad("cuda", "fan_in", 4, Hw=128, Hp=128, epn=2, B=12, num_sms=2)
 
 
