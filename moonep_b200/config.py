@@ -9,6 +9,9 @@ MOONEP_COPY_PATH      ``bulk`` (default: TMA bulk copies through shared memory) 
                       register copies) whatever ``MOONEP_COPY_PATH`` says.
 MOONEP_RING_STAGES    2..6 (default 4): 2 KB stages per warp of the prefetch kernel's cp.async ring (read by the native
                       library).
+MOONEP_LOCAL_ROWS     ``0``: the send role of dispatch also writes the rows that stay on the rank (default: the
+                      destination-side role writes them from the input).
+MOONEP_BWD_OVERLAP    ``1``: the MoE layer reduces each weight's gradients beside the remaining backward GEMMs (default 0).
 MOONEP_EXPAND_PATH    ``bulk`` (default) or ``ldst``: how the destination side of dispatch copies duplicate rows and clears
                       pad rows (read by the native library).
 MOONEP_COMBINE        ``push`` (default: the expert side folds duplicates and pushes rows to the tokens' home ranks,
@@ -102,10 +105,18 @@ def wgrad_on_kernel() -> bool:
     return os.environ.get("MOONEP_WGRAD", "kernel").lower() != "torch"
 
 
+def local_rows_by_expand() -> bool:
+    """The rows of a rank's own tokens are written by the destination-side role of the dispatch kernel straight from
+    the input (primary row and duplicates from one read) instead of by the CTAs that drive NVLink.
+    MOONEP_LOCAL_ROWS=0: the send role writes them like every other row."""
+    return os.environ.get("MOONEP_LOCAL_ROWS", "1") not in _FALSE
+
+
 def backward_overlap() -> bool:
-    """The MoE layer's backward starts ``reduce_grad`` of each weight on the communication stream as soon as that
-    weight's gradients exist, beside the remaining GEMMs (which then leave ``num_sms`` SMs to it).
-    MOONEP_BWD_OVERLAP=0 runs one ``reduce_grad`` for all three weights after the backward's combine."""
+    """MOONEP_BWD_OVERLAP=1: the MoE layer's backward starts ``reduce_grad`` of each weight on the communication stream
+    as soon as that weight's gradients exist, beside the remaining GEMMs (which then leave ``num_sms`` SMs to it).
+    Default 0: one ``reduce_grad`` for all three weights after the backward's combine (with balanced routing few
+    prefetch slots are in use and the smaller GEMM grid costs more than the overlap returns)."""
     return os.environ.get("MOONEP_BWD_OVERLAP", "0") not in _FALSE
 
 

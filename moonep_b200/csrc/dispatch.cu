@@ -89,6 +89,7 @@ struct DispatchArgs {
   int bulk;
   int expand_bulk;  // EXPAND copies through shared memory with bulk copies (needs (kExpandCopyWarps + 1) pieces of smem)
   int build_only;  // EXPAND: only build the duplicate map (no zero fill, no copies)
+  int local_rows;  // rows whose source is this rank are written by EXPAND from the input; SEND skips them
 };
 
 __device__ __forceinline__ void decode_dst(int d, int NvS, int& dest, int& loff) {
@@ -327,7 +328,7 @@ __device__ void flag_helper(const MoonepDevCtx& c, const DispatchArgs& a, int ep
         const int d = a.dst[tok * c.K + lane];
         int dest, loff;
         decode_dst(d, c.NvS, dest, loff);
-        if (d >= 0 && dst_in_range(c, dest, loff)) f = rowflag_ptr(c, dest, loff);
+        if (d >= 0 && dst_in_range(c, dest, loff) && !(a.local_rows && dest == c.rank)) f = rowflag_ptr(c, dest, loff);
       }
       unsigned m = __ballot_sync(0xffffffffu, f != nullptr);
       while (m) {
@@ -362,7 +363,9 @@ __device__ void send_ldst(const MoonepDevCtx& c, const DispatchArgs& a, int epoc
         if (!valid) record_status(c, MOONEP_STATUS_BAD_INDEX, MOONEP_K_DISPATCH_SEND, 6, d, token, lane);
       }
       if (valid) push_weights(c, a, token, lane, dest, loff);
-      const unsigned prim = __ballot_sync(0xffffffffu, valid && d >= 0);
+      const bool mine = valid && d >= 0 && !(a.local_rows && dest == c.rank);  // a row this role writes
+      const unsigned prim = __ballot_sync(0xffffffffu, mine);
+      if (prim == 0) continue;
       const uint16_t* src = a.hidden + (long long)token * H;
       if (a.vec_ok) {
         const int nvec = H / 8;
@@ -399,7 +402,7 @@ __device__ void send_ldst(const MoonepDevCtx& c, const DispatchArgs& a, int epoc
           for (int i = lane; i < H; i += 32) o[i] = src[i];
         }
       }
-      release_row_flags(c, valid ? d : -1, lane, epoch);
+      release_row_flags(c, mine ? d : -1, lane, epoch);
     }
   }
 }
@@ -430,6 +433,27 @@ __device__ bool send_bulk(const MoonepDevCtx& c, const DispatchArgs& a, int epoc
       batch_next = b;
       batch_end = min(S, b + kTokenBatch);
       cur_chunk = 0;
+    }
+    if (a.local_rows && cur_chunk == 0) {
+      // a token whose rows all stay on this rank is the EXPAND role's: only its gate weights are stored here
+      for (;;) {
+        int d = 0, dest = 0, loff = 0;
+        bool valid = false;
+        if (lane < K) {
+          d = a.dst[batch_next * K + lane];
+          decode_dst(d, c.NvS, dest, loff);
+          valid = dst_in_range(c, dest, loff);
+        }
+        if (__ballot_sync(0xffffffffu, valid && d >= 0 && dest != c.rank) != 0) break;
+        if (lane < K && !valid) record_status(c, MOONEP_STATUS_BAD_INDEX, MOONEP_K_DISPATCH_SEND, 6, d, batch_next, lane);
+        if (valid) push_weights(c, a, batch_next, lane, dest, loff);
+        if (++batch_next == batch_end) {
+          const int b = grab_tokens(work, lane);
+          if (b >= S) return false;
+          batch_next = b;
+          batch_end = min(S, b + kTokenBatch);
+        }
+      }
     }
     tok = batch_next;
     ch = cur_chunk;
@@ -500,7 +524,7 @@ __device__ bool send_bulk(const MoonepDevCtx& c, const DispatchArgs& a, int epoc
       if (!valid) record_status(c, MOONEP_STATUS_BAD_INDEX, MOONEP_K_DISPATCH_SEND, 6, d, ctok, lane);
     }
     if (valid && cch == 0) push_weights(c, a, ctok, lane, dest, loff);
-    unsigned m = __ballot_sync(0xffffffffu, valid && d >= 0);
+    unsigned m = __ballot_sync(0xffffffffu, valid && d >= 0 && !(a.local_rows && dest == c.rank));
     int got = 1;
     if (lane == 0) got = mbar_wait(bar + s, (unsigned)((done / kBulkStages) & 1), c.timeout_ns) ? 1 : 0;
     got = __shfl_sync(0xffffffffu, got, 0);
@@ -550,11 +574,12 @@ __device__ bool send_bulk(const MoonepDevCtx& c, const DispatchArgs& a, int epoc
 
 // ---- expand role ---------------------------------------------------------------------------------
 
-// Copy row `primary` of the local shard to the rows lane q holds in my_dup (q < dn), then flag them.
-__device__ void expand_group(const MoonepDevCtx& c, int primary, int my_dup, int dn, int vec_ok, int epoch, int lane) {
+// Copy the row at `src` (a row of the local shard, or of the dispatch's input) to the rows of the local shard that
+// lane q holds in my_dup (q < dn), then flag them.
+__device__ void expand_group(const MoonepDevCtx& c, const uint16_t* src, int my_dup, int dn, int vec_ok, int epoch,
+                             int lane) {
   const int H = c.H;
   uint16_t* shard = c.hidden_peer[c.rank];
-  const uint16_t* src = shard + (long long)primary * H;
   if (vec_ok) {
     const int nvec = H / 8;
     const int4* s4 = reinterpret_cast<const int4*>(src);
@@ -612,9 +637,9 @@ __device__ __forceinline__ void flag_pending(const MoonepDevCtx& c, const Pendin
 // (count 1), phase: its parity, flipped per use.  The rows of this group are flagged one group late (`pend`: the
 // previous group's rows), so that waiting for the completion of a group's stores overlaps the next group's load;
 // the caller flushes the last group with expand_flush().  Returns false after a timeout.
-__device__ bool expand_group_bulk(const MoonepDevCtx& c, int primary, int my_dup, int dn, int epoch, int lane,
-                                  unsigned char* stage, int chunk_bytes, unsigned long long* bar, unsigned& phase,
-                                  PendingRows& pend) {
+__device__ bool expand_group_bulk(const MoonepDevCtx& c, const unsigned char* src_row, int my_dup, int dn, int epoch,
+                                  int lane, unsigned char* stage, int chunk_bytes, unsigned long long* bar,
+                                  unsigned& phase, PendingRows& pend) {
   const long long row_bytes = (long long)c.H * 2;
   unsigned char* shard = reinterpret_cast<unsigned char*>(c.hidden_peer[c.rank]);
   bool ok = true;
@@ -624,9 +649,9 @@ __device__ bool expand_group_bulk(const MoonepDevCtx& c, int primary, int my_dup
     if (lane == 0) {
       bulk_wait_read<0>();  // the stage is free once the previous stores have read it
       mbar_expect_tx(bar, len);
-      bulk_g2s(stage, shard + (long long)primary * row_bytes + off, len, bar);
+      bulk_g2s(stage, src_row + off, len, bar);
       got = mbar_wait(bar, phase, c.timeout_ns) ? 1 : 0;
-      if (!got) record_status(c, MOONEP_STATUS_TIMEOUT, MOONEP_K_DISPATCH_EXPAND, 100, primary, dn, 0);
+      if (!got) record_status(c, MOONEP_STATUS_TIMEOUT, MOONEP_K_DISPATCH_EXPAND, 100, dn, (int)off, 0);
     }
     phase ^= 1u;
     ok = __shfl_sync(0xffffffffu, got, 0) != 0;
@@ -662,33 +687,51 @@ __device__ __forceinline__ void expand_flush(const MoonepDevCtx& c, PendingRows&
   pend.dn = 0;
 }
 
-// Expands the groups of this warp, `count` of them, group number `group_of(k)` (negative: nothing to do), in the
-// order in which their primary rows arrive rather than in list order: rows land in the senders' token order, which
-// has nothing to do with the order of the rows in the shard, and a warp that sat on its first missing row would push
-// all its copies to the end of the kernel.  Lane 0 polls the row flags of up to 32 pending groups per round; a round
-// without progress sleeps, and the usual time limit applies to the whole wait.
-template <class GroupOf>
-__device__ bool expand_as_rows_arrive(const MoonepDevCtx& c, const DispatchArgs& a, int count, GroupOf group_of, int epoch,
-                                      int lane, bool bulk, unsigned char* my_stage, unsigned long long* my_bar,
-                                      unsigned& xphase, PendingRows& pend) {
+// Work of this warp in the expansion: `count` entries, entry_of(k) >= 0 a duplicate group (its number), <= -2 a
+// primary row without duplicates whose token lives on this rank (row -entry-2), -1 nothing.  With a.local_rows the
+// rows whose source is this rank are written here, straight from the dispatch's input (the SEND role skips them): a
+// group of such a token gets its primary row and its duplicates from one read of the input row, and nothing is
+// waited for.  The other groups are expanded from their primary row in the order in which those rows arrive, not in
+// list order: rows land in the senders' token order, which has nothing to do with the order of the rows in the
+// shard, and a warp that sat on its first missing row would push all its copies to the end of the kernel.  Lanes poll
+// the row flags of up to 32 pending entries per round; a round without progress sleeps, and the usual time limit
+// applies to the whole wait.  info: src_info of the rows of this rank (entry src * NvS + token * K + k).
+template <class EntryOf>
+__device__ bool expand_as_rows_arrive(const MoonepDevCtx& c, const DispatchArgs& a, int count, EntryOf entry_of,
+                                      const int* __restrict__ info, int epoch, int lane, bool bulk,
+                                      unsigned char* my_stage, unsigned long long* my_bar, unsigned& xphase,
+                                      PendingRows& pend) {
   const int* rowflag = c.meta_peer[c.rank] + c.rowflag_off;
   const int NvS = c.NvS;
+  const long long row_bytes = (long long)c.H * 2;
+  const unsigned char* shard = reinterpret_cast<const unsigned char*>(c.hidden_peer[c.rank]);
+  const unsigned char* input = reinterpret_cast<const unsigned char*>(a.hidden);
   for (int k0 = 0; k0 < count; k0 += 32) {
     const int nk = min(32, count - k0);
     unsigned pending = nk == 32 ? 0xffffffffu : ((1u << nk) - 1u);
     unsigned long long t0 = 0;
     unsigned idle = 0;
     while (pending != 0) {
-      // lane k looks at group k0 + k: which of the pending groups have their primary row?
-      int g = -1, primary = -1;
+      // lane k looks at entry k0 + k: is it ready (its source row present)?
+      int g = -1, primary = -1, token = -1;  // token >= 0: the source is row `token` of the input
       bool ready = false;
       if (lane < nk && ((pending >> lane) & 1u)) {
-        g = group_of(k0 + lane);
-        if (g >= 0) {
+        const int e = entry_of(k0 + lane);
+        if (e >= 0) {
+          g = e;
           primary = a.dup_groups[3 * g];
-          if (primary < 0 || primary >= NvS) g = -1;
+        } else if (e <= -2) {
+          primary = -e - 2;
         }
-        ready = g < 0 || ld_acquire_sys(rowflag + primary) - epoch >= 0;
+        if (primary < 0 || primary >= NvS) {
+          g = primary = -1;
+        } else if (a.local_rows && info != nullptr) {
+          const int si = info[primary];
+          if (si >= 0 && si / NvS == c.rank) token = (si % NvS) / c.K;
+          if (token >= c.S) token = -1;
+        }
+        if (e <= -2 && token < 0) primary = -1;  // a lone row of another rank's token: nothing to do here
+        ready = primary < 0 || token >= 0 || ld_acquire_sys(rowflag + primary) - epoch >= 0;
       }
       unsigned now = __ballot_sync(0xffffffffu, ready);
       if (now == 0) {
@@ -699,7 +742,7 @@ __device__ bool expand_as_rows_arrive(const MoonepDevCtx& c, const DispatchArgs&
         int give_up = 0;
         if (lane == 0 && (idle & 15u) == 0 && (globaltimer_ns() - t0 > c.timeout_ns || poisoned(c))) {
           const int k = __ffs(pending) - 1;
-          record_status(c, MOONEP_STATUS_TIMEOUT, MOONEP_K_DISPATCH_EXPAND, 200, group_of(k0 + k), epoch, (int)pending);
+          record_status(c, MOONEP_STATUS_TIMEOUT, MOONEP_K_DISPATCH_EXPAND, 200, entry_of(k0 + k), epoch, (int)pending);
           give_up = 1;
         }
         if (__shfl_sync(0xffffffffu, give_up, 0)) return false;
@@ -712,15 +755,26 @@ __device__ bool expand_as_rows_arrive(const MoonepDevCtx& c, const DispatchArgs&
         const int k = __ffs(now) - 1;
         now &= now - 1;
         const int gk = __shfl_sync(0xffffffffu, g, k);
-        if (gk < 0) continue;
         const int pk = __shfl_sync(0xffffffffu, primary, k);
-        const int ds = a.dup_groups[3 * gk + 1], dn = a.dup_groups[3 * gk + 2];
-        if (ds < 0 || dn < 0 || ds + dn > NvS) continue;
-        const int my_dup = lane < dn ? a.dup_loffs[ds + lane] : -1;
+        const int tk = __shfl_sync(0xffffffffu, token, k);
+        if (pk < 0) continue;
+        int dn = 0, my_row = -1;
+        if (gk >= 0) {
+          const int ds = a.dup_groups[3 * gk + 1];
+          dn = a.dup_groups[3 * gk + 2];
+          if (ds < 0 || dn < 0 || dn >= 32 || ds + dn > NvS) continue;
+          if (lane < dn) my_row = a.dup_loffs[ds + lane];
+        }
+        if (tk >= 0) {  // the primary row itself is written here as well
+          if (lane == dn) my_row = pk;
+          ++dn;
+        }
+        if (dn == 0) continue;
+        const unsigned char* src = tk >= 0 ? input + (long long)tk * row_bytes : shard + (long long)pk * row_bytes;
         if (bulk) {
-          if (!expand_group_bulk(c, pk, my_dup, dn, epoch, lane, my_stage, a.chunk_bytes, my_bar, xphase, pend)) return false;
+          if (!expand_group_bulk(c, src, my_row, dn, epoch, lane, my_stage, a.chunk_bytes, my_bar, xphase, pend)) return false;
         } else {
-          expand_group(c, pk, my_dup, dn, a.vec_ok, epoch, lane);
+          expand_group(c, reinterpret_cast<const uint16_t*>(src), my_row, dn, a.vec_ok, epoch, lane);
         }
       }
     }
@@ -788,11 +842,14 @@ __device__ bool expand_role(const MoonepDevCtx& c, const DispatchArgs& a, int xi
       for (int base = s0; base < s1; base += blockDim.x) {  // uniform trip count: the ballots need whole warps
         const int loff = base + threadIdx.x;
         int dup_n = 0, first = -1;
+        bool single = false;  // a primary row without duplicates whose token lives on this rank
         if (loff < s1) {
           const int si = src_info[loff];
           const int l = si >= 0 ? link[loff] : 0;
           if (a.plan_src_info != nullptr) a.plan_src_info[loff] = si;
           if (a.plan_link != nullptr) a.plan_link[loff] = l;
+          single = a.local_rows && si >= 0 && (l & MOONEP_LINK_PRIMARY) && !(l & MOONEP_LINK_HAS_NEXT) &&
+                   si / NvS == c.rank;
           if (si >= 0 && (l & MOONEP_LINK_PRIMARY) && (l & MOONEP_LINK_HAS_NEXT)) {
             first = l & MOONEP_NVS_MASK;
             int cur = first;
@@ -808,6 +865,13 @@ __device__ bool expand_role(const MoonepDevCtx& c, const DispatchArgs& a, int xi
               cur = l2 & MOONEP_NVS_MASK;
             }
           }
+        }
+        const unsigned lone = __ballot_sync(0xffffffffu, single);
+        if (lone != 0) {
+          int sbase = 0;
+          if (lane == 0) sbase = atomicAdd(&s_ngroups, __popc(lone));
+          sbase = __shfl_sync(0xffffffffu, sbase, 0);
+          if (single) s_groups[sbase + __popc(lone & ((1u << lane) - 1u))] = -loff - 2;
         }
         const unsigned has = __ballot_sync(0xffffffffu, dup_n > 0);
         if (has == 0) continue;
@@ -850,8 +914,8 @@ __device__ bool expand_role(const MoonepDevCtx& c, const DispatchArgs& a, int xi
       const int ng = a.build_only ? 0 : s_ngroups;
       if (ok && warp < copy_warps && warp < ng)
         ok = expand_as_rows_arrive(
-            c, a, (ng - warp + copy_warps - 1) / copy_warps, [&](int k) { return s_groups[warp + k * copy_warps]; }, epoch,
-            lane, bulk, my_stage, s_xbar + warp, xphase, pend);
+            c, a, (ng - warp + copy_warps - 1) / copy_warps, [&](int k) { return s_groups[warp + k * copy_warps]; },
+            src_info, epoch, lane, bulk, my_stage, s_xbar + warp, xphase, pend);
       if (bulk && warp < copy_warps) expand_flush(c, pend, epoch, lane);
       ok = __syncthreads_and(ok ? 1 : 0) != 0;
     }
@@ -862,8 +926,33 @@ __device__ bool expand_role(const MoonepDevCtx& c, const DispatchArgs& a, int xi
     const int g0 = xidx * copy_warps + warp, gstride = xcnt * copy_warps;
     if (warp < copy_warps && g0 < ngroups)
       ok = expand_as_rows_arrive(
-          c, a, (ngroups - g0 + gstride - 1) / gstride, [&](int k) { return g0 + k * gstride; }, epoch, lane, bulk,
-          my_stage, s_xbar + warp, xphase, pend);
+          c, a, (ngroups - g0 + gstride - 1) / gstride, [&](int k) { return g0 + k * gstride; }, a.plan_src_info, epoch,
+          lane, bulk, my_stage, s_xbar + warp, xphase, pend);
+    if (a.local_rows && a.plan_src_info != nullptr && a.plan_link != nullptr) {
+      // the lone primary rows of this rank's own tokens: found in the plan's copy of the link words, a slice of rows
+      // per CTA and round
+      const int per_cta = (NvS + xcnt - 1) / xcnt;
+      const int lo = xidx * per_cta, hi = min(NvS, lo + per_cta);
+      for (int s0 = lo; s0 < hi && ok; s0 += kExpandSlice) {
+        const int s1 = min(hi, s0 + kExpandSlice);
+        __syncthreads();
+        if (threadIdx.x == 0) s_ngroups = 0;
+        __syncthreads();
+        for (int loff = s0 + threadIdx.x; loff < s1; loff += blockDim.x) {
+          const int si = a.plan_src_info[loff];
+          const int l = si >= 0 ? a.plan_link[loff] : 0;
+          if (si >= 0 && (l & MOONEP_LINK_PRIMARY) && !(l & MOONEP_LINK_HAS_NEXT) && si / NvS == c.rank)
+            s_groups[atomicAdd(&s_ngroups, 1)] = -loff - 2;
+        }
+        __syncthreads();
+        const int ng = s_ngroups;
+        if (ok && warp < copy_warps && warp < ng)
+          ok = expand_as_rows_arrive(
+              c, a, (ng - warp + copy_warps - 1) / copy_warps, [&](int k) { return s_groups[warp + k * copy_warps]; },
+              a.plan_src_info, epoch, lane, bulk, my_stage, s_xbar + warp, xphase, pend);
+        ok = __syncthreads_and(ok ? 1 : 0) != 0;
+      }
+    }
     if (bulk && warp < copy_warps) expand_flush(c, pend, epoch, lane);
     ok = __syncthreads_and(ok ? 1 : 0) != 0;
   }
@@ -1034,6 +1123,10 @@ extern "C" int moonep_dispatch(void* ctx, int roles, int fresh, const int* topk,
   a.plan_src_info = plan_src_info;
   a.plan_link = plan_link;
   a.fresh = fresh;
+  // the modifier needs the input rows in the EXPAND launch and src_info of the landed rows
+  a.local_rows = ((roles & MOONEP_ROLE_LOCAL_ROWS) && hidden != nullptr && !build_only &&
+                  (fresh || (plan_src_info != nullptr && plan_link != nullptr))) ? 1 : 0;
+  roles &= ~MOONEP_ROLE_LOCAL_ROWS;
   a.roles = roles;
   a.build_only = build_only;
   a.with_weights = with_weights;
@@ -1089,6 +1182,8 @@ extern "C" int moonep_dispatch(void* ctx, int roles, int fresh, const int* topk,
   a.n_send = 0;
   if (senders) {
     a.n_send = imax(1, imin(n_send > 0 ? n_send : c.num_sms, h->sm_count - (expanders ? 2 : 0)));
+    // a single rank whose rows are all written by the EXPAND role: the senders only store gate weights
+    if (c.R == 1 && a.local_rows && expanders) a.n_send = imin(a.n_send, 4);
     grid = a.n_send;
   }
   if (expanders) {

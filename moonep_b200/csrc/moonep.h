@@ -111,6 +111,10 @@
 #define MOONEP_ROLE_TOKENS 2   // token stage of the planner
 #define MOONEP_ROLE_SEND 4     // push rows, gate weights and row flags
 #define MOONEP_ROLE_EXPAND 8   // zero fill, duplicate map, duplicate expansion as rows arrive
+// Modifier, given to the SEND and the EXPAND launch alike (or to the one launch that has both roles): the rows whose
+// token lives on this rank are written by EXPAND straight from the input (primary row and duplicates from one read),
+// SEND leaves them out.  Needs src_info of the landed rows: a fresh plan, or a replayed plan that carries src_info.
+#define MOONEP_ROLE_LOCAL_ROWS 16
 // Roles of the push-combine kernel.
 #define MOONEP_ROLE_PUSH 1     // expert side: copy primary rows (folded where they have duplicates) to the tokens' home ranks
 #define MOONEP_ROLE_SUM 2      // home side: sum the rows of a token as they arrive

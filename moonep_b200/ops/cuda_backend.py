@@ -46,6 +46,7 @@ _KERNEL_NAMES = {
 }  # fmt: skip
 _PHASE_NAMES = ("tables", "tokens", "send", "zero_fill", "wait_plan", "build_expand", "wait_sent", "fold", "push", "sum")
 ROLE_TABLES, ROLE_TOKENS, ROLE_SEND, ROLE_EXPAND = 1, 2, 4, 8
+ROLE_LOCAL_ROWS = 16  # modifier: EXPAND writes the rows of this rank's own tokens from the input, SEND skips them
 ROLE_PUSH, ROLE_SUM, ROLE_FOLD = 1, 2, 4
 _FAMILY_NAMES = {0: "READY", 1: "TPE", 2: "PLAN", 3: "SENT", 4: "COMB", 5: "GRAD_READY", 6: "GRAD_DONE", 7: "PREFETCH"}
 _BIAS_OFF, _CTR_TABLES_READY = 32, 18  # words of the counters block (csrc/moonep.h)
@@ -361,6 +362,7 @@ class CudaBackend:
         plan: an optional READY round plus one launch (push and expansion).  Emulated ranks run one role per phase."""
         with_w = route_weights_sk is not None
         self._sent_weights = with_w
+        lr = ROLE_LOCAL_ROWS if config.local_rows_by_expand() else 0
         if planning_args is not None:
             topk_flat, tpe, cu_seqlens = planning_args
             self.plan_publish(tpe, topk_flat)
@@ -376,15 +378,15 @@ class CudaBackend:
                       with_weights=with_w, wait_family=wf, wait_epoch=we, epoch_sent=sent)  # fmt: skip
             plan_roles = (ROLE_TABLES | ROLE_TOKENS) if on_dev else 0
             if not self.phased:
-                self._dispatch_launch(plan_roles | ROLE_SEND | ROLE_EXPAND, True, plan, tag="dispatch_fused", **kw)
+                self._dispatch_launch(plan_roles | ROLE_SEND | ROLE_EXPAND | lr, True, plan, tag="dispatch_fused", **kw)
             else:
                 if config.force_phased() and plan_roles:  # per-role timing: planner and send as separate launches
                     self._dispatch_launch(plan_roles, True, plan, tag="dispatch_plan", **kw)
-                    self._dispatch_launch(ROLE_SEND, True, plan, tag="dispatch_send", **kw)
+                    self._dispatch_launch(ROLE_SEND | lr, True, plan, tag="dispatch_send", **kw)
                 else:
-                    self._dispatch_launch(plan_roles | ROLE_SEND, True, plan, tag="dispatch_plan_send", **kw)
+                    self._dispatch_launch(plan_roles | ROLE_SEND | lr, True, plan, tag="dispatch_plan_send", **kw)
                 self.world.step()
-                self._dispatch_launch(ROLE_EXPAND, True, plan, tag="dispatch_expand", **kw)
+                self._dispatch_launch(ROLE_EXPAND | lr, True, plan, tag="dispatch_expand", **kw)
             self._quiesced = True
         else:
             wf, we = -1, 0
@@ -396,11 +398,11 @@ class CudaBackend:
             kw = dict(hidden=hidden_sh, weights=route_weights_sk, with_weights=with_w, wait_family=wf, wait_epoch=we,
                       epoch_sent=sent)  # fmt: skip
             if not self.phased:
-                self._dispatch_launch(ROLE_SEND | ROLE_EXPAND, False, plan, tag="dispatch_replay", **kw)
+                self._dispatch_launch(ROLE_SEND | ROLE_EXPAND | lr, False, plan, tag="dispatch_replay", **kw)
             else:
-                self._dispatch_launch(ROLE_SEND, False, plan, tag="dispatch_send", **kw)
+                self._dispatch_launch(ROLE_SEND | lr, False, plan, tag="dispatch_send", **kw)
                 self.world.step()
-                self._dispatch_launch(ROLE_EXPAND, False, plan, tag="dispatch_expand", **kw)
+                self._dispatch_launch(ROLE_EXPAND | lr, False, plan, tag="dispatch_expand", **kw)
         self.world.step()
 
     def copy_out(self, out_hidden, out_weights):

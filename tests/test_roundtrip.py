@@ -107,6 +107,26 @@ def test_round_trip_on_the_alternative_copy_paths(case, paths, monkeypatch):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("local_rows", ["0", "1"])
+@pytest.mark.parametrize("expand", ["bulk", "ldst"])
+@pytest.mark.parametrize("R", [1, 2, 4])
+@pytest.mark.parametrize("case", ROUNDTRIP_CASES[:4] + ROUNDTRIP_CASES[7:10], ids=lambda c: c.name)
+def test_round_trip_with_local_rows_written_by_either_role(case, R, expand, local_rows, monkeypatch):
+    """The rows of a rank's own tokens come from the destination-side role (straight from the input, primary row and
+    duplicates from one read; ``MOONEP_LOCAL_ROWS=1``) or from the send role like every other row (``0``); both on
+    the bulk-copy and the register variant of the expansion, with one rank (every row is local) and several."""
+    if not case.supports(R):
+        pytest.skip("case needs another rank count")
+    monkeypatch.setenv("MOONEP_LOCAL_ROWS", local_rows)
+    monkeypatch.setenv("MOONEP_EXPAND_PATH", expand)
+    recs, tabs, dst_pos = _check(case, R, "cuda")
+    want = expected_combine(case, R, recs, dst_pos)
+    for r in range(R):
+        assert_within_ulp(recs[r]["out"], want[r], max_ulps=1, what=f"rank {r} combine")
+        assert torch.equal(recs[r]["weights_back"], recs[r]["w"]), f"rank {r}: weights did not round-trip"
+
+
+@pytest.mark.gpu
 def test_large_stride_dispatch_and_identity_combine():
     """S=8192, K=16, H=7168 on two emulated ranks: every rank's shard is 1.9 GB, so element offsets inside the mapped
     range pass 2**31 and byte offsets inside one shard pass 2**30 by far (parity: reference tests/test_dispatch.py:124-134
