@@ -11,6 +11,8 @@ MOONEP_RING_STAGES    2..6 (default 4): 2 KB stages per warp of the prefetch ker
                       library).
 MOONEP_LOCAL_ROWS     ``0``: the send role of dispatch also writes the rows that stay on the rank (default: the
                       destination-side role writes them from the input).
+MOONEP_LOCAL_HOME     ``0``: the push role of combine also moves the rows whose token lives on the rank (default: the fold
+                      role puts them into the local staging chunk).
 MOONEP_BWD_OVERLAP    ``1``: the MoE layer reduces each weight's gradients beside the remaining backward GEMMs (default 0).
 MOONEP_EXPAND_PATH    ``bulk`` (default) or ``ldst``: how the destination side of dispatch copies duplicate rows and clears
                       pad rows (read by the native library).
@@ -110,6 +112,13 @@ def local_rows_by_expand() -> bool:
     the input (primary row and duplicates from one read) instead of by the CTAs that drive NVLink.
     MOONEP_LOCAL_ROWS=0: the send role writes them like every other row."""
     return os.environ.get("MOONEP_LOCAL_ROWS", "1") not in _FALSE
+
+
+def local_home_by_fold() -> bool:
+    """Push combine: the rows of a rank's own tokens skip the CTAs that drive NVLink; the fold role writes them
+    (folded, or as they are) straight into the rank's own staging chunk.  MOONEP_LOCAL_HOME=0: they go through the
+    push role like every other row."""
+    return os.environ.get("MOONEP_LOCAL_HOME", "0") not in _FALSE
 
 
 def backward_overlap() -> bool:

@@ -63,6 +63,7 @@ struct PushArgs {
   int* fold_flag;           // [fold_rows] local: COMB epoch of the combine that last folded the group
   int fold_rows;
   int direct;               // single rank: FOLD writes the results straight into out / out_w
+  int local_home;           // rows of this rank's own tokens go from FOLD straight into the local staging chunk
 };
 
 __device__ __forceinline__ void acc_add(float* acc, const int4& v) {
@@ -158,8 +159,10 @@ __device__ void fold_role(const MoonepDevCtx& c, const PushArgs& a) {
     if (ngroups > a.fold_rows) record_status(c, MOONEP_STATUS_BAD_INDEX, MOONEP_K_COMBINE_PUSH, 10, ngroups, a.fold_rows, 0);
     ngroups = 0;
   }
-  // with a single rank this role also copies the rows that have no duplicates
-  const int nbatches = a.direct ? (NvS + kPushRowBatch - 1) / kPushRowBatch : 0;
+  // with a single rank this role also copies the rows that have no duplicates to the output; with local_home it
+  // copies those of this rank's own tokens into the local staging chunk (the PUSH role leaves them out)
+  const int nbatches = (a.direct || a.local_home) ? (NvS + kPushRowBatch - 1) / kPushRowBatch : 0;
+  unsigned char* stage_local = a.local_home ? c.stage_peer[c.rank] : nullptr;
   for (;;) {
     int item = 0;
     if (lane == 0) item = atomicAdd(work, 1);
@@ -178,17 +181,42 @@ __device__ void fold_role(const MoonepDevCtx& c, const PushArgs& a) {
         const int j = __ffs(prim) - 1;
         prim &= prim - 1;
         const int p_si = __shfl_sync(0xffffffffu, si, j);
+        const int p_l = __shfl_sync(0xffffffffu, l, j);
         const int slot = p_si % NvS;
         if (slot >= S * K) continue;
         const int prow = base + j;
+        uint16_t* o = nullptr;
+        int* sflag = nullptr;
+        if (a.direct) {
+          o = a.out + (long long)(slot / K) * H;
+        } else {
+          // local_home: only the rows of this rank's own tokens; slot (token, position among the token's primaries)
+          const int ord = (p_l >> MOONEP_LINK_ORD_SHIFT) & MOONEP_LINK_ORD_MASK;
+          if (p_si / NvS != c.rank || ord >= c.kp) continue;
+          const long long stage_row = (long long)(slot / K) * c.kp + ord;
+          o = reinterpret_cast<uint16_t*>(stage_local + stage_row * row_bytes);
+          sflag = reinterpret_cast<int*>(stage_local + c.stage_flag_off) + stage_row;
+        }
         if (!wait_block_ready(c, a, prow, lane)) return;
-        if (a.in_w != nullptr && a.out_w != nullptr && lane == 0) a.out_w[slot] = a.in_w[prow];
+        if (a.in_w != nullptr && lane == 0) {
+          if (a.direct) {
+            if (a.out_w != nullptr) a.out_w[slot] = a.in_w[prow];
+          } else {
+            reinterpret_cast<float*>(stage_local + c.stage_w_off)[slot] = a.in_w[prow];
+          }
+        }
         const uint16_t* src = a.in_rows + (long long)prow * H;
-        uint16_t* o = a.out + (long long)(slot / K) * H;
         if (a.vec_ok) {
           for (int i = lane; i < H / 8; i += 32) st16(reinterpret_cast<int4*>(o) + i, ld16(reinterpret_cast<const int4*>(src) + i));
         } else {
           for (int i = lane; i < H; i += 32) o[i] = src[i];
+        }
+        if (sflag != nullptr) {
+          __syncwarp();
+          if (lane == 0) {
+            fence_gpu();
+            st_relaxed_gpu(sflag, epoch);
+          }
         }
       }
       continue;
@@ -204,6 +232,21 @@ __device__ void fold_role(const MoonepDevCtx& c, const PushArgs& a) {
       if (!ok) return;
     }
     uint16_t* o = a.fold_buf + (long long)item * H;
+    int* sflag = nullptr;  // local_home and a token of this rank: the folded row goes straight into the local staging
+    if (a.local_home) {
+      const int p_si = a.src_info[prow];
+      if (p_si >= 0 && p_si / NvS == c.rank) {
+        const int slot = p_si - c.rank * NvS;
+        const int ord = (a.link[prow] >> MOONEP_LINK_ORD_SHIFT) & MOONEP_LINK_ORD_MASK;
+        if (slot >= S * K || ord >= c.kp) {
+          record_status(c, MOONEP_STATUS_BAD_INDEX, MOONEP_K_COMBINE_PUSH, 8, p_si, prow, ord);
+          continue;
+        }
+        const long long stage_row = (long long)(slot / K) * c.kp + ord;
+        o = reinterpret_cast<uint16_t*>(stage_local + stage_row * row_bytes);
+        sflag = reinterpret_cast<int*>(stage_local + c.stage_flag_off) + stage_row;
+      }
+    }
     if (!a.direct && a.in_w != nullptr && lane < n_rows) {
       // gate weights of all entries of this group travel to the home rank's weight staging
       const int s_q = a.src_info[my_row];
@@ -278,9 +321,14 @@ __device__ void fold_role(const MoonepDevCtx& c, const PushArgs& a) {
     }
     __syncwarp();
     if (lane == 0 && !a.direct) {
-      // the weights went to another GPU: they must have arrived before the PUSH role's flag for this row can
-      if (a.in_w != nullptr) fence_sys(); else fence_gpu();
-      st_relaxed_gpu(a.fold_flag + item, epoch);
+      if (sflag != nullptr) {
+        fence_gpu();  // row and weights are in this GPU's memory
+        st_relaxed_gpu(sflag, epoch);
+      } else {
+        // the weights went to another GPU: they must have arrived before the PUSH role's flag for this row can
+        if (a.in_w != nullptr) fence_sys(); else fence_gpu();
+        st_relaxed_gpu(a.fold_flag + item, epoch);
+      }
     }
   }
 }
@@ -405,6 +453,7 @@ struct PushJobs {
       record_status(c, MOONEP_STATUS_BAD_INDEX, MOONEP_K_COMBINE_PUSH, 8, p_si, prow, ord);
       return false;
     }
+    if (a.local_home && home == c.rank) return false;  // the FOLD role puts this row into the local staging chunk
     unsigned char* stage_home = c.stage_peer[home];
     const long long stage_row = (long long)token * c.kp + ord;
     j_dst = stage_home + stage_row * ((long long)c.H * 2);
@@ -816,6 +865,8 @@ extern "C" int moonep_combine_push(void* ctx, int roles, const int* src_info, co
                                    int* fold_flag, int fold_rows, int n_push, int n_local, void* stream) {
   auto* h = (HostCtx*)ctx;
   const MoonepDevCtx& c = h->dev;
+  const int local_home = ((roles & MOONEP_ROLE_LOCAL_HOME) && c.R > 1 && c.stage_peer != nullptr) ? 1 : 0;
+  roles &= ~MOONEP_ROLE_LOCAL_HOME;
   const int direct = (c.R == 1 && roles == MOONEP_ROLE_FOLD) ? 1 : 0;
   if (c.stage_peer == nullptr && !direct) {
     set_error("moonep_combine_push: this Buffer has no combine staging memory");
@@ -842,6 +893,7 @@ extern "C" int moonep_combine_push(void* ctx, int roles, const int* src_info, co
   a.fold_flag = fold_flag;
   a.fold_rows = fold_rows;
   a.direct = direct;
+  a.local_home = local_home;
   const bool al = ((reinterpret_cast<uintptr_t>(in_rows) | reinterpret_cast<uintptr_t>(out_hidden) |
                     reinterpret_cast<uintptr_t>(fold_buf)) & 15u) == 0;
   a.vec_ok = (c.H % 8 == 0) && al;

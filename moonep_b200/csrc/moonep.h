@@ -119,6 +119,9 @@
 #define MOONEP_ROLE_PUSH 1     // expert side: copy primary rows (folded where they have duplicates) to the tokens' home ranks
 #define MOONEP_ROLE_SUM 2      // home side: sum the rows of a token as they arrive
 #define MOONEP_ROLE_FOLD 4     // expert side: fold the duplicate groups into a local buffer
+// Modifier, given to every launch of one combine alike: rows whose token lives on this rank do not go through the
+// PUSH role; the FOLD role writes them (folded, or as they are) straight into this rank's own staging chunk.
+#define MOONEP_ROLE_LOCAL_HOME 8
 
 // Routing entries per planner block (whole tokens, at most this many entries).
 #define MOONEP_PLAN_BLOCK 512

@@ -48,6 +48,7 @@ _PHASE_NAMES = ("tables", "tokens", "send", "zero_fill", "wait_plan", "build_exp
 ROLE_TABLES, ROLE_TOKENS, ROLE_SEND, ROLE_EXPAND = 1, 2, 4, 8
 ROLE_LOCAL_ROWS = 16  # modifier: EXPAND writes the rows of this rank's own tokens from the input, SEND skips them
 ROLE_PUSH, ROLE_SUM, ROLE_FOLD = 1, 2, 4
+ROLE_LOCAL_HOME = 8  # modifier: rows of this rank's own tokens go from FOLD straight into the local staging chunk
 _FAMILY_NAMES = {0: "READY", 1: "TPE", 2: "PLAN", 3: "SENT", 4: "COMB", 5: "GRAD_READY", 6: "GRAD_DONE", 7: "PREFETCH"}
 _BIAS_OFF, _CTR_TABLES_READY = 32, 18  # words of the counters block (csrc/moonep.h)
 
@@ -460,6 +461,7 @@ class CudaBackend:
             return
         self._quiesced = False
         comb = self._next(FLAG_COMB)
+        lh = ROLE_LOCAL_HOME if config.local_home_by_fold() else 0
         fold_buf, fold_flag = self._fold_scratch()
         args = (_ptr(plan.src_info), _ptr(plan.link), _ptr(plan.dst), _ptr(hidden_nvsh), _ptr(route_weights_nvs),
                 _ptr(out_hidden), _ptr(out_weights_sk), wf, we, comb, _ptr(ready), int(ready_expect),
@@ -468,12 +470,12 @@ class CudaBackend:
         if self.ctx["R"] == 1:  # nothing to stage: the fold role writes the results itself
             self._call("moonep_combine_push", ROLE_FOLD, *args, tag="combine_fold")
         elif not self.phased:
-            self._call("moonep_combine_push", ROLE_FOLD | ROLE_PUSH | ROLE_SUM, *args, tag="combine_fused")
+            self._call("moonep_combine_push", ROLE_FOLD | ROLE_PUSH | ROLE_SUM | lh, *args, tag="combine_fused")
         else:
-            self._call("moonep_combine_push", ROLE_FOLD, *args, tag="combine_fold")
-            self._call("moonep_combine_push", ROLE_PUSH, *args, tag="combine_push")
+            self._call("moonep_combine_push", ROLE_FOLD | lh, *args, tag="combine_fold")
+            self._call("moonep_combine_push", ROLE_PUSH | lh, *args, tag="combine_push")
             self.world.step()
-            self._call("moonep_combine_push", ROLE_SUM, *args, tag="combine_sum")
+            self._call("moonep_combine_push", ROLE_SUM | lh, *args, tag="combine_sum")
         self.world.step()
 
     def _fold_scratch(self):

@@ -107,17 +107,20 @@ def test_round_trip_on_the_alternative_copy_paths(case, paths, monkeypatch):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("local_rows", ["0", "1"])
+@pytest.mark.parametrize("local_rows", ["0", "1"], ids=["send_all", "local_rows"])
 @pytest.mark.parametrize("expand", ["bulk", "ldst"])
 @pytest.mark.parametrize("R", [1, 2, 4])
 @pytest.mark.parametrize("case", ROUNDTRIP_CASES[:4] + ROUNDTRIP_CASES[7:10], ids=lambda c: c.name)
 def test_round_trip_with_local_rows_written_by_either_role(case, R, expand, local_rows, monkeypatch):
     """The rows of a rank's own tokens come from the destination-side role (straight from the input, primary row and
     duplicates from one read; ``MOONEP_LOCAL_ROWS=1``) or from the send role like every other row (``0``); both on
-    the bulk-copy and the register variant of the expansion, with one rank (every row is local) and several."""
+    the bulk-copy and the register variant of the expansion, with one rank (every row is local) and several.  On the
+    way back the same rows reach the local staging chunk through the fold role (``MOONEP_LOCAL_HOME=1``) or the push
+    role."""
     if not case.supports(R):
         pytest.skip("case needs another rank count")
     monkeypatch.setenv("MOONEP_LOCAL_ROWS", local_rows)
+    monkeypatch.setenv("MOONEP_LOCAL_HOME", local_rows)  # the same choice on the way back: fold role or push role
     monkeypatch.setenv("MOONEP_EXPAND_PATH", expand)
     recs, tabs, dst_pos = _check(case, R, "cuda")
     want = expected_combine(case, R, recs, dst_pos)
