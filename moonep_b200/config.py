@@ -118,7 +118,7 @@ def local_home_by_fold() -> bool:
     """Push combine: the rows of a rank's own tokens skip the CTAs that drive NVLink; the fold role writes them
     (folded, or as they are) straight into the rank's own staging chunk.  MOONEP_LOCAL_HOME=0: they go through the
     push role like every other row."""
-    return os.environ.get("MOONEP_LOCAL_HOME", "0") not in _FALSE
+    return os.environ.get("MOONEP_LOCAL_HOME", "1") not in _FALSE
 
 
 def backward_overlap() -> bool:
