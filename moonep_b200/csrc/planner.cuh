@@ -296,10 +296,17 @@ __device__ inline void plan_tokens_block(const MoonepDevCtx& c, const int* __res
   for (int e = tid; e < E; e += blockDim.x) s_hist[e] = 0;
   __syncthreads();
   {
-    const long long total = (long long)block * E;  // rows of the blocks before this one
-    for (long long idx = tid; idx < total; idx += blockDim.x) {
-      const int v = c.block_hist[idx];
-      if (v) atomicAdd(s_hist + (int)(idx % E), v);
+    // column sums over the rows of the blocks before this one: a thread walks one expert's column (coalesced across
+    // the threads of a row), `parts` threads share a column and meet in one shared-memory add each
+    const int cols = min(E, (int)blockDim.x);
+    const int parts = (int)blockDim.x / cols;
+    const int part = tid / cols, col0 = tid - part * cols;
+    if (part < parts) {
+      for (int e = col0; e < E; e += cols) {
+        int sum = 0;
+        for (int r = part; r < block; r += parts) sum += c.block_hist[(long long)r * E + e];
+        if (sum) atomicAdd(s_hist + e, sum);
+      }
     }
   }
   for (int i = tid; i < nent; i += blockDim.x) {
@@ -322,15 +329,16 @@ __device__ inline void plan_tokens_block(const MoonepDevCtx& c, const int* __res
     int dstv = -1, dest = -1;
     if (e >= 0) {
       const int g = c.tpe_prev[e] + s.lc[i];
+      // first destination whose running allocation exceeds g; no early exit, so that the loads are independent
       const int* ac = c.alloc_cum + (long long)e * R;
-      int prev = 0;
+      int prev = 0, last = 0;
       for (int d = 0; d < R; ++d) {
         const int cum = ac[d];
-        if (g < cum) {
+        if (dest < 0 && g < cum) {
           dest = d;
-          break;
+          prev = last;
         }
-        prev = cum;
+        last = cum;
       }
       if (dest >= 0) {
         const int loff = c.expert_off[(long long)dest * E + e] + (g - prev);
