@@ -77,6 +77,11 @@ def copy_path(which: str = "") -> str:
     return raw
 
 
+def copy_path_is_set(which: str) -> bool:
+    """True when the environment names the copy path of this kernel explicitly."""
+    return bool(os.environ.get(f"MOONEP_{which.upper()}_PATH"))
+
+
 def local_sms(sm_count: int) -> int:
     """CTAs for kernels that only touch local memory (planner, dedup expansion, duplicate folding)."""
     raw = os.environ.get("MOONEP_LOCAL_SMS")
