@@ -791,6 +791,7 @@ __global__ void __launch_bounds__(kPushThreads, 1) combine_push_kernel(const Moo
   }
   fence_barrier_init();
   griddep_wait();  // the set-up above may overlap the previous kernel's tail; its results are needed from here on
+  griddep_launch();  // the next kernel of the stream may set itself up on SMs as the CTAs of this one leave them
   __syncthreads();
   const bool has_push = (a.roles & MOONEP_ROLE_PUSH) != 0;
   const bool has_local = (a.roles & (MOONEP_ROLE_FOLD | MOONEP_ROLE_SUM)) != 0;

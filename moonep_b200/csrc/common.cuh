@@ -97,6 +97,9 @@ __device__ __forceinline__ void stat_phase(const MoonepDevCtx& c, int phase, uns
 // Programmatic dependent launch: everything before this call may run while the previous kernel of the stream is
 // still finishing; after it, that kernel has completed and its writes are visible.  A no-op for ordinary launches.
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Lets a kernel launched with programmatic stream serialisation behind this one start its CTAs as soon as SMs have room
+// (it still waits in griddepcontrol.wait until this grid has completed and its writes are visible).
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // Absolute epoch of a launch argument: argument + this family's bias (see the header comment).
 __device__ __forceinline__ int abs_epoch(const MoonepDevCtx& c, int family, int epoch) {

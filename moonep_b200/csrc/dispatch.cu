@@ -992,6 +992,7 @@ __global__ void __launch_bounds__(kDispatchThreads, 1) dispatch_kernel(const Moo
   }
   fence_barrier_init();
   griddep_wait();  // the set-up above may overlap the previous kernel's tail; its results are needed from here on
+  griddep_launch();  // the next kernel of the stream may set itself up on SMs as the CTAs of this one leave them
   __syncthreads();
   bool ok = !poisoned(c);
 

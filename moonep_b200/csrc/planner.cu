@@ -28,6 +28,7 @@ __global__ void __launch_bounds__(kTokensThreads)
     plan_publish_kernel(const MoonepDevCtx c, const int* __restrict__ topk, const int* __restrict__ tpe, int tpe_is_2d,
                         int tokens_per_block, int epoch_tpe) {
   extern __shared__ int s_hist[];  // [E]
+  griddep_launch();  // the dispatch kernel behind this one may set itself up meanwhile
   const bool live = !poisoned(c);
   if (live) {
     const int tid = blockIdx.x * blockDim.x + threadIdx.x;
