@@ -13,6 +13,8 @@ MOONEP_LOCAL_ROWS     ``0``: the send role of dispatch also writes the rows that
                       destination-side role writes them from the input).
 MOONEP_LOCAL_HOME     ``0``: the push role of combine also moves the rows whose token lives on the rank (default: the fold
                       role puts them into the local staging chunk).
+MOONEP_SUM_SLOTS      ``2``: a warp of combine's sum role holds two tokens and sums the one that completes first (read by
+                      the native library; default 1: measured equal or slower on 2 GPUs, not measured on more).
 MOONEP_BWD_OVERLAP    ``1``: the MoE layer reduces each weight's gradients beside the remaining backward GEMMs (default 0).
 MOONEP_EXPAND_PATH    ``bulk`` (default) or ``ldst``: how the destination side of dispatch copies duplicate rows and clears
                       pad rows (read by the native library).

@@ -26,6 +26,8 @@
 // after the other.  With a single rank the FOLD role alone writes the results.
 //
 // Parity: reference moonep_td/combine_prologue.py:19-40 and moonep_td/combine.py:22-68.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "host.h"
 
@@ -37,6 +39,9 @@ constexpr int kPushThreads = 512;
 constexpr int kPushMaxChunk = 8192;     // bytes of a row piece (one ring stage): 8 warps x 3 stages x 7 KB for H=7168
 constexpr int kPushRowBatch = 32;       // rows handed out per grab (the primaries without duplicates among them are sent)
 constexpr int kPushGroupBatch = 8;      // duplicate groups handed out per grab
+constexpr int kFoldRowBatch = 4;        // rows per work item when the FOLD role copies rows without duplicates: rows of one
+                                        // source rank are neighbours in the shard, so a large batch would hand one warp
+                                        // dozens of copies in a row
 constexpr int kFoldVec = 4;             // int4 per lane per inner step (2 KB per warp)
 constexpr int kFoldRows = 4;            // rows of a duplicate group whose loads are in flight together
 constexpr int kSumVec = 4;
@@ -64,6 +69,7 @@ struct PushArgs {
   int fold_rows;
   int direct;               // single rank: FOLD writes the results straight into out / out_w
   int local_home;           // rows of this rank's own tokens go from FOLD straight into the local staging chunk
+  int sum_two;              // SUM: a warp holds two tokens and sums the one that completes first
 };
 
 __device__ __forceinline__ void acc_add(float* acc, const int4& v) {
@@ -161,7 +167,7 @@ __device__ void fold_role(const MoonepDevCtx& c, const PushArgs& a) {
   }
   // with a single rank this role also copies the rows that have no duplicates to the output; with local_home it
   // copies those of this rank's own tokens into the local staging chunk (the PUSH role leaves them out)
-  const int nbatches = (a.direct || a.local_home) ? (NvS + kPushRowBatch - 1) / kPushRowBatch : 0;
+  const int nbatches = (a.direct || a.local_home) ? (NvS + kFoldRowBatch - 1) / kFoldRowBatch : 0;
   unsigned char* stage_local = a.local_home ? c.stage_peer[c.rank] : nullptr;
   for (;;) {
     int item = 0;
@@ -170,9 +176,9 @@ __device__ void fold_role(const MoonepDevCtx& c, const PushArgs& a) {
     if (item >= ngroups + nbatches) break;
     if (item >= ngroups) {
       // single rank: rows without duplicates go to the output as they are
-      const int base = (item - ngroups) * kPushRowBatch;
+      const int base = (item - ngroups) * kFoldRowBatch;
       int si = -1, l = 0;
-      if (lane < kPushRowBatch && base + lane < NvS) {
+      if (lane < kFoldRowBatch && base + lane < NvS) {
         si = a.src_info[base + lane];
         l = si >= 0 ? a.link[base + lane] : 0;
       }
@@ -207,7 +213,23 @@ __device__ void fold_role(const MoonepDevCtx& c, const PushArgs& a) {
         }
         const uint16_t* src = a.in_rows + (long long)prow * H;
         if (a.vec_ok) {
-          for (int i = lane; i < H / 8; i += 32) st16(reinterpret_cast<int4*>(o) + i, ld16(reinterpret_cast<const int4*>(src) + i));
+          // kFoldVec loads in flight per lane: a plain load-store loop would run one 16-byte round trip at a time
+          const int nvec = H / 8;
+          const int4* s4 = reinterpret_cast<const int4*>(src);
+          int4* o4 = reinterpret_cast<int4*>(o);
+          for (int i0 = 0; i0 < nvec; i0 += 32 * kFoldVec) {
+            int4 v[kFoldVec];
+#pragma unroll
+            for (int jv = 0; jv < kFoldVec; ++jv) {
+              const int i = i0 + jv * 32 + lane;
+              if (i < nvec) v[jv] = ld16(s4 + i);
+            }
+#pragma unroll
+            for (int jv = 0; jv < kFoldVec; ++jv) {
+              const int i = i0 + jv * 32 + lane;
+              if (i < nvec) st16(o4 + i, v[jv]);
+            }
+          }
         } else {
           for (int i = lane; i < H; i += 32) o[i] = src[i];
         }
@@ -671,15 +693,145 @@ __device__ void push_role(const MoonepDevCtx& c, const PushArgs& a, unsigned cha
 
 // ---- SUM role ----------------------------------------------------------------------------------------
 
+// Sums the staged rows of `token` (all present) in fp32 in ascending k, stores the bf16 result and copies the gate
+// weights.  valid: this lane's routing entry is in range; nprim: primaries of the token (rows in its staging slots).
+__device__ void sum_token(const MoonepDevCtx& c, const PushArgs& a, int token, bool valid, int nprim, int lane) {
+  const int K = c.K, H = c.H, kp = c.kp;
+  const long long row_bytes = (long long)H * 2;
+  const unsigned char* stage = c.stage_peer[c.rank];
+  const float* wst = reinterpret_cast<const float*>(stage + c.stage_w_off);
+  if (a.out_w != nullptr && lane < K) a.out_w[token * K + lane] = valid ? wst[token * K + lane] : 0.f;
+  const unsigned char* rows = stage + (long long)token * kp * row_bytes;
+  uint16_t* orow = a.out + (long long)token * H;
+  if (a.vec_ok) {
+    const int nvec = H / 8;
+    for (int c0 = 0; c0 < nvec; c0 += 32 * kSumVec) {
+      float acc[kSumVec][8];
+#pragma unroll
+      for (int j = 0; j < kSumVec; ++j)
+#pragma unroll
+        for (int q = 0; q < 8; ++q) acc[j][q] = 0.f;
+      for (int p0 = 0; p0 < nprim; p0 += kSumRows) {
+        int4 v[kSumRows][kSumVec];
+#pragma unroll
+        for (int r = 0; r < kSumRows; ++r) {
+          if (p0 + r < nprim) {
+            const int4* r4 = reinterpret_cast<const int4*>(rows + (long long)(p0 + r) * row_bytes);
+#pragma unroll
+            for (int j = 0; j < kSumVec; ++j) {
+              const int i = c0 + j * 32 + lane;
+              if (i < nvec) v[r][j] = ld16(r4 + i);
+            }
+          }
+        }
+#pragma unroll
+        for (int r = 0; r < kSumRows; ++r) {
+          if (p0 + r < nprim) {
+#pragma unroll
+            for (int j = 0; j < kSumVec; ++j) {
+              const int i = c0 + j * 32 + lane;
+              if (i < nvec) acc_add(acc[j], v[r][j]);
+            }
+          }
+        }
+      }
+      int4* o4 = reinterpret_cast<int4*>(orow);
+#pragma unroll
+      for (int j = 0; j < kSumVec; ++j) {
+        const int i = c0 + j * 32 + lane;
+        if (i < nvec) st16(o4 + i, acc_pack(acc[j]));
+      }
+    }
+  } else {
+    for (int i = lane; i < H; i += 32) {
+      float acc = 0.f;
+      for (int p = 0; p < nprim; ++p)
+        acc += bf16_to_f32(reinterpret_cast<const uint16_t*>(rows + (long long)p * row_bytes)[i]);
+      orow[i] = f32_to_bf16(acc);
+    }
+  }
+}
+
+// This lane's routing entry of `token` (lanes >= K: none); false when out of range (status recorded).
+__device__ __forceinline__ bool sum_entry(const MoonepDevCtx& c, const PushArgs& a, int token, int lane, int& d) {
+  d = 0;
+  if (lane >= c.K) return false;
+  d = a.dst[token * c.K + lane];
+  const int raw = d < 0 ? -d - 1 : d;
+  const int dest = raw / c.NvS;
+  const int loff = raw - dest * c.NvS;
+  const bool valid = dest >= 0 && dest < c.R && loff >= 0 && loff < c.NvS;
+  if (!valid) record_status(c, MOONEP_STATUS_BAD_INDEX, MOONEP_K_COMBINE_SUM, 6, d, token, lane);
+  return valid;
+}
+
+// A warp holds two tokens at a time and sums whichever is complete first.  Rows of a token come from up to min(K, R)
+// ranks in no particular order, so most tokens complete late in the transfer; with one token per warp the tokens
+// beyond the first wave would only get a warp once an earlier token has completed, and pile up at the end.
+__device__ void sum_role_two(const MoonepDevCtx& c, const PushArgs& a) {
+  const int lane = threadIdx.x & 31;
+  const int S = c.S, kp = c.kp;
+  const int epoch = abs_epoch(c, MOONEP_FLAG_COMB, a.epoch_comb);
+  int* work = c.counters + MOONEP_CTR_SUM_WORK;
+  const int* flags = reinterpret_cast<const int*>(c.stage_peer[c.rank] + c.stage_flag_off);
+  int tok[2] = {-1, -1}, dd[2] = {0, 0};
+  bool vv[2] = {false, false};
+  bool more = true;
+  unsigned long long t0 = 0;
+  unsigned idle = 0;
+  for (;;) {
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      if (tok[q] < 0 && more) {
+        int t = 0;
+        if (lane == 0) t = atomicAdd(work, 1);
+        t = __shfl_sync(0xffffffffu, t, 0);
+        if (t >= S) {
+          more = false;
+        } else {
+          tok[q] = t;
+          vv[q] = sum_entry(c, a, t, lane, dd[q]);
+        }
+      }
+    }
+    if (tok[0] < 0 && tok[1] < 0) break;
+    bool progressed = false;
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      if (tok[q] < 0) continue;
+      const unsigned prim = __ballot_sync(0xffffffffu, vv[q] && dd[q] >= 0);
+      int nprim = __popc(prim);
+      if (nprim > kp) nprim = kp;
+      const int ord = __popc(prim & ((1u << lane) - 1u));
+      bool here = true;
+      if (vv[q] && dd[q] >= 0 && ord < kp) here = ld_acquire_sys(flags + (long long)tok[q] * kp + ord) - epoch >= 0;
+      if (!__all_sync(0xffffffffu, here)) continue;
+      sum_token(c, a, tok[q], vv[q], nprim, lane);
+      tok[q] = -1;
+      progressed = true;
+    }
+    if (progressed) {
+      idle = 0;
+      continue;
+    }
+    if (idle++ == 0) t0 = globaltimer_ns();
+    int give_up = 0;
+    if (lane == 0 && (idle & 15u) == 0 && (globaltimer_ns() - t0 > c.timeout_ns || poisoned(c))) {
+      record_status(c, MOONEP_STATUS_TIMEOUT, MOONEP_K_COMBINE_SUM, 202, tok[0] >= 0 ? tok[0] : tok[1], epoch, 0);
+      give_up = 1;
+    }
+    if (__shfl_sync(0xffffffffu, give_up, 0)) break;
+    __nanosleep(128);
+  }
+}
+
 __device__ void sum_role(const MoonepDevCtx& c, const PushArgs& a) {
   const int lane = threadIdx.x & 31;
   const int NvS = c.NvS, K = c.K, H = c.H, S = c.S, kp = c.kp;
-  const long long row_bytes = (long long)H * 2;
   const int epoch = abs_epoch(c, MOONEP_FLAG_COMB, a.epoch_comb);
   int* work = c.counters + MOONEP_CTR_SUM_WORK;
   const unsigned char* stage = c.stage_peer[c.rank];
   const int* flags = reinterpret_cast<const int*>(stage + c.stage_flag_off);
-  const float* wst = reinterpret_cast<const float*>(stage + c.stage_w_off);
   for (;;) {
     int token = 0;
     if (lane == 0) token = atomicAdd(work, 1);
@@ -718,56 +870,7 @@ __device__ void sum_role(const MoonepDevCtx& c, const PushArgs& a) {
       }
     }
     if (!__all_sync(0xffffffffu, ok)) break;
-    if (a.out_w != nullptr && lane < K) a.out_w[token * K + lane] = valid ? wst[token * K + lane] : 0.f;
-    const unsigned char* rows = stage + (long long)token * kp * row_bytes;
-    uint16_t* orow = a.out + (long long)token * H;
-    if (a.vec_ok) {
-      const int nvec = H / 8;
-      for (int c0 = 0; c0 < nvec; c0 += 32 * kSumVec) {
-        float acc[kSumVec][8];
-#pragma unroll
-        for (int j = 0; j < kSumVec; ++j)
-#pragma unroll
-          for (int q = 0; q < 8; ++q) acc[j][q] = 0.f;
-        for (int p0 = 0; p0 < nprim; p0 += kSumRows) {
-          int4 v[kSumRows][kSumVec];
-#pragma unroll
-          for (int r = 0; r < kSumRows; ++r) {
-            if (p0 + r < nprim) {
-              const int4* r4 = reinterpret_cast<const int4*>(rows + (long long)(p0 + r) * row_bytes);
-#pragma unroll
-              for (int j = 0; j < kSumVec; ++j) {
-                const int i = c0 + j * 32 + lane;
-                if (i < nvec) v[r][j] = ld16(r4 + i);
-              }
-            }
-          }
-#pragma unroll
-          for (int r = 0; r < kSumRows; ++r) {
-            if (p0 + r < nprim) {
-#pragma unroll
-              for (int j = 0; j < kSumVec; ++j) {
-                const int i = c0 + j * 32 + lane;
-                if (i < nvec) acc_add(acc[j], v[r][j]);
-              }
-            }
-          }
-        }
-        int4* o4 = reinterpret_cast<int4*>(orow);
-#pragma unroll
-        for (int j = 0; j < kSumVec; ++j) {
-          const int i = c0 + j * 32 + lane;
-          if (i < nvec) st16(o4 + i, acc_pack(acc[j]));
-        }
-      }
-    } else {
-      for (int i = lane; i < H; i += 32) {
-        float acc = 0.f;
-        for (int p = 0; p < nprim; ++p)
-          acc += bf16_to_f32(reinterpret_cast<const uint16_t*>(rows + (long long)p * row_bytes)[i]);
-        orow[i] = f32_to_bf16(acc);
-      }
-    }
+    sum_token(c, a, token, valid, nprim, lane);
   }
 }
 
@@ -819,7 +922,7 @@ __global__ void __launch_bounds__(kPushThreads, 1) combine_push_kernel(const Moo
       t0 = globaltimer_ns();
     }
     if (a.roles & MOONEP_ROLE_SUM) {
-      sum_role(c, a);
+      if (a.sum_two) sum_role_two(c, a); else sum_role(c, a);
       __syncthreads();
       if (threadIdx.x == 0) stat_phase(c, MOONEP_PH_SUM, t0);
     }
@@ -895,6 +998,10 @@ extern "C" int moonep_combine_push(void* ctx, int roles, const int* src_info, co
   a.fold_rows = fold_rows;
   a.direct = direct;
   a.local_home = local_home;
+  {
+    const char* st = getenv("MOONEP_SUM_SLOTS");  // 2: a SUM warp holds two tokens (default 1)
+    a.sum_two = (st != nullptr && atoi(st) == 2) ? 1 : 0;
+  }
   const bool al = ((reinterpret_cast<uintptr_t>(in_rows) | reinterpret_cast<uintptr_t>(out_hidden) |
                     reinterpret_cast<uintptr_t>(fold_buf)) & 15u) == 0;
   a.vec_ok = (c.H % 8 == 0) && al;

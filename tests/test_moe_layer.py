@@ -15,6 +15,19 @@ DEVICES = ["cpu", pytest.param("cuda", marks=pytest.mark.gpu)]
 @pytest.mark.parametrize("device", DEVICES)
 @pytest.mark.parametrize("R,routing", [(1, "softmax"), (2, "biased"), (4, "zipf")])
 def test_moe_layer_forward_backward_matches_dense_reference(device, R, routing):
+    _layer_against_dense(device, R, routing)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("R,routing", [(2, "biased"), (4, "zipf")])
+def test_moe_layer_backward_with_reduce_grad_beside_the_gemms(R, routing, monkeypatch):
+    """``MOONEP_BWD_OVERLAP=1``: each weight's gradients are reduced on the communication stream as soon as they
+    exist, one ``reduce_grad`` per weight, while the remaining GEMMs run on fewer SMs; same results."""
+    monkeypatch.setenv("MOONEP_BWD_OVERLAP", "1")
+    _layer_against_dense("cuda", R, routing)
+
+
+def _layer_against_dense(device, R, routing):
     S, H, I, K, epn, Bslots = 96, 256, 256, 2, 2, 1
     E = R * epn
     lw = LocalWorld(R, device)

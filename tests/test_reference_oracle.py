@@ -1,5 +1,6 @@
 """Cross-check of the host planner against the reference implementation's own planning oracle, when a copy of the
-reference is available (``MOONEP_REFERENCE_DIR``, default ``/root/reference``); skipped otherwise.
+reference is available (``MOONEP_REFERENCE_DIR``, default: a directory ``reference`` beside this repository); skipped
+otherwise.
 
 The reference's ``tests/planning_reference.launch_planning_torch_reference(ctx, topk, tokens_per_expert)`` accepts a
 2-D tokens-per-expert table, in which case it needs no process group (with ``materialize_dedup=False`` for more than
@@ -20,7 +21,8 @@ from moonep_b200.layout import compute_layout
 from moonep_b200.models.routing import make_routing
 from tests.cases import PLANNING_CASES
 
-REF_DIR = os.environ.get("MOONEP_REFERENCE_DIR", "/root/reference")
+_BESIDE = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
+REF_DIR = os.environ.get("MOONEP_REFERENCE_DIR", _BESIDE)
 REF_FILE = os.path.join(REF_DIR, "tests", "planning_reference.py")
 _ref = None
 
