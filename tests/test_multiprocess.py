@@ -38,7 +38,7 @@ def test_cuda_backend_nccl_processes():
     n = torch.cuda.device_count()
     if n < 2:
         pytest.skip("needs at least two GPUs")
-    # two ranks unless MOONEP_TEST_MP_RANKS asks for more (up to the GPUs present)
-    want = int(os.environ.get("MOONEP_TEST_MP_RANKS", "2"))
+    # up to four ranks (MOONEP_TEST_MP_RANKS changes the bound), one per GPU present
+    want = int(os.environ.get("MOONEP_TEST_MP_RANKS", "4"))
     # NVLS off: a rank that dies while its memory is bound to an in-switch reduction object can fault its peers
     _run_worker(max(2, min(n, want)), "nccl", 29631, 900, {"NCCL_NVLS_ENABLE": "0"})
