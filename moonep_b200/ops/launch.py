@@ -67,7 +67,8 @@ def launch_dispatch(ctx, hidden_sh, route_weights_sk, plan, *, build_dedup_map=F
     assert hidden_sh.dtype == torch.bfloat16 and hidden_sh.is_contiguous(), "hidden_sh must be contiguous bf16"
     assert tuple(hidden_sh.shape) == (S, H), "hidden_sh shape mismatch"
     if route_weights_sk is not None:
-        assert route_weights_sk.dtype == torch.float32 and route_weights_sk.is_contiguous()
+        assert route_weights_sk.dtype == torch.float32 and route_weights_sk.is_contiguous(), \
+            "route_weights_sk must be contiguous fp32"
         assert tuple(route_weights_sk.shape) == (S, K), "route_weights_sk shape mismatch"
     check_plan_for_ctx(ctx, plan, hidden_sh.device)
     be = _be(ctx)
@@ -88,6 +89,7 @@ def launch_dedup_builder(ctx, plan) -> None:
 def launch_dispatch_epilogue(ctx, plan, *, pdl_launch=False) -> None:
     """Zero the pad rows and copy every primary row to its duplicates inside the local shard."""
     del pdl_launch
+    check_plan_for_ctx(ctx, plan, plan.dst.device)
     _be(ctx).dispatch_expand(plan, None, None, True)
 
 
@@ -103,7 +105,7 @@ def launch_combine(ctx, output_sh, dst, output_sk=None, *, pdl_launch=False) -> 
     assert output_sh.dtype == torch.bfloat16 and output_sh.is_contiguous(), "output_sh must be contiguous bf16"
     assert dst.dtype == torch.int32 and dst.is_contiguous(), "dst must be contiguous int32"
     if output_sk is not None:
-        assert output_sk.dtype == torch.float32 and output_sk.is_contiguous()
+        assert output_sk.dtype == torch.float32 and output_sk.is_contiguous(), "output_sk must be contiguous fp32"
         assert tuple(output_sk.shape) == (ctx["S"], ctx["K"]), "output_sk shape mismatch"
     _be(ctx).combine_pull(dst, output_sh, output_sk)
 

@@ -149,10 +149,20 @@ def check_planning_outputs(ctx: dict, cu_seqlens: torch.Tensor, plan: MoonEPComm
 
 
 def check_plan_for_ctx(ctx: dict, plan: MoonEPCommPlan, device) -> None:
-    """Shape/dtype/device checks before a plan is handed to a kernel."""
+    """Shape/dtype/device checks before a plan is handed to a kernel; the message names the field that is wrong
+    (parity: the assertions of reference moonep_td/dispatch.py:126-160 and moonep_td/dispatch_epilogue.py:45-60)."""
     assert isinstance(plan, MoonEPCommPlan), "plan must be a MoonEPCommPlan"
     assert plan.N == ctx["N"] and plan.R == ctx["R"] and plan.K == ctx["K"] and plan.NvS == ctx["NvS"]
     assert plan.E == ctx["E"] and plan.B == ctx["B"]
-    for t in plan.tensors():
-        assert t.dtype == torch.int32 and t.is_contiguous(), "plan tensors must be contiguous int32"
-        assert t.device == torch.device(device), "plan tensor on the wrong device"
+    E, B, N, NvS, R = ctx["E"], ctx["B"], ctx["N"], ctx["NvS"], ctx["R"]
+    shapes = {
+        "dst": (N,), "experts_to_copy": (R, B), "zero_fill_ranges": (E + B, 2), "remote_stats": (2,),
+        "dup_groups": (NvS, 3), "dup_loffs": (NvS,), "dup_counts": (2,), "src_info": (NvS,), "link": (NvS,),
+    }  # fmt: skip
+    for name, shape in shapes.items():
+        t = getattr(plan, name)
+        if t is None:  # the two optional trailing fields
+            continue
+        assert t.dtype == torch.int32 and t.is_contiguous(), f"plan.{name} must be contiguous int32"
+        assert tuple(t.shape) == shape, f"plan.{name} must have shape {shape}, got {tuple(t.shape)}"
+        assert t.device == torch.device(device), f"plan.{name} is on the wrong device"

@@ -62,3 +62,48 @@ def test_launch_functions_match_buffer_methods(device):
     for r, flags in enumerate(lw.run(body)):
         assert all(flags), f"rank {r}: dst/cu/rows/weights/out/weights_back equal? {flags}"
     lw.run(lambda r: bufs[r].destroy())
+
+
+@pytest.mark.parametrize("device", DEVICES)
+def test_launch_functions_reject_bad_inputs(device):
+    """Wrong dtypes and shapes are refused before anything is launched, and the message names the argument (parity:
+    reference tests/test_dispatch.py:436-490 and tests/test_combine.py:332-355)."""
+    from moonep_td import Buffer
+
+    S, H, K, E = 8, 64, 2, 4
+    lw = LocalWorld(1, device)
+    buf = Buffer(S, H, K, E, 1, num_sms=2, token_padding=16, B=1, world=lw.view(0))
+    ctx = buf._require_ctx()
+    topk, tpe, gates = make_routing("balanced", S, K, E, 1, 0, device=device)
+    x = torch.randn(S, H, device=device).to(torch.bfloat16)
+    plan, cu = L.allocate_planning_outputs(ctx)
+    L.launch_planning(ctx, topk.reshape(-1).contiguous(), tpe, cu, plan)
+
+    with pytest.raises(AssertionError, match="hidden_sh"):
+        L.launch_dispatch(ctx, x.float(), gates, plan, build_dedup_map=True)
+    with pytest.raises(AssertionError, match="hidden_sh"):
+        L.launch_dispatch(ctx, x[: S // 2].contiguous(), gates, plan, build_dedup_map=True)
+    with pytest.raises(AssertionError, match="route_weights_sk"):
+        L.launch_dispatch(ctx, x, gates.double(), plan, build_dedup_map=True)
+    with pytest.raises(AssertionError, match="route_weights_sk"):
+        L.launch_dispatch(ctx, x, gates[:, : K - 1].contiguous(), plan, build_dedup_map=True)
+    bad = plan.clone()
+    object.__setattr__(bad, "dst", plan.dst.long())
+    with pytest.raises(AssertionError, match="dst"):
+        L.launch_dispatch(ctx, x, gates, bad, build_dedup_map=True)
+    bad = plan.clone()
+    object.__setattr__(bad, "dup_loffs", plan.dup_loffs.flatten()[:-1].contiguous())
+    with pytest.raises(AssertionError, match="dup_loffs"):
+        L.launch_dispatch_epilogue(ctx, bad)
+    out = torch.empty(S, H, dtype=torch.bfloat16, device=device)
+    with pytest.raises(AssertionError, match="output_sk"):
+        L.launch_combine(ctx, out, plan.dst, output_sk=torch.empty(S, K, dtype=torch.bfloat16, device=device))
+    with pytest.raises(AssertionError, match="output_sh"):
+        L.launch_combine(ctx, out.float(), plan.dst)
+    # nothing above consumed the plan: the regular sequence still runs
+    L.launch_dispatch(ctx, x, gates, plan, build_dedup_map=True)
+    L.launch_dispatch_epilogue(ctx, plan)
+    if device == "cuda":
+        torch.cuda.synchronize()
+        buf.check_status()
+    buf.destroy()
