@@ -244,8 +244,9 @@ class ExpertParallelMoE:
         dgate_nvs = ctx["weights_buf_local"].view(torch.float32)  # gate gradients ride the weights channel home
         swiglu_bwd(saved["a"], saved["u"], g, w_nvs, cu[-1:], dadu, hsw, dgate_nvs)
         del g
-        # Weight by weight: as soon as the gradients of one weight exist, its reduce_grad starts on the communication
-        # stream and runs beside the GEMMs that follow, which leave the communication kernels their SMs.
+        # With MOONEP_BWD_OVERLAP=1, weight by weight: as soon as the gradients of one weight exist, its reduce_grad starts
+        # on the communication stream and runs beside the GEMMs that follow, which leave the communication kernels their
+        # SMs.  Otherwise one reduce_grad for all three weights follows the combine.
         reduced, grads = [], (self.g_gate, self.g_up, self.g_down)
 
         def reduce_one(i):
