@@ -90,6 +90,9 @@ struct DispatchArgs {
   int expand_bulk;  // EXPAND copies through shared memory with bulk copies (needs (kExpandCopyWarps + 1) pieces of smem)
   int build_only;  // EXPAND: only build the duplicate map (no zero fill, no copies)
   int local_rows;  // rows whose source is this rank are written by EXPAND from the input; SEND skips them
+  int publish;     // the launch starts with the exchange plan_publish does as a kernel of its own
+  const int* tpe_row;  // [E] this rank's tokens per expert, pushed to every peer by the publish step (null: a [R, E]
+                       // table was given and nothing is pushed)
 };
 
 __device__ __forceinline__ void decode_dst(int d, int NvS, int& dest, int& loff) {
@@ -996,6 +999,49 @@ __global__ void __launch_bounds__(kDispatchThreads, 1) dispatch_kernel(const Moo
   __syncthreads();
   bool ok = !poisoned(c);
 
+  if (a.publish) {
+    // What plan_publish does as a kernel of its own, on all CTAs of this launch: reset this rank's src_info, push
+    // the tokens-per-expert row into every peer's meta chunk, count the experts of every planner block; the last
+    // CTA to finish signals FLAG_TPE to every peer (which also tells them that this rank is done with every
+    // earlier use of the buffers).
+    ok = __syncthreads_and(ok ? 1 : 0) != 0;  // one answer per CTA: the loops below contain barriers
+    if (ok) {
+      const int tid = blockIdx.x * blockDim.x + threadIdx.x;
+      const int nth = gridDim.x * blockDim.x;
+      int* src_info = c.meta_peer[c.rank] + c.src_info_off;
+      for (int i = tid; i < c.NvS; i += nth) src_info[i] = -1;
+      if (a.tpe_row != nullptr) {
+        const int total = c.R * c.E;
+        for (int i = tid; i < total; i += nth) {
+          const int d = i / c.E;
+          const int e = i - d * c.E;
+          c.meta_peer[d][c.tpe_off + c.rank * c.E + e] = a.tpe_row[e];
+        }
+      }
+      int* s_hist = reinterpret_cast<int*>(s_dyn);
+      const int E = c.E;
+      for (int b = blockIdx.x; b < a.n_blocks; b += gridDim.x) {
+        for (int e = threadIdx.x; e < E; e += blockDim.x) s_hist[e] = 0;
+        __syncthreads();
+        const int start = b * a.tokens_per_block * c.K;
+        const int end = min(c.N, start + a.tokens_per_block * c.K);
+        for (int i = start + threadIdx.x; i < end; i += blockDim.x) {
+          const int e = a.topk[i];
+          if (e >= 0 && e < E) atomicAdd(s_hist + e, 1);
+        }
+        __syncthreads();
+        int* out = c.block_hist + (long long)b * E;
+        for (int e = threadIdx.x; e < E; e += blockDim.x) out[e] = s_hist[e];
+        __syncthreads();
+      }
+    }
+    if (role_tail(c, MOONEP_CTR_PUBLISH_ARRIVE, gridDim.x) && ok && !poisoned(c)) {
+      const int tpe_epoch = abs_epoch(c, MOONEP_FLAG_TPE, a.epoch_tpe);
+      for (int r = threadIdx.x; r < c.R; r += blockDim.x) st_release_sys(flag_ptr(c, r, MOONEP_FLAG_TPE, c.rank), tpe_epoch);
+    }
+    __syncthreads();
+  }
+
   // which roles this CTA plays
   const bool mixed = (roles & MOONEP_ROLE_EXPAND) && (roles & (MOONEP_ROLE_TOKENS | MOONEP_ROLE_SEND));
   const int s0 = (mixed && (roles & MOONEP_ROLE_TABLES)) ? 1 : 0;
@@ -1103,7 +1149,7 @@ extern "C" int moonep_dispatch(void* ctx, int roles, int fresh, const int* topk,
                                const void* hidden, const float* weights, int with_weights, int* dup_groups,
                                int* dup_loffs, int* dup_counts, int* plan_src_info, int* plan_link, int wait_family,
                                int wait_epoch, int epoch_tpe, int epoch_plan, int epoch_sent, int path, int n_send,
-                               int n_expand, int build_only, void* stream) {
+                               int n_expand, int build_only, const int* tpe_row, void* stream) {
   auto* h = (HostCtx*)ctx;
   const MoonepDevCtx& c = h->dev;
   DispatchArgs a;
@@ -1128,6 +1174,9 @@ extern "C" int moonep_dispatch(void* ctx, int roles, int fresh, const int* topk,
   a.local_rows = ((roles & MOONEP_ROLE_LOCAL_ROWS) && hidden != nullptr && !build_only &&
                   (fresh || (plan_src_info != nullptr && plan_link != nullptr))) ? 1 : 0;
   roles &= ~MOONEP_ROLE_LOCAL_ROWS;
+  a.publish = ((roles & MOONEP_ROLE_PUBLISH) && (roles & MOONEP_ROLE_TOKENS) && topk != nullptr) ? 1 : 0;
+  roles &= ~MOONEP_ROLE_PUBLISH;
+  a.tpe_row = tpe_row;
   a.roles = roles;
   a.build_only = build_only;
   a.with_weights = with_weights;

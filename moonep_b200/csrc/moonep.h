@@ -78,6 +78,7 @@
 #define MOONEP_CTR_COMBINE_ARRIVE 25 // CTAs of the push-combine kernel that reached its end
 #define MOONEP_CTR_PREFETCH_ARRIVE 26  // CTAs of the prefetch kernel that reached its end
 #define MOONEP_CTR_FOLD_WORK 27      // group hand-out of the combine fold role
+#define MOONEP_CTR_PUBLISH_ARRIVE 28 // CTAs of the dispatch kernel that finished the publish role
 // stats[MOONEP_STAT_WAIT_MAX_NS + family]: longest time CTA 0 of any kernel spun on a flag of that family (ns);
 // stats[MOONEP_STAT_WAIT_COUNT + family]: number of such waits that did not find the flag already set.
 #define MOONEP_STAT_WAIT_MAX_NS 0
@@ -115,6 +116,9 @@
 // token lives on this rank are written by EXPAND straight from the input (primary row and duplicates from one read),
 // SEND leaves them out.  Needs src_info of the landed rows: a fresh plan, or a replayed plan that carries src_info.
 #define MOONEP_ROLE_LOCAL_ROWS 16
+// The launch begins with what plan_publish does as a kernel of its own (push of the tokens-per-expert row, reset of
+// src_info, per-block expert counts, FLAG_TPE to every peer), spread over all CTAs of the launch.
+#define MOONEP_ROLE_PUBLISH 32
 // Roles of the push-combine kernel.
 #define MOONEP_ROLE_PUSH 1     // expert side: copy primary rows (folded where they have duplicates) to the tokens' home ranks
 #define MOONEP_ROLE_SUM 2      // home side: sum the rows of a token as they arrive
@@ -209,7 +213,7 @@ int moonep_dispatch(void* ctx, int roles, int fresh, const int* topk, const int*
                     int* experts_to_copy, int* zero_fill, int* remote_stats, const void* hidden, const float* weights,
                     int with_weights, int* dup_groups, int* dup_loffs, int* dup_counts, int* plan_src_info,
                     int* plan_link, int wait_family, int wait_epoch, int epoch_tpe, int epoch_plan, int epoch_sent,
-                    int path, int n_send, int n_expand, int build_only, void* stream);
+                    int path, int n_send, int n_expand, int build_only, const int* tpe_row, void* stream);
 
 // Combine.
 int moonep_combine_prologue(void* ctx, const int* dup_groups, const int* dup_loffs, const int* dup_counts,

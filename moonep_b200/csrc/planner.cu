@@ -98,5 +98,5 @@ extern "C" int moonep_plan_compute(void* ctx, const int* topk, const int* tpe2d,
   return moonep_dispatch(ctx, MOONEP_ROLE_TABLES | MOONEP_ROLE_TOKENS, 1, topk, tpe2d, dst, cu_seqlens, experts_to_copy,
                          zero_fill, remote_stats, nullptr, nullptr, 0, nullptr, nullptr, dup_counts, nullptr, nullptr, -1,
                          0, wait_epoch_tpe, signal_epoch_plan, 0, MOONEP_PATH_LDST, imin(h->dev.local_sms, h->sm_count), 0,
-                         0, stream);
+                         0, nullptr, stream);
 }

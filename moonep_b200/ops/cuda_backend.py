@@ -46,6 +46,7 @@ _KERNEL_NAMES = {
 }  # fmt: skip
 _PHASE_NAMES = ("tables", "tokens", "send", "zero_fill", "wait_plan", "build_expand", "wait_sent", "fold", "push", "sum")
 ROLE_TABLES, ROLE_TOKENS, ROLE_SEND, ROLE_EXPAND = 1, 2, 4, 8
+ROLE_PUBLISH = 32  # modifier: the launch begins with the exchange that plan_publish does as a kernel of its own
 ROLE_LOCAL_ROWS = 16  # modifier: EXPAND writes the rows of this rank's own tokens from the input, SEND skips them
 ROLE_PUSH, ROLE_SUM, ROLE_FOLD = 1, 2, 4
 ROLE_LOCAL_HOME = 8  # modifier: rows of this rank's own tokens go from FOLD straight into the local staging chunk
@@ -349,13 +350,14 @@ class CudaBackend:
                          tag=None):  # fmt: skip
         """One launch of the dispatch kernel with the given roles (``csrc/dispatch.cu``)."""
         tpe2d = _ptr(tpe) if (tpe is not None and tpe.dim() == 2) else None
+        tpe_row = _ptr(tpe) if (tpe is not None and tpe.dim() == 1 and (roles & ROLE_PUBLISH)) else None
         self._call(
             "moonep_dispatch", int(roles), int(bool(fresh)), _ptr(topk), tpe2d, _ptr(plan.dst), _ptr(cu_seqlens),
             _ptr(plan.experts_to_copy), _ptr(plan.zero_fill_ranges), _ptr(plan.remote_stats), _ptr(hidden),
             _ptr(weights), int(bool(with_weights)), _ptr(plan.dup_groups), _ptr(plan.dup_loffs), _ptr(plan.dup_counts),
             _ptr(plan.src_info), _ptr(plan.link), int(wait_family), int(wait_epoch), self._cur(FLAG_TPE),
             self._cur(FLAG_PLAN), int(epoch_sent), self.send_path, int(n_send), int(self.n_expand), int(bool(build_only)),
-            _stream(),
+            tpe_row, _stream(),
             tag=tag,
         )  # fmt: skip
 
@@ -368,8 +370,15 @@ class CudaBackend:
         lr = ROLE_LOCAL_ROWS if config.local_rows_by_expand() else 0
         if planning_args is not None:
             topk_flat, tpe, cu_seqlens = planning_args
-            self.plan_publish(tpe, topk_flat)
             on_dev = config.planner_on_gpu()
+            # one launch for everything when nothing forces separate phases: the exchange of plan_publish becomes the
+            # first step of the dispatch kernel
+            fuse_publish = on_dev and not self.phased and config.fuse_plan_publish()
+            if fuse_publish:
+                self._topk = topk_flat
+                self._next(FLAG_TPE)
+            else:
+                self.plan_publish(tpe, topk_flat)
             if not on_dev:
                 self._plan_compute_host(topk_flat, tpe, cu_seqlens, plan)
                 wf, we = FLAG_PLAN, self._cur(FLAG_PLAN)
@@ -381,7 +390,8 @@ class CudaBackend:
                       with_weights=with_w, wait_family=wf, wait_epoch=we, epoch_sent=sent)  # fmt: skip
             plan_roles = (ROLE_TABLES | ROLE_TOKENS) if on_dev else 0
             if not self.phased:
-                self._dispatch_launch(plan_roles | ROLE_SEND | ROLE_EXPAND | lr, True, plan, tag="dispatch_fused", **kw)
+                self._dispatch_launch(plan_roles | ROLE_SEND | ROLE_EXPAND | lr | (ROLE_PUBLISH if fuse_publish else 0), True,
+                                      plan, tag="dispatch_fused", **kw)
             else:
                 if config.force_phased() and plan_roles:  # per-role timing: planner and send as separate launches
                     self._dispatch_launch(plan_roles, True, plan, tag="dispatch_plan", **kw)

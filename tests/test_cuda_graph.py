@@ -14,7 +14,10 @@ def _expected(x, K):
     return (x.float() * K).to(torch.bfloat16)
 
 
-def test_captured_round_trip_replays_and_mixes_with_eager_calls():
+@pytest.mark.parametrize("fuse_publish", ["0", "1"], ids=["publish_kernel", "publish_fused"])
+def test_captured_round_trip_replays_and_mixes_with_eager_calls(fuse_publish, monkeypatch):
+    # with MOONEP_FUSE_PUBLISH=1 the tokens-per-expert exchange is the first step of the dispatch kernel
+    monkeypatch.setenv("MOONEP_FUSE_PUBLISH", fuse_publish)
     S, H, K, E = 256, 512, 4, 8
     buf = Buffer(S, H, K, E, 1, num_sms=8, token_padding=16, explicitly_destroy=True)
     be = buf._require_ctx()["_backend"]
