@@ -499,10 +499,45 @@ def run_p2p_peak(args, rank, n):
     t = max_over_ranks(min(a_.elapsed_time(b_) for a_, b_ in ev), n)
     t_mean = max_over_ranks(sum(a_.elapsed_time(b_) for a_, b_ in ev) / args.steps, n)
     barrier_sync(n)
+    # The same transfer driven by SMs: CTAs stream the buffer through a shared-memory ring of bulk copies, as the
+    # dispatch send role does, without routing, flags or weights (csrc/p2p_bench.cu).  The ceiling of the send and
+    # push roles, for num_sms CTAs and for all SMs.
+    from moonep_b200.ops import _lib
+
+    lib = _lib.load()
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    sm_rates = {}
+    stream = torch.cuda.current_stream().cuda_stream
+    # the last 1 MiB of the peer's chunk receives the helper warps' flag-like stores
+    flag_words = dst[nbytes - (1 << 20):].view(torch.int32)
+    copy_bytes = nbytes - (1 << 20)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    for grid, fence_warps in ((args.num_sms, 0), (2 * args.num_sms, 0), (sms, 0), (args.num_sms, 4)):
+        def once():
+            rc = lib.moonep_peer_store_bench(dst.data_ptr(), src.data_ptr(), copy_bytes, 14336, grid, err.data_ptr(), 5000,
+                                             fence_warps, flag_words.data_ptr() if fence_warps else None, stream)
+            assert rc == 0, lib.moonep_last_error().decode()
+        for _ in range(3):
+            once()
+        barrier_sync(n)
+        ev2 = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+        for a_, b_ in ev2:
+            a_.record()
+            once()
+            b_.record()
+        barrier_sync(n)
+        t_sm = max_over_ranks(min(a_.elapsed_time(b_) for a_, b_ in ev2), n)
+        key = f"{grid}_ctas" + (f"_with_{fence_warps}_fencing_warps" if fence_warps else "")
+        sm_rates[key] = copy_bytes / (t_sm / 1e3) / 1e9
+    assert int(err.item()) == 0, "the measurement kernel gave up a wait"
+    barrier_sync(n)
     w.free_symmetric(st)
     return {"metric": "peer_copy_GBps_per_direction", "n_gpus": n, "bytes": nbytes, "best_ms": t, "mean_ms": t_mean,
             "value": nbytes / (t / 1e3) / 1e9, "mean_GBps": nbytes / (t_mean / 1e3) / 1e9,
-            "note": "every rank writes 1 GiB into the next rank's memory at the same time (device copy engine)"}  # fmt: skip
+            "sm_bulk_store_GBps": sm_rates,
+            "note": "every rank writes 1 GiB into the next rank's memory at the same time: device copy engine (value), "
+                    "and SM-driven cp.async.bulk rings of 14 KB pieces with the given number of CTAs, once with four more "
+                    "warps per CTA that issue system-scope fences and 4-byte peer stores all the while"}  # fmt: skip
 
 
 def main():

@@ -110,6 +110,7 @@ _SIGNATURES = {
     "moonep_plan_publish": (_i, [_vp, _vp, _vp, _i, _i, _vp]),
     "moonep_plan_compute": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp]),
     "moonep_dispatch": (_i, [_vp, _i, _i] + [_vp] * 9 + [_i] + [_vp] * 5 + [_i] * 9 + [_vp, _vp]),
+    "moonep_peer_store_bench": (_i, [_vp, _vp, _ll, _i, _i, _vp, _ll, _i, _vp, _vp]),
     "moonep_stage_layout": (_ll, [_i, _i, _i, _i, ctypes.POINTER(_ll), ctypes.POINTER(_ll)]),
     "moonep_combine_push": (_i, [_vp, _i] + [_vp] * 7 + [_i, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "moonep_combine_prologue": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
