@@ -18,12 +18,14 @@ def _free_port() -> int:
         return sk.getsockname()[1]
 
 
-def _run_worker(nproc, backend, port, timeout, extra_env=None):
+def _run_worker(nproc, backend, port, timeout, extra_env=None, scenarios=None):
     port = _free_port()  # a fixed port can still be in TIME_WAIT from the previous run
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", MOONEP_TIMEOUT_MS=os.environ.get("MOONEP_TIMEOUT_MS", "5000"))
     env.update(extra_env or {})
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr",
            "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "mp_worker.py"), "--backend", backend]  # fmt: skip
+    if scenarios:
+        cmd += ["--scenarios", scenarios]
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env, cwd=ROOT)
     assert out.returncode == 0, f"worker failed:\n{out.stdout[-4000:]}\n{out.stderr[-6000:]}"
     assert out.stdout.count("WORKER OK") == nproc, out.stdout[-4000:]
@@ -31,6 +33,12 @@ def _run_worker(nproc, backend, port, timeout, extra_env=None):
 
 def test_cpu_backend_two_gloo_processes():
     _run_worker(2, "gloo", 29621, 600)
+
+
+def test_cpu_backend_four_gloo_processes():
+    """Four ranks: every rank has three peers, experts_to_copy rows differ per rank, a token's entries spread over up
+    to four destinations."""
+    _run_worker(4, "gloo", 29622, 900, scenarios="round_trips,plan_reuse,weights")
 
 
 @pytest.mark.gpu
