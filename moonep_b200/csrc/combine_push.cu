@@ -98,11 +98,6 @@ __device__ __forceinline__ uint16_t f32_to_bf16(float f) {
   return *reinterpret_cast<uint16_t*>(&b);
 }
 
-__device__ __forceinline__ void sts16(void* p, const int4& v) {
-  asm volatile("st.shared.v4.s32 [%0], {%1,%2,%3,%4};" ::"r"(smem_u32(p)), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
-               : "memory");
-}
-
 // Warp-wide bounded wait until the producer of in_rows has finished the 128-row block of `row`.
 __device__ bool wait_block_ready(const MoonepDevCtx& c, const PushArgs& a, int row, int lane) {
   if (a.ready == nullptr) return true;
@@ -827,7 +822,7 @@ __device__ void sum_role_two(const MoonepDevCtx& c, const PushArgs& a) {
 
 __device__ void sum_role(const MoonepDevCtx& c, const PushArgs& a) {
   const int lane = threadIdx.x & 31;
-  const int NvS = c.NvS, K = c.K, H = c.H, S = c.S, kp = c.kp;
+  const int NvS = c.NvS, K = c.K, S = c.S, kp = c.kp;
   const int epoch = abs_epoch(c, MOONEP_FLAG_COMB, a.epoch_comb);
   int* work = c.counters + MOONEP_CTR_SUM_WORK;
   const unsigned char* stage = c.stage_peer[c.rank];

@@ -1047,11 +1047,10 @@ __global__ void __launch_bounds__(kDispatchThreads, 1) dispatch_kernel(const Moo
   const int s0 = (mixed && (roles & MOONEP_ROLE_TABLES)) ? 1 : 0;
   bool is_sender = (roles & (MOONEP_ROLE_TOKENS | MOONEP_ROLE_SEND)) != 0;
   bool is_expander = (roles & MOONEP_ROLE_EXPAND) != 0;
-  int sidx = blockIdx.x, scnt = gridDim.x, xidx = blockIdx.x, xcnt = gridDim.x;
+  int scnt = gridDim.x, xidx = blockIdx.x, xcnt = gridDim.x;
   if (mixed) {
     is_sender = (int)blockIdx.x >= s0 && (int)blockIdx.x < s0 + a.n_send;
     is_expander = !is_sender;
-    sidx = blockIdx.x - s0;
     scnt = a.n_send;
     xidx = (int)blockIdx.x < s0 ? blockIdx.x : blockIdx.x - a.n_send;
     xcnt = gridDim.x - a.n_send;
