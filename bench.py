@@ -98,12 +98,14 @@ def barrier_sync(n):
 
 def reference_arm(args):
     out = {"impl": "reference"}
+    first = os.environ.get("RANK", "0") == "0"  # under torch.distributed.run every rank gets here: one line in all
     sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
     try:
         import moonep_td  # noqa: F401
     except Exception as exc:  # noqa: BLE001
         out["unavailable"] = f"reference package not installed under baseline/_ref: {exc!r}"
-        print(json.dumps(out))
+        if first:
+            print(json.dumps(out))
         return
     try:
         import nvshmem.core  # noqa: F401
@@ -113,7 +115,8 @@ def reference_arm(args):
             "reference needs triton_dist (Triton-distributed) and nvshmem4py, neither is in this image "
             f"and there is no network: {exc!r}"
         )
-        print(json.dumps(out))
+        if first:
+            print(json.dumps(out))
         return
     # Both runtimes import: run the reference's own Buffer on the same config.
     from moonep_td import Buffer as RefBuffer
