@@ -338,3 +338,20 @@ def test_stats_report_rows_and_dedup(device):
     assert max(st[0]["rows_per_rank"]) <= S * K
     assert 1.0 <= st[0]["imbalance"] <= st[0]["imbalance_without_balancing"] + 1e-9
     lw.run(lambda r: bufs[r].destroy())
+
+
+def test_reduce_grad_needs_a_gradient_with_its_buffer():
+    """Leaving a weight out means leaving out both its gradient and its reduce buffer; leaving out all is an error."""
+    lw, bufs = _world(1, "cpu", S=8, H=16, K=2, epn=4, B=1)
+    buf = bufs[0]
+    topk, tpe, gates = make_routing("balanced", 8, 2, 4, 1, 0)
+    x = torch.randn(8, 16).to(torch.bfloat16)
+    plan = buf.dispatch(x, gates, topk, tpe)[3]
+    g = torch.zeros(4, 128, 128)
+    red = torch.zeros(1, 1, 128, 128)
+    with pytest.raises(AssertionError, match="reduce buffer"):
+        buf.reduce_grad(plan, False, g, None, None, None, None, None)  # a gradient without its buffer
+    with pytest.raises(AssertionError, match="at least one"):
+        buf.reduce_grad(plan, False)
+    buf.reduce_grad(plan, False, None, None, g, None, None, red)  # the down projection alone
+    buf.destroy()
