@@ -9,3 +9,13 @@ from moonep_b200.parallel.symm import (  # noqa: F401
     release_nvl_dist_tensor,
     view_nvl_dist_rows,
 )
+
+
+def ensure_nvshmem_initialized(group=None) -> None:
+    """Kept for code written against the reference (moonep_td/buffer.py:40), which initialises NVSHMEM here.  This
+    implementation has no such runtime: symmetric memory comes from its own CUDA-VMM allocator, set up when the first
+    ``Buffer`` or symmetric tensor of a process group is created.  Only checks that a process group exists."""
+    import torch.distributed as dist
+
+    if group is None and not dist.is_initialized():
+        raise RuntimeError("initialise torch.distributed (backend 'nccl' on GPUs) before creating symmetric memory")

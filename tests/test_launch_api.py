@@ -16,8 +16,19 @@ def test_reference_import_name():
     from moonep_td.buffer import create_nvl_dist_tensor, pad_dim0_for_alignment  # noqa: F401
     from moonep_td.planning import MoonEPCommPlan, allocate_planning_outputs, launch_planning  # noqa: F401
 
+    from moonep_td._dedup_builder import launch_dedup_builder  # noqa: F401
+    from moonep_td.buffer import ensure_nvshmem_initialized  # noqa: F401
+    from moonep_td.combine import launch_combine
+    from moonep_td.combine_prologue import launch_combine_prologue  # noqa: F401
+    from moonep_td.dispatch import launch_dispatch
+    from moonep_td.dispatch_epilogue import launch_dispatch_epilogue  # noqa: F401
+    from moonep_td.grad_reduce import launch_grad_reduce  # noqa: F401
+    from moonep_td.inter_rank_sync import launch_inter_rank_sync  # noqa: F401
+    from moonep_td.prefetch import launch_prefetch  # noqa: F401
+
     import moonep_b200
 
+    assert launch_dispatch is L.launch_dispatch and launch_combine is L.launch_combine
     assert moonep_td.Buffer is moonep_b200.Buffer and moonep_td.MoonEPCommPlan is moonep_b200.MoonEPCommPlan
     assert pad_dim0_for_alignment([3, 48], torch.bfloat16) * 96 % 128 == 0
 
