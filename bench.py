@@ -49,7 +49,9 @@ def parse_args():
     p.add_argument("--config", default="headline", choices=["headline", "skew", "sweep", "moe_step", "weights", "p2p_peak"],
                    help="headline: S=4096,H=7168,K=8,E=256 softmax routing; skew: S=8192,H=4096,E=64,K=6 Zipf(1.2); "
                         "sweep: S in {128..16384} with uniform routing, ours and NCCL; moe_step: SwiGLU MoE layer "
-                        "forward+backward+SGD with intermediate size --inter")  # fmt: skip
+                        "forward+backward+SGD with intermediate size --inter; weights: worst-case prefetch_weight and "
+                        "reduce_grad traffic (every slot in use); p2p_peak: peer-copy bandwidth of the copy engines and "
+                        "of SM-driven bulk-copy rings (2 or more GPUs)")  # fmt: skip
     p.add_argument("--inter", type=int, default=2048)
     return p.parse_args()
 
